@@ -1,0 +1,312 @@
+/*
+ * psi_cuda.h - C ABI of the B200 (sm_100a) backend for psi-dec's paged GQA decode path.
+ *
+ * The reference has no FFI for this path: its boundary is the set of Rust component types of
+ * crates/inference-backend-metal (GQAKVPageWrite, GQASplitKVSingleQ/TiledQ kernels, GQASplitKV selector) and the
+ * executor-side owners in crates/inference-executor-metal (GQARequestPageTable, PageArena, GQAMetadataBuffers,
+ * GQA::record).  A Rust crate `inference-backend-cuda` binds the functions below with `extern "C"` declarations and
+ * re-creates those component types on top of them; every entry point names the reference interface it stands in for
+ * (paths relative to the reference project root).
+ *
+ * Conventions
+ *   - every function returns a psi_status (0 = PSI_OK); nothing throws or aborts across the boundary.  The reference
+ *     panics on violated invariants; here the same checks run on the host before any launch and come back as
+ *     PSI_ERR_INVALID_ARGUMENT, with the message available from psi_ctx_last_error / psi_last_error.
+ *   - a psi_ctx is bound to one device and one stream and is used from one host thread at a time (the reference
+ *     executor is one thread with one in-flight submission per stream).  Calls enqueue work on the context's stream
+ *     and return; only psi_ctx_sync, the *_read / *_export functions and psi_gqa_decode_step_host block.
+ *   - device data layouts are the reference's, row-major, innermost last:
+ *       q, out        dtype [T][Hq][D]
+ *       k, v (append) dtype [T][Hkv][D]
+ *       pages         dtype [num_pages][2 (K,V)][Hkv][tokens_per_page][D]
+ *       page table    u32   [num_req_slots][num_gqa_layers][num_blocks][num_page_ids_per_block]
+ *   - there is no CPU fallback: every compute entry point needs a CUDA device.
+ */
+#ifndef PSI_CUDA_H
+#define PSI_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define PSI_API __attribute__((visibility("default")))
+#else
+#define PSI_API
+#endif
+
+typedef struct psi_ctx psi_ctx;
+typedef struct psi_pages psi_pages;
+typedef struct psi_table psi_table;
+typedef struct psi_gqa psi_gqa;
+typedef struct psi_id_allocator psi_id_allocator;
+
+typedef enum psi_status {
+    PSI_OK = 0,
+    PSI_ERR_INVALID_ARGUMENT = 1,   /* a contract the reference asserts (shape, index domain, capacity) */
+    PSI_ERR_RESOURCE_EXHAUSTED = 2, /* "not enough ID", out of device memory */
+    PSI_ERR_INTERNAL = 3,
+    PSI_ERR_TIMEOUT = 4, /* a bounded device-side wait gave up */
+    PSI_ERR_CUDA = 5     /* a CUDA runtime call failed; the message holds the CUDA error string */
+} psi_status;
+
+/* Storage dtype of q/k/v/out and of the page arena.  F32 and BF16 are the reference's dtypes
+ * (crates/inference-backend-metal/src/components/gqa_split_kv_single_q.rs:73); F16 is an extension with the same
+ * semantics. */
+typedef enum psi_dtype { PSI_DTYPE_F32 = 0, PSI_DTYPE_BF16 = 1, PSI_DTYPE_F16 = 2 } psi_dtype;
+
+/* crates/inference-executor-core/src/attn/gqa/core.rs:145-159 (GQAPageTableLayout) */
+typedef struct psi_page_table_layout {
+    uint32_t num_req_slots;
+    uint32_t num_gqa_layers;
+    uint32_t num_blocks;
+    uint32_t num_page_ids_per_block;
+} psi_page_table_layout;
+
+/* crates/inference-executor-core/src/attn/gqa/core.rs:93-143 (GQAReplayShape) */
+typedef struct psi_replay_shape {
+    uint32_t num_tokens;
+    uint32_t num_total_tokens;
+    uint32_t num_q_token_tiles;
+    uint32_t num_total_q_token_tiles;
+    uint32_t num_sdpa_map_task_templates;
+    uint32_t num_total_sdpa_map_task_templates;
+    uint32_t reduce_sdpa_partial_outputs; /* bool */
+} psi_replay_shape;
+
+/* crates/inference-backend-metal/src/components/gqa_split_kv.rs:8-19 (GQASplitKVVariant) */
+typedef struct psi_split_kv_variant {
+    uint32_t tiled_q;            /* 0 = SingleQ, 1 = TiledQ */
+    uint32_t q_token_tile_size;  /* TiledQ only, else 0 */
+    uint32_t kv_token_tile_size;
+    uint32_t num_threads_per_threadblock; /* SingleQ only, else 0 */
+    uint32_t q_head_tile_size;
+} psi_split_kv_variant;
+
+/* How psi_gqa_prepare cuts the step into device work. */
+typedef enum psi_plan_mode {
+    /* Equal KV bytes per resident CTA: the flattened (q tile, KV head) work list is cut into one contiguous share per
+     * CTA slot of the device, in whole 16-token KV tiles. */
+    PSI_PLAN_BALANCED = 0,
+    /* The reference's planner and variant selector (batch_metadata.rs:352-523, gqa_split_kv.rs:127-157): one CTA per
+     * (KV split, KV head), split count capped by max_tokens. */
+    PSI_PLAN_REFERENCE = 1
+} psi_plan_mode;
+
+typedef enum psi_kernel_mode {
+    PSI_KERNEL_AUTO = 0,    /* tensor-core kernel when the profile allows, else the generic kernel */
+    PSI_KERNEL_GENERIC = 1, /* CUDA-core kernel: any dtype, head_dim <= 256, any tokens_per_page */
+    PSI_KERNEL_MMA = 2      /* bf16/f16 mma kernel: head_dim in {64,128,256}, tokens_per_page % 8 == 0 */
+} psi_kernel_mode;
+
+/* Replay capacity policy of psi_gqa_prepare (batch_metadata.rs:60-69, GQAReplayCapacity). */
+typedef enum psi_capacity_mode {
+    PSI_CAPACITY_EXACT = 0,
+    PSI_CAPACITY_BUCKETED = 1,
+    PSI_CAPACITY_CALLER_TOKENS = 2
+} psi_capacity_mode;
+
+/* GQA::new + GQAMetalConfig + GQAScratch sizing (crates/inference-executor-metal/src/attn/gqa/backend.rs:253-282,
+ * scratch.rs:49-92). */
+typedef struct psi_gqa_config {
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    float scale; /* softmax scale, applied as given (never assumed 1/sqrt(D)) */
+    uint32_t page_bytes;
+    uint32_t dtype; /* psi_dtype */
+    psi_page_table_layout layout;
+    uint32_t max_tokens;  /* flat query-token capacity of one step */
+    uint32_t plan_mode;   /* psi_plan_mode */
+    uint32_t kernel_mode; /* psi_kernel_mode */
+    uint32_t max_ctas;    /* 0 = one CTA slot per SM x resident CTAs; otherwise caps the balanced plan's CTA count */
+} psi_gqa_config;
+
+/* ---- context ---------------------------------------------------------------------------------------------------- */
+
+/* Device::system_default() + Stream::new (crates/inference-backend-metal/src/metal/device.rs, stream/mod.rs).
+ * psi_ctx_create makes its own non-blocking stream; psi_ctx_create_on_stream borrows the caller's cudaStream_t. */
+PSI_API int32_t psi_ctx_create(int32_t device, psi_ctx** out);
+PSI_API int32_t psi_ctx_create_on_stream(int32_t device, void* cuda_stream, psi_ctx** out);
+PSI_API int32_t psi_ctx_destroy(psi_ctx* ctx);
+/* ExecutionSubmission::wait (crates/inference-executor-core/src/backend/runtime.rs:8-17) */
+PSI_API int32_t psi_ctx_sync(psi_ctx* ctx);
+PSI_API int32_t psi_ctx_stream(psi_ctx* ctx, void** out_cuda_stream);
+PSI_API int32_t psi_ctx_sm_count(psi_ctx* ctx, int32_t* out);
+/* Copies the context's last error message (NUL-terminated, truncated to n) into buf. */
+PSI_API int32_t psi_ctx_last_error(psi_ctx* ctx, char* buf, size_t n);
+/* Last error of the calling thread for calls that have no context yet (creation failures). */
+PSI_API int32_t psi_last_error(char* buf, size_t n);
+
+/* ---- page arena (crates/inference-executor-metal/src/model/page_arena.rs:6-46) ------------------------------------ */
+
+/* PageArena::new: num_pages x page_bytes of device memory, zero-filled. */
+PSI_API int32_t psi_pages_create(psi_ctx* ctx, uint64_t num_pages, uint32_t page_bytes, psi_pages** out);
+/* The same view over caller-owned device memory (not freed by psi_pages_destroy, not zeroed). */
+PSI_API int32_t psi_pages_wrap(psi_ctx* ctx, void* device_ptr, uint64_t num_pages, uint32_t page_bytes,
+                               psi_pages** out);
+PSI_API int32_t psi_pages_destroy(psi_pages* pages);
+/* PageArena::buffer */
+PSI_API int32_t psi_pages_device_ptr(psi_pages* pages, void** out);
+/* PageArena::release_resources / allocate_resources (hibernation); allocate zero-fills again. */
+PSI_API int32_t psi_pages_release(psi_pages* pages);
+PSI_API int32_t psi_pages_allocate(psi_pages* pages);
+/* Selected page-ID range [page_begin, page_end) to / from host memory (page_arena/file_io.rs; blocking). */
+PSI_API int32_t psi_pages_export_range(psi_pages* pages, uint64_t page_begin, uint64_t page_end, void* host_out);
+PSI_API int32_t psi_pages_import_range(psi_pages* pages, uint64_t page_begin, uint64_t page_end, const void* host_in);
+
+/* ---- request page table (crates/inference-executor-metal/src/attn/gqa/request_page_table.rs:13-122) --------------- */
+
+/* GQARequestPageTable::new: zero-initialised u32 table on the device with a host mirror. */
+PSI_API int32_t psi_table_create(psi_ctx* ctx, const psi_page_table_layout* layout, psi_table** out);
+PSI_API int32_t psi_table_destroy(psi_table* table);
+/* write_page_ids: n must equal num_page_ids_per_block. */
+PSI_API int32_t psi_table_write(psi_table* table, uint32_t req_slot, uint32_t layer, uint32_t block,
+                                const uint32_t* page_ids, uint32_t n);
+/* Qwen3xGQAState::write_page_ids (crates/inference-executor-metal/src/model/qwen/v3_x/state/gqa.rs:88-106): one block
+ * of every layer, n == num_gqa_layers * num_page_ids_per_block, every id < num_cache_pages. */
+PSI_API int32_t psi_table_write_all_layers(psi_table* table, uint32_t req_slot, uint32_t block,
+                                           const uint32_t* page_ids, uint32_t n, uint64_t num_cache_pages);
+/* read_page_ids (blocking; reads the device copy). */
+PSI_API int32_t psi_table_read(psi_table* table, uint32_t req_slot, uint32_t layer, uint32_t block, uint32_t* out,
+                               uint32_t n);
+/* reset_req_slots: zero every row of the listed slots. */
+PSI_API int32_t psi_table_reset_slots(psi_table* table, const uint32_t* req_slots, uint32_t n);
+/* page_ids_buffer */
+PSI_API int32_t psi_table_device_ptr(psi_table* table, void** out);
+/* Bulk load of whole (slot, layer) rows from host memory: ids holds num_blocks*num_page_ids_per_block entries. */
+PSI_API int32_t psi_table_write_row(psi_table* table, uint32_t req_slot, uint32_t layer, const uint32_t* ids,
+                                    uint32_t n);
+
+/* ---- host-side policy (no device work) ----------------------------------------------------------------------------- */
+
+/* ReplayBucketPolicy::with_topology_boundaries / buckets (crates/inference-executor-core/src/replay.rs:25-55):
+ * writes the bucket list into out (capacity out_cap) and its length into out_n. */
+PSI_API int32_t psi_replay_bucket_policy(uint32_t max_capacity, const uint32_t* topology_boundaries,
+                                         uint32_t num_boundaries, uint32_t* out, uint64_t out_cap, uint64_t* out_n);
+/* ReplayBucketPolicy::capacity (replay.rs:57-62) */
+PSI_API int32_t psi_replay_bucket_capacity(uint32_t max_capacity, const uint32_t* topology_boundaries,
+                                           uint32_t num_boundaries, uint32_t active, uint32_t* out);
+/* GQASplitKV::new / new_dspark_history + select (crates/inference-backend-metal/src/components/gqa_split_kv.rs:85-157).
+ * out_max_q_tokens_per_partial may be NULL. */
+PSI_API int32_t psi_split_kv_select(uint32_t io_dtype, uint32_t page_bytes, uint32_t num_q_heads,
+                                    uint32_t num_kv_heads, uint32_t head_dim, uint32_t dspark_history,
+                                    uint32_t num_tokens, uint32_t num_q_token_tiles, psi_split_kv_variant* out,
+                                    uint32_t* out_max_q_tokens_per_partial);
+
+/* GQAMetadataBuffers::update / update_bucketed / update_bucketed_with_token_capacity on caller-provided host arrays
+ * (crates/inference-executor-metal/src/attn/gqa/batch_metadata.rs:128-317): the metadata half of psi_gqa_prepare
+ * without a device.  The five buffers are capacity-sized (max_tokens, max_tokens, 2*max_tokens, 3*max_tokens,
+ * max_tokens+1 u32) and only the prefixes the reference writes change. */
+PSI_API int32_t psi_metadata_update_host(uint32_t max_tokens, const uint32_t* req_slots, const uint32_t* token_indices,
+                                         const uint32_t* cu_tokens, uint32_t num_reqs,
+                                         const psi_split_kv_variant* variant, uint32_t capacity_mode,
+                                         const uint32_t* token_topology_boundaries, uint32_t num_boundaries,
+                                         uint32_t caller_num_total_tokens, uint32_t* buf_req_slots,
+                                         uint32_t* buf_flat_token_indices, uint32_t* buf_q_token_tiles,
+                                         uint32_t* buf_kv_splits, uint32_t* buf_cu_kv_splits,
+                                         psi_replay_shape* out_shape);
+/* The balanced device work plan of a batch, computed on the host (what psi_gqa_prepare uploads in
+ * PSI_PLAN_BALANCED).  out_items receives 6 u32 per item {q tile, head selection, kv_begin, kv_end, partial slot or
+ * 0xFFFFFFFF, flat token begin of the tile}; out_cta_item_begin receives num_ctas+1 entries; out_counts receives
+ * {items, ctas, partial slots, reduce units, q tiles, total 16-token KV tiles (saturated)}.  No reference counterpart:
+ * the reference's planner is psi_metadata_update_host. */
+PSI_API int32_t psi_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint32_t* token_indices,
+                                 const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
+                                 uint32_t min_kv_tiles_per_cta, uint32_t* out_items, uint64_t items_cap,
+                                 uint32_t* out_cta_item_begin, uint64_t cta_cap, uint32_t* out_counts);
+
+/* U32IDAllocator (crates/inference-runtime-core/src/memory/u32_id_allocator.rs:69-172): freed IDs first, in the order
+ * they were freed, then fresh IDs from a counter.  Runtime core keeps its own allocator; this one drives synthetic
+ * admit/finish traces with the same observable behaviour. */
+PSI_API int32_t psi_id_allocator_create(uint64_t capacity, psi_id_allocator** out);
+PSI_API int32_t psi_id_allocator_destroy(psi_id_allocator* a);
+PSI_API int32_t psi_id_allocator_alloc_many(psi_id_allocator* a, uint64_t count, uint32_t* out_ids);
+PSI_API int32_t psi_id_allocator_free_many(psi_id_allocator* a, const uint32_t* ids, uint64_t count);
+PSI_API int32_t psi_id_allocator_bitmap(psi_id_allocator* a, uint64_t* out_words, uint64_t cap, uint64_t* out_n);
+PSI_API int32_t psi_id_allocator_free_count(psi_id_allocator* a, uint64_t* out);
+
+/* ---- the GQA component (crates/inference-executor-metal/src/attn/gqa/backend.rs:253-657) -------------------------- */
+
+/* GQA::new + GQAMetadataBuffers::new + GQA::new_scratch: fixes the profile, allocates the device metadata block and
+ * the partial-output scratch. */
+PSI_API int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out);
+PSI_API int32_t psi_gqa_destroy(psi_gqa* gqa);
+/* GQAReplayBucketPolicy::new's token topology boundaries (batch_metadata.rs:20-27); default none. */
+PSI_API int32_t psi_gqa_set_token_topology_boundaries(psi_gqa* gqa, const uint32_t* boundaries, uint32_t n);
+
+/* GQA::prepare / prepare_bucketed / prepare_bucketed_with_token_capacity -> GQAMetadataBuffers::update*
+ * (backend.rs:283-356, batch_metadata.rs:128-317).  Host arrays: req_slots[num_reqs], token_indices[num_reqs]
+ * (request-absolute position of each request's first query token), cu_tokens[num_reqs+1].  Builds the per-token
+ * metadata, selects the SplitKV variant, plans the KV splits, and uploads everything in one copy on the stream. */
+PSI_API int32_t psi_gqa_prepare(psi_gqa* gqa, const uint32_t* req_slots, const uint32_t* token_indices,
+                                const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t capacity_mode,
+                                uint32_t caller_num_total_tokens, psi_replay_shape* out_shape);
+/* The variant the last prepare selected (GQAMetadataBuffers::split_kv_variant). */
+PSI_API int32_t psi_gqa_split_kv_variant(psi_gqa* gqa, psi_split_kv_variant* out);
+
+typedef enum psi_metadata_array {
+    PSI_MD_REQ_SLOTS = 0,          /* [max_tokens] */
+    PSI_MD_FLAT_TOKEN_INDICES = 1, /* [max_tokens] */
+    PSI_MD_Q_TOKEN_TILES = 2,      /* [max_tokens][2] */
+    PSI_MD_KV_SPLITS = 3,          /* [max_tokens][3] */
+    PSI_MD_CU_KV_SPLITS = 4        /* [max_tokens+1] */
+} psi_metadata_array;
+/* Read / overwrite the reference-format metadata arrays (GQAMetadataBuffers::req_slots() ... cu_kv_splits(),
+ * Buffer::read_typed / write_typed).  Offsets and counts are in u32 elements. */
+PSI_API int32_t psi_gqa_metadata_read(psi_gqa* gqa, uint32_t which, uint64_t offset, uint32_t* out, uint64_t n);
+PSI_API int32_t psi_gqa_metadata_write(psi_gqa* gqa, uint32_t which, uint64_t offset, const uint32_t* in, uint64_t n);
+
+/* Plan statistics of the last prepare: out[0]=CTAs launched by the map kernel, out[1]=work items, out[2]=partial
+ * slots, out[3]=reduce units, out[4]=exec q tiles, out[5]=kernel (1 generic, 2 mma), out[6]=total 16-token KV tiles,
+ * out[7]=rows per q tile. */
+PSI_API int32_t psi_gqa_plan_stats(psi_gqa* gqa, uint32_t* out, uint32_t n);
+
+/* KV append: GQAKVPageWrite::invoke_bucketed (crates/inference-backend-metal/src/components/gqa_kv_page_write.rs:
+ * 125-177; shader metal/gqa_kv_page_write.metal:6-53).  k, v: device [num_total_tokens][Hkv][D]; rows at or beyond
+ * the prepared num_tokens are not read and their pages not touched.  Bit copy. */
+PSI_API int32_t psi_gqa_kv_append(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer, const void* k,
+                                  const void* v);
+
+/* Attention over the paged cache: SplitKV map + reduce (gqa_split_kv_single_q.rs:293-383, gqa_split_kv_tiled_q.rs:
+ * 246-327; shaders metal/gqa_split_kv_single_q_{map,reduce}.metal, metal/gqa_split_kv_tiled_q.metal).  q, out: device
+ * [num_total_tokens][Hq][D]; query token i of a request sees keys [0, token_index+i]; output rows at or beyond the
+ * prepared num_tokens are left untouched.  Enqueue after psi_gqa_kv_append of the same step (stream order is the
+ * reference's barrier) so that a token attends to itself. */
+PSI_API int32_t psi_gqa_attend(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer, const void* q,
+                               void* out);
+
+/* The same map + reduce, stopping before normalisation to the output dtype: f32 o [T][Hq][D] (normalised within the
+ * local KV), m [T][Hq] (natural-log running max of scale*q.k), l [T][Hq] (sum of exp(logit - m)).  This is the
+ * reference's partial-output ABI (gqa_split_kv_single_q_map.metal:231-252) lifted to one partial per device, for KV
+ * ranges that are split across devices.  o/m/l may point into a peer device's memory when peer access is enabled. */
+PSI_API int32_t psi_gqa_attend_partial(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
+                                       const void* q, float* o, float* m, float* l);
+
+/* Merge n partials per (token, head) exactly like the reference reduce (gqa_split_kv_single_q_reduce.metal:27-48):
+ * M = max m_i, w_i = exp(m_i - M) * l_i (0 when m_i is not finite), out = sum w_i o_i / sum w_i (0 when the sum is 0).
+ * o/m/l are host arrays of n device pointers; out is device [num_tokens][Hq][D] in the component's dtype. */
+PSI_API int32_t psi_gqa_combine(psi_gqa* gqa, const float* const* o, const float* const* m, const float* const* l,
+                                uint32_t n, uint32_t num_tokens, void* out);
+
+/* One whole decode step through host memory: copies k, v [T][Hkv][D] and q [T][Hq][D] host->device, runs append then
+ * attend, copies out [T][Hq][D] device->host and waits.  T is the prepared num_tokens. */
+PSI_API int32_t psi_gqa_decode_step_host(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
+                                         const void* k_host, const void* v_host, const void* q_host, void* out_host);
+
+/* Page gather: tokens [tok_begin, tok_end) of one request slot and layer into contiguous device K and V
+ * [n][Hkv][D].  The reference fuses this address walk into its map kernels
+ * (metal/gqa_split_kv_single_q_map.metal:96-111,195-209); standalone it is the inverse of the append. */
+PSI_API int32_t psi_page_gather(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t req_slot, uint32_t layer,
+                                uint32_t tok_begin, uint32_t tok_end, void* k_out, void* v_out);
+
+/* Number of kernels this library has launched on the context since creation (for launch accounting). */
+PSI_API int32_t psi_ctx_launch_count(psi_ctx* ctx, uint64_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PSI_CUDA_H */

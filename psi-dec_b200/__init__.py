@@ -1,0 +1,10 @@
+"""B200-native paged GQA decode path of psi-dec: Python front-end of ``libpsi_cuda.so``.
+
+The directory name carries a hyphen, so the package is loaded by path (``__graft_entry__.load_package()``) and
+registered as ``psi_dec_b200``.
+"""
+from .binding import (  # noqa: F401
+    BF16, F16, F32, CAPACITY_BUCKETED, CAPACITY_CALLER_TOKENS, CAPACITY_EXACT, KERNEL_AUTO, KERNEL_GENERIC, KERNEL_MMA,
+    PLAN_BALANCED, PLAN_REFERENCE, Context, GQA, GQAConfig, GQAPageTableLayout, GQAReplayShape, GQARequestPageTable,
+    GQASplitKV, GQASplitKVVariant, PageArena, PsiError, ReplayBucketPolicy, U32IDAllocator, library, library_path,
+)

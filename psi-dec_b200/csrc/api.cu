@@ -1,0 +1,1115 @@
+// C ABI of the library: opaque objects, host-side validation, metadata upload and kernel launches.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "host_logic.hpp"
+#include "kernels.cuh"
+#include "psi_cuda.h"
+
+using namespace psi;
+
+namespace {
+
+struct CudaError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+thread_local std::string g_thread_error;
+
+void cuda_check(cudaError_t err, const char* what) {
+    if (err != cudaSuccess) {
+        throw CudaError(std::string(what) + ": " + cudaGetErrorName(err) + " (" + cudaGetErrorString(err) + ")");
+    }
+}
+
+constexpr uint32_t kWordAlign = 8;  // sections of the device metadata block start on 32-byte boundaries
+uint64_t pad_words(uint64_t n) { return (n + kWordAlign - 1) / kWordAlign * kWordAlign; }
+
+}  // namespace
+
+struct psi_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 0;
+    uint64_t launches = 0;
+    std::string last_error;
+    void bind() const { cuda_check(cudaSetDevice(device), "cudaSetDevice"); }
+};
+
+namespace {
+
+// Grow-only device allocation owned by a context.
+struct DeviceBuffer {
+    void* ptr = nullptr;
+    uint64_t bytes = 0;
+    void ensure(psi_ctx* ctx, uint64_t wanted, bool zero) {
+        if (wanted <= bytes) return;
+        if (ptr != nullptr) {
+            cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+            cuda_check(cudaFree(ptr), "cudaFree");
+            ptr = nullptr;
+            bytes = 0;
+        }
+        cudaError_t err = cudaMalloc(&ptr, wanted);
+        if (err == cudaErrorMemoryAllocation) {
+            (void)cudaGetLastError();
+            throw ExhaustedError("out of device memory");
+        }
+        cuda_check(err, "cudaMalloc");
+        bytes = wanted;
+        if (zero) cuda_check(cudaMemsetAsync(ptr, 0, wanted, ctx->stream), "cudaMemsetAsync");
+    }
+    void release() {
+        if (ptr != nullptr) (void)cudaFree(ptr);
+        ptr = nullptr;
+        bytes = 0;
+    }
+};
+
+}  // namespace
+
+struct psi_pages {
+    psi_ctx* ctx = nullptr;
+    void* ptr = nullptr;
+    bool owned = false;
+    uint64_t num_pages = 0;
+    uint32_t page_bytes = 0;
+};
+
+struct psi_table {
+    psi_ctx* ctx = nullptr;
+    psi_page_table_layout layout{};
+    uint32_t* dev = nullptr;
+    std::vector<uint32_t> host;
+    uint64_t row_words() const { return uint64_t(layout.num_blocks) * layout.num_page_ids_per_block; }
+    uint64_t start_index(uint32_t slot, uint32_t layer, uint32_t block) const {
+        return ((uint64_t(slot) * layout.num_gqa_layers + layer) * layout.num_blocks + block) *
+               layout.num_page_ids_per_block;
+    }
+};
+
+struct psi_id_allocator {
+    IdAllocator impl;
+    explicit psi_id_allocator(uint64_t capacity) : impl(capacity) {}
+};
+
+struct psi_gqa {
+    psi_ctx* ctx = nullptr;
+    psi_gqa_config cfg{};
+    uint32_t tokens_per_page = 0;
+    uint32_t kernel = PSI_KERNEL_GENERIC;  // resolved kernel
+    uint32_t grid_cap = 1;
+    PlanGeometry geo{};
+    std::unique_ptr<SplitKvSelector> selector;  // null when the profile is outside the reference selector's domain
+    std::unique_ptr<ReferenceMetadata> md;
+    std::vector<uint32_t> boundaries;
+    psi_replay_shape shape{};
+    psi_split_kv_variant variant{};
+    WorkPlan plan;
+    bool prepared = false;
+
+    DeviceBuffer block;       // device metadata block
+    uint32_t* staging = nullptr;  // pinned mirror of the block
+    uint64_t staging_words = 0;
+    cudaEvent_t upload_done = nullptr;
+    // section offsets (in words) of the block uploaded by the last prepare
+    uint64_t off_req_slots = 0, off_token_indices = 0, off_tiles = 0, off_cta = 0, off_reduces = 0, off_items = 0;
+
+    DeviceBuffer partial_o, partial_ml;  // [slots][16][D] and [2][slots][16]
+    uint64_t partial_slots_cap = 0;
+    DeviceBuffer step_k, step_v, step_q, step_out;  // psi_gqa_decode_step_host staging
+    DeviceBuffer combine_ptrs;
+};
+
+namespace {
+
+template <typename F>
+int32_t guarded(psi_ctx* ctx, F&& body) {
+    int32_t status = PSI_OK;
+    std::string message;
+    try {
+        body();
+    } catch (const ContractError& e) {
+        status = PSI_ERR_INVALID_ARGUMENT;
+        message = e.what();
+    } catch (const ExhaustedError& e) {
+        status = PSI_ERR_RESOURCE_EXHAUSTED;
+        message = e.what();
+    } catch (const CudaError& e) {
+        status = PSI_ERR_CUDA;
+        message = e.what();
+    } catch (const std::bad_alloc&) {
+        status = PSI_ERR_RESOURCE_EXHAUSTED;
+        message = "out of host memory";
+    } catch (const std::exception& e) {
+        status = PSI_ERR_INTERNAL;
+        message = e.what();
+    } catch (...) {
+        status = PSI_ERR_INTERNAL;
+        message = "unknown error";
+    }
+    if (status != PSI_OK) {
+        g_thread_error = message;
+        if (ctx != nullptr) ctx->last_error = message;
+    }
+    return status;
+}
+
+int32_t copy_message(const std::string& message, char* buf, size_t n) {
+    if (buf == nullptr || n == 0) return PSI_ERR_INVALID_ARGUMENT;
+    size_t len = std::min(message.size(), n - 1);
+    std::memcpy(buf, message.data(), len);
+    buf[len] = '\0';
+    return PSI_OK;
+}
+
+void validate_layout(const psi_page_table_layout& l) {
+    require(l.num_req_slots > 0 && l.num_blocks > 0 && l.num_gqa_layers > 0 && l.num_page_ids_per_block > 0,
+            "GQA page-table layout dimensions must be positive");
+    const uint64_t per_req = uint64_t(l.num_blocks) * l.num_page_ids_per_block;
+    require(per_req <= kU32Max, "GQA per-request physical page count must fit u32");
+    const long double total = (long double)l.num_req_slots * l.num_gqa_layers * (long double)per_req;
+    require(total < 4.0e18L, "GQA page-table element count must fit usize");
+}
+
+PageGeometry page_geometry(const psi_gqa* g, const psi_pages* pages, const psi_table* table, uint32_t layer) {
+    require(pages != nullptr && table != nullptr, "pages and table must not be null");
+    require(pages->ctx == g->ctx && table->ctx == g->ctx, "pages, table and GQA component must share one context");
+    require(pages->ptr != nullptr, "page arena state must be loaded before execution");
+    require(pages->page_bytes == g->cfg.page_bytes, "page arena page_bytes differs from the GQA configuration");
+    const auto& a = table->layout;
+    const auto& b = g->cfg.layout;
+    require(a.num_req_slots == b.num_req_slots && a.num_gqa_layers == b.num_gqa_layers &&
+                a.num_blocks == b.num_blocks && a.num_page_ids_per_block == b.num_page_ids_per_block,
+            "page table layout differs from the GQA configuration");
+    require(layer < b.num_gqa_layers, "GQA page-table index exceeds layer count");
+    PageGeometry geo{};
+    geo.pages = pages->ptr;
+    geo.page_ids = table->dev;
+    geo.elem_bytes = dtype_bytes(g->cfg.dtype);
+    geo.page_elems = g->cfg.page_bytes / geo.elem_bytes;
+    geo.layer = layer;
+    geo.num_layers = b.num_gqa_layers;
+    geo.pages_per_req = static_cast<uint32_t>(table->row_words());
+    geo.tokens_per_page = g->tokens_per_page;
+    geo.num_kv_heads = g->cfg.num_kv_heads;
+    geo.head_dim = g->cfg.head_dim;
+    return geo;
+}
+
+const uint32_t* block_words(const psi_gqa* g, uint64_t offset) {
+    return static_cast<const uint32_t*>(g->block.ptr) + offset;
+}
+
+AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* table, uint32_t layer, const void* q) {
+    require(g->prepared, "GQA batch metadata must be updated before recording");
+    require(q != nullptr, "q must not be null");
+    AttendParams p{};
+    p.geo = page_geometry(g, pages, table, layer);
+    p.q = q;
+    p.req_slots = block_words(g, g->off_req_slots);
+    p.flat_token_indices = block_words(g, g->off_token_indices);
+    p.tiles = reinterpret_cast<const ExecTile*>(block_words(g, g->off_tiles));
+    p.items = reinterpret_cast<const WorkItem*>(block_words(g, g->off_items));
+    p.cta_item_begin = block_words(g, g->off_cta);
+    p.reduces = reinterpret_cast<const ReduceUnit*>(block_words(g, g->off_reduces));
+    p.partial_o = static_cast<float*>(g->partial_o.ptr);
+    p.partial_m = static_cast<float*>(g->partial_ml.ptr);
+    p.partial_l = p.partial_m == nullptr ? nullptr : p.partial_m + g->partial_slots_cap * kMaxRows;
+    p.scalars = block_words(g, 0);
+    p.num_q_heads = g->cfg.num_q_heads;
+    p.group = g->geo.group;
+    p.heads_per_tile = g->geo.heads_per_tile;
+    p.head_tiles = g->geo.head_tiles;
+    p.dtype = g->cfg.dtype;
+    p.scale_log2 = g->cfg.scale * 1.4426950408889634f;
+    return p;
+}
+
+void run_attend(psi_gqa* g, const AttendParams& p) {
+    psi_ctx* ctx = g->ctx;
+    const uint32_t num_ctas = g->plan.num_ctas();
+    if (g->kernel == PSI_KERNEL_MMA) {
+        cuda_check(launch_attend_mma(p, num_ctas, ctx->stream), "attend (mma) launch");
+    } else {
+        cuda_check(launch_attend_generic(p, num_ctas, ctx->stream), "attend (generic) launch");
+    }
+    ctx->launches += num_ctas > 0;
+    const uint32_t num_reduces = static_cast<uint32_t>(g->plan.reduces.size());
+    cuda_check(launch_attend_reduce(p, num_reduces, ctx->stream), "attend reduce launch");
+    ctx->launches += num_reduces > 0;
+}
+
+void run_append(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* k, const void* v) {
+    require(g->prepared, "GQA batch metadata must be updated before recording");
+    require(k != nullptr && v != nullptr, "k and v must not be null");
+    AppendParams p{};
+    p.geo = page_geometry(g, pages, table, layer);
+    p.flat_k = k;
+    p.flat_v = v;
+    p.req_slots = block_words(g, g->off_req_slots);
+    p.flat_token_indices = block_words(g, g->off_token_indices);
+    p.scalars = block_words(g, 0);
+    p.num_total_tokens = g->shape.num_total_tokens;
+    cuda_check(launch_kv_append(p, g->ctx->stream), "kv append launch");
+    g->ctx->launches += 1;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------------
+// context
+// ---------------------------------------------------------------------------------------------------------------------
+extern "C" {
+
+int32_t psi_last_error(char* buf, size_t n) { return copy_message(g_thread_error, buf, n); }
+
+static int32_t ctx_create(int32_t device, void* stream, bool own, psi_ctx** out) {
+    return guarded(nullptr, [&] {
+        require(out != nullptr, "out must not be null");
+        *out = nullptr;
+        int count = 0;
+        cudaError_t err = cudaGetDeviceCount(&count);
+        if (err != cudaSuccess || count == 0) {
+            (void)cudaGetLastError();
+            throw CudaError("no CUDA device is available; this library has no CPU fallback");
+        }
+        require(device >= 0 && device < count, "device index out of range");
+        auto ctx = std::make_unique<psi_ctx>();
+        ctx->device = device;
+        ctx->bind();
+        cuda_check(cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device),
+                   "cudaDeviceGetAttribute");
+        if (own) {
+            cuda_check(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreateWithFlags");
+            ctx->owns_stream = true;
+        } else {
+            ctx->stream = static_cast<cudaStream_t>(stream);
+        }
+        *out = ctx.release();
+    });
+}
+
+int32_t psi_ctx_create(int32_t device, psi_ctx** out) { return ctx_create(device, nullptr, true, out); }
+
+int32_t psi_ctx_create_on_stream(int32_t device, void* cuda_stream, psi_ctx** out) {
+    return ctx_create(device, cuda_stream, false, out);
+}
+
+int32_t psi_ctx_destroy(psi_ctx* ctx) {
+    if (ctx == nullptr) return PSI_OK;
+    int32_t status = guarded(nullptr, [&] {
+        ctx->bind();
+        if (ctx->owns_stream) {
+            (void)cudaStreamSynchronize(ctx->stream);
+            (void)cudaStreamDestroy(ctx->stream);
+        }
+    });
+    delete ctx;
+    return status;
+}
+
+int32_t psi_ctx_sync(psi_ctx* ctx) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        ctx->bind();
+        cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    });
+}
+
+int32_t psi_ctx_stream(psi_ctx* ctx, void** out) {
+    if (ctx == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    *out = ctx->stream;
+    return PSI_OK;
+}
+
+int32_t psi_ctx_sm_count(psi_ctx* ctx, int32_t* out) {
+    if (ctx == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    *out = ctx->sm_count;
+    return PSI_OK;
+}
+
+int32_t psi_ctx_last_error(psi_ctx* ctx, char* buf, size_t n) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return copy_message(ctx->last_error, buf, n);
+}
+
+int32_t psi_ctx_launch_count(psi_ctx* ctx, uint64_t* out) {
+    if (ctx == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    *out = ctx->launches;
+    return PSI_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// page arena
+// ---------------------------------------------------------------------------------------------------------------------
+static void pages_allocate(psi_pages* pages) {
+    require(pages->ptr == nullptr, "page arena state is already loaded");
+    const uint64_t bytes = pages->num_pages * pages->page_bytes;
+    cudaError_t err = cudaMalloc(&pages->ptr, bytes);
+    if (err == cudaErrorMemoryAllocation) {
+        (void)cudaGetLastError();
+        pages->ptr = nullptr;
+        throw ExhaustedError("out of device memory for the page arena");
+    }
+    cuda_check(err, "cudaMalloc");
+    cuda_check(cudaMemsetAsync(pages->ptr, 0, bytes, pages->ctx->stream), "cudaMemsetAsync");
+}
+
+int32_t psi_pages_create(psi_ctx* ctx, uint64_t num_pages, uint32_t page_bytes, psi_pages** out) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        require(out != nullptr, "out must not be null");
+        *out = nullptr;
+        require(num_pages > 0, "page arena requires pages");
+        require(page_bytes > 0, "page arena requires nonzero page size");
+        require(num_pages <= (uint64_t(1) << 62) / page_bytes, "page arena byte length must fit usize");
+        ctx->bind();
+        auto pages = std::make_unique<psi_pages>();
+        pages->ctx = ctx;
+        pages->owned = true;
+        pages->num_pages = num_pages;
+        pages->page_bytes = page_bytes;
+        pages_allocate(pages.get());
+        *out = pages.release();
+    });
+}
+
+int32_t psi_pages_wrap(psi_ctx* ctx, void* device_ptr, uint64_t num_pages, uint32_t page_bytes, psi_pages** out) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        require(out != nullptr && device_ptr != nullptr, "out and device_ptr must not be null");
+        require(num_pages > 0 && page_bytes > 0, "page arena requires pages of nonzero size");
+        auto pages = std::make_unique<psi_pages>();
+        pages->ctx = ctx;
+        pages->ptr = device_ptr;
+        pages->owned = false;
+        pages->num_pages = num_pages;
+        pages->page_bytes = page_bytes;
+        *out = pages.release();
+    });
+}
+
+int32_t psi_pages_destroy(psi_pages* pages) {
+    if (pages == nullptr) return PSI_OK;
+    int32_t status = guarded(pages->ctx, [&] {
+        pages->ctx->bind();
+        if (pages->owned && pages->ptr != nullptr) {
+            (void)cudaStreamSynchronize(pages->ctx->stream);
+            cuda_check(cudaFree(pages->ptr), "cudaFree");
+        }
+    });
+    delete pages;
+    return status;
+}
+
+int32_t psi_pages_device_ptr(psi_pages* pages, void** out) {
+    if (pages == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(pages->ctx, [&] {
+        require(pages->ptr != nullptr, "page arena state must be loaded before execution");
+        *out = pages->ptr;
+    });
+}
+
+int32_t psi_pages_release(psi_pages* pages) {
+    if (pages == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(pages->ctx, [&] {
+        require(pages->owned, "a wrapped page arena does not own its memory");
+        require(pages->ptr != nullptr, "page arena state is not loaded");
+        pages->ctx->bind();
+        cuda_check(cudaStreamSynchronize(pages->ctx->stream), "cudaStreamSynchronize");
+        cuda_check(cudaFree(pages->ptr), "cudaFree");
+        pages->ptr = nullptr;
+    });
+}
+
+int32_t psi_pages_allocate(psi_pages* pages) {
+    if (pages == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(pages->ctx, [&] {
+        require(pages->owned, "a wrapped page arena does not own its memory");
+        pages->ctx->bind();
+        pages_allocate(pages);
+    });
+}
+
+static int32_t pages_copy_range(psi_pages* pages, uint64_t begin, uint64_t end, void* host, bool to_host) {
+    if (pages == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(pages->ctx, [&] {
+        require(host != nullptr, "host buffer must not be null");
+        require(pages->ptr != nullptr, "page arena state must be loaded before execution");
+        require(begin <= end && end <= pages->num_pages, "page-ID range outside the page arena");
+        pages->ctx->bind();
+        auto* dev = static_cast<unsigned char*>(pages->ptr) + begin * pages->page_bytes;
+        const uint64_t bytes = (end - begin) * pages->page_bytes;
+        if (bytes == 0) return;
+        if (to_host) {
+            cuda_check(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, pages->ctx->stream), "cudaMemcpyAsync");
+        } else {
+            cuda_check(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, pages->ctx->stream), "cudaMemcpyAsync");
+        }
+        cuda_check(cudaStreamSynchronize(pages->ctx->stream), "cudaStreamSynchronize");
+    });
+}
+
+int32_t psi_pages_export_range(psi_pages* pages, uint64_t page_begin, uint64_t page_end, void* host_out) {
+    return pages_copy_range(pages, page_begin, page_end, host_out, true);
+}
+
+int32_t psi_pages_import_range(psi_pages* pages, uint64_t page_begin, uint64_t page_end, const void* host_in) {
+    return pages_copy_range(pages, page_begin, page_end, const_cast<void*>(host_in), false);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// request page table
+// ---------------------------------------------------------------------------------------------------------------------
+int32_t psi_table_create(psi_ctx* ctx, const psi_page_table_layout* layout, psi_table** out) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        require(out != nullptr && layout != nullptr, "out and layout must not be null");
+        *out = nullptr;
+        validate_layout(*layout);
+        ctx->bind();
+        auto table = std::make_unique<psi_table>();
+        table->ctx = ctx;
+        table->layout = *layout;
+        const uint64_t words = uint64_t(layout->num_req_slots) * layout->num_gqa_layers * table->row_words();
+        table->host.assign(words, 0);
+        cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&table->dev), words * sizeof(uint32_t));
+        if (err == cudaErrorMemoryAllocation) {
+            (void)cudaGetLastError();
+            throw ExhaustedError("out of device memory for the page table");
+        }
+        cuda_check(err, "cudaMalloc");
+        cuda_check(cudaMemsetAsync(table->dev, 0, words * sizeof(uint32_t), ctx->stream), "cudaMemsetAsync");
+        *out = table.release();
+    });
+}
+
+int32_t psi_table_destroy(psi_table* table) {
+    if (table == nullptr) return PSI_OK;
+    int32_t status = guarded(table->ctx, [&] {
+        table->ctx->bind();
+        (void)cudaStreamSynchronize(table->ctx->stream);
+        if (table->dev != nullptr) cuda_check(cudaFree(table->dev), "cudaFree");
+    });
+    delete table;
+    return status;
+}
+
+static void table_check(const psi_table* t, uint32_t slot, uint32_t layer, uint32_t block) {
+    require(slot < t->layout.num_req_slots, "GQA request page table req_slot out of range");
+    require(layer < t->layout.num_gqa_layers, "GQA request page table layer out of range");
+    require(block < t->layout.num_blocks, "GQA request page table block out of range");
+}
+
+static void table_upload(psi_table* t, uint64_t start, uint64_t count) {
+    if (count == 0) return;
+    cuda_check(cudaMemcpyAsync(t->dev + start, t->host.data() + start, count * sizeof(uint32_t),
+                               cudaMemcpyHostToDevice, t->ctx->stream),
+               "cudaMemcpyAsync");
+}
+
+int32_t psi_table_write(psi_table* table, uint32_t req_slot, uint32_t layer, uint32_t block, const uint32_t* page_ids,
+                        uint32_t n) {
+    if (table == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(table->ctx, [&] {
+        require(page_ids != nullptr, "page_ids must not be null");
+        table_check(table, req_slot, layer, block);
+        require(n == table->layout.num_page_ids_per_block,
+                "GQA page-id count must match one request/GQA-layer/block entry");
+        table->ctx->bind();
+        const uint64_t start = table->start_index(req_slot, layer, block);
+        std::copy(page_ids, page_ids + n, table->host.begin() + start);
+        table_upload(table, start, n);
+    });
+}
+
+int32_t psi_table_write_all_layers(psi_table* table, uint32_t req_slot, uint32_t block, const uint32_t* page_ids,
+                                   uint32_t n, uint64_t num_cache_pages) {
+    if (table == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(table->ctx, [&] {
+        require(page_ids != nullptr, "page_ids must not be null");
+        table_check(table, req_slot, 0, block);
+        const uint32_t per_layer = table->layout.num_page_ids_per_block;
+        require(uint64_t(n) == uint64_t(table->layout.num_gqa_layers) * per_layer,
+                "GQA cache block must contain all layer page IDs");
+        for (uint32_t i = 0; i < n; ++i) {
+            require(page_ids[i] < num_cache_pages, "runtime supplied a GQA page ID outside the cache-page buffer");
+        }
+        table->ctx->bind();
+        for (uint32_t layer = 0; layer < table->layout.num_gqa_layers; ++layer) {
+            const uint64_t start = table->start_index(req_slot, layer, block);
+            std::copy(page_ids + uint64_t(layer) * per_layer, page_ids + uint64_t(layer + 1) * per_layer,
+                      table->host.begin() + start);
+            table_upload(table, start, per_layer);
+        }
+    });
+}
+
+int32_t psi_table_write_row(psi_table* table, uint32_t req_slot, uint32_t layer, const uint32_t* ids, uint32_t n) {
+    if (table == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(table->ctx, [&] {
+        require(ids != nullptr, "ids must not be null");
+        table_check(table, req_slot, layer, 0);
+        require(n <= table->row_words(), "page-id count exceeds one request/GQA-layer row");
+        table->ctx->bind();
+        const uint64_t start = table->start_index(req_slot, layer, 0);
+        std::copy(ids, ids + n, table->host.begin() + start);
+        table_upload(table, start, n);
+    });
+}
+
+int32_t psi_table_read(psi_table* table, uint32_t req_slot, uint32_t layer, uint32_t block, uint32_t* out, uint32_t n) {
+    if (table == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(table->ctx, [&] {
+        require(out != nullptr, "out must not be null");
+        table_check(table, req_slot, layer, block);
+        require(n == table->layout.num_page_ids_per_block,
+                "GQA page-id count must match one request/GQA-layer/block entry");
+        table->ctx->bind();
+        const uint64_t start = table->start_index(req_slot, layer, block);
+        cuda_check(cudaMemcpyAsync(out, table->dev + start, n * sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                                   table->ctx->stream),
+                   "cudaMemcpyAsync");
+        cuda_check(cudaStreamSynchronize(table->ctx->stream), "cudaStreamSynchronize");
+    });
+}
+
+int32_t psi_table_reset_slots(psi_table* table, const uint32_t* req_slots, uint32_t n) {
+    if (table == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(table->ctx, [&] {
+        require(req_slots != nullptr || n == 0, "req_slots must not be null");
+        for (uint32_t i = 0; i < n; ++i) require(req_slots[i] < table->layout.num_req_slots,
+                                                 "GQA request page table req_slot out of range");
+        table->ctx->bind();
+        const uint64_t per_req = table->layout.num_gqa_layers * table->row_words();
+        for (uint32_t i = 0; i < n; ++i) {
+            const uint64_t start = table->start_index(req_slots[i], 0, 0);
+            std::fill(table->host.begin() + start, table->host.begin() + start + per_req, 0u);
+            cuda_check(cudaMemsetAsync(table->dev + start, 0, per_req * sizeof(uint32_t), table->ctx->stream),
+                       "cudaMemsetAsync");
+        }
+    });
+}
+
+int32_t psi_table_device_ptr(psi_table* table, void** out) {
+    if (table == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    *out = table->dev;
+    return PSI_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// host-side policy
+// ---------------------------------------------------------------------------------------------------------------------
+int32_t psi_replay_bucket_policy(uint32_t max_capacity, const uint32_t* boundaries, uint32_t num_boundaries,
+                                 uint32_t* out, uint64_t out_cap, uint64_t* out_n) {
+    return guarded(nullptr, [&] {
+        require(out_n != nullptr, "out_n must not be null");
+        BucketPolicy policy(max_capacity, std::vector<uint32_t>(boundaries, boundaries + num_boundaries));
+        *out_n = policy.buckets().size();
+        require(out != nullptr && out_cap >= policy.buckets().size(), "bucket output capacity too small");
+        std::copy(policy.buckets().begin(), policy.buckets().end(), out);
+    });
+}
+
+int32_t psi_replay_bucket_capacity(uint32_t max_capacity, const uint32_t* boundaries, uint32_t num_boundaries,
+                                   uint32_t active, uint32_t* out) {
+    return guarded(nullptr, [&] {
+        require(out != nullptr, "out must not be null");
+        BucketPolicy policy(max_capacity, std::vector<uint32_t>(boundaries, boundaries + num_boundaries));
+        *out = policy.capacity(active);
+    });
+}
+
+int32_t psi_split_kv_select(uint32_t io_dtype, uint32_t page_bytes, uint32_t num_q_heads, uint32_t num_kv_heads,
+                            uint32_t head_dim, uint32_t dspark_history, uint32_t num_tokens,
+                            uint32_t num_q_token_tiles, psi_split_kv_variant* out, uint32_t* out_max_q) {
+    return guarded(nullptr, [&] {
+        require(out != nullptr, "out must not be null");
+        SplitKvSelector selector(io_dtype, page_bytes, num_q_heads, num_kv_heads, head_dim, dspark_history != 0);
+        if (out_max_q != nullptr) *out_max_q = selector.max_q_tokens_per_partial_output();
+        *out = selector.select(num_tokens, num_q_token_tiles);
+    });
+}
+
+int32_t psi_metadata_update_host(uint32_t max_tokens, const uint32_t* req_slots, const uint32_t* token_indices,
+                                 const uint32_t* cu_tokens, uint32_t num_reqs, const psi_split_kv_variant* variant,
+                                 uint32_t capacity_mode, const uint32_t* boundaries, uint32_t num_boundaries,
+                                 uint32_t caller_num_total_tokens, uint32_t* buf_req_slots,
+                                 uint32_t* buf_flat_token_indices, uint32_t* buf_q_token_tiles, uint32_t* buf_kv_splits,
+                                 uint32_t* buf_cu_kv_splits, psi_replay_shape* out_shape) {
+    return guarded(nullptr, [&] {
+        require(req_slots && token_indices && cu_tokens && variant && out_shape, "metadata inputs must not be null");
+        require(buf_req_slots && buf_flat_token_indices && buf_q_token_tiles && buf_kv_splits && buf_cu_kv_splits,
+                "metadata buffers must not be null");
+        require(capacity_mode <= PSI_CAPACITY_CALLER_TOKENS, "unknown capacity mode");
+        ReferenceMetadata md(max_tokens);
+        const size_t t = max_tokens;
+        std::copy(buf_req_slots, buf_req_slots + t, md.req_slots.begin());
+        std::copy(buf_flat_token_indices, buf_flat_token_indices + t, md.flat_token_indices.begin());
+        std::copy(buf_q_token_tiles, buf_q_token_tiles + 2 * t, md.q_token_tiles.begin());
+        std::copy(buf_kv_splits, buf_kv_splits + 3 * t, md.kv_splits.begin());
+        std::copy(buf_cu_kv_splits, buf_cu_kv_splits + t + 1, md.cu_kv_splits.begin());
+        *out_shape = md.update(req_slots, token_indices, cu_tokens, num_reqs, *variant, capacity_mode,
+                               std::vector<uint32_t>(boundaries, boundaries + num_boundaries), caller_num_total_tokens);
+        std::copy(md.req_slots.begin(), md.req_slots.end(), buf_req_slots);
+        std::copy(md.flat_token_indices.begin(), md.flat_token_indices.end(), buf_flat_token_indices);
+        std::copy(md.q_token_tiles.begin(), md.q_token_tiles.end(), buf_q_token_tiles);
+        std::copy(md.kv_splits.begin(), md.kv_splits.end(), buf_kv_splits);
+        std::copy(md.cu_kv_splits.begin(), md.cu_kv_splits.end(), buf_cu_kv_splits);
+    });
+}
+
+int32_t psi_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint32_t* token_indices,
+                         const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas, uint32_t min_kv_tiles_per_cta,
+                         uint32_t* out_items, uint64_t items_cap, uint32_t* out_cta_item_begin, uint64_t cta_cap,
+                         uint32_t* out_counts) {
+    return guarded(nullptr, [&] {
+        require(token_indices && cu_tokens && out_counts, "plan inputs must not be null");
+        require(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
+                "GQA q heads must be a positive multiple of kv heads");
+        require(num_reqs > 0 && cu_tokens[0] == 0, "GQA batch cu_tokens must start at zero");
+        for (uint32_t r = 0; r < num_reqs; ++r)
+            require(cu_tokens[r] <= cu_tokens[r + 1], "GQA batch cu_tokens must be nondecreasing");
+        const WorkPlan plan = build_balanced_plan(plan_geometry(num_q_heads, num_kv_heads), token_indices, cu_tokens,
+                                                  num_reqs, max_ctas, min_kv_tiles_per_cta);
+        out_counts[0] = static_cast<uint32_t>(plan.items.size());
+        out_counts[1] = plan.num_ctas();
+        out_counts[2] = plan.num_partial_slots;
+        out_counts[3] = static_cast<uint32_t>(plan.reduces.size());
+        out_counts[4] = static_cast<uint32_t>(plan.tiles.size());
+        out_counts[5] = static_cast<uint32_t>(std::min<uint64_t>(plan.total_kv_tiles, kU32Max));
+        if (out_items != nullptr) {
+            require(items_cap >= plan.items.size(), "item output capacity too small");
+            for (size_t i = 0; i < plan.items.size(); ++i) {
+                const WorkItem& it = plan.items[i];
+                uint32_t* o = out_items + i * 6;
+                o[0] = it.tile;
+                o[1] = it.head_sel;
+                o[2] = it.kv_begin;
+                o[3] = it.kv_end;
+                o[4] = it.partial_slot;
+                o[5] = plan.tiles[it.tile].flat_begin;
+            }
+        }
+        if (out_cta_item_begin != nullptr) {
+            require(cta_cap >= plan.cta_item_begin.size(), "cta output capacity too small");
+            std::copy(plan.cta_item_begin.begin(), plan.cta_item_begin.end(), out_cta_item_begin);
+        }
+    });
+}
+
+int32_t psi_id_allocator_create(uint64_t capacity, psi_id_allocator** out) {
+    return guarded(nullptr, [&] {
+        require(out != nullptr, "out must not be null");
+        *out = new psi_id_allocator(capacity);
+    });
+}
+
+int32_t psi_id_allocator_destroy(psi_id_allocator* a) {
+    delete a;
+    return PSI_OK;
+}
+
+int32_t psi_id_allocator_alloc_many(psi_id_allocator* a, uint64_t count, uint32_t* out_ids) {
+    if (a == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(nullptr, [&] {
+        require(out_ids != nullptr || count == 0, "out_ids must not be null");
+        a->impl.alloc_many(count, out_ids);
+    });
+}
+
+int32_t psi_id_allocator_free_many(psi_id_allocator* a, const uint32_t* ids, uint64_t count) {
+    if (a == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(nullptr, [&] {
+        require(ids != nullptr || count == 0, "ids must not be null");
+        a->impl.free_many(ids, count);
+    });
+}
+
+int32_t psi_id_allocator_bitmap(psi_id_allocator* a, uint64_t* out_words, uint64_t cap, uint64_t* out_n) {
+    if (a == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(nullptr, [&] {
+        const auto& words = a->impl.bitmap();
+        if (out_n != nullptr) *out_n = words.size();
+        for (uint64_t i = 0; i < words.size() && i < cap && out_words != nullptr; ++i) out_words[i] = words[i];
+    });
+}
+
+int32_t psi_id_allocator_free_count(psi_id_allocator* a, uint64_t* out) {
+    if (a == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    *out = a->impl.free_count();
+    return PSI_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// GQA component
+// ---------------------------------------------------------------------------------------------------------------------
+int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        require(out != nullptr && config != nullptr, "out and config must not be null");
+        *out = nullptr;
+        const psi_gqa_config& c = *config;
+        require(c.num_q_heads > 0 && c.num_kv_heads > 0 && c.head_dim > 0, "GQA head counts and head_dim must be positive");
+        require(c.num_q_heads % c.num_kv_heads == 0, "GQA q heads must be a multiple of kv heads");
+        require(c.scale > 0.0f && std::isfinite(c.scale), "GQA scale must be positive");
+        require(c.dtype <= PSI_DTYPE_F16, "unsupported GQA dtype");
+        require(c.max_tokens > 0, "GQA batch metadata requires tokens");
+        require(c.plan_mode <= PSI_PLAN_REFERENCE && c.kernel_mode <= PSI_KERNEL_MMA, "unknown plan or kernel mode");
+        validate_layout(c.layout);
+        const uint64_t per_token = uint64_t(c.num_kv_heads) * c.head_dim * 2u * dtype_bytes(c.dtype);
+        require(per_token <= kU32Max, "GQA K/V bytes per token must fit u32");
+        require(c.page_bytes > 0 && c.page_bytes % per_token == 0,
+                "GQA page_bytes must be divisible by the K/V bytes per token");
+        require(uint64_t(c.max_tokens) * c.num_q_heads * c.head_dim <= kU32Max,
+                "GQA SDPA query/output exceeds the shader u32 count domain");
+        require(c.head_dim <= 256, "GQA head_dim above 256 is not supported");
+        ctx->bind();
+
+        auto g = std::make_unique<psi_gqa>();
+        g->ctx = ctx;
+        g->cfg = c;
+        g->tokens_per_page = c.page_bytes / static_cast<uint32_t>(per_token);
+        g->geo = plan_geometry(c.num_q_heads, c.num_kv_heads);
+        const bool mma_ok = attend_mma_supported(c.dtype, c.head_dim, g->tokens_per_page);
+        if (c.kernel_mode == PSI_KERNEL_MMA) require(mma_ok, "the mma kernel does not support this profile");
+        g->kernel = (c.kernel_mode == PSI_KERNEL_GENERIC || !mma_ok) ? PSI_KERNEL_GENERIC : PSI_KERNEL_MMA;
+        const uint32_t per_sm =
+            g->kernel == PSI_KERNEL_MMA ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm();
+        g->grid_cap = c.max_ctas > 0 ? c.max_ctas : static_cast<uint32_t>(ctx->sm_count) * per_sm;
+        if (c.dtype != PSI_DTYPE_F16) {
+            g->selector = std::make_unique<SplitKvSelector>(c.dtype, c.page_bytes, c.num_q_heads, c.num_kv_heads,
+                                                            c.head_dim, false);
+        }
+        g->md = std::make_unique<ReferenceMetadata>(c.max_tokens);
+        cuda_check(cudaEventCreateWithFlags(&g->upload_done, cudaEventDisableTiming), "cudaEventCreateWithFlags");
+        *out = g.release();
+    });
+}
+
+int32_t psi_gqa_destroy(psi_gqa* g) {
+    if (g == nullptr) return PSI_OK;
+    int32_t status = guarded(g->ctx, [&] {
+        g->ctx->bind();
+        (void)cudaStreamSynchronize(g->ctx->stream);
+        g->block.release();
+        g->partial_o.release();
+        g->partial_ml.release();
+        g->step_k.release();
+        g->step_v.release();
+        g->step_q.release();
+        g->step_out.release();
+        g->combine_ptrs.release();
+        if (g->staging != nullptr) (void)cudaFreeHost(g->staging);
+        if (g->upload_done != nullptr) (void)cudaEventDestroy(g->upload_done);
+    });
+    delete g;
+    return status;
+}
+
+int32_t psi_gqa_set_token_topology_boundaries(psi_gqa* g, const uint32_t* boundaries, uint32_t n) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(boundaries != nullptr || n == 0, "boundaries must not be null");
+        for (uint32_t i = 0; i < n; ++i) require(boundaries[i] > 0, "replay topology boundary must be positive");
+        g->boundaries.assign(boundaries, boundaries + n);
+    });
+}
+
+int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
+                        uint32_t num_reqs, uint32_t capacity_mode, uint32_t caller_num_total_tokens,
+                        psi_replay_shape* out_shape) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(req_slots != nullptr && token_indices != nullptr && cu_tokens != nullptr, "metadata inputs must not be null");
+        require(capacity_mode <= PSI_CAPACITY_CALLER_TOKENS, "unknown capacity mode");
+        require(num_reqs > 0, "GQA batch metadata requires tokens");
+        psi_ctx* ctx = g->ctx;
+        ctx->bind();
+        g->prepared = false;
+
+        // Variant selection as the reference's executor does it (crates/inference-executor-metal/src/attn/gqa/mod.rs:
+        // 64-94, without its measured D256/page8 work model, which tunes a different device).
+        require(cu_tokens[0] == 0, "GQA batch cu_tokens must start at zero");
+        uint64_t ref_q_tiles = 0;
+        for (uint32_t r = 0; r < num_reqs; ++r) {
+            require(cu_tokens[r] <= cu_tokens[r + 1], "GQA batch cu_tokens must be nondecreasing");
+            ref_q_tiles += (uint64_t(cu_tokens[r + 1] - cu_tokens[r]) + 7) / 8;
+        }
+        const uint32_t num_tokens = cu_tokens[num_reqs];
+        require(num_tokens > 0, "GQA batch metadata requires tokens");
+        require(num_tokens <= g->cfg.max_tokens, "GQA batch exceeds the metadata token capacity");
+        psi_split_kv_variant variant{};
+        if (g->selector) {
+            variant = g->selector->select(num_tokens, static_cast<uint32_t>(ref_q_tiles));
+        } else {
+            variant.kv_token_tile_size = 256;  // f16 has no reference profile: SingleQ geometry of a 256-thread block
+            variant.num_threads_per_threadblock = 256;
+            variant.q_head_tile_size = std::min(g->geo.group, 8u);
+        }
+        const psi_replay_shape shape = g->md->update(req_slots, token_indices, cu_tokens, num_reqs, variant,
+                                                     capacity_mode, g->boundaries, caller_num_total_tokens);
+
+        const uint64_t table_tokens =
+            uint64_t(g->cfg.layout.num_blocks) * g->cfg.layout.num_page_ids_per_block * g->tokens_per_page;
+        for (uint32_t r = 0; r < num_reqs; ++r) {
+            require(req_slots[r] < g->cfg.layout.num_req_slots, "GQA request page table req_slot out of range");
+            require(uint64_t(token_indices[r]) + (cu_tokens[r + 1] - cu_tokens[r]) <= table_tokens,
+                    "GQA request context does not fit the request page table");
+        }
+
+        if (g->cfg.plan_mode == PSI_PLAN_REFERENCE) {
+            g->plan = build_reference_plan(g->geo, *g->md, shape, variant.tiled_q != 0);
+        } else {
+            const uint32_t min_tiles = g->kernel == PSI_KERNEL_MMA ? 8u : 4u;
+            g->plan = build_balanced_plan(g->geo, token_indices, cu_tokens, num_reqs, g->grid_cap, min_tiles);
+        }
+        const WorkPlan& plan = g->plan;
+
+        // Pack the device block: scalars | req_slots | flat_token_indices | tiles | cta ranges | reduces | items.
+        uint64_t cursor = pad_words(kScalarCount);
+        g->off_req_slots = cursor;
+        cursor += pad_words(num_tokens);
+        g->off_token_indices = cursor;
+        cursor += pad_words(num_tokens);
+        g->off_tiles = cursor;
+        cursor += pad_words(plan.tiles.size() * 2);
+        g->off_cta = cursor;
+        cursor += pad_words(plan.cta_item_begin.size());
+        g->off_reduces = cursor;
+        cursor += pad_words(plan.reduces.size() * 2);
+        g->off_items = cursor;
+        cursor += pad_words(plan.items.size() * 8);
+        const uint64_t words = cursor;
+
+        if (g->staging_words < words) {
+            if (g->staging != nullptr) {
+                cuda_check(cudaEventSynchronize(g->upload_done), "cudaEventSynchronize");
+                cuda_check(cudaFreeHost(g->staging), "cudaFreeHost");
+                g->staging = nullptr;
+            }
+            const uint64_t grown = std::max<uint64_t>(words * 2, 4096);
+            cuda_check(cudaMallocHost(reinterpret_cast<void**>(&g->staging), grown * sizeof(uint32_t)), "cudaMallocHost");
+            g->staging_words = grown;
+        } else {
+            cuda_check(cudaEventSynchronize(g->upload_done), "cudaEventSynchronize");  // previous upload left staging
+        }
+        g->block.ensure(ctx, g->staging_words * sizeof(uint32_t), false);
+        if (plan.num_partial_slots > g->partial_slots_cap) {
+            const uint64_t slots = std::max<uint64_t>(plan.num_partial_slots, 2ull * g->grid_cap);
+            g->partial_o.ensure(ctx, slots * kMaxRows * g->cfg.head_dim * sizeof(float), false);
+            g->partial_ml.ensure(ctx, 2 * slots * kMaxRows * sizeof(float), false);
+            g->partial_slots_cap = slots;
+        }
+
+        uint32_t* s = g->staging;
+        std::fill(s, s + kScalarCount, 0u);
+        s[kScalarNumActiveTokens] = num_tokens;
+        s[kScalarNumCtas] = plan.num_ctas();
+        s[kScalarNumReduces] = static_cast<uint32_t>(plan.reduces.size());
+        std::copy(g->md->req_slots.begin(), g->md->req_slots.begin() + num_tokens, s + g->off_req_slots);
+        std::copy(g->md->flat_token_indices.begin(), g->md->flat_token_indices.begin() + num_tokens,
+                  s + g->off_token_indices);
+        if (!plan.tiles.empty()) std::memcpy(s + g->off_tiles, plan.tiles.data(), plan.tiles.size() * sizeof(ExecTile));
+        std::copy(plan.cta_item_begin.begin(), plan.cta_item_begin.end(), s + g->off_cta);
+        if (!plan.reduces.empty())
+            std::memcpy(s + g->off_reduces, plan.reduces.data(), plan.reduces.size() * sizeof(ReduceUnit));
+        if (!plan.items.empty()) std::memcpy(s + g->off_items, plan.items.data(), plan.items.size() * sizeof(WorkItem));
+        cuda_check(cudaMemcpyAsync(g->block.ptr, s, words * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream),
+                   "cudaMemcpyAsync");
+        cuda_check(cudaEventRecord(g->upload_done, ctx->stream), "cudaEventRecord");
+
+        g->shape = shape;
+        g->variant = variant;
+        g->prepared = true;
+        if (out_shape != nullptr) *out_shape = shape;
+    });
+}
+
+int32_t psi_gqa_split_kv_variant(psi_gqa* g, psi_split_kv_variant* out) {
+    if (g == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(g->prepared, "GQA batch metadata must be updated before recording");
+        *out = g->variant;
+    });
+}
+
+static std::vector<uint32_t>* metadata_array(psi_gqa* g, uint32_t which) {
+    switch (which) {
+        case PSI_MD_REQ_SLOTS: return &g->md->req_slots;
+        case PSI_MD_FLAT_TOKEN_INDICES: return &g->md->flat_token_indices;
+        case PSI_MD_Q_TOKEN_TILES: return &g->md->q_token_tiles;
+        case PSI_MD_KV_SPLITS: return &g->md->kv_splits;
+        case PSI_MD_CU_KV_SPLITS: return &g->md->cu_kv_splits;
+        default: return nullptr;
+    }
+}
+
+int32_t psi_gqa_metadata_read(psi_gqa* g, uint32_t which, uint64_t offset, uint32_t* out, uint64_t n) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        auto* array = metadata_array(g, which);
+        require(array != nullptr && out != nullptr, "unknown metadata array or null output");
+        require(offset <= array->size() && n <= array->size() - offset, "metadata range out of bounds");
+        std::copy(array->begin() + offset, array->begin() + offset + n, out);
+    });
+}
+
+int32_t psi_gqa_metadata_write(psi_gqa* g, uint32_t which, uint64_t offset, const uint32_t* in, uint64_t n) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        auto* array = metadata_array(g, which);
+        require(array != nullptr && in != nullptr, "unknown metadata array or null input");
+        require(offset <= array->size() && n <= array->size() - offset, "metadata range out of bounds");
+        std::copy(in, in + n, array->begin() + offset);
+    });
+}
+
+int32_t psi_gqa_plan_stats(psi_gqa* g, uint32_t* out, uint32_t n) {
+    if (g == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(g->prepared, "GQA batch metadata must be updated before recording");
+        const uint32_t stats[8] = {g->plan.num_ctas(),
+                                   static_cast<uint32_t>(g->plan.items.size()),
+                                   g->plan.num_partial_slots,
+                                   static_cast<uint32_t>(g->plan.reduces.size()),
+                                   static_cast<uint32_t>(g->plan.tiles.size()),
+                                   g->kernel,
+                                   static_cast<uint32_t>(std::min<uint64_t>(g->plan.total_kv_tiles, kU32Max)),
+                                   g->geo.tokens_per_tile * g->geo.heads_per_tile};
+        for (uint32_t i = 0; i < n && i < 8; ++i) out[i] = stats[i];
+    });
+}
+
+int32_t psi_gqa_kv_append(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* k, const void* v) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        g->ctx->bind();
+        run_append(g, pages, table, layer, k, v);
+    });
+}
+
+int32_t psi_gqa_attend(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* q, void* out) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(out != nullptr, "out must not be null");
+        g->ctx->bind();
+        AttendParams p = attend_params(g, pages, table, layer, q);
+        p.out = out;
+        run_attend(g, p);
+    });
+}
+
+int32_t psi_gqa_attend_partial(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* q, float* o,
+                               float* m, float* l) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(o != nullptr && m != nullptr && l != nullptr, "partial outputs must not be null");
+        require((reinterpret_cast<uintptr_t>(o) & 15u) == 0, "partial output o must be 16-byte aligned");
+        g->ctx->bind();
+        AttendParams p = attend_params(g, pages, table, layer, q);
+        p.ext_o = o;
+        p.ext_m = m;
+        p.ext_l = l;
+        run_attend(g, p);
+    });
+}
+
+int32_t psi_gqa_combine(psi_gqa* g, const float* const* o, const float* const* m, const float* const* l, uint32_t n,
+                        uint32_t num_tokens, void* out) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(o != nullptr && m != nullptr && l != nullptr && out != nullptr, "combine arguments must not be null");
+        require(n > 0 && n <= 64, "combine takes between 1 and 64 partials");
+        require(num_tokens > 0 && num_tokens <= g->cfg.max_tokens, "combine token count out of range");
+        psi_ctx* ctx = g->ctx;
+        ctx->bind();
+        g->combine_ptrs.ensure(ctx, 3 * 64 * sizeof(void*), false);
+        std::vector<const float*> host(3 * 64, nullptr);
+        for (uint32_t i = 0; i < n; ++i) {
+            require(o[i] != nullptr && m[i] != nullptr && l[i] != nullptr, "combine partial pointers must not be null");
+            host[i] = o[i];
+            host[64 + i] = m[i];
+            host[128 + i] = l[i];
+        }
+        // Pageable source: the runtime stages the bytes before the call returns, so `host` may go out of scope.
+        cuda_check(cudaMemcpyAsync(g->combine_ptrs.ptr, host.data(), host.size() * sizeof(void*),
+                                   cudaMemcpyHostToDevice, ctx->stream),
+                   "cudaMemcpyAsync");
+        CombineParams p{};
+        auto* base = static_cast<const float* const*>(g->combine_ptrs.ptr);
+        p.o = base;
+        p.m = base + 64;
+        p.l = base + 128;
+        p.n = n;
+        p.num_rows = num_tokens * g->cfg.num_q_heads;
+        p.head_dim = g->cfg.head_dim;
+        p.dtype = g->cfg.dtype;
+        p.out = out;
+        cuda_check(launch_combine(p, ctx->stream), "combine launch");
+        ctx->launches += 1;
+    });
+}
+
+int32_t psi_gqa_decode_step_host(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* k_host,
+                                 const void* v_host, const void* q_host, void* out_host) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(k_host != nullptr && v_host != nullptr && q_host != nullptr && out_host != nullptr,
+                "host buffers must not be null");
+        require(g->prepared, "GQA batch metadata must be updated before recording");
+        psi_ctx* ctx = g->ctx;
+        ctx->bind();
+        const uint64_t esz = dtype_bytes(g->cfg.dtype);
+        const uint64_t kv_cap = uint64_t(g->cfg.max_tokens) * g->cfg.num_kv_heads * g->cfg.head_dim * esz;
+        const uint64_t q_cap = uint64_t(g->cfg.max_tokens) * g->cfg.num_q_heads * g->cfg.head_dim * esz;
+        g->step_k.ensure(ctx, kv_cap, false);
+        g->step_v.ensure(ctx, kv_cap, false);
+        g->step_q.ensure(ctx, q_cap, false);
+        g->step_out.ensure(ctx, q_cap, false);
+        const uint64_t kv_bytes = uint64_t(g->shape.num_tokens) * g->cfg.num_kv_heads * g->cfg.head_dim * esz;
+        const uint64_t q_bytes = uint64_t(g->shape.num_tokens) * g->cfg.num_q_heads * g->cfg.head_dim * esz;
+        cuda_check(cudaMemcpyAsync(g->step_k.ptr, k_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D k");
+        cuda_check(cudaMemcpyAsync(g->step_v.ptr, v_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D v");
+        cuda_check(cudaMemcpyAsync(g->step_q.ptr, q_host, q_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D q");
+        run_append(g, pages, table, layer, g->step_k.ptr, g->step_v.ptr);
+        AttendParams p = attend_params(g, pages, table, layer, g->step_q.ptr);
+        p.out = g->step_out.ptr;
+        run_attend(g, p);
+        cuda_check(cudaMemcpyAsync(out_host, g->step_out.ptr, q_bytes, cudaMemcpyDeviceToHost, ctx->stream), "D2H out");
+        cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    });
+}
+
+int32_t psi_page_gather(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t req_slot, uint32_t layer,
+                        uint32_t tok_begin, uint32_t tok_end, void* k_out, void* v_out) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(k_out != nullptr && v_out != nullptr, "gather outputs must not be null");
+        require(tok_begin <= tok_end, "gather token range is reversed");
+        g->ctx->bind();
+        GatherParams p{};
+        p.geo = page_geometry(g, pages, table, layer);
+        require(req_slot < g->cfg.layout.num_req_slots, "GQA request page table req_slot out of range");
+        require(uint64_t(tok_end) <= uint64_t(p.geo.pages_per_req) * g->tokens_per_page,
+                "gather token range does not fit the request page table");
+        p.req_slot = req_slot;
+        p.tok_begin = tok_begin;
+        p.tok_end = tok_end;
+        p.k_out = k_out;
+        p.v_out = v_out;
+        cuda_check(launch_page_gather(p, g->ctx->stream), "page gather launch");
+        g->ctx->launches += tok_end > tok_begin;
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,214 @@
+// Generic split-KV flash-decode map kernel on CUDA cores, the partial reduce and the cross-device combine.
+//
+// The generic map kernel takes every profile the reference's SingleQ kernel takes (f32 / bf16, any tokens_per_page,
+// head_dim up to 256) plus f16: one warp per CTA walks its work items; lanes split head_dim, every KV row is read
+// once per item and scored against all rows (tokens x group heads) of the item with f32 accumulation and an online
+// softmax in the log2 domain.  Semantics follow
+// crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_map.metal:85-252 (visibility through
+// kv_end only) extended with the per-row causal limit of metal/gqa_split_kv_tiled_q.metal:233-244.
+#include <cmath>
+
+#include "device_common.cuh"
+
+namespace psi {
+
+namespace {
+
+constexpr int kGenericThreads = 32;
+
+template <int DPL>
+__global__ void __launch_bounds__(kGenericThreads) attend_generic_kernel(AttendParams p) {
+    const uint32_t cta = blockIdx.x;
+    if (cta >= p.scalars[kScalarNumCtas]) return;
+    const uint32_t lane = threadIdx.x;
+    const uint32_t D = p.geo.head_dim;
+    __shared__ float q_s[kMaxRows * 256];
+    __shared__ uint32_t limit_s[kMaxRows];
+
+    for (uint32_t index = p.cta_item_begin[cta]; index < p.cta_item_begin[cta + 1]; ++index) {
+        const ItemView v = view_item(p, p.items[index]);
+        __syncwarp();
+        for (uint32_t i = lane; i < v.rows * D; i += kGenericThreads) {
+            const uint32_t r = i / D, d = i % D;
+            q_s[r * D + d] = load_as_float(p.q, item_row_index(p, v, r) * D + d, p.dtype);
+        }
+        if (lane < v.rows) limit_s[lane] = p.flat_token_indices[v.flat_begin + lane / v.num_heads] + 1;
+        __syncwarp();
+
+        float m[kMaxRows], l[kMaxRows], o[kMaxRows][DPL];
+#pragma unroll
+        for (int r = 0; r < int(kMaxRows); ++r) {
+            m[r] = -INFINITY;
+            l[r] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o[r][i] = 0.0f;
+        }
+
+        const uint32_t* row_ids = table_row(p.geo, v.req_slot);
+        const uint64_t v_off = v_region_offset(p.geo);
+        for (uint32_t t = v.kv_begin; t < v.kv_end; ++t) {
+            const uint32_t page_id = row_ids[t / p.geo.tokens_per_page];
+            const uint64_t base = kv_row_offset(p.geo, page_id, v.kv_head, t % p.geo.tokens_per_page);
+            float kreg[DPL], vreg[DPL];
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                const uint32_t d = lane + 32 * i;
+                kreg[i] = d < D ? load_as_float(p.geo.pages, base + d, p.dtype) : 0.0f;
+                vreg[i] = d < D ? load_as_float(p.geo.pages, base + v_off + d, p.dtype) : 0.0f;
+            }
+#pragma unroll
+            for (int r = 0; r < int(kMaxRows); ++r) {
+                if (r < int(v.rows)) {
+                    float dot = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) {
+                        const uint32_t d = lane + 32 * i;
+                        dot += d < D ? q_s[r * D + d] * kreg[i] : 0.0f;
+                    }
+                    dot = warp_sum(dot);
+                    if (t < limit_s[r]) {
+                        const float x = dot * p.scale_log2;
+                        const float m_new = fmaxf(m[r], x);
+                        const float corr = exp2f(m[r] - m_new);  // m = -inf -> 0
+                        const float w = exp2f(x - m_new);
+                        l[r] = l[r] * corr + w;
+#pragma unroll
+                        for (int i = 0; i < DPL; ++i) o[r][i] = o[r][i] * corr + w * vreg[i];
+                        m[r] = m_new;
+                    }
+                }
+            }
+        }
+
+#pragma unroll
+        for (int r = 0; r < int(kMaxRows); ++r) {
+            if (r < int(v.rows)) {
+                const float inv = l[r] > 0.0f ? 1.0f / l[r] : 0.0f;
+                const uint64_t row = item_row_index(p, v, r);
+                if (v.partial_slot != kU32Max) {
+                    const uint64_t prow = static_cast<uint64_t>(v.partial_slot) * kMaxRows + r;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) {
+                        const uint32_t d = lane + 32 * i;
+                        if (d < D) p.partial_o[prow * D + d] = o[r][i] * inv;
+                    }
+                    if (lane == 0) {
+                        p.partial_m[prow] = m[r];
+                        p.partial_l[prow] = l[r];
+                    }
+                } else if (p.ext_o != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) {
+                        const uint32_t d = lane + 32 * i;
+                        if (d < D) p.ext_o[row * D + d] = o[r][i] * inv;
+                    }
+                    if (lane == 0) {
+                        p.ext_m[row] = m[r] * kLn2;
+                        p.ext_l[row] = l[r];
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) {
+                        const uint32_t d = lane + 32 * i;
+                        if (d < D) store_from_float(p.out, row * D + d, p.dtype, o[r][i] * inv);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// One CTA per (tile, head selection) unit that more than one item contributed to:
+// M = max m_i, w_i = 2^(m_i - M) * l_i (0 when m_i is not finite), out = sum w_i o_i / sum w_i (0 when empty),
+// crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_reduce.metal:27-48.
+constexpr int kReduceThreads = 128;
+
+__global__ void __launch_bounds__(kReduceThreads) attend_reduce_kernel(AttendParams p) {
+    const uint32_t unit = blockIdx.x;
+    if (unit >= p.scalars[kScalarNumReduces]) return;
+    const ReduceUnit ru = p.reduces[unit];
+    const ItemView v = view_item(p, p.items[ru.first_item]);
+    const uint32_t D = p.geo.head_dim;
+    const uint32_t first_slot = v.partial_slot;  // slots of one unit are consecutive
+    for (uint32_t i = threadIdx.x; i < v.rows * D; i += kReduceThreads) {
+        const uint32_t r = i / D, d = i % D;
+        float global_max = -INFINITY;
+        for (uint32_t s = 0; s < ru.num_items; ++s)
+            global_max = fmaxf(global_max, p.partial_m[static_cast<uint64_t>(first_slot + s) * kMaxRows + r]);
+        float sum = 0.0f, acc = 0.0f;
+        for (uint32_t s = 0; s < ru.num_items; ++s) {
+            const uint64_t prow = static_cast<uint64_t>(first_slot + s) * kMaxRows + r;
+            const float pm = p.partial_m[prow];
+            const float w = isfinite(pm) ? exp2f(pm - global_max) * p.partial_l[prow] : 0.0f;
+            sum += w;
+            acc += w * p.partial_o[prow * D + d];
+        }
+        const float value = sum > 0.0f ? acc / sum : 0.0f;
+        const uint64_t row = item_row_index(p, v, r);
+        if (p.ext_o != nullptr) {
+            p.ext_o[row * D + d] = value;
+            if (d == 0) {
+                p.ext_m[row] = global_max * kLn2;
+                p.ext_l[row] = sum;
+            }
+        } else {
+            store_from_float(p.out, row * D + d, p.dtype, value);
+        }
+    }
+}
+
+// Cross-device merge of per-device partials in the natural-log domain (same algebra as above).
+__global__ void __launch_bounds__(kReduceThreads) combine_kernel(CombineParams p) {
+    const uint64_t total = static_cast<uint64_t>(p.num_rows) * p.head_dim;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kReduceThreads + threadIdx.x; i < total;
+         i += static_cast<uint64_t>(gridDim.x) * kReduceThreads) {
+        const uint64_t row = i / p.head_dim;
+        float global_max = -INFINITY;
+        for (uint32_t s = 0; s < p.n; ++s) global_max = fmaxf(global_max, p.m[s][row]);
+        float sum = 0.0f, acc = 0.0f;
+        for (uint32_t s = 0; s < p.n; ++s) {
+            const float pm = p.m[s][row];
+            const float w = isfinite(pm) ? expf(pm - global_max) * p.l[s][row] : 0.0f;
+            sum += w;
+            acc += w * p.o[s][i];
+        }
+        store_from_float(p.out, i, p.dtype, sum > 0.0f ? acc / sum : 0.0f);
+    }
+}
+
+}  // namespace
+
+uint32_t attend_generic_ctas_per_sm() { return 8; }
+
+cudaError_t launch_attend_generic(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
+    if (num_ctas == 0) return cudaSuccess;
+    const uint32_t dpl = (p.geo.head_dim + 31) / 32;
+    if (dpl <= 1) {
+        attend_generic_kernel<1><<<num_ctas, kGenericThreads, 0, stream>>>(p);
+    } else if (dpl <= 2) {
+        attend_generic_kernel<2><<<num_ctas, kGenericThreads, 0, stream>>>(p);
+    } else if (dpl <= 4) {
+        attend_generic_kernel<4><<<num_ctas, kGenericThreads, 0, stream>>>(p);
+    } else if (dpl <= 8) {
+        attend_generic_kernel<8><<<num_ctas, kGenericThreads, 0, stream>>>(p);
+    } else {
+        return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attend_reduce(const AttendParams& p, uint32_t num_reduces, cudaStream_t stream) {
+    if (num_reduces == 0) return cudaSuccess;
+    attend_reduce_kernel<<<num_reduces, kReduceThreads, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream) {
+    const uint64_t total = static_cast<uint64_t>(p.num_rows) * p.head_dim;
+    if (total == 0) return cudaSuccess;
+    const uint64_t blocks = (total + kReduceThreads - 1) / kReduceThreads;
+    combine_kernel<<<static_cast<unsigned>(blocks < 4096 ? blocks : 4096), kReduceThreads, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace psi

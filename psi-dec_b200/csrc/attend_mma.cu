@@ -1,0 +1,445 @@
+// Split-KV flash-decode map kernel for bf16 / f16 on sm_100a.
+//
+// One CTA per device CTA slot walks a contiguous share of the step's work items.  A work item is all query rows of
+// one (q tile, KV head) - the tokens of the tile times the heads of the GQA group, at most 16 rows - against a range
+// of KV tokens, so every KV byte of the step is read from HBM exactly once.
+//
+// Inside a CTA each of the four warps owns every fourth 16-token KV tile of the item and streams it through its own
+// ring of shared-memory stages with 16-byte cp.async copies (a warp-wide copy covers 512 contiguous bytes of one
+// page), so the steady state has no CTA-wide barrier: a warp waits only for its own oldest stage.  The 16 query rows
+// are one m16 MMA tile: S = Q K^T and O += P V run as mma.sync.m16n8k16 with f32 accumulators, operands fetched by
+// ldmatrix from XOR-swizzled rows; the online softmax runs on the accumulator fragments with quad shuffles in the
+// log2 domain, and O is rescaled only when a row's running max moved.  At the end of an item the four warps merge
+// their (O, m, l) through shared memory and write either the final output or one partial slot.
+//
+// The arithmetic this replaces: crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_map.metal
+// (decode rows) and metal/gqa_split_kv_tiled_q.metal:161-319 (several query tokens of one request with the in-kernel
+// causal limit).
+#include <cmath>
+
+#include "device_common.cuh"
+
+namespace psi {
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kTile = 16;  // KV tokens per tile == query rows per item
+
+template <typename T>
+struct Mma;
+
+template <>
+struct Mma<__nv_bfloat16> {
+    __device__ static __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __device__ static __forceinline__ void store4(void* dst, float4 v) {
+        uint2 packed = make_uint2(pack(v.x, v.y), pack(v.z, v.w));
+        *reinterpret_cast<uint2*>(dst) = packed;
+    }
+};
+
+template <>
+struct Mma<__half> {
+    __device__ static __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __device__ static __forceinline__ void store4(void* dst, float4 v) {
+        uint2 packed = make_uint2(pack(v.x, v.y), pack(v.z, v.w));
+        *reinterpret_cast<uint2*>(dst) = packed;
+    }
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+// 16-byte global->shared copy; src_bytes == 0 zero-fills the destination without reading the source.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold `row_bytes` bytes: the chunk index is
+// XOR-ed with the low row bits so that the eight rows one ldmatrix phase reads fall into distinct banks.
+__device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk, uint32_t row_bytes) {
+    return row * row_bytes + ((chunk ^ (row & 7u)) << 4);
+}
+
+template <int D, int NSTAGE>
+struct SmemLayout {
+    static constexpr uint32_t kRowBytes = D * 2;
+    static constexpr uint32_t kTileBytes = kTile * kRowBytes;        // one K or V tile
+    static constexpr uint32_t kStageBytes = 2 * kTileBytes;          // K then V
+    static constexpr uint32_t kQBytes = kTile * kRowBytes;
+    static constexpr uint32_t kStagesOffset = kQBytes;
+    static constexpr uint32_t kMergeStride = D + 8;                  // floats per merged row
+    static constexpr uint32_t kMergeBytes = kWarps * kTile * kMergeStride * 4;
+    static constexpr uint32_t kRingBytes = kWarps * NSTAGE * kStageBytes;
+    static constexpr uint32_t kTotal = kStagesOffset + (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes);
+};
+
+template <typename T, int D, int NSTAGE>
+__global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p) {
+    using L = SmemLayout<D, NSTAGE>;
+    constexpr uint32_t kChunks = D / 8;        // 16-byte chunks per row
+    constexpr uint32_t kRowsPerCopy = 32 / (kChunks < 32 ? kChunks : 32);
+    constexpr int kKSteps = D / 16;
+
+    const uint32_t cta = blockIdx.x;
+    if (cta >= p.scalars[kScalarNumCtas]) return;
+
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ uint32_t limit_s[kTile];
+    __shared__ float merge_m[kWarps][kTile];
+    __shared__ float merge_l[kWarps][kTile];
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t warp = tid >> 5;
+    const uint32_t lane = tid & 31;
+    const uint32_t quad_row = lane >> 2;  // accumulator rows quad_row and quad_row + 8
+    const uint32_t quad_col = lane & 3;
+
+    const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const uint32_t q_base = smem_base;
+    const uint32_t ring_base = smem_base + L::kStagesOffset + warp * NSTAGE * L::kStageBytes;
+    float* merge_o = reinterpret_cast<float*>(smem + L::kStagesOffset);
+
+    const uint32_t P = p.geo.tokens_per_page;
+    const unsigned char* pages = static_cast<const unsigned char*>(p.geo.pages);
+    const uint64_t page_bytes = p.geo.page_elems * 2;
+    const uint64_t v_region_bytes = v_region_offset(p.geo) * 2;
+
+    // ldmatrix lane roles (constant for the whole kernel)
+    const uint32_t mat = lane >> 3, mat_row = lane & 7;
+    const uint32_t q_row = mat_row + 8 * (mat & 1), q_hi = mat >> 1;           // A operand: rows x k-halves
+    const uint32_t k_row = mat_row + 8 * (mat >> 1), k_hi = mat & 1;           // B operand of Q K^T
+    const uint32_t v_row = mat_row + 8 * (mat & 1), v_hi = mat >> 1;           // B operand of P V (transposed)
+
+    for (uint32_t index = p.cta_item_begin[cta]; index < p.cta_item_begin[cta + 1]; ++index) {
+        const ItemView v = view_item(p, p.items[index]);
+        __syncthreads();  // the previous item's merge is done with the ring and with q
+
+        // ---- stage the query rows (zero rows beyond the item's) and the per-row causal limits ----------------------
+        for (uint32_t i = tid; i < kTile * kChunks; i += kThreads) {
+            const uint32_t r = i / kChunks, c = i % kChunks;
+            uint4 value = make_uint4(0, 0, 0, 0);
+            if (r < v.rows) {
+                const T* src = static_cast<const T*>(p.q) + item_row_index(p, v, r) * D + c * 8;
+                value = *reinterpret_cast<const uint4*>(src);
+            }
+            *reinterpret_cast<uint4*>(smem + swizzled(r, c, L::kRowBytes)) = value;
+        }
+        if (tid < kTile) {
+            uint32_t limit = v.kv_end;
+            if (tid < v.rows) limit = min(limit, p.flat_token_indices[v.flat_begin + tid / v.num_heads] + 1);
+            limit_s[tid] = limit;
+        }
+        __syncthreads();
+
+        const uint32_t limit0 = limit_s[quad_row], limit1 = limit_s[quad_row + 8];
+        uint32_t limit_min = v.kv_end;
+        for (uint32_t r = 0; r < v.rows; ++r) limit_min = min(limit_min, limit_s[r]);
+
+        // ---- this warp's share of the item's KV tiles ----------------------------------------------------------------
+        const uint32_t first_tile = v.kv_begin / kTile;
+        const uint32_t end_tile = (v.kv_end + kTile - 1) / kTile;
+        const uint32_t item_tiles = end_tile - first_tile;
+        const uint32_t my_tiles = item_tiles > warp ? (item_tiles - warp + kWarps - 1) / kWarps : 0;
+        const uint32_t* row_ids = table_row(p.geo, v.req_slot);
+
+        // Page ids of the two 8-token halves of local tile i (equal when a page holds 16 tokens or more).
+        auto lookup = [&](uint32_t i, uint32_t& id_lo, uint32_t& id_hi) {
+            const uint32_t token = (first_tile + warp + i * kWarps) * kTile;
+            id_lo = token < v.kv_end ? row_ids[token / P] : 0u;
+            id_hi = token + 8 < v.kv_end ? row_ids[(token + 8) / P] : 0u;
+        };
+        // Issues the copies of local tile i into ring stage `stage`.
+        auto issue = [&](uint32_t i, uint32_t stage, uint32_t id_lo, uint32_t id_hi) {
+            const uint32_t token0 = (first_tile + warp + i * kWarps) * kTile;
+            const uint32_t stage_base = ring_base + stage * L::kStageBytes;
+#pragma unroll
+            for (uint32_t it = 0; it < kTile / kRowsPerCopy; ++it) {
+                const uint32_t row = it * kRowsPerCopy + lane / kChunks;
+                const uint32_t chunk = lane % kChunks;
+                const uint32_t token = token0 + row;
+                const bool valid = token < v.kv_end;
+                const uint32_t page_id = row < 8 ? id_lo : id_hi;
+                const unsigned char* src =
+                    pages + (valid ? static_cast<uint64_t>(page_id) * page_bytes +
+                                         (static_cast<uint64_t>(v.kv_head) * P + token % P) * L::kRowBytes + chunk * 16
+                                   : 0);
+                const uint32_t dst = stage_base + swizzled(row, chunk, L::kRowBytes);
+                cp_async_16(dst, src, valid ? 16u : 0u);
+                cp_async_16(dst + L::kTileBytes, valid ? src + v_region_bytes : src, valid ? 16u : 0u);
+            }
+        };
+
+        float o[D / 8][4];
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+
+        uint32_t next_lo = 0, next_hi = 0;
+#pragma unroll
+        for (uint32_t s = 0; s < NSTAGE - 1; ++s) {
+            if (s < my_tiles) {
+                lookup(s, next_lo, next_hi);
+                issue(s, s, next_lo, next_hi);
+            }
+            cp_async_commit();
+        }
+        if (NSTAGE - 1 < my_tiles) lookup(NSTAGE - 1, next_lo, next_hi);
+
+        for (uint32_t i = 0; i < my_tiles; ++i) {
+            cp_async_wait<NSTAGE - 2>();
+            __syncwarp();
+            const uint32_t ahead = i + NSTAGE - 1;
+            if (ahead < my_tiles) issue(ahead, ahead % NSTAGE, next_lo, next_hi);
+            cp_async_commit();
+            if (ahead + 1 < my_tiles) lookup(ahead + 1, next_lo, next_hi);
+
+            const uint32_t k_base = ring_base + (i % NSTAGE) * L::kStageBytes;
+            const uint32_t v_base = k_base + L::kTileBytes;
+            const uint32_t token0 = (first_tile + warp + i * kWarps) * kTile;
+
+            // ---- S = Q K^T: two 8-token column tiles, even and odd k-steps in separate accumulators --------------------
+            float s_even[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < kKSteps; ++ks) {
+                uint32_t a[4], b[4];
+                ldmatrix_x4(a, q_base + swizzled(q_row, 2 * ks + q_hi, L::kRowBytes));
+                ldmatrix_x4(b, k_base + swizzled(k_row, 2 * ks + k_hi, L::kRowBytes));
+                if (ks & 1) {
+                    Mma<T>::run(s_odd[0], a, b[0], b[1]);
+                    Mma<T>::run(s_odd[1], a, b[2], b[3]);
+                } else {
+                    Mma<T>::run(s_even[0], a, b[0], b[1]);
+                    Mma<T>::run(s_even[1], a, b[2], b[3]);
+                }
+            }
+            float s[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[n][e] = (s_even[n][e] + s_odd[n][e]) * p.scale_log2;
+
+            // ---- visibility: keys at or beyond a row's limit, or before the item's range, do not count ----------------
+            if (token0 < v.kv_begin || token0 + kTile > limit_min) {
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t token = token0 + 8 * n + 2 * quad_col + (e & 1);
+                        const uint32_t limit = e < 2 ? limit0 : limit1;
+                        if (token >= limit || token < v.kv_begin) s[n][e] = -INFINITY;
+                    }
+            }
+
+            // ---- online softmax on the fragments -------------------------------------------------------------------
+            float max0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+            float max1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+            max0 = fmaxf(max0, __shfl_xor_sync(0xFFFFFFFFu, max0, 1));
+            max0 = fmaxf(max0, __shfl_xor_sync(0xFFFFFFFFu, max0, 2));
+            max1 = fmaxf(max1, __shfl_xor_sync(0xFFFFFFFFu, max1, 1));
+            max1 = fmaxf(max1, __shfl_xor_sync(0xFFFFFFFFu, max1, 2));
+            const float new0 = fmaxf(m0, max0), new1 = fmaxf(m1, max1);
+            const bool moved = new0 > m0 || new1 > m1;
+            if (__any_sync(0xFFFFFFFFu, moved)) {
+                const float corr0 = new0 == -INFINITY ? 1.0f : exp2f(m0 - new0);
+                const float corr1 = new1 == -INFINITY ? 1.0f : exp2f(m1 - new1);
+                l0 *= corr0;
+                l1 *= corr1;
+#pragma unroll
+                for (int j = 0; j < D / 8; ++j) {
+                    o[j][0] *= corr0;
+                    o[j][1] *= corr0;
+                    o[j][2] *= corr1;
+                    o[j][3] *= corr1;
+                }
+                m0 = new0;
+                m1 = new1;
+            }
+            const float base0 = m0 == -INFINITY ? 0.0f : m0, base1 = m1 == -INFINITY ? 0.0f : m1;
+            uint32_t pa[4];
+            {
+                const float p00 = exp2f(s[0][0] - base0), p01 = exp2f(s[0][1] - base0);
+                const float p02 = exp2f(s[0][2] - base1), p03 = exp2f(s[0][3] - base1);
+                const float p10 = exp2f(s[1][0] - base0), p11 = exp2f(s[1][1] - base0);
+                const float p12 = exp2f(s[1][2] - base1), p13 = exp2f(s[1][3] - base1);
+                l0 += (p00 + p01) + (p10 + p11);
+                l1 += (p02 + p03) + (p12 + p13);
+                pa[0] = Mma<T>::pack(p00, p01);
+                pa[1] = Mma<T>::pack(p02, p03);
+                pa[2] = Mma<T>::pack(p10, p11);
+                pa[3] = Mma<T>::pack(p12, p13);
+            }
+
+            // ---- O += P V ----------------------------------------------------------------------------------------------
+#pragma unroll
+            for (int j = 0; j < D / 16; ++j) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, v_base + swizzled(v_row, 2 * j + v_hi, L::kRowBytes));
+                Mma<T>::run(o[2 * j], pa, b[0], b[1]);
+                Mma<T>::run(o[2 * j + 1], pa, b[2], b[3]);
+            }
+        }
+
+        // ---- merge the four warps' partial results ---------------------------------------------------------------------
+        cp_async_wait<0>();
+        __syncthreads();  // every warp is done with its ring: the merge buffer may overwrite it
+        l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1);
+        l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
+        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1);
+        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+        if (quad_col == 0) {
+            merge_m[warp][quad_row] = m0;
+            merge_m[warp][quad_row + 8] = m1;
+            merge_l[warp][quad_row] = l0;
+            merge_l[warp][quad_row + 8] = l1;
+        }
+        {
+            float* mine = merge_o + warp * kTile * L::kMergeStride;
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) {
+                const uint32_t col = 8 * j + 2 * quad_col;
+                *reinterpret_cast<float2*>(mine + quad_row * L::kMergeStride + col) = make_float2(o[j][0], o[j][1]);
+                *reinterpret_cast<float2*>(mine + (quad_row + 8) * L::kMergeStride + col) = make_float2(o[j][2], o[j][3]);
+            }
+        }
+        __syncthreads();
+
+        for (uint32_t i = tid; i < v.rows * (D / 4); i += kThreads) {
+            const uint32_t r = i / (D / 4), c4 = i % (D / 4);
+            float row_max = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) row_max = fmaxf(row_max, merge_m[w][r]);
+            float sum = 0.0f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float wm = merge_m[w][r];
+                const float weight = wm == -INFINITY ? 0.0f : exp2f(wm - row_max);
+                sum += weight * merge_l[w][r];
+                const float4 part =
+                    *reinterpret_cast<const float4*>(merge_o + (w * kTile + r) * L::kMergeStride + 4 * c4);
+                acc.x += weight * part.x;
+                acc.y += weight * part.y;
+                acc.z += weight * part.z;
+                acc.w += weight * part.w;
+            }
+            const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+            acc.x *= inv;
+            acc.y *= inv;
+            acc.z *= inv;
+            acc.w *= inv;
+            if (v.partial_slot != kU32Max) {
+                const uint64_t prow = static_cast<uint64_t>(v.partial_slot) * kMaxRows + r;
+                *reinterpret_cast<float4*>(p.partial_o + prow * D + 4 * c4) = acc;
+                if (c4 == 0) {
+                    p.partial_m[prow] = row_max;
+                    p.partial_l[prow] = sum;
+                }
+            } else {
+                const uint64_t row = item_row_index(p, v, r);
+                if (p.ext_o != nullptr) {
+                    *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc;
+                    if (c4 == 0) {
+                        p.ext_m[row] = row_max * kLn2;
+                        p.ext_l[row] = sum;
+                    }
+                } else {
+                    Mma<T>::store4(static_cast<T*>(p.out) + row * D + 4 * c4, acc);
+                }
+            }
+        }
+    }
+}
+
+template <int D>
+constexpr int stages_for() {
+    return D == 256 ? 3 : (D == 128 ? 6 : 8);
+}
+
+template <typename T, int D>
+cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
+    constexpr int NSTAGE = stages_for<D>();
+    using L = SmemLayout<D, NSTAGE>;
+    auto kernel = attend_mma_kernel<T, D, NSTAGE>;
+    static bool configured = false;  // per instantiation; the attribute is per device, set again on every device below
+    static int configured_device = -1;
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return err;
+    if (!configured || configured_device != device) {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kTotal));
+        if (err != cudaSuccess) return err;
+        configured = true;
+        configured_device = device;
+    }
+    kernel<<<num_ctas, kThreads, L::kTotal, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_for_dim(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
+    switch (p.geo.head_dim) {
+        case 64: return launch_one<T, 64>(p, num_ctas, stream);
+        case 128: return launch_one<T, 128>(p, num_ctas, stream);
+        case 256: return launch_one<T, 256>(p, num_ctas, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace
+
+bool attend_mma_supported(uint32_t dtype, uint32_t head_dim, uint32_t tokens_per_page) {
+    const bool dtype_ok = dtype == PSI_DTYPE_BF16 || dtype == PSI_DTYPE_F16;
+    const bool dim_ok = head_dim == 64 || head_dim == 128 || head_dim == 256;
+    return dtype_ok && dim_ok && tokens_per_page % 8 == 0;
+}
+
+uint32_t attend_mma_ctas_per_sm(uint32_t /*head_dim*/) { return 1; }
+
+cudaError_t launch_attend_mma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
+    if (num_ctas == 0) return cudaSuccess;
+    if ((reinterpret_cast<uintptr_t>(p.q) & 15u) != 0 || (reinterpret_cast<uintptr_t>(p.geo.pages) & 15u) != 0 ||
+        (p.out != nullptr && (reinterpret_cast<uintptr_t>(p.out) & 7u) != 0)) {
+        return cudaErrorMisalignedAddress;
+    }
+    return p.dtype == PSI_DTYPE_BF16 ? launch_for_dim<__nv_bfloat16>(p, num_ctas, stream)
+                                     : launch_for_dim<__half>(p, num_ctas, stream);
+}
+
+}  // namespace psi

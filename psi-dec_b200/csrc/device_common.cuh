@@ -1,0 +1,92 @@
+// Device helpers shared by the kernels: dtype conversion, page addressing, warp reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "kernels.cuh"
+
+namespace psi {
+
+__device__ __forceinline__ float load_as_float(const void* base, uint64_t index, uint32_t dtype) {
+    if (dtype == PSI_DTYPE_F32) return static_cast<const float*>(base)[index];
+    if (dtype == PSI_DTYPE_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[index]);
+    return __half2float(static_cast<const __half*>(base)[index]);
+}
+
+__device__ __forceinline__ void store_from_float(void* base, uint64_t index, uint32_t dtype, float value) {
+    if (dtype == PSI_DTYPE_F32) {
+        static_cast<float*>(base)[index] = value;
+    } else if (dtype == PSI_DTYPE_BF16) {
+        static_cast<__nv_bfloat16*>(base)[index] = __float2bfloat16_rn(value);
+    } else {
+        static_cast<__half*>(base)[index] = __float2half_rn(value);
+    }
+}
+
+// First element of the (slot, layer) row of the page table.
+__device__ __forceinline__ const uint32_t* table_row(const PageGeometry& g, uint32_t req_slot) {
+    return g.page_ids + (static_cast<uint64_t>(req_slot) * g.num_layers + g.layer) * g.pages_per_req;
+}
+
+// Element offset of K row (kv_head, token) inside the arena; V is `v_region` further.  Within one (slot, layer) row
+// the two-level (block, page_id_index) address of the reference collapses to token / tokens_per_page.
+__device__ __forceinline__ uint64_t kv_row_offset(const PageGeometry& g, uint32_t page_id, uint32_t kv_head,
+                                                  uint32_t page_token) {
+    return static_cast<uint64_t>(page_id) * g.page_elems +
+           (static_cast<uint64_t>(kv_head) * g.tokens_per_page + page_token) * g.head_dim;
+}
+
+__device__ __forceinline__ uint64_t v_region_offset(const PageGeometry& g) {
+    return static_cast<uint64_t>(g.num_kv_heads) * g.tokens_per_page * g.head_dim;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);
+    return v;
+}
+
+}  // namespace psi
+
+namespace psi {
+
+// What one work item means once its tile and head selection are resolved.
+struct ItemView {
+    uint32_t flat_begin;   // first flat query token of the tile
+    uint32_t num_tokens;   // query tokens in the tile
+    uint32_t kv_head;
+    uint32_t head0;        // first q head the item carries
+    uint32_t num_heads;    // q heads the item carries
+    uint32_t rows;         // num_tokens * num_heads (<= 16); row r = (token r / num_heads, head r % num_heads)
+    uint32_t kv_begin;
+    uint32_t kv_end;
+    uint32_t partial_slot;
+    uint32_t req_slot;
+};
+
+__device__ __forceinline__ ItemView view_item(const AttendParams& p, const WorkItem& item) {
+    ItemView v;
+    const ExecTile tile = p.tiles[item.tile];
+    v.flat_begin = tile.flat_begin;
+    v.num_tokens = tile.flat_end - tile.flat_begin;
+    v.kv_head = item.head_sel / p.head_tiles;
+    const uint32_t head_tile = item.head_sel % p.head_tiles;
+    v.head0 = v.kv_head * p.group + head_tile * p.heads_per_tile;
+    v.num_heads = min(p.heads_per_tile, p.group - head_tile * p.heads_per_tile);
+    v.rows = v.num_tokens * v.num_heads;
+    v.kv_begin = item.kv_begin;
+    v.kv_end = item.kv_end;
+    v.partial_slot = item.partial_slot;
+    v.req_slot = p.req_slots[tile.flat_begin];
+    return v;
+}
+
+// Flat (token, head) row of q / out / ext_* that item row r stands for.
+__device__ __forceinline__ uint64_t item_row_index(const AttendParams& p, const ItemView& v, uint32_t r) {
+    return static_cast<uint64_t>(v.flat_begin + r / v.num_heads) * p.num_q_heads + v.head0 + r % v.num_heads;
+}
+
+constexpr float kLn2 = 0.6931471805599453f;
+
+}  // namespace psi

@@ -1,0 +1,144 @@
+// Host-side policy of the paged GQA decode path: replay buckets, SplitKV variant selection, the reference-format
+// batch metadata, the device work plan and the page-ID allocator.  Pure C++ (no CUDA), shared by the C ABI.
+#pragma once
+
+#include <cstdint>
+#include <deque>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "psi_cuda.h"
+
+namespace psi {
+
+// A violated caller contract (the reference panics); mapped to PSI_ERR_INVALID_ARGUMENT at the C ABI.
+struct ContractError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+struct ExhaustedError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+inline void require(bool ok, const char* message) {
+    if (!ok) throw ContractError(message);
+}
+
+constexpr uint32_t kU32Max = 0xFFFFFFFFu;
+constexpr uint32_t kKvTile = 16;    // KV tokens per device work tile
+constexpr uint32_t kMaxRows = 16;   // query rows (tokens x heads) one work item carries
+
+inline uint32_t dtype_bytes(uint32_t dtype) { return dtype == PSI_DTYPE_F32 ? 4u : 2u; }
+
+// ---- replay buckets (crates/inference-executor-core/src/replay.rs) ------------------------------------------------
+class BucketPolicy {
+public:
+    BucketPolicy(uint32_t max_capacity, const std::vector<uint32_t>& topology_boundaries);
+    const std::vector<uint32_t>& buckets() const { return buckets_; }
+    uint32_t max_capacity() const { return max_capacity_; }
+    uint32_t capacity(uint32_t active) const;
+
+private:
+    uint32_t max_capacity_;
+    std::vector<uint32_t> buckets_;
+};
+
+// ---- SplitKV variant selector (crates/inference-backend-metal/src/components/gqa_split_kv.rs) ---------------------
+class SplitKvSelector {
+public:
+    SplitKvSelector(uint32_t io_dtype, uint32_t page_bytes, uint32_t num_q_heads, uint32_t num_kv_heads,
+                    uint32_t head_dim, bool dspark_history);
+    psi_split_kv_variant select(uint32_t num_tokens, uint32_t num_q_token_tiles) const;
+    uint32_t tiled_q_token_tile_size() const { return 8; }
+    uint32_t max_q_tokens_per_partial_output() const { return supports_tiled_ ? 8u : 1u; }
+    uint32_t tokens_per_page() const { return tokens_per_page_; }
+
+private:
+    uint32_t group_;
+    uint32_t tokens_per_page_;
+    bool supports_tiled_;
+    bool full_group_for_tiled_;
+    uint32_t single_threads_;
+};
+
+// ---- reference-format batch metadata (crates/inference-executor-metal/src/attn/gqa/batch_metadata.rs) -------------
+struct ReferenceMetadata {
+    // Capacity-sized host mirrors; only the prefixes the reference writes are touched by update().
+    std::vector<uint32_t> req_slots, flat_token_indices, q_token_tiles, kv_splits, cu_kv_splits;
+    explicit ReferenceMetadata(uint32_t max_tokens);
+    uint32_t max_tokens() const { return static_cast<uint32_t>(req_slots.size()); }
+    psi_replay_shape update(const uint32_t* req_slots_by_req, const uint32_t* token_indices, const uint32_t* cu_tokens,
+                            uint32_t num_reqs, const psi_split_kv_variant& variant, uint32_t capacity_mode,
+                            const std::vector<uint32_t>& token_topology_boundaries, uint32_t caller_num_total_tokens);
+};
+
+// ---- device work plan ------------------------------------------------------------------------------------------------
+// One query tile the kernels execute: consecutive flat tokens of one request, at most tokens_per_tile of them.
+struct ExecTile {
+    uint32_t flat_begin;
+    uint32_t flat_end;
+};
+
+// One unit of map work: the rows of (tile, head_sel) against KV tokens [kv_begin, kv_end).  32 bytes on the device.
+struct WorkItem {
+    uint32_t tile;
+    uint32_t head_sel;      // kv_head * head_tiles + head_tile
+    uint32_t kv_begin;
+    uint32_t kv_end;
+    uint32_t partial_slot;  // kU32Max: the item covers its unit alone and writes the final output itself
+    uint32_t reserved[3];
+};
+
+struct ReduceUnit {
+    uint32_t first_item;
+    uint32_t num_items;
+};
+
+struct PlanGeometry {
+    uint32_t group;            // q heads per kv head
+    uint32_t heads_per_tile;   // q heads of one group one item carries (<= 16)
+    uint32_t head_tiles;       // ceil(group / heads_per_tile)
+    uint32_t tokens_per_tile;  // query tokens one item carries
+    uint32_t num_kv_heads;
+};
+
+PlanGeometry plan_geometry(uint32_t num_q_heads, uint32_t num_kv_heads);
+
+struct WorkPlan {
+    std::vector<ExecTile> tiles;
+    std::vector<WorkItem> items;
+    std::vector<uint32_t> cta_item_begin;  // [num_ctas + 1]
+    std::vector<ReduceUnit> reduces;
+    uint32_t num_partial_slots = 0;
+    uint64_t total_kv_tiles = 0;
+    uint32_t num_ctas() const { return cta_item_begin.empty() ? 0u : static_cast<uint32_t>(cta_item_begin.size() - 1); }
+};
+
+// Equal-share plan: the (tile, head_sel) units laid end to end in 16-token KV tiles, cut into `max_ctas` (or fewer)
+// contiguous shares.
+WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* token_indices, const uint32_t* cu_tokens,
+                             uint32_t num_reqs, uint32_t max_ctas, uint32_t min_kv_tiles_per_cta);
+
+// One CTA per (reference KV split, head_sel); reference q tiles wider than tokens_per_tile are cut into sub-tiles
+// that share the split boundaries.
+WorkPlan build_reference_plan(const PlanGeometry& geo, const ReferenceMetadata& md, const psi_replay_shape& shape,
+                              bool tiled_q);
+
+// ---- page-ID allocator (crates/inference-runtime-core/src/memory/u32_id_allocator.rs) --------------------------------
+class IdAllocator {
+public:
+    explicit IdAllocator(uint64_t capacity);
+    void alloc_many(uint64_t count, uint32_t* out);
+    void free_many(const uint32_t* ids, uint64_t count);
+    const std::vector<uint64_t>& bitmap() const { return bitmap_; }
+    uint64_t free_count() const { return free_ids_.size() + (capacity_ - counter_); }
+
+private:
+    void mark(uint32_t id, bool live);
+    uint64_t capacity_;
+    uint64_t counter_ = 0;
+    std::deque<uint32_t> free_ids_;
+    std::vector<uint64_t> bitmap_;
+};
+
+}  // namespace psi

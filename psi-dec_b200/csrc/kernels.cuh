@@ -1,0 +1,101 @@
+// Launch interface between the C ABI (api.cu) and the sm_100a kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "host_logic.hpp"
+
+namespace psi {
+
+// Device scalar block rewritten by every prepare (the analogue of the reference's replay parameter buffer).
+enum ScalarSlot : uint32_t {
+    kScalarNumActiveTokens = 0,
+    kScalarNumCtas = 1,
+    kScalarNumReduces = 2,
+    kScalarCount = 8
+};
+
+struct PageGeometry {
+    const void* pages;
+    const uint32_t* page_ids;     // whole table
+    uint64_t page_elems;          // elements per page
+    uint32_t layer;
+    uint32_t num_layers;
+    uint32_t pages_per_req;       // num_blocks * num_page_ids_per_block: one (slot, layer) row of the table
+    uint32_t tokens_per_page;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t elem_bytes;
+};
+
+struct AppendParams {
+    PageGeometry geo;
+    const void* flat_k;
+    const void* flat_v;
+    const uint32_t* req_slots;
+    const uint32_t* flat_token_indices;
+    const uint32_t* scalars;
+    uint32_t num_total_tokens;    // launch capacity; rows >= scalars[kScalarNumActiveTokens] do nothing
+};
+
+struct GatherParams {
+    PageGeometry geo;
+    uint32_t req_slot;
+    uint32_t tok_begin;
+    uint32_t tok_end;
+    void* k_out;
+    void* v_out;
+};
+
+struct AttendParams {
+    PageGeometry geo;
+    const void* q;
+    void* out;                    // [T][Hq][D] in the I/O dtype, or nullptr when ext_* are set
+    float* ext_o;                 // [T][Hq][D] f32 normalised partial (attend_partial), else nullptr
+    float* ext_m;                 // [T][Hq] natural-log max
+    float* ext_l;                 // [T][Hq] exp-sum
+    const uint32_t* req_slots;
+    const uint32_t* flat_token_indices;
+    const ExecTile* tiles;
+    const WorkItem* items;
+    const uint32_t* cta_item_begin;
+    const ReduceUnit* reduces;
+    float* partial_o;             // [slots][16][D] normalised
+    float* partial_m;             // [slots][16] log2-domain max
+    float* partial_l;             // [slots][16]
+    const uint32_t* scalars;
+    uint32_t num_q_heads;
+    uint32_t group;
+    uint32_t heads_per_tile;
+    uint32_t head_tiles;
+    uint32_t dtype;
+    float scale_log2;             // scale * log2(e)
+};
+
+struct CombineParams {
+    const float* const* o;        // device array of n pointers
+    const float* const* m;
+    const float* const* l;
+    uint32_t n;
+    uint32_t num_rows;            // num_tokens * Hq
+    uint32_t head_dim;
+    uint32_t dtype;
+    void* out;
+};
+
+cudaError_t launch_kv_append(const AppendParams& p, cudaStream_t stream);
+cudaError_t launch_page_gather(const GatherParams& p, cudaStream_t stream);
+
+// Map kernels.  `num_ctas` CTAs walk cta_item_begin.  The generic kernel takes any profile with head_dim <= 256; the
+// mma kernel needs bf16/f16, head_dim in {64,128,256} and tokens_per_page % 8 == 0.
+bool attend_mma_supported(uint32_t dtype, uint32_t head_dim, uint32_t tokens_per_page);
+uint32_t attend_mma_ctas_per_sm(uint32_t head_dim);
+uint32_t attend_generic_ctas_per_sm();
+cudaError_t launch_attend_generic(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
+cudaError_t launch_attend_mma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
+cudaError_t launch_attend_reduce(const AttendParams& p, uint32_t num_reduces, cudaStream_t stream);
+cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
+
+}  // namespace psi

@@ -1,0 +1,224 @@
+"""Seeded synthetic decode workloads with the shapes, sizes and value distributions of the benchmark configurations,
+and a ``Session`` that lays one of them out on a GPU through the library's public objects.
+
+No public dataset stands behind these configurations: lengths, block tables and values are drawn from seeded
+generators (numpy PCG64 for integers, torch's Philox for values), and the seed is part of the spec.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import binding as B
+
+_ELEM_BYTES = {B.F32: 4, B.BF16: 2, B.F16: 2}
+
+
+@dataclass
+class Spec:
+    name: str
+    dtype: int
+    num_q_heads: int
+    num_kv_heads: int
+    head_dim: int
+    tokens_per_page: int
+    context_lens: np.ndarray          # tokens already cached per sequence, before this step's append
+    q_len: np.ndarray                 # query (= appended) tokens per sequence this step
+    seed: int
+    pool_factor: float = 1.25
+    ids_per_block: int = 1
+    num_layers: int = 1
+    layer: int = 0
+    scale: float = 0.0
+    do_append: bool = True                # False: this step's K/V rows are already resident (KV-range shards)
+    block_tables: list = field(default_factory=list)   # per sequence: physical page ids in logical order
+    num_pages: int = 0
+
+    def __post_init__(self):
+        self.context_lens = np.asarray(self.context_lens, dtype=np.int64)
+        self.q_len = np.broadcast_to(np.asarray(self.q_len, dtype=np.int64), self.context_lens.shape).copy()
+        if self.scale == 0.0:
+            self.scale = 1.0 / math.sqrt(self.head_dim)
+        if not self.block_tables:
+            self._draw_block_tables()
+
+    # -- derived sizes ------------------------------------------------------------------------------------------------
+    @property
+    def elem_bytes(self) -> int:
+        return _ELEM_BYTES[self.dtype]
+
+    @property
+    def page_bytes(self) -> int:
+        return 2 * self.num_kv_heads * self.tokens_per_page * self.head_dim * self.elem_bytes
+
+    @property
+    def num_seqs(self) -> int:
+        return len(self.context_lens)
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.q_len.sum())
+
+    @property
+    def visible(self) -> np.ndarray:
+        return self.context_lens + self.q_len
+
+    def pages_per_seq(self) -> np.ndarray:
+        return -(-self.visible // self.tokens_per_page)
+
+    def _draw_block_tables(self):
+        rng = np.random.default_rng(self.seed)
+        pages = self.pages_per_seq()
+        total = int(pages.sum())
+        self.num_pages = max(int(math.ceil(total * self.pool_factor)), total, 1)
+        pool = rng.permutation(self.num_pages).astype(np.uint32)
+        start = 0
+        for n in pages:
+            self.block_tables.append(pool[start:start + int(n)].copy())
+            start += int(n)
+
+    # -- batch description in the reference's request-level form ---------------------------------------------------------
+    def batch(self):
+        req_slots = list(range(self.num_seqs))
+        token_indices = [int(c) for c in self.context_lens]
+        cu = [0]
+        for n in self.q_len:
+            cu.append(cu[-1] + int(n))
+        return req_slots, token_indices, cu
+
+    def algorithmic_bytes(self) -> dict:
+        """Bytes one step must move: every visible K/V byte once, q in, out out, appended rows in and out, and one
+        table entry per visible page."""
+        e = self.elem_bytes
+        kv = int(self.visible.sum()) * 2 * self.num_kv_heads * self.head_dim * e
+        t = self.num_tokens
+        q_o = t * self.num_q_heads * self.head_dim * 2 * e
+        app = 2 * t * 2 * self.num_kv_heads * self.head_dim * e
+        table = int(self.pages_per_seq().sum()) * 4
+        return {"kv": kv, "q_o": q_o, "append": app, "table": table, "total": kv + q_o + app + table}
+
+    def shard(self, rank: int, world: int) -> "Spec":
+        """Sequence shard ``rank`` of ``world``: longest-first round robin, so every rank carries a similar KV load.
+        Each rank owns its sequences' pages in an arena of its own."""
+        order = np.argsort(-self.visible, kind="stable")
+        mine = np.sort(order[rank::world])
+        return Spec(name=f"{self.name}/shard{rank}of{world}", dtype=self.dtype, num_q_heads=self.num_q_heads,
+                    num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, tokens_per_page=self.tokens_per_page,
+                    context_lens=self.context_lens[mine], q_len=self.q_len[mine], seed=self.seed * 1000 + rank,
+                    pool_factor=self.pool_factor, ids_per_block=self.ids_per_block, num_layers=self.num_layers,
+                    layer=self.layer, scale=self.scale)
+
+    def kv_range_shard(self, rank: int, world: int) -> "Spec":
+        """KV-range shard for one very long context per sequence: rank j holds the j-th page-aligned slice of every
+        sequence's context; the appended token lands on the last rank.  Lengths are in the rank's local coordinates."""
+        p = self.tokens_per_page
+        pages = -(-self.context_lens // p)
+        lo = pages * rank // world * p
+        hi = np.minimum(pages * (rank + 1) // world * p, self.context_lens)
+        local = hi - lo
+        last = rank == world - 1
+        return Spec(name=f"{self.name}/kvrange{rank}of{world}", dtype=self.dtype, num_q_heads=self.num_q_heads,
+                    num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, tokens_per_page=p,
+                    context_lens=local if last else local - self.q_len, q_len=self.q_len,
+                    seed=self.seed * 1000 + rank, pool_factor=self.pool_factor, scale=self.scale, do_append=bool(last))
+
+
+def config(index: int, scale_down: int = 1, seed: int | None = None) -> Spec:
+    """The five benchmark configurations; ``scale_down`` divides batch and context sizes for small test runs."""
+    s = max(1, scale_down)
+    if index == 1:
+        return Spec("cfg1-cpu-scale", B.F16, 4, 1, 128, 16, [256], 1, seed or 1, pool_factor=64 / 17)
+    if index == 2:
+        rng = np.random.default_rng(seed or 2)
+        ctx = rng.integers(1024 // s, 8192 // s + 1, size=max(1, 32 // s))
+        return Spec("cfg2-a3b-layer-decode", B.BF16, 16, 2, 256, 16, ctx, 1, seed or 2)
+    if index == 3:
+        rng = np.random.default_rng(seed or 3)
+        ctx = np.exp(rng.normal(math.log(8192 / s), 0.5, size=max(1, 128 // s)))
+        ctx = np.clip(ctx, 4096 // s, 32768 // s).astype(np.int64)
+        return Spec("cfg3-27b-mtp-verify", B.BF16, 24, 4, 256, 16, ctx, 2, seed or 3)
+    if index == 4:
+        return Spec("cfg4-long-context", B.BF16, 16, 2, 256, 16, [262144 // s] * 4, 1, seed or 4, pool_factor=1.0)
+    if index == 5:
+        rng = np.random.default_rng(seed or 5)
+        n = max(1, 256 // s)
+        lo, hi = 128, max(256, 131072 // s)
+        support = np.arange(lo, hi + 1, dtype=np.float64)
+        weights = support ** -1.1
+        cdf = np.cumsum(weights) / weights.sum()
+        ctx = lo + np.searchsorted(cdf, rng.random(n))
+        q_len = np.where(rng.random(n) < 0.3, 512 // min(s, 8), 1)
+        return Spec("cfg5-churn", B.BF16, 16, 2, 256, 16, ctx, q_len, seed or 5)
+    raise ValueError(f"unknown configuration {index}")
+
+
+class Session:
+    """One workload resident on one GPU: arena (random K/V everywhere), block tables, GQA component, q/k/v/out."""
+
+    def __init__(self, spec: Spec, device: int = 0, plan_mode: int = B.PLAN_BALANCED, kernel_mode: int = B.KERNEL_AUTO,
+                 max_ctas: int = 0, own_arena: bool = False, fill: str = "normal"):
+        import torch
+        self.torch = torch
+        self.spec = spec
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        self.stream = torch.cuda.current_stream(self.device)
+        self.ctx = B.Context(device, stream=self.stream.cuda_stream)
+        tdtype = {B.F32: torch.float32, B.BF16: torch.bfloat16, B.F16: torch.float16}[spec.dtype]
+        self.tdtype = tdtype
+        page_elems = spec.page_bytes // spec.elem_bytes
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(spec.seed)
+        if own_arena:
+            self.pages = B.PageArena(self.ctx, spec.num_pages, spec.page_bytes)
+            self.arena = None
+        else:
+            self.arena = torch.empty((spec.num_pages, page_elems), dtype=tdtype, device=self.device)
+            chunk = max(1, (256 << 20) // (page_elems * 4))
+            for start in range(0, spec.num_pages, chunk):
+                part = self.arena[start:start + chunk]
+                if fill == "normal":
+                    part.copy_(torch.randn(part.shape, generator=gen, device=self.device, dtype=torch.float32))
+                else:
+                    part.zero_()
+            self.pages = B.PageArena(self.ctx, spec.num_pages, spec.page_bytes, device_ptr=self.arena)
+        pages_per_block = spec.ids_per_block
+        max_pages = int(spec.pages_per_seq().max())
+        self.layout = B.GQAPageTableLayout(spec.num_seqs, spec.num_layers, -(-max_pages // pages_per_block),
+                                           pages_per_block)
+        self.table = B.GQARequestPageTable(self.ctx, self.layout)
+        for slot, ids in enumerate(spec.block_tables):
+            self.table.write_row(slot, spec.layer, ids)
+        cfg = B.GQAConfig(spec.num_q_heads, spec.num_kv_heads, spec.head_dim, spec.scale, spec.page_bytes, spec.dtype,
+                          self.layout, max(spec.num_tokens, 1), plan_mode, kernel_mode, max_ctas)
+        self.gqa = B.GQA(self.ctx, cfg)
+        t = spec.num_tokens
+        self.q = torch.randn((t, spec.num_q_heads, spec.head_dim), generator=gen, device=self.device,
+                             dtype=torch.float32).to(tdtype)
+        self.k = torch.randn((t, spec.num_kv_heads, spec.head_dim), generator=gen, device=self.device,
+                             dtype=torch.float32).to(tdtype)
+        self.v = torch.randn((t, spec.num_kv_heads, spec.head_dim), generator=gen, device=self.device,
+                             dtype=torch.float32).to(tdtype)
+        self.out = torch.zeros_like(self.q)
+        self.shape = self.gqa.prepare(*spec.batch())
+
+    def append(self):
+        self.gqa.kv_page_write(self.pages, self.table, self.spec.layer, self.k, self.v)
+
+    def attend(self):
+        self.gqa.attend(self.pages, self.table, self.spec.layer, self.q, self.out)
+
+    def step(self):
+        """One pass of the hot path with inputs resident in HBM: append this step's K/V, then attend."""
+        if self.spec.do_append:
+            self.append()
+        self.attend()
+
+    def close(self):
+        self.ctx.sync()
+        self.gqa.close()
+        self.table.close()
+        self.pages.close()
+        self.ctx.close()
