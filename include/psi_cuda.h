@@ -306,6 +306,20 @@ PSI_API int32_t psi_page_gather(psi_gqa* gqa, psi_pages* pages, psi_table* table
 /* Number of kernels this library has launched on the context since creation (for launch accounting). */
 PSI_API int32_t psi_ctx_launch_count(psi_ctx* ctx, uint64_t* out);
 
+/* Per-kernel device timing for measurement harnesses (the reference offers no GPU timestamps; its benches time whole
+ * submissions).  While enabled, every launch of the library on this context is bracketed by CUDA events on the
+ * context's stream.  psi_ctx_kernel_timing waits for the stream, then returns the summed duration and the launch
+ * count of one kernel class since timing was last enabled or reset. */
+typedef enum psi_kernel_class {
+    PSI_KERNEL_CLASS_APPEND = 0,
+    PSI_KERNEL_CLASS_ATTEND_MAP = 1,
+    PSI_KERNEL_CLASS_ATTEND_REDUCE = 2,
+    PSI_KERNEL_CLASS_COMBINE = 3,
+    PSI_KERNEL_CLASS_GATHER = 4
+} psi_kernel_class;
+PSI_API int32_t psi_ctx_enable_kernel_timing(psi_ctx* ctx, int32_t enable);
+PSI_API int32_t psi_ctx_kernel_timing(psi_ctx* ctx, uint32_t kernel_class, float* out_total_ms, uint64_t* out_launches);
+
 #ifdef __cplusplus
 }
 #endif

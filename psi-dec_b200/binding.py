@@ -128,6 +128,16 @@ class Context:
         _check(library().psi_ctx_launch_count(self._h, C.byref(out)), self._h)
         return out.value
 
+    def enable_kernel_timing(self, enable: bool = True):
+        _check(library().psi_ctx_enable_kernel_timing(self._h, C.c_int32(1 if enable else 0)), self._h)
+
+    def kernel_timing(self, kernel_class: int):
+        """(total milliseconds, launches) of one kernel class (0 append, 1 attend map, 2 attend reduce, 3 combine,
+        4 gather) since timing was enabled."""
+        ms, n = C.c_float(), C.c_uint64()
+        _check(library().psi_ctx_kernel_timing(self._h, C.c_uint32(kernel_class), C.byref(ms), C.byref(n)), self._h)
+        return ms.value, n.value
+
     @property
     def stream(self) -> int:
         out = C.c_void_p()

@@ -34,6 +34,8 @@ uint64_t pad_words(uint64_t n) { return (n + kWordAlign - 1) / kWordAlign * kWor
 
 }  // namespace
 
+constexpr uint32_t kKernelClasses = 5;
+
 struct psi_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -41,8 +43,42 @@ struct psi_ctx {
     int sm_count = 0;
     uint64_t launches = 0;
     std::string last_error;
+    bool timing = false;
+    // (begin, end) event pairs per kernel class, recorded while timing is on
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed[kKernelClasses];
     void bind() const { cuda_check(cudaSetDevice(device), "cudaSetDevice"); }
+    void clear_timing() {
+        for (auto& list : timed) {
+            for (auto& pair : list) {
+                (void)cudaEventDestroy(pair.first);
+                (void)cudaEventDestroy(pair.second);
+            }
+            list.clear();
+        }
+    }
 };
+
+namespace {
+
+// Counts one launch and, while timing is on, brackets it with events on the context's stream.
+struct LaunchScope {
+    psi_ctx* ctx;
+    cudaEvent_t end = nullptr;
+    LaunchScope(psi_ctx* c, uint32_t kernel_class) : ctx(c) {
+        ctx->launches += 1;
+        if (!ctx->timing) return;
+        cudaEvent_t begin = nullptr;
+        cuda_check(cudaEventCreate(&begin), "cudaEventCreate");
+        cuda_check(cudaEventCreate(&end), "cudaEventCreate");
+        ctx->timed[kernel_class].emplace_back(begin, end);
+        cuda_check(cudaEventRecord(begin, ctx->stream), "cudaEventRecord");
+    }
+    ~LaunchScope() {
+        if (end != nullptr) (void)cudaEventRecord(end, ctx->stream);
+    }
+};
+
+}  // namespace
 
 namespace {
 
@@ -237,15 +273,19 @@ AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* 
 void run_attend(psi_gqa* g, const AttendParams& p) {
     psi_ctx* ctx = g->ctx;
     const uint32_t num_ctas = g->plan.num_ctas();
-    if (g->kernel == PSI_KERNEL_MMA) {
-        cuda_check(launch_attend_mma(p, num_ctas, ctx->stream), "attend (mma) launch");
-    } else {
-        cuda_check(launch_attend_generic(p, num_ctas, ctx->stream), "attend (generic) launch");
+    if (num_ctas > 0) {
+        LaunchScope scope(ctx, PSI_KERNEL_CLASS_ATTEND_MAP);
+        if (g->kernel == PSI_KERNEL_MMA) {
+            cuda_check(launch_attend_mma(p, num_ctas, ctx->stream), "attend (mma) launch");
+        } else {
+            cuda_check(launch_attend_generic(p, num_ctas, ctx->stream), "attend (generic) launch");
+        }
     }
-    ctx->launches += num_ctas > 0;
     const uint32_t num_reduces = static_cast<uint32_t>(g->plan.reduces.size());
-    cuda_check(launch_attend_reduce(p, num_reduces, ctx->stream), "attend reduce launch");
-    ctx->launches += num_reduces > 0;
+    if (num_reduces > 0) {
+        LaunchScope scope(ctx, PSI_KERNEL_CLASS_ATTEND_REDUCE);
+        cuda_check(launch_attend_reduce(p, num_reduces, ctx->stream), "attend reduce launch");
+    }
 }
 
 void run_append(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* k, const void* v) {
@@ -259,8 +299,8 @@ void run_append(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, 
     p.flat_token_indices = block_words(g, g->off_token_indices);
     p.scalars = block_words(g, 0);
     p.num_total_tokens = g->shape.num_total_tokens;
+    LaunchScope scope(g->ctx, PSI_KERNEL_CLASS_APPEND);
     cuda_check(launch_kv_append(p, g->ctx->stream), "kv append launch");
-    g->ctx->launches += 1;
 }
 
 }  // namespace
@@ -308,10 +348,9 @@ int32_t psi_ctx_destroy(psi_ctx* ctx) {
     if (ctx == nullptr) return PSI_OK;
     int32_t status = guarded(nullptr, [&] {
         ctx->bind();
-        if (ctx->owns_stream) {
-            (void)cudaStreamSynchronize(ctx->stream);
-            (void)cudaStreamDestroy(ctx->stream);
-        }
+        (void)cudaStreamSynchronize(ctx->stream);
+        ctx->clear_timing();
+        if (ctx->owns_stream) (void)cudaStreamDestroy(ctx->stream);
     });
     delete ctx;
     return status;
@@ -340,6 +379,34 @@ int32_t psi_ctx_sm_count(psi_ctx* ctx, int32_t* out) {
 int32_t psi_ctx_last_error(psi_ctx* ctx, char* buf, size_t n) {
     if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
     return copy_message(ctx->last_error, buf, n);
+}
+
+int32_t psi_ctx_enable_kernel_timing(psi_ctx* ctx, int32_t enable) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        ctx->bind();
+        cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+        ctx->clear_timing();
+        ctx->timing = enable != 0;
+    });
+}
+
+int32_t psi_ctx_kernel_timing(psi_ctx* ctx, uint32_t kernel_class, float* out_total_ms, uint64_t* out_launches) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        require(kernel_class < kKernelClasses, "unknown kernel class");
+        require(out_total_ms != nullptr && out_launches != nullptr, "outputs must not be null");
+        ctx->bind();
+        cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+        float total = 0.0f;
+        for (const auto& pair : ctx->timed[kernel_class]) {
+            float ms = 0.0f;
+            cuda_check(cudaEventElapsedTime(&ms, pair.first, pair.second), "cudaEventElapsedTime");
+            total += ms;
+        }
+        *out_total_ms = total;
+        *out_launches = ctx->timed[kernel_class].size();
+    });
 }
 
 int32_t psi_ctx_launch_count(psi_ctx* ctx, uint64_t* out) {
@@ -1055,8 +1122,8 @@ int32_t psi_gqa_combine(psi_gqa* g, const float* const* o, const float* const* m
         p.head_dim = g->cfg.head_dim;
         p.dtype = g->cfg.dtype;
         p.out = out;
+        LaunchScope scope(ctx, PSI_KERNEL_CLASS_COMBINE);
         cuda_check(launch_combine(p, ctx->stream), "combine launch");
-        ctx->launches += 1;
     });
 }
 
@@ -1107,8 +1174,10 @@ int32_t psi_page_gather(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t
         p.tok_end = tok_end;
         p.k_out = k_out;
         p.v_out = v_out;
-        cuda_check(launch_page_gather(p, g->ctx->stream), "page gather launch");
-        g->ctx->launches += tok_end > tok_begin;
+        if (tok_end > tok_begin) {
+            LaunchScope scope(g->ctx, PSI_KERNEL_CLASS_GATHER);
+            cuda_check(launch_page_gather(p, g->ctx->stream), "page gather launch");
+        }
     });
 }
 

@@ -1,0 +1,570 @@
+"""GPU parity tests: the CUDA path through the C ABI against the CPU oracle on the same inputs.
+
+The fixtures restate the reference's own parity tests for the path (cited per test); larger cases use the seeded
+synthetic configurations.  Bit-exact for append / gather / table contents; attention within 2e-5 max-abs for f32 and
+within 2e-2 max-abs / 2e-3 mean-abs for 16-bit outputs against the f32 oracle.
+"""
+import math
+
+import numpy as np
+import pytest
+
+import checks
+import gpuharness as G
+import workloads as W
+from oracle import psi_oracle as O
+from refdata import fixture_values, generated_half_range_values, generated_values, kv_page_values, pattern
+
+pkg = G.pkg
+pytestmark = pytest.mark.gpu
+
+MODES = [(pkg.PLAN_BALANCED, "balanced"), (pkg.PLAN_REFERENCE, "reference")]
+
+
+def _decode(tensor, dtype):
+    return O.decode(G.bits_of(tensor), dtype)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# KV append / gather / table / arena
+# ---------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,np_dtype", [(pkg.BF16, np.uint16), (pkg.F32, np.float32)])
+def test_kv_page_write_fixed(dtype, np_dtype):
+    # crates/inference-backend-metal/src/components/gqa_kv_page_write.rs:344-364
+    import torch
+    rig = G.Rig(dtype, 1, 1, 2, 2, 1.0, (1, 1, 1, 1), 1, num_pages=1)
+    rig.set_pages(0, 0, [0])
+    rig.gqa.prepare([0], [1], [0, 1])
+    k = torch.from_numpy(np.array([10, 11], dtype=np_dtype).view(np.int16 if np_dtype == np.uint16 else np.float32)).cuda()
+    v = torch.from_numpy(np.array([20, 21], dtype=np_dtype).view(np.int16 if np_dtype == np.uint16 else np.float32)).cuda()
+    rig.gqa.kv_page_write(rig.pages, rig.table, 0, k, v)
+    rig.ctx.sync()
+    assert rig.arena_bits().tolist() == [0, 0, 10, 11, 0, 0, 20, 21]
+    rig.close()
+
+
+def test_kv_page_write_bucketed_preserves_inactive_page():
+    # gqa_kv_page_write.rs:284-342: capacity 4, 3 active writes leave page 1 all 0x7777; 4 active writes touch it.
+    import torch
+    sentinel = 0x7777
+    for active_reqs, expect_touched in (([0, 0, 0], False), ([0, 0, 0, 1], True)):
+        rig = G.Rig(pkg.BF16, 1, 1, 2, 4, 1.0, (2, 1, 1, 1), 4, arena_bits=np.full(32, sentinel, dtype=np.uint16))
+        rig.set_pages(0, 0, [0])
+        rig.set_pages(1, 0, [1])
+        k = torch.from_numpy(np.arange(10, 18, dtype=np.int16)).cuda()
+        v = torch.from_numpy(np.arange(20, 28, dtype=np.int16)).cuda()
+        if expect_touched:
+            shape = rig.gqa.prepare_bucketed_with_token_capacity([0, 1], [0, 0], [0, 3, 4], 4)
+        else:
+            shape = rig.gqa.prepare_bucketed_with_token_capacity([0], [0], [0, 3], 4)
+        assert shape.num_total_tokens == 4
+        rig.gqa.kv_page_write(rig.pages, rig.table, 0, k, v)
+        rig.ctx.sync()
+        bits = rig.arena_bits()
+        assert bits[:16].tolist() == [10, 11, 12, 13, 14, 15, sentinel, sentinel, 20, 21, 22, 23, 24, 25, sentinel,
+                                      sentinel]
+        if expect_touched:
+            assert bits[16:18].tolist() == [16, 17] and bits[24:26].tolist() == [26, 27]
+        else:
+            assert bits[16:].tolist() == [sentinel] * 16
+        rig.close()
+
+
+@pytest.mark.parametrize("dtype", [pkg.BF16, pkg.F32, pkg.F16])
+@pytest.mark.parametrize("head_dim,tokens_per_page,ipb", [(2, 4, 2), (24, 3, 1), (128, 16, 4), (256, 8, 2)])
+def test_append_and_gather_bit_exact_with_two_level_table(dtype, head_dim, tokens_per_page, ipb):
+    import torch
+    rng = np.random.default_rng(head_dim * 7 + ipb)
+    hkv, slots, layers, blocks = 2, 3, 2, 5
+    pages_per_row = blocks * ipb
+    num_pages = slots * layers * pages_per_row
+    rig = G.Rig(dtype, 2 * hkv, hkv, head_dim, tokens_per_page, 0.5, (slots, layers, blocks, ipb), 64,
+                num_pages=num_pages)
+    perm = rng.permutation(num_pages).astype(np.uint32).reshape(slots, layers, pages_per_row)
+    for s in range(slots):
+        for l in range(layers):
+            rig.set_pages(s, l, perm[s, l])
+    cap = pages_per_row * tokens_per_page
+    lens = [5, 11, 7]
+    starts = [0, cap - 11, 3]
+    cu = [0, 5, 16, 23]
+    t = cu[-1]
+    npd = np.float32 if dtype == pkg.F32 else np.uint16
+    kbits = rng.integers(1, 60000, size=(t, hkv, head_dim)).astype(npd)
+    vbits = rng.integers(1, 60000, size=(t, hkv, head_dim)).astype(npd)
+    as_torch = lambda a: torch.from_numpy(a.view(np.int16) if npd == np.uint16 else a).cuda()
+    k, v = as_torch(kbits), as_torch(vbits)
+    rig.gqa.prepare([0, 1, 2], starts, cu)
+    before = rig.arena_bits().copy()
+    rig.gqa.kv_page_write(rig.pages, rig.table, 1, k, v)
+    rig.ctx.sync()
+    expected = before.copy()
+    slots_flat, pos_flat = G.flat_metadata([0, 1, 2], starts, cu)
+    O.kv_page_write(expected, kbits, vbits, slots_flat, pos_flat, rig.table_host.reshape(-1), t, 1, rig.olayout, hkv,
+                    head_dim, rig.page_bytes)
+    assert np.array_equal(rig.arena_bits(), expected)
+    # gather is the inverse of the append
+    for s in range(slots):
+        lo, hi = starts[s], starts[s] + lens[s]
+        kout = torch.zeros((hi - lo, hkv, head_dim), dtype=G.torch_dtype(dtype), device="cuda:0")
+        vout = torch.zeros_like(kout)
+        rig.gqa.page_gather(rig.pages, rig.table, s, 1, lo, hi, kout, vout)
+        rig.ctx.sync()
+        assert np.array_equal(G.bits_of(kout), kbits[cu[s]:cu[s + 1]])
+        assert np.array_equal(G.bits_of(vout), vbits[cu[s]:cu[s + 1]])
+        ek, ev = O.page_gather(expected, rig.table_host.reshape(-1), s, 1, rig.olayout, hkv, head_dim, rig.page_bytes,
+                               lo, hi)
+        assert np.array_equal(G.bits_of(kout), ek) and np.array_equal(G.bits_of(vout), ev)
+    rig.close()
+
+
+def test_page_table_lifecycle_on_device():
+    # crates/inference-executor-metal/src/attn/gqa/request_page_table.rs:140-174
+    import torch
+    ctx = pkg.Context(0)
+    table = pkg.GQARequestPageTable(ctx, pkg.GQAPageTableLayout(4, 3, 6, 2))
+    table.write_page_ids(1, 0, 0, [10, 11])
+    table.write_page_ids(1, 0, 1, [12, 13])
+    table.write_page_ids(1, 2, 0, [20, 21])
+    table.write_page_ids(2, 1, 0, [30, 31])
+    table.write_page_ids(3, 0, 0, [40, 41])
+    assert table.read_page_ids(1, 0, 0) == [10, 11] and table.read_page_ids(1, 0, 1) == [12, 13]
+    assert table.read_page_ids(1, 2, 0) == [20, 21]
+    table.reset_req_slot(1)
+    assert table.read_page_ids(1, 0, 0) == [0, 0] and table.read_page_ids(1, 0, 1) == [0, 0]
+    assert table.read_page_ids(1, 2, 0) == [0, 0]
+    assert table.read_page_ids(2, 1, 0) == [30, 31] and table.read_page_ids(3, 0, 0) == [40, 41]
+    # role-block write with the page-ID domain check (model/qwen/v3_x/state/gqa.rs:88-106)
+    table.write_all_layer_page_ids(0, 2, [1, 2, 3, 4, 5, 6], num_cache_pages=7)
+    assert [table.read_page_ids(0, l, 2) for l in range(3)] == [[1, 2], [3, 4], [5, 6]]
+    with pytest.raises(pkg.PsiError, match="outside the cache-page buffer"):
+        table.write_all_layer_page_ids(0, 2, [1, 2, 3, 4, 5, 7], num_cache_pages=7)
+    with pytest.raises(pkg.PsiError, match="must contain all layer page IDs"):
+        table.write_all_layer_page_ids(0, 2, [1, 2], num_cache_pages=7)
+    with pytest.raises(pkg.PsiError, match="req_slot out of range"):
+        table.write_page_ids(4, 0, 0, [1, 2])
+    with pytest.raises(pkg.PsiError, match="layer out of range"):
+        table.write_page_ids(0, 3, 0, [1, 2])
+    with pytest.raises(pkg.PsiError, match="block out of range"):
+        table.read_page_ids(0, 0, 6)
+    with pytest.raises(pkg.PsiError, match="page-id count must match"):
+        table.write_page_ids(0, 0, 0, [1])
+    table.close()
+    ctx.close()
+
+
+def test_page_arena_is_zeroed_and_round_trips_selected_ranges():
+    # crates/inference-executor-metal/src/model/page_arena.rs:67-153 (full and selected state unload / load)
+    ctx = pkg.Context(0)
+    arena = pkg.PageArena(ctx, 3, 16)
+    assert arena.export_range(0, 3) == bytes(48)
+    data = bytes((i * 5 + 3) % 256 for i in range(48))
+    arena.import_range(0, 3, data)
+    assert arena.export_range(0, 3) == data and arena.export_range(1, 2) == data[16:32]
+    arena.release_resources()
+    with pytest.raises(pkg.PsiError, match="must be loaded before execution"):
+        arena.buffer()
+    with pytest.raises(pkg.PsiError, match="not loaded"):
+        arena.release_resources()
+    arena.allocate_resources()
+    assert arena.export_range(0, 3) == bytes(48)
+    with pytest.raises(pkg.PsiError, match="already loaded"):
+        arena.allocate_resources()
+    arena.import_range(2, 3, data[:16])
+    assert arena.export_range(0, 3) == bytes(32) + data[:16]
+    with pytest.raises(pkg.PsiError, match="outside the page arena"):
+        arena.export_range(2, 4)
+    arena.close()
+    ctx.close()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# SingleQ fixtures of the reference (f32, tolerance 2e-5)
+# ---------------------------------------------------------------------------------------------------------------------
+def _single_q_rig(plan_mode, num_req_slots=1, ipb=1, max_tokens=4):
+    # fixture_config(): crates/inference-backend-metal/src/components/gqa_split_kv_single_q_test.rs:267-289
+    return dict(dtype=pkg.F32, num_q_heads=4, num_kv_heads=2, head_dim=2, tokens_per_page=4, scale=0.5,
+                layout=(num_req_slots, 1, 1, ipb), max_tokens=max_tokens, plan_mode=plan_mode)
+
+
+def _run_single_q(rig, q, req_slots, token_indices, cu_tokens):
+    import torch
+    qd = G.to_device(q, pkg.F32).reshape(-1, rig.hq, rig.d)
+    out = torch.full_like(qd, -321.0)
+    rig.gqa.prepare(req_slots, token_indices, cu_tokens)
+    rig.gqa.attend(rig.pages, rig.table, 0, qd, out)
+    rig.ctx.sync()
+    return out.cpu().numpy().reshape(-1)
+
+
+@pytest.mark.parametrize("plan_mode,_name", MODES)
+@pytest.mark.parametrize("case", ["fixed", "random"])
+def test_single_q_fixed_and_random(plan_mode, _name, case):
+    # gqa_split_kv_single_q_test.rs:50-83 (fixed) and :145-183 (random)
+    n_out, stride = 2 * 4 * 2, 2 * 2
+    if case == "fixed":
+        q, k, v = fixture_values(n_out, 0.125, 3), fixture_values(2 * stride, 0.0625, 5), fixture_values(2 * stride, 0.25, 7)
+    else:
+        seed = 0x4C8F17D2
+        q, k, v = generated_values(n_out, seed), generated_values(2 * stride, seed + 1), generated_values(2 * stride, seed + 2)
+    rig = G.Rig(arena_f32=kv_page_values(2, 2, 4, [(k, v)]), **_single_q_rig(plan_mode))
+    rig.set_pages(0, 0, [0])
+    actual = _run_single_q(rig, q, [0], [0], [0, 2])
+    expected = O.projected_gqa_reference(4, 2, 2, 0.5, [0, 2], [0], q, [k], [v])
+    assert np.max(np.abs(actual - expected)) <= 2e-5
+    rig.close()
+
+
+@pytest.mark.parametrize("plan_mode,_name", MODES)
+def test_single_q_ragged_random(plan_mode, _name):
+    # gqa_split_kv_single_q_test.rs:185-223: two request slots, flat tokens (slot 0 @1), (slot 1 @0), (slot 1 @1)
+    seed = 0xD2056AB9
+    stride = 4
+    q = generated_values(3 * 4 * 2, seed)
+    r0k, r0v = generated_values(2 * stride, seed + 1), generated_values(2 * stride, seed + 2)
+    r1k, r1v = generated_values(2 * stride, seed + 3), generated_values(2 * stride, seed + 4)
+    rig = G.Rig(arena_f32=kv_page_values(2, 2, 4, [(r0k, r0v), (r1k, r1v)]), **_single_q_rig(plan_mode, num_req_slots=2))
+    rig.set_pages(0, 0, [0])
+    rig.set_pages(1, 0, [1])
+    actual = _run_single_q(rig, q, [0, 1], [1, 0], [0, 1, 3])
+    expected = O.projected_gqa_reference(4, 2, 2, 0.5, [0, 1, 3], [1, 0], q, [r0k, r1k], [r0v, r1v])
+    assert np.max(np.abs(actual - expected)) <= 2e-5
+    rig.close()
+
+
+@pytest.mark.parametrize("plan_mode,_name", MODES)
+def test_single_q_multiple_page_ids_per_block(plan_mode, _name):
+    # gqa_split_kv_single_q_test.rs:225-265: one block with two page ids, token index 7 sees 8 keys over two pages
+    stride = 4
+    q = fixture_values(1 * 4 * 2, 0.125, 3)
+    k, v = fixture_values(8 * stride, 0.0625, 5), fixture_values(8 * stride, 0.25, 7)
+    arena = kv_page_values(2, 2, 4, [(k[:4 * stride], v[:4 * stride]), (k[4 * stride:], v[4 * stride:])])
+    rig = G.Rig(arena_f32=arena, **_single_q_rig(plan_mode, ipb=2))
+    rig.set_pages(0, 0, [0, 1])
+    actual = _run_single_q(rig, q, [0], [7], [0, 1])
+    expected = O.projected_gqa_reference(4, 2, 2, 0.5, [0, 1], [7], q, [k], [v])
+    assert np.max(np.abs(actual - expected)) <= 2e-5
+    rig.close()
+
+
+@pytest.mark.parametrize("plan_mode,_name", MODES)
+def test_single_q_bucketed_replay_preserves_output_tail(plan_mode, _name):
+    # gqa_split_kv_single_q_test.rs:85-143: capacity 4 tokens, 3 then 4 active; inactive output rows keep -321
+    import torch
+    stride = 4
+    q = generated_values(4 * 4 * 2, 0x8B1D5A73)
+    k, v = generated_values(4 * stride, 0x8B1D5A74), generated_values(4 * stride, 0x8B1D5A75)
+    rig = G.Rig(arena_f32=kv_page_values(2, 2, 4, [(k, v)]), **_single_q_rig(plan_mode))
+    rig.set_pages(0, 0, [0])
+    qd = G.to_device(q, pkg.F32).reshape(4, 4, 2)
+    for active in (3, 4):
+        out = torch.full_like(qd, -321.0)
+        shape = rig.gqa.prepare_bucketed_with_token_capacity([0], [0], [0, active], 4)
+        assert shape.num_tokens == active and shape.num_total_tokens == 4
+        rig.gqa.attend(rig.pages, rig.table, 0, qd, out)
+        rig.ctx.sync()
+        got = out.cpu().numpy().reshape(-1)
+        n = active * 8
+        expected = O.projected_gqa_reference(4, 2, 2, 0.5, [0, active], [0], q[:n], [k[:active * stride]],
+                                             [v[:active * stride]])
+        assert np.max(np.abs(got[:n] - expected)) <= 2e-5
+        assert np.all(got[n:] == -321.0)
+    rig.close()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Multi-query (TiledQ) cases of the reference (bf16, tolerance 2e-2)
+# ---------------------------------------------------------------------------------------------------------------------
+KERNELS = [(pkg.KERNEL_MMA, "mma"), (pkg.KERNEL_GENERIC, "generic")]
+
+
+def _run_tiled_case(num_tokens_per_req, num_q_heads, head_dim, tokens_per_page, start, plan_mode, kernel_mode):
+    # run_case(): crates/inference-executor-metal/tests/gqa_split_kv_tiled_q.rs:247-462
+    import torch
+    reqs = len(num_tokens_per_req)
+    num_tokens = sum(num_tokens_per_req)
+    num_blocks = -(-(start + max(num_tokens_per_req)) // tokens_per_page)
+    q = pattern(num_tokens * num_q_heads * head_dim, 29, 0.015625)
+    ks, vs, pages = [], [], []
+    for r in range(reqs):
+        n = num_blocks * tokens_per_page * head_dim
+        k, v = pattern(n, 31 + r, 0.015625), pattern(n, 37 + r, 0.03125)
+        ks.append(k)
+        vs.append(v)
+        for b in range(num_blocks):
+            lo, hi = b * tokens_per_page * head_dim, (b + 1) * tokens_per_page * head_dim
+            pages.append((k[lo:hi], v[lo:hi]))
+    arena = kv_page_values(1, head_dim, tokens_per_page, pages)
+    scale = np.float32(1.0) / np.sqrt(np.float32(head_dim))
+    rig = G.Rig(pkg.BF16, num_q_heads, 1, head_dim, tokens_per_page, float(scale), (reqs, 1, num_blocks, 1), num_tokens,
+                arena_f32=arena, plan_mode=plan_mode, kernel_mode=kernel_mode)
+    for r in range(reqs):
+        rig.set_pages(r, 0, np.arange(r * num_blocks, (r + 1) * num_blocks))
+    cu = [0]
+    for n in num_tokens_per_req:
+        cu.append(cu[-1] + n)
+    qd = G.to_device(q, pkg.BF16).reshape(num_tokens, num_q_heads, head_dim)
+    out = torch.zeros_like(qd)
+    rig.gqa.prepare(list(range(reqs)), [start] * reqs, cu)
+    rig.gqa.attend(rig.pages, rig.table, 0, qd, out)
+    rig.ctx.sync()
+    bf = lambda x: O.decode(O.encode(x, O.BF16), O.BF16)
+    expected = O.projected_gqa_reference(
+        num_q_heads, 1, head_dim, float(scale), cu, [start] * reqs, bf(q),
+        [bf(ks[r][: (start + num_tokens_per_req[r]) * head_dim]) for r in range(reqs)],
+        [bf(vs[r][: (start + num_tokens_per_req[r]) * head_dim]) for r in range(reqs)])
+    actual = _decode(out, pkg.BF16).reshape(-1)
+    stats = rig.gqa.plan_stats()
+    rig.close()
+    assert stats["kernel"] == kernel_mode
+    assert np.max(np.abs(actual - expected)) <= 0.02, np.max(np.abs(actual - expected))
+    assert np.mean(np.abs(actual - expected)) <= 2e-3
+
+
+@pytest.mark.parametrize("kernel_mode,_kname", KERNELS)
+@pytest.mark.parametrize("plan_mode,_name", MODES)
+@pytest.mark.parametrize("case", [
+    ([16], 8, 256, 16, 17),                          # test_fixed
+    ([16], 6, 256, 8, 9),                            # test_qwen38_27b_profile
+    ([1, 2, 4, 6, 8, 11, 16, 16], 6, 256, 16, 17),   # test_ragged
+    ([32, 8], 8, 256, 16, 17),                       # test_multiple_tiles
+    ([1, 4, 8, 13], 5, 128, 8, 9),                   # test_qwen3_profile
+])
+def test_tiled_q_integration_cases(case, plan_mode, _name, kernel_mode, _kname):
+    # crates/inference-executor-metal/tests/gqa_split_kv_tiled_q.rs:27-50
+    _run_tiled_case(*case, plan_mode, kernel_mode)
+
+
+@pytest.mark.parametrize("kernel_mode,_kname", KERNELS)
+def test_tiled_q_bucketed_replay_with_poison_and_canary_tails(kernel_mode, _kname):
+    # crates/inference-backend-metal/src/components/gqa_split_kv_tiled_q_test.rs:17-199: one request, 5 -> 8 -> 5
+    # active tokens of capacity 8; inactive q / K / V rows are NaN, inactive index entries are u32::MAX, and the
+    # inactive output rows must keep the canary (case 0) or the previous full result (case 2).
+    import torch
+    hq, d, p = 5, 128, 8
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
+    bf = lambda x: O.decode(O.encode(x, O.BF16), O.BF16)
+    qv = bf(generated_half_range_values(8 * hq * d, 0x47514154))
+    kv = bf(generated_half_range_values(p * d, 0x47514155))
+    vv = bf(generated_half_range_values(p * d, 0x47514156))
+    canary = 0x42B6
+    rig = G.Rig(pkg.BF16, hq, 1, d, p, scale, (1, 1, 1, 1), 8, num_pages=1, kernel_mode=kernel_mode)
+    rig.set_pages(0, 0, [0])
+    out = torch.from_numpy(np.full((8, hq, d), canary, dtype=np.uint16).view(np.int16)).cuda().view(torch.bfloat16)
+    full_out = None
+    for case_index, active in enumerate((5, 8, 5)):
+        q_sub, k_sub, v_sub = qv.copy(), kv.copy(), vv.copy()
+        q_sub[active * hq * d:] = np.nan
+        k_sub[active * d:] = np.nan
+        v_sub[active * d:] = np.nan
+        rig.arena.copy_(G.to_device(kv_page_values(1, d, p, [(k_sub, v_sub)]).reshape(1, -1), pkg.BF16))
+        qd = G.to_device(q_sub, pkg.BF16).reshape(8, hq, d)
+        rig.gqa.prepare_bucketed_with_token_capacity([0], [0], [0, active], 8)
+        rig.gqa.attend(rig.pages, rig.table, 0, qd, out)
+        rig.ctx.sync()
+        n = active * hq * d
+        expected = O.projected_gqa_reference(hq, 1, d, scale, [0, active], [0], qv[:n], [kv[:active * d]],
+                                             [vv[:active * d]])
+        bits = G.bits_of(out).reshape(-1)
+        actual = O.decode(bits[:n], O.BF16)
+        assert np.max(np.abs(actual - expected)) <= 2e-2
+        if case_index == 0:
+            assert np.all(bits[n:] == canary)
+        elif case_index == 1:
+            full_out = bits.copy()
+        else:
+            assert np.array_equal(bits[n:], full_out[n:])
+    rig.close()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Benchmark configurations
+# ---------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kernel_mode,_kname", KERNELS)
+def test_config1_append_then_attend(kernel_mode, _kname):
+    s = W.Session(W.config(1), kernel_mode=kernel_mode)
+    before = checks.to_numpy_bits(s.arena)
+    s.step()
+    s.ctx.sync()
+    expected = checks.expected_arena_after_append(s, before)
+    assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), expected)
+    checks.assert_attention_close(s)
+    s.close()
+
+
+@pytest.mark.parametrize("index,scale_down", [(2, 8), (3, 16), (4, 64), (5, 64)])
+@pytest.mark.parametrize("plan_mode,_name", MODES)
+def test_scaled_configs_full_parity(index, scale_down, plan_mode, _name):
+    spec = W.config(index, scale_down=scale_down)
+    if plan_mode == pkg.PLAN_REFERENCE and spec.num_tokens > 512:
+        pytest.skip("the reference planner's O(max_tokens * tiles) greedy loop is slow at this token count")
+    s = W.Session(spec, plan_mode=plan_mode)
+    before = checks.to_numpy_bits(s.arena)
+    s.step()
+    s.ctx.sync()
+    expected = checks.expected_arena_after_append(s, before)
+    assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), expected)
+    checks.assert_attention_close(s)
+    s.close()
+
+
+def test_config2_full_size_parity_and_idempotence():
+    import torch
+    s = W.Session(W.config(2))
+    assert s.gqa.plan_stats()["kernel"] == pkg.KERNEL_MMA
+    s.step()
+    s.ctx.sync()
+    first = s.out.clone()
+    checks.assert_attention_close(s)
+    # a second pass appends the same rows to the same slots: pages and outputs must not change
+    arena = s.arena.clone()
+    s.step()
+    s.ctx.sync()
+    assert torch.equal(arena.view(torch.int16), s.arena.view(torch.int16))
+    assert torch.equal(first.view(torch.int16), s.out.view(torch.int16))
+    s.close()
+
+
+def test_config3_full_size_sampled_parity_and_gather_round_trip():
+    import torch
+    spec = W.config(3)
+    s = W.Session(spec)
+    s.step()
+    s.ctx.sync()
+    order = np.argsort(spec.visible)
+    sample = [int(order[0]), int(order[len(order) // 2]), int(order[-1])]
+    checks.assert_attention_close(s, sample)
+    # size-independent property at full size: gathering the appended positions returns exactly this step's k, v
+    cu = np.concatenate([[0], np.cumsum(spec.q_len)])
+    for seq in sample:
+        lo = int(spec.context_lens[seq])
+        kout = torch.zeros((2, spec.num_kv_heads, spec.head_dim), dtype=s.tdtype, device=s.device)
+        vout = torch.zeros_like(kout)
+        s.gqa.page_gather(s.pages, s.table, seq, 0, lo, lo + 2, kout, vout)
+        s.ctx.sync()
+        assert torch.equal(kout.view(torch.int16), s.k[cu[seq]:cu[seq] + 2].view(torch.int16))
+        assert torch.equal(vout.view(torch.int16), s.v[cu[seq]:cu[seq] + 2].view(torch.int16))
+    s.close()
+
+
+def test_partials_and_combine_match_full_attention():
+    # KV-range split of configuration 4 (scaled): two local shards produce (o, m, l); combine equals the unsplit run.
+    import torch
+    spec = W.config(4, scale_down=64)
+    full = W.Session(spec)
+    full.step()
+    full.ctx.sync()
+    checks.assert_attention_close(full)
+    t, hq, d = spec.num_tokens, spec.num_q_heads, spec.head_dim
+    # shard sessions draw their own K/V; rebuild the unsplit context from both shards' gathered tokens via the oracle
+    shards = [W.Session(spec.kv_range_shard(r, 2)) for r in range(2)]
+    parts = []
+    for sh in shards:
+        sh.q.copy_(full.q)
+        if sh.spec.do_append:
+            sh.append()
+        o = torch.zeros((t, hq, d), dtype=torch.float32, device="cuda:0")
+        m = torch.zeros((t, hq), dtype=torch.float32, device="cuda:0")
+        l = torch.zeros((t, hq), dtype=torch.float32, device="cuda:0")
+        sh.gqa.attend_partial(sh.pages, sh.table, 0, sh.q, o, m, l)
+        sh.ctx.sync()
+        parts.append((o, m, l))
+        # each partial against the oracle on the shard's own arena
+        prob = checks.host_problem(sh)
+        q = checks.to_numpy_bits(sh.q)[prob["tok_rows"]]
+        eo, em, es = O.paged_attention(prob["arena"], spec.dtype, q, prob["req_slots"], prob["positions"],
+                                       prob["table"], 0, prob["layout"], hq, spec.num_kv_heads, d, spec.page_bytes,
+                                       spec.scale, want_stats=True)
+        assert np.max(np.abs(o.cpu().numpy() - eo)) <= 2e-2
+        assert np.max(np.abs(m.cpu().numpy() - em)) <= 2e-3
+        assert np.max(np.abs(l.cpu().numpy() / es - 1.0)) <= 2e-2
+    out = torch.zeros_like(full.q)
+    shards[0].gqa.combine([p[0] for p in parts], [p[1] for p in parts], [p[2] for p in parts], t, out)
+    shards[0].ctx.sync()
+    # oracle merge of the oracle partials is the expectation for the combined output
+    merged = np.zeros((t, hq, d), dtype=np.float32)
+    po = [p[0].cpu().numpy() for p in parts]
+    pm = [p[1].cpu().numpy() for p in parts]
+    pl = [p[2].cpu().numpy() for p in parts]
+    for i in range(t):
+        for h in range(hq):
+            merged[i, h] = O.merge_partials(np.stack([po[0][i, h], po[1][i, h]]), [pm[0][i, h], pm[1][i, h]],
+                                            [pl[0][i, h], pl[1][i, h]])
+    assert np.max(np.abs(_decode(out, spec.dtype) - merged)) <= 2e-2
+    for sh in shards:
+        sh.close()
+    full.close()
+
+
+def test_decode_step_through_host_buffers():
+    import torch
+    spec = W.config(2, scale_down=8)
+    s = W.Session(spec)
+    before = checks.to_numpy_bits(s.arena)
+    kh, vh, qh = s.k.cpu().pin_memory(), s.v.cpu().pin_memory(), s.q.cpu().pin_memory()
+    oh = torch.zeros_like(qh).pin_memory()
+    s.gqa.decode_step_host(s.pages, s.table, 0, kh, vh, qh, oh)
+    expected = checks.expected_arena_after_append(s, before)
+    assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), expected)
+    s.out.copy_(oh.cuda())
+    checks.assert_attention_close(s)
+    s.close()
+
+
+def test_layer_index_selects_the_table_row():
+    # two layers share one arena; each layer's rows map the same logical pages to different physical pages
+    import torch
+    rng = np.random.default_rng(3)
+    hq, hkv, d, p = 8, 2, 64, 16
+    rig = G.Rig(pkg.BF16, hq, hkv, d, p, 0.125, (2, 2, 4, 1), 2,
+                arena_f32=rng.standard_normal((16, 2 * hkv * p * d)).astype(np.float32))
+    ids = rng.permutation(16).astype(np.uint32).reshape(2, 2, 4)
+    for s in range(2):
+        for l in range(2):
+            rig.set_pages(s, l, ids[s, l])
+    q = G.to_device(rng.standard_normal((2, hq, d)).astype(np.float32), pkg.BF16)
+    rig.gqa.prepare([0, 1], [40, 63], [0, 1, 2])
+    for layer in range(2):
+        out = torch.zeros_like(q)
+        rig.gqa.attend(rig.pages, rig.table, layer, q, out)
+        rig.ctx.sync()
+        expected = rig.oracle_attention(q, [0, 1], [40, 63], layer=layer)
+        assert np.max(np.abs(_decode(out, pkg.BF16) - expected)) <= 2e-2
+    rig.close()
+
+
+def test_host_side_contracts_on_the_component():
+    # the reference's panics, returned as invalid-argument before anything launches
+    ctx = pkg.Context(0)
+    layout = pkg.GQAPageTableLayout(2, 1, 4, 1)
+    good = dict(num_q_heads=4, num_kv_heads=2, head_dim=64, scale=0.125, page_bytes=2 * 2 * 16 * 64 * 2,
+                dtype=pkg.BF16, layout=layout, max_tokens=8, plan_mode=0, kernel_mode=0, max_ctas=0)
+    def make(**kw):
+        return pkg.GQA(ctx, pkg.GQAConfig(**{**good, **kw}))
+    with pytest.raises(pkg.PsiError, match="multiple of kv heads"):
+        make(num_q_heads=5)
+    with pytest.raises(pkg.PsiError, match="divisible by the K/V bytes per token"):
+        make(page_bytes=1000)
+    with pytest.raises(pkg.PsiError, match="scale must be positive"):
+        make(scale=0.0)
+    with pytest.raises(pkg.PsiError, match="exceeds the shader u32 count domain"):
+        make(max_tokens=1 << 30)
+    with pytest.raises(pkg.PsiError, match="does not support this profile"):
+        make(dtype=pkg.F32, page_bytes=2 * 2 * 16 * 64 * 4, kernel_mode=pkg.KERNEL_MMA)
+    g = make()
+    with pytest.raises(pkg.PsiError, match="must be updated before recording"):
+        g.plan_stats()
+    with pytest.raises(pkg.PsiError, match="exceeds the metadata token capacity"):
+        g.prepare([0], [0], [0, 9])
+    with pytest.raises(pkg.PsiError, match="does not fit the request page table"):
+        g.prepare([0], [60], [0, 5])
+    with pytest.raises(pkg.PsiError, match="req_slot out of range"):
+        g.prepare([2], [0], [0, 1])
+    table = pkg.GQARequestPageTable(ctx, pkg.GQAPageTableLayout(2, 1, 5, 1))
+    arena = pkg.PageArena(ctx, 4, good["page_bytes"])
+    g.prepare([0], [0], [0, 1])
+    with pytest.raises(pkg.PsiError, match="layout differs"):
+        g.attend(arena, table, 0, arena.buffer(), arena.buffer())
+    for obj in (g, table, arena):
+        obj.close()
+    ctx.close()
