@@ -160,6 +160,7 @@ struct psi_gqa {
     uint64_t off_req_slots = 0, off_token_indices = 0, off_tiles = 0, off_cta = 0, off_reduces = 0, off_items = 0;
 
     DeviceBuffer partial_o, partial_ml;  // [slots][16][D] and [2][slots][16]
+    DeviceBuffer unit_counters;          // [slots] u32, zero between launches
     uint64_t partial_slots_cap = 0;
     DeviceBuffer step_k, step_v, step_q, step_out;  // psi_gqa_decode_step_host staging
     DeviceBuffer combine_ptrs;
@@ -260,6 +261,7 @@ AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* 
     p.partial_o = static_cast<float*>(g->partial_o.ptr);
     p.partial_m = static_cast<float*>(g->partial_ml.ptr);
     p.partial_l = p.partial_m == nullptr ? nullptr : p.partial_m + g->partial_slots_cap * kMaxRows;
+    p.unit_counters = static_cast<uint32_t*>(g->unit_counters.ptr);
     p.scalars = block_words(g, 0);
     p.num_q_heads = g->cfg.num_q_heads;
     p.group = g->geo.group;
@@ -281,7 +283,9 @@ void run_attend(psi_gqa* g, const AttendParams& p) {
             cuda_check(launch_attend_generic(p, num_ctas, ctx->stream), "attend (generic) launch");
         }
     }
-    const uint32_t num_reduces = static_cast<uint32_t>(g->plan.reduces.size());
+    // The mma kernel merges a unit's partials in the CTA that delivers the last one; the generic kernel needs the
+    // separate reduce pass.
+    const uint32_t num_reduces = g->kernel == PSI_KERNEL_MMA ? 0u : static_cast<uint32_t>(g->plan.reduces.size());
     if (num_reduces > 0) {
         LaunchScope scope(ctx, PSI_KERNEL_CLASS_ATTEND_REDUCE);
         cuda_check(launch_attend_reduce(p, num_reduces, ctx->stream), "attend reduce launch");
@@ -871,6 +875,7 @@ int32_t psi_gqa_destroy(psi_gqa* g) {
         g->block.release();
         g->partial_o.release();
         g->partial_ml.release();
+        g->unit_counters.release();
         g->step_k.release();
         g->step_v.release();
         g->step_q.release();
@@ -975,7 +980,14 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
             const uint64_t slots = std::max<uint64_t>(plan.num_partial_slots, 2ull * g->grid_cap);
             g->partial_o.ensure(ctx, slots * kMaxRows * g->cfg.head_dim * sizeof(float), false);
             g->partial_ml.ensure(ctx, 2 * slots * kMaxRows * sizeof(float), false);
+            g->unit_counters.ensure(ctx, slots * sizeof(uint32_t), true);
             g->partial_slots_cap = slots;
+        }
+        if (g->kernel == PSI_KERNEL_MMA && !plan.reduces.empty()) {
+            // Arrival counters return to zero by themselves; clearing them here keeps one aborted launch from
+            // poisoning the next step.
+            cuda_check(cudaMemsetAsync(g->unit_counters.ptr, 0, plan.reduces.size() * sizeof(uint32_t), ctx->stream),
+                       "cudaMemsetAsync");
         }
 
         uint32_t* s = g->staging;

@@ -4,13 +4,15 @@
 // one (q tile, KV head) - the tokens of the tile times the heads of the GQA group, at most 16 rows - against a range
 // of KV tokens, so every KV byte of the step is read from HBM exactly once.
 //
-// Inside a CTA each of the four warps owns every fourth 16-token KV tile of the item and streams it through its own
-// ring of shared-memory stages with 16-byte cp.async copies (a warp-wide copy covers 512 contiguous bytes of one
-// page), so the steady state has no CTA-wide barrier: a warp waits only for its own oldest stage.  The 16 query rows
-// are one m16 MMA tile: S = Q K^T and O += P V run as mma.sync.m16n8k16 with f32 accumulators, operands fetched by
-// ldmatrix from XOR-swizzled rows; the online softmax runs on the accumulator fragments with quad shuffles in the
-// log2 domain, and O is rescaled only when a row's running max moved.  At the end of an item the four warps merge
-// their (O, m, l) through shared memory and write either the final output or one partial slot.
+// Inside a CTA each of the eight warps owns every eighth 16-token KV tile of the item and streams it through its own
+// ring of shared-memory slots (K tile, V tile, K tile, ...) with 16-byte cp.async copies (a warp-wide copy covers 512
+// contiguous bytes of one page), so the steady state has no CTA-wide barrier: a warp waits only for its own oldest
+// slot, and two warps per scheduler hide each other's instruction latencies.  The 16 query rows are one m16 MMA
+// tile: S = Q K^T and O += P V run as mma.sync.m16n8k16 with f32 accumulators, operands fetched by ldmatrix from
+// XOR-swizzled rows; the online softmax runs on the accumulator fragments with quad shuffles in the log2 domain, and
+// O is rescaled only when a row's running max moved.  At the end of an item the warps merge their (O, m, l) through
+// shared memory and write either the final output or one partial slot; the CTA that delivers the last partial of a
+// (q tile, KV head) unit merges the unit's partials itself (arrival counter, no waiting), so no second kernel runs.
 //
 // The arithmetic this replaces: crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_map.metal
 // (decode rows) and metal/gqa_split_kv_tiled_q.metal:161-319 (several query tokens of one request with the in-kernel
@@ -23,7 +25,7 @@ namespace psi {
 
 namespace {
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kTile = 16;  // KV tokens per tile == query rows per item
 
@@ -96,23 +98,22 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk, uint3
     return row * row_bytes + ((chunk ^ (row & 7u)) << 4);
 }
 
-template <int D, int NSTAGE>
+template <int D, int NSLOT>
 struct SmemLayout {
     static constexpr uint32_t kRowBytes = D * 2;
-    static constexpr uint32_t kTileBytes = kTile * kRowBytes;        // one K or V tile
-    static constexpr uint32_t kStageBytes = 2 * kTileBytes;          // K then V
+    static constexpr uint32_t kTileBytes = kTile * kRowBytes;        // one K or V tile = one ring slot
     static constexpr uint32_t kQBytes = kTile * kRowBytes;
-    static constexpr uint32_t kStagesOffset = kQBytes;
+    static constexpr uint32_t kRingOffset = kQBytes;
     static constexpr uint32_t kMergeStride = D + 8;                  // floats per merged row
     static constexpr uint32_t kMergeBytes = kWarps * kTile * kMergeStride * 4;
-    static constexpr uint32_t kRingBytes = kWarps * NSTAGE * kStageBytes;
-    static constexpr uint32_t kTotal = kStagesOffset + (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes);
+    static constexpr uint32_t kRingBytes = kWarps * NSLOT * kTileBytes;
+    static constexpr uint32_t kTotal = kRingOffset + (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes);
 };
 
-template <typename T, int D, int NSTAGE>
+template <typename T, int D, int NSLOT>
 __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p) {
-    using L = SmemLayout<D, NSTAGE>;
-    constexpr uint32_t kChunks = D / 8;        // 16-byte chunks per row
+    using L = SmemLayout<D, NSLOT>;
+    constexpr uint32_t kChunks = D / 8;                      // 16-byte chunks per row
     constexpr uint32_t kRowsPerCopy = 32 / (kChunks < 32 ? kChunks : 32);
     constexpr int kKSteps = D / 16;
 
@@ -123,6 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     __shared__ uint32_t limit_s[kTile];
     __shared__ float merge_m[kWarps][kTile];
     __shared__ float merge_l[kWarps][kTile];
+    __shared__ uint32_t arrival_s;
 
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = tid >> 5;
@@ -132,19 +134,28 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
 
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     const uint32_t q_base = smem_base;
-    const uint32_t ring_base = smem_base + L::kStagesOffset + warp * NSTAGE * L::kStageBytes;
-    float* merge_o = reinterpret_cast<float*>(smem + L::kStagesOffset);
+    const uint32_t ring_base = smem_base + L::kRingOffset + warp * NSLOT * L::kTileBytes;
+    float* merge_o = reinterpret_cast<float*>(smem + L::kRingOffset);
 
-    const uint32_t P = p.geo.tokens_per_page;
+    const uint32_t page_mask = p.geo.tokens_per_page - 1;          // tokens_per_page is a power of two
+    const uint32_t page_shift = 31 - __clz(p.geo.tokens_per_page);
     const unsigned char* pages = static_cast<const unsigned char*>(p.geo.pages);
     const uint64_t page_bytes = p.geo.page_elems * 2;
     const uint64_t v_region_bytes = v_region_offset(p.geo) * 2;
 
-    // ldmatrix lane roles (constant for the whole kernel)
+    // ldmatrix lane roles (constant for the whole kernel), pre-folded into byte offsets
     const uint32_t mat = lane >> 3, mat_row = lane & 7;
-    const uint32_t q_row = mat_row + 8 * (mat & 1), q_hi = mat >> 1;           // A operand: rows x k-halves
-    const uint32_t k_row = mat_row + 8 * (mat >> 1), k_hi = mat & 1;           // B operand of Q K^T
-    const uint32_t v_row = mat_row + 8 * (mat & 1), v_hi = mat >> 1;           // B operand of P V (transposed)
+    const uint32_t q_row = mat_row + 8 * (mat & 1);                 // A operand: rows x k-halves
+    const uint32_t k_row = mat_row + 8 * (mat >> 1);                // B operand of Q K^T
+    const uint32_t v_row = mat_row + 8 * (mat & 1);                 // B operand of P V (transposed)
+    const uint32_t q_lane = q_base + q_row * L::kRowBytes, q_x = ((mat >> 1) ^ (q_row & 7)) << 4;
+    const uint32_t k_lane = k_row * L::kRowBytes, k_x = ((mat & 1) ^ (k_row & 7)) << 4;
+    const uint32_t v_lane = v_row * L::kRowBytes, v_x = ((mat >> 1) ^ (v_row & 7)) << 4;
+
+    // copy lane roles: this lane moves chunk copy_chunk of rows copy_row, copy_row + kRowsPerCopy, ...
+    const uint32_t copy_row = lane / kChunks, copy_chunk = lane % kChunks;
+    const uint32_t copy_src = copy_row * L::kRowBytes + copy_chunk * 16;
+    const uint32_t copy_x = copy_chunk ^ copy_row;                  // copy_row < 8: XOR-able with the row step below
 
     for (uint32_t index = p.cta_item_begin[cta]; index < p.cta_item_begin[cta + 1]; ++index) {
         const ItemView v = view_item(p, p.items[index]);
@@ -176,32 +187,41 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         const uint32_t end_tile = (v.kv_end + kTile - 1) / kTile;
         const uint32_t item_tiles = end_tile - first_tile;
         const uint32_t my_tiles = item_tiles > warp ? (item_tiles - warp + kWarps - 1) / kWarps : 0;
+        const uint32_t my_halves = 2 * my_tiles;  // K tile, V tile, K tile, ...
         const uint32_t* row_ids = table_row(p.geo, v.req_slot);
+        const uint64_t head_bytes = static_cast<uint64_t>(v.kv_head) * p.geo.tokens_per_page * L::kRowBytes;
 
         // Page ids of the two 8-token halves of local tile i (equal when a page holds 16 tokens or more).
         auto lookup = [&](uint32_t i, uint32_t& id_lo, uint32_t& id_hi) {
             const uint32_t token = (first_tile + warp + i * kWarps) * kTile;
-            id_lo = token < v.kv_end ? row_ids[token / P] : 0u;
-            id_hi = token + 8 < v.kv_end ? row_ids[(token + 8) / P] : 0u;
+            id_lo = token < v.kv_end ? row_ids[token >> page_shift] : 0u;
+            id_hi = token + 8 < v.kv_end ? row_ids[(token + 8) >> page_shift] : 0u;
         };
-        // Issues the copies of local tile i into ring stage `stage`.
-        auto issue = [&](uint32_t i, uint32_t stage, uint32_t id_lo, uint32_t id_hi) {
-            const uint32_t token0 = (first_tile + warp + i * kWarps) * kTile;
-            const uint32_t stage_base = ring_base + stage * L::kStageBytes;
+        // Issues the copies of half-tile h (K of tile h/2 when h is even, else V) into ring slot `slot`.
+        auto issue = [&](uint32_t h, uint32_t slot, uint32_t id_lo, uint32_t id_hi) {
+            const uint32_t token0 = (first_tile + warp + (h >> 1) * kWarps) * kTile;
+            const uint32_t dst0 = ring_base + slot * L::kTileBytes + copy_row * L::kRowBytes;
+            const uint64_t region = head_bytes + ((h & 1) ? v_region_bytes : 0) + copy_src;
+            const unsigned char* src_lo =
+                pages + static_cast<uint64_t>(id_lo) * page_bytes + region + (token0 & page_mask) * L::kRowBytes;
+            const unsigned char* src_hi =
+                pages + static_cast<uint64_t>(id_hi) * page_bytes + region + ((token0 + 8) & page_mask) * L::kRowBytes;
+            if (token0 + kTile <= v.kv_end) {
 #pragma unroll
-            for (uint32_t it = 0; it < kTile / kRowsPerCopy; ++it) {
-                const uint32_t row = it * kRowsPerCopy + lane / kChunks;
-                const uint32_t chunk = lane % kChunks;
-                const uint32_t token = token0 + row;
-                const bool valid = token < v.kv_end;
-                const uint32_t page_id = row < 8 ? id_lo : id_hi;
-                const unsigned char* src =
-                    pages + (valid ? static_cast<uint64_t>(page_id) * page_bytes +
-                                         (static_cast<uint64_t>(v.kv_head) * P + token % P) * L::kRowBytes + chunk * 16
-                                   : 0);
-                const uint32_t dst = stage_base + swizzled(row, chunk, L::kRowBytes);
-                cp_async_16(dst, src, valid ? 16u : 0u);
-                cp_async_16(dst + L::kTileBytes, valid ? src + v_region_bytes : src, valid ? 16u : 0u);
+                for (uint32_t it = 0; it < kTile / kRowsPerCopy; ++it) {
+                    const uint32_t row0 = it * kRowsPerCopy;  // this lane's row is row0 + copy_row
+                    const unsigned char* src = row0 < 8 ? src_lo + row0 * L::kRowBytes : src_hi + (row0 - 8) * L::kRowBytes;
+                    cp_async_16(dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4), src, 16u);
+                }
+            } else {
+#pragma unroll
+                for (uint32_t it = 0; it < kTile / kRowsPerCopy; ++it) {
+                    const uint32_t row0 = it * kRowsPerCopy;
+                    const bool valid = token0 + row0 + copy_row < v.kv_end;
+                    const unsigned char* src = row0 < 8 ? src_lo + row0 * L::kRowBytes : src_hi + (row0 - 8) * L::kRowBytes;
+                    cp_async_16(dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4), valid ? src : pages,
+                                valid ? 16u : 0u);
+                }
             }
         };
 
@@ -210,90 +230,101 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 
-        uint32_t next_lo = 0, next_hi = 0;
+        // ids of the tile whose halves are issued next, and of the tile after it
+        uint32_t cur_lo = 0, cur_hi = 0, next_lo = 0, next_hi = 0;
+        if (my_tiles > 0) lookup(0, cur_lo, cur_hi);
+        if (my_tiles > 1) lookup(1, next_lo, next_hi);
 #pragma unroll
-        for (uint32_t s = 0; s < NSTAGE - 1; ++s) {
-            if (s < my_tiles) {
-                lookup(s, next_lo, next_hi);
-                issue(s, s, next_lo, next_hi);
+        for (uint32_t h = 0; h < NSLOT - 1; ++h) {
+            if (h < my_halves) {
+                issue(h, h, cur_lo, cur_hi);
+                if (h & 1) {  // the tile is fully issued: advance the id window
+                    cur_lo = next_lo;
+                    cur_hi = next_hi;
+                    if ((h >> 1) + 2 < my_tiles) lookup((h >> 1) + 2, next_lo, next_hi);
+                }
             }
             cp_async_commit();
         }
-        if (NSTAGE - 1 < my_tiles) lookup(NSTAGE - 1, next_lo, next_hi);
 
-        for (uint32_t i = 0; i < my_tiles; ++i) {
-            cp_async_wait<NSTAGE - 2>();
+        float s[2][4];
+        uint32_t pa[4];
+        for (uint32_t h = 0; h < my_halves; ++h) {
+            cp_async_wait<NSLOT - 2>();
             __syncwarp();
-            const uint32_t ahead = i + NSTAGE - 1;
-            if (ahead < my_tiles) issue(ahead, ahead % NSTAGE, next_lo, next_hi);
-            cp_async_commit();
-            if (ahead + 1 < my_tiles) lookup(ahead + 1, next_lo, next_hi);
-
-            const uint32_t k_base = ring_base + (i % NSTAGE) * L::kStageBytes;
-            const uint32_t v_base = k_base + L::kTileBytes;
-            const uint32_t token0 = (first_tile + warp + i * kWarps) * kTile;
-
-            // ---- S = Q K^T: two 8-token column tiles, even and odd k-steps in separate accumulators --------------------
-            float s_even[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-            for (int ks = 0; ks < kKSteps; ++ks) {
-                uint32_t a[4], b[4];
-                ldmatrix_x4(a, q_base + swizzled(q_row, 2 * ks + q_hi, L::kRowBytes));
-                ldmatrix_x4(b, k_base + swizzled(k_row, 2 * ks + k_hi, L::kRowBytes));
-                if (ks & 1) {
-                    Mma<T>::run(s_odd[0], a, b[0], b[1]);
-                    Mma<T>::run(s_odd[1], a, b[2], b[3]);
-                } else {
-                    Mma<T>::run(s_even[0], a, b[0], b[1]);
-                    Mma<T>::run(s_even[1], a, b[2], b[3]);
+            const uint32_t ahead = h + NSLOT - 1;
+            if (ahead < my_halves) {
+                issue(ahead, ahead % NSLOT, cur_lo, cur_hi);
+                if (ahead & 1) {
+                    cur_lo = next_lo;
+                    cur_hi = next_hi;
+                    if ((ahead >> 1) + 2 < my_tiles) lookup((ahead >> 1) + 2, next_lo, next_hi);
                 }
             }
-            float s[2][4];
-#pragma unroll
-            for (int n = 0; n < 2; ++n)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) s[n][e] = (s_even[n][e] + s_odd[n][e]) * p.scale_log2;
+            cp_async_commit();
 
-            // ---- visibility: keys at or beyond a row's limit, or before the item's range, do not count ----------------
-            if (token0 < v.kv_begin || token0 + kTile > limit_min) {
+            const uint32_t slot_base = ring_base + (h % NSLOT) * L::kTileBytes;
+            if ((h & 1) == 0) {
+                // ---- S = Q K^T: two 8-token column tiles, even and odd k-steps in separate accumulators ----------------
+                const uint32_t token0 = (first_tile + warp + (h >> 1) * kWarps) * kTile;
+                float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+#pragma unroll
+                for (int ks = 0; ks < kKSteps; ++ks) {
+                    uint32_t a[4], b[4];
+                    ldmatrix_x4(a, q_lane + (q_x ^ (32u * ks)));
+                    ldmatrix_x4(b, slot_base + k_lane + (k_x ^ (32u * ks)));
+                    if (ks & 1) {
+                        Mma<T>::run(s_odd[0], a, b[0], b[1]);
+                        Mma<T>::run(s_odd[1], a, b[2], b[3]);
+                    } else {
+                        Mma<T>::run(s[0], a, b[0], b[1]);
+                        Mma<T>::run(s[1], a, b[2], b[3]);
+                    }
+                }
 #pragma unroll
                 for (int n = 0; n < 2; ++n)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const uint32_t token = token0 + 8 * n + 2 * quad_col + (e & 1);
-                        const uint32_t limit = e < 2 ? limit0 : limit1;
-                        if (token >= limit || token < v.kv_begin) s[n][e] = -INFINITY;
-                    }
-            }
+                    for (int e = 0; e < 4; ++e) s[n][e] = (s[n][e] + s_odd[n][e]) * p.scale_log2;
 
-            // ---- online softmax on the fragments -------------------------------------------------------------------
-            float max0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-            float max1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-            max0 = fmaxf(max0, __shfl_xor_sync(0xFFFFFFFFu, max0, 1));
-            max0 = fmaxf(max0, __shfl_xor_sync(0xFFFFFFFFu, max0, 2));
-            max1 = fmaxf(max1, __shfl_xor_sync(0xFFFFFFFFu, max1, 1));
-            max1 = fmaxf(max1, __shfl_xor_sync(0xFFFFFFFFu, max1, 2));
-            const float new0 = fmaxf(m0, max0), new1 = fmaxf(m1, max1);
-            const bool moved = new0 > m0 || new1 > m1;
-            if (__any_sync(0xFFFFFFFFu, moved)) {
-                const float corr0 = new0 == -INFINITY ? 1.0f : exp2f(m0 - new0);
-                const float corr1 = new1 == -INFINITY ? 1.0f : exp2f(m1 - new1);
-                l0 *= corr0;
-                l1 *= corr1;
+                // ---- visibility: keys at or beyond a row's limit, or before the item's range, do not count ------------
+                if (token0 < v.kv_begin || token0 + kTile > limit_min) {
 #pragma unroll
-                for (int j = 0; j < D / 8; ++j) {
-                    o[j][0] *= corr0;
-                    o[j][1] *= corr0;
-                    o[j][2] *= corr1;
-                    o[j][3] *= corr1;
+                    for (int n = 0; n < 2; ++n)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t token = token0 + 8 * n + 2 * quad_col + (e & 1);
+                            const uint32_t limit = e < 2 ? limit0 : limit1;
+                            if (token >= limit || token < v.kv_begin) s[n][e] = -INFINITY;
+                        }
                 }
-                m0 = new0;
-                m1 = new1;
-            }
-            const float base0 = m0 == -INFINITY ? 0.0f : m0, base1 = m1 == -INFINITY ? 0.0f : m1;
-            uint32_t pa[4];
-            {
+
+                // ---- online softmax on the fragments ---------------------------------------------------------------
+                float max0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+                float max1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+                max0 = fmaxf(max0, __shfl_xor_sync(0xFFFFFFFFu, max0, 1));
+                max0 = fmaxf(max0, __shfl_xor_sync(0xFFFFFFFFu, max0, 2));
+                max1 = fmaxf(max1, __shfl_xor_sync(0xFFFFFFFFu, max1, 1));
+                max1 = fmaxf(max1, __shfl_xor_sync(0xFFFFFFFFu, max1, 2));
+                const float new0 = fmaxf(m0, max0), new1 = fmaxf(m1, max1);
+                const bool moved = new0 > m0 || new1 > m1;
+                if (__any_sync(0xFFFFFFFFu, moved)) {
+                    const float corr0 = new0 == -INFINITY ? 1.0f : exp2f(m0 - new0);
+                    const float corr1 = new1 == -INFINITY ? 1.0f : exp2f(m1 - new1);
+                    l0 *= corr0;
+                    l1 *= corr1;
+#pragma unroll
+                    for (int j = 0; j < D / 8; ++j) {
+                        o[j][0] *= corr0;
+                        o[j][1] *= corr0;
+                        o[j][2] *= corr1;
+                        o[j][3] *= corr1;
+                    }
+                    m0 = new0;
+                    m1 = new1;
+                }
+                const float base0 = m0 == -INFINITY ? 0.0f : m0, base1 = m1 == -INFINITY ? 0.0f : m1;
                 const float p00 = exp2f(s[0][0] - base0), p01 = exp2f(s[0][1] - base0);
                 const float p02 = exp2f(s[0][2] - base1), p03 = exp2f(s[0][3] - base1);
                 const float p10 = exp2f(s[1][0] - base0), p11 = exp2f(s[1][1] - base0);
@@ -304,19 +335,19 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                 pa[1] = Mma<T>::pack(p02, p03);
                 pa[2] = Mma<T>::pack(p10, p11);
                 pa[3] = Mma<T>::pack(p12, p13);
-            }
-
-            // ---- O += P V ----------------------------------------------------------------------------------------------
+            } else {
+                // ---- O += P V ----------------------------------------------------------------------------------------------
 #pragma unroll
-            for (int j = 0; j < D / 16; ++j) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, v_base + swizzled(v_row, 2 * j + v_hi, L::kRowBytes));
-                Mma<T>::run(o[2 * j], pa, b[0], b[1]);
-                Mma<T>::run(o[2 * j + 1], pa, b[2], b[3]);
+                for (int j = 0; j < D / 16; ++j) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, slot_base + v_lane + (v_x ^ (32u * j)));
+                    Mma<T>::run(o[2 * j], pa, b[0], b[1]);
+                    Mma<T>::run(o[2 * j + 1], pa, b[2], b[3]);
+                }
             }
         }
 
-        // ---- merge the four warps' partial results ---------------------------------------------------------------------
+        // ---- merge the warps' partial results --------------------------------------------------------------------------
         cp_async_wait<0>();
         __syncthreads();  // every warp is done with its ring: the merge buffer may overwrite it
         l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1);
@@ -340,6 +371,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         }
         __syncthreads();
 
+        const bool is_partial = v.partial_slot != kU32Max;
         for (uint32_t i = tid; i < v.rows * (D / 4); i += kThreads) {
             const uint32_t r = i / (D / 4), c4 = i % (D / 4);
             float row_max = -INFINITY;
@@ -364,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             acc.y *= inv;
             acc.z *= inv;
             acc.w *= inv;
-            if (v.partial_slot != kU32Max) {
+            if (is_partial) {
                 const uint64_t prow = static_cast<uint64_t>(v.partial_slot) * kMaxRows + r;
                 *reinterpret_cast<float4*>(p.partial_o + prow * D + 4 * c4) = acc;
                 if (c4 == 0) {
@@ -384,19 +416,66 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                 }
             }
         }
+
+        // ---- the CTA that delivers a unit's last partial merges the unit -------------------------------------------------
+        if (is_partial) {
+            __threadfence();  // this thread's partial stores are visible device-wide before the arrival is counted
+            __syncthreads();
+            if (tid == 0) arrival_s = atomicAdd(p.unit_counters + v.reduce_unit, 1u);
+            __syncthreads();
+            if (arrival_s == v.unit_num_items - 1) {
+                __threadfence();
+                for (uint32_t i = tid; i < v.rows * (D / 4); i += kThreads) {
+                    const uint32_t r = i / (D / 4), c4 = i % (D / 4);
+                    float global_max = -INFINITY;
+                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
+                        global_max = fmaxf(global_max, __ldcg(p.partial_m + static_cast<uint64_t>(v.unit_first_slot + s_i) * kMaxRows + r));
+                    }
+                    float sum = 0.0f;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
+                        const uint64_t prow = static_cast<uint64_t>(v.unit_first_slot + s_i) * kMaxRows + r;
+                        const float pm = __ldcg(p.partial_m + prow);
+                        const float weight = pm == -INFINITY ? 0.0f : exp2f(pm - global_max) * __ldcg(p.partial_l + prow);
+                        const float4 part = __ldcg(reinterpret_cast<const float4*>(p.partial_o + prow * D + 4 * c4));
+                        sum += weight;
+                        acc.x += weight * part.x;
+                        acc.y += weight * part.y;
+                        acc.z += weight * part.z;
+                        acc.w += weight * part.w;
+                    }
+                    const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+                    acc.x *= inv;
+                    acc.y *= inv;
+                    acc.z *= inv;
+                    acc.w *= inv;
+                    const uint64_t row = item_row_index(p, v, r);
+                    if (p.ext_o != nullptr) {
+                        *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc;
+                        if (c4 == 0) {
+                            p.ext_m[row] = global_max * kLn2;
+                            p.ext_l[row] = sum;
+                        }
+                    } else {
+                        Mma<T>::store4(static_cast<T*>(p.out) + row * D + 4 * c4, acc);
+                    }
+                }
+                if (tid == 0) p.unit_counters[v.reduce_unit] = 0;  // ready for the next launch
+            }
+        }
     }
 }
 
 template <int D>
 constexpr int stages_for() {
-    return D == 256 ? 3 : (D == 128 ? 6 : 8);
+    return D == 256 ? 3 : (D == 128 ? 6 : 8);  // ring slots (one K or V tile each) per warp
 }
 
 template <typename T, int D>
 cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
-    constexpr int NSTAGE = stages_for<D>();
-    using L = SmemLayout<D, NSTAGE>;
-    auto kernel = attend_mma_kernel<T, D, NSTAGE>;
+    constexpr int NSLOT = stages_for<D>();
+    using L = SmemLayout<D, NSLOT>;
+    auto kernel = attend_mma_kernel<T, D, NSLOT>;
     static bool configured = false;  // per instantiation; the attribute is per device, set again on every device below
     static int configured_device = -1;
     int device = 0;
@@ -427,7 +506,8 @@ cudaError_t launch_for_dim(const AttendParams& p, uint32_t num_ctas, cudaStream_
 bool attend_mma_supported(uint32_t dtype, uint32_t head_dim, uint32_t tokens_per_page) {
     const bool dtype_ok = dtype == PSI_DTYPE_BF16 || dtype == PSI_DTYPE_F16;
     const bool dim_ok = head_dim == 64 || head_dim == 128 || head_dim == 256;
-    return dtype_ok && dim_ok && tokens_per_page % 8 == 0;
+    const bool page_ok = tokens_per_page >= 8 && (tokens_per_page & (tokens_per_page - 1)) == 0;
+    return dtype_ok && dim_ok && page_ok;
 }
 
 uint32_t attend_mma_ctas_per_sm(uint32_t /*head_dim*/) { return 1; }

@@ -62,6 +62,9 @@ struct ItemView {
     uint32_t kv_begin;
     uint32_t kv_end;
     uint32_t partial_slot;
+    uint32_t reduce_unit;
+    uint32_t unit_first_slot;
+    uint32_t unit_num_items;
     uint32_t req_slot;
 };
 
@@ -78,6 +81,9 @@ __device__ __forceinline__ ItemView view_item(const AttendParams& p, const WorkI
     v.kv_begin = item.kv_begin;
     v.kv_end = item.kv_end;
     v.partial_slot = item.partial_slot;
+    v.reduce_unit = item.reduce_unit;
+    v.unit_first_slot = item.unit_first_slot;
+    v.unit_num_items = item.unit_num_items;
     v.req_slot = p.req_slots[tile.flat_begin];
     return v;
 }

@@ -262,8 +262,15 @@ void finish_plan(WorkPlan& plan) {
         if (j - i == 1) {
             plan.items[i].partial_slot = kU32Max;
         } else {
+            const uint32_t unit = static_cast<uint32_t>(plan.reduces.size());
+            const uint32_t first_slot = plan.num_partial_slots;
             plan.reduces.push_back({static_cast<uint32_t>(i), static_cast<uint32_t>(j - i)});
-            for (size_t k = i; k < j; ++k) plan.items[k].partial_slot = plan.num_partial_slots++;
+            for (size_t k = i; k < j; ++k) {
+                plan.items[k].partial_slot = plan.num_partial_slots++;
+                plan.items[k].reduce_unit = unit;
+                plan.items[k].unit_first_slot = first_slot;
+                plan.items[k].unit_num_items = static_cast<uint32_t>(j - i);
+            }
         }
         i = j;
     }

@@ -86,7 +86,9 @@ struct WorkItem {
     uint32_t kv_begin;
     uint32_t kv_end;
     uint32_t partial_slot;  // kU32Max: the item covers its unit alone and writes the final output itself
-    uint32_t reserved[3];
+    uint32_t reduce_unit;   // index into the plan's reduce list when partial_slot is set
+    uint32_t unit_first_slot;  // partial slot of the unit's first item (slots of one unit are consecutive)
+    uint32_t unit_num_items;   // items that share the unit
 };
 
 struct ReduceUnit {

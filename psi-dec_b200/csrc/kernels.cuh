@@ -65,6 +65,7 @@ struct AttendParams {
     float* partial_o;             // [slots][16][D] normalised
     float* partial_m;             // [slots][16] log2-domain max
     float* partial_l;             // [slots][16]
+    uint32_t* unit_counters;      // [reduce units], zero between launches: arrivals of a unit's items (mma kernel)
     const uint32_t* scalars;
     uint32_t num_q_heads;
     uint32_t group;
