@@ -279,6 +279,14 @@ PSI_API int32_t psi_gqa_kv_append(psi_gqa* gqa, psi_pages* pages, psi_table* tab
 PSI_API int32_t psi_gqa_attend(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer, const void* q,
                                void* out);
 
+/* The two stages above as one launch: the attention kernel itself writes this step's K/V rows into their pages and
+ * reads them from k / v instead of from the pages, so the step has no kernel boundary between append and attend
+ * (GQA::record's kv_page_write -> barrier -> SplitKV map -> reduce, crates/inference-executor-metal/src/attn/gqa/
+ * backend.rs:493-612, in one submission).  Same results as psi_gqa_kv_append followed by psi_gqa_attend.  k, v must
+ * be 16-byte aligned. */
+PSI_API int32_t psi_gqa_append_attend(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer, const void* k,
+                                      const void* v, const void* q, void* out);
+
 /* The same map + reduce, stopping before normalisation to the output dtype: f32 o [T][Hq][D] (normalised within the
  * local KV), m [T][Hq] (natural-log running max of scale*q.k), l [T][Hq] (sum of exp(logit - m)).  This is the
  * reference's partial-output ABI (gqa_split_kv_single_q_map.metal:231-252) lifted to one partial per device, for KV

@@ -397,6 +397,11 @@ class GQA:
         _check(library().psi_gqa_attend(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(q), _ptr(out)),
                self.ctx._h)
 
+    def append_attend(self, pages: PageArena, table: GQARequestPageTable, layer: int, k, v, q, out):
+        """KV append and attention as one launch (same results as ``kv_page_write`` then ``attend``)."""
+        _check(library().psi_gqa_append_attend(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(k), _ptr(v),
+                                               _ptr(q), _ptr(out)), self.ctx._h)
+
     def attend_partial(self, pages, table, layer, q, o, m, l):
         _check(library().psi_gqa_attend_partial(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(q), _ptr(o),
                                                 _ptr(m), _ptr(l)), self.ctx._h)

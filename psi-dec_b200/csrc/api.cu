@@ -157,7 +157,7 @@ struct psi_gqa {
     uint64_t staging_words = 0;
     cudaEvent_t upload_done = nullptr;
     // section offsets (in words) of the block uploaded by the last prepare
-    uint64_t off_req_slots = 0, off_token_indices = 0, off_tiles = 0, off_cta = 0, off_reduces = 0, off_items = 0;
+    uint64_t off_req_slots = 0, off_token_indices = 0, off_cta = 0, off_reduces = 0, off_items = 0;
 
     DeviceBuffer partial_o, partial_ml;  // [slots][16][D] and [2][slots][16]
     DeviceBuffer unit_counters;          // [slots] u32, zero between launches
@@ -252,10 +252,7 @@ AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* 
     AttendParams p{};
     p.geo = page_geometry(g, pages, table, layer);
     p.q = q;
-    p.req_slots = block_words(g, g->off_req_slots);
-    p.flat_token_indices = block_words(g, g->off_token_indices);
-    p.tiles = reinterpret_cast<const ExecTile*>(block_words(g, g->off_tiles));
-    p.items = reinterpret_cast<const WorkItem*>(block_words(g, g->off_items));
+    p.items = reinterpret_cast<const DeviceItem*>(block_words(g, g->off_items));
     p.cta_item_begin = block_words(g, g->off_cta);
     p.reduces = reinterpret_cast<const ReduceUnit*>(block_words(g, g->off_reduces));
     p.partial_o = static_cast<float*>(g->partial_o.ptr);
@@ -264,9 +261,6 @@ AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* 
     p.unit_counters = static_cast<uint32_t*>(g->unit_counters.ptr);
     p.scalars = block_words(g, 0);
     p.num_q_heads = g->cfg.num_q_heads;
-    p.group = g->geo.group;
-    p.heads_per_tile = g->geo.heads_per_tile;
-    p.head_tiles = g->geo.head_tiles;
     p.dtype = g->cfg.dtype;
     p.scale_log2 = g->cfg.scale * 1.4426950408889634f;
     return p;
@@ -750,8 +744,9 @@ int32_t psi_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint
         require(num_reqs > 0 && cu_tokens[0] == 0, "GQA batch cu_tokens must start at zero");
         for (uint32_t r = 0; r < num_reqs; ++r)
             require(cu_tokens[r] <= cu_tokens[r + 1], "GQA batch cu_tokens must be nondecreasing");
-        const WorkPlan plan = build_balanced_plan(plan_geometry(num_q_heads, num_kv_heads), token_indices, cu_tokens,
-                                                  num_reqs, max_ctas, min_kv_tiles_per_cta);
+        const std::vector<uint32_t> slots(num_reqs, 0u);
+        const WorkPlan plan = build_balanced_plan(plan_geometry(num_q_heads, num_kv_heads), slots.data(), token_indices,
+                                                  cu_tokens, num_reqs, max_ctas, min_kv_tiles_per_cta);
         out_counts[0] = static_cast<uint32_t>(plan.items.size());
         out_counts[1] = plan.num_ctas();
         out_counts[2] = plan.num_partial_slots;
@@ -940,27 +935,28 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         }
 
         if (g->cfg.plan_mode == PSI_PLAN_REFERENCE) {
-            g->plan = build_reference_plan(g->geo, *g->md, shape, variant.tiled_q != 0);
+            g->plan = build_reference_plan(g->geo, *g->md, shape, variant.tiled_q != 0, token_indices, cu_tokens,
+                                           num_reqs);
         } else {
-            const uint32_t min_tiles = g->kernel == PSI_KERNEL_MMA ? 8u : 4u;
-            g->plan = build_balanced_plan(g->geo, token_indices, cu_tokens, num_reqs, g->grid_cap, min_tiles);
+            const uint32_t min_tiles = g->kernel == PSI_KERNEL_MMA ? 16u : 4u;
+            g->plan = build_balanced_plan(g->geo, req_slots, token_indices, cu_tokens, num_reqs, g->grid_cap,
+                                          min_tiles);
         }
         const WorkPlan& plan = g->plan;
+        const std::vector<DeviceItem> device_items = flatten_plan(plan, g->geo);
 
-        // Pack the device block: scalars | req_slots | flat_token_indices | tiles | cta ranges | reduces | items.
+        // Pack the device block: scalars | req_slots | flat_token_indices | cta ranges | reduces | items.
         uint64_t cursor = pad_words(kScalarCount);
         g->off_req_slots = cursor;
         cursor += pad_words(num_tokens);
         g->off_token_indices = cursor;
         cursor += pad_words(num_tokens);
-        g->off_tiles = cursor;
-        cursor += pad_words(plan.tiles.size() * 2);
         g->off_cta = cursor;
         cursor += pad_words(plan.cta_item_begin.size());
         g->off_reduces = cursor;
         cursor += pad_words(plan.reduces.size() * 2);
         g->off_items = cursor;
-        cursor += pad_words(plan.items.size() * 8);
+        cursor += pad_words(device_items.size() * (sizeof(DeviceItem) / sizeof(uint32_t)));
         const uint64_t words = cursor;
 
         if (g->staging_words < words) {
@@ -998,11 +994,11 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         std::copy(g->md->req_slots.begin(), g->md->req_slots.begin() + num_tokens, s + g->off_req_slots);
         std::copy(g->md->flat_token_indices.begin(), g->md->flat_token_indices.begin() + num_tokens,
                   s + g->off_token_indices);
-        if (!plan.tiles.empty()) std::memcpy(s + g->off_tiles, plan.tiles.data(), plan.tiles.size() * sizeof(ExecTile));
         std::copy(plan.cta_item_begin.begin(), plan.cta_item_begin.end(), s + g->off_cta);
         if (!plan.reduces.empty())
             std::memcpy(s + g->off_reduces, plan.reduces.data(), plan.reduces.size() * sizeof(ReduceUnit));
-        if (!plan.items.empty()) std::memcpy(s + g->off_items, plan.items.data(), plan.items.size() * sizeof(WorkItem));
+        if (!device_items.empty())
+            std::memcpy(s + g->off_items, device_items.data(), device_items.size() * sizeof(DeviceItem));
         cuda_check(cudaMemcpyAsync(g->block.ptr, s, words * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream),
                    "cudaMemcpyAsync");
         cuda_check(cudaEventRecord(g->upload_done, ctx->stream), "cudaEventRecord");
@@ -1088,6 +1084,29 @@ int32_t psi_gqa_attend(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t 
     });
 }
 
+int32_t psi_gqa_append_attend(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* k,
+                              const void* v, const void* q, void* out) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(out != nullptr && k != nullptr && v != nullptr, "k, v and out must not be null");
+        g->ctx->bind();
+        if (g->kernel != PSI_KERNEL_MMA) {  // the generic kernel has no fused form: two launches in stream order
+            run_append(g, pages, table, layer, k, v);
+            AttendParams p = attend_params(g, pages, table, layer, q);
+            p.out = out;
+            run_attend(g, p);
+            return;
+        }
+        require((reinterpret_cast<uintptr_t>(k) & 15u) == 0 && (reinterpret_cast<uintptr_t>(v) & 15u) == 0,
+                "k and v must be 16-byte aligned");
+        AttendParams p = attend_params(g, pages, table, layer, q);
+        p.out = out;
+        p.new_k = k;
+        p.new_v = v;
+        run_attend(g, p);
+    });
+}
+
 int32_t psi_gqa_attend_partial(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* q, float* o,
                                float* m, float* l) {
     if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
@@ -1160,9 +1179,14 @@ int32_t psi_gqa_decode_step_host(psi_gqa* g, psi_pages* pages, psi_table* table,
         cuda_check(cudaMemcpyAsync(g->step_k.ptr, k_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D k");
         cuda_check(cudaMemcpyAsync(g->step_v.ptr, v_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D v");
         cuda_check(cudaMemcpyAsync(g->step_q.ptr, q_host, q_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D q");
-        run_append(g, pages, table, layer, g->step_k.ptr, g->step_v.ptr);
         AttendParams p = attend_params(g, pages, table, layer, g->step_q.ptr);
         p.out = g->step_out.ptr;
+        if (g->kernel == PSI_KERNEL_MMA) {
+            p.new_k = g->step_k.ptr;
+            p.new_v = g->step_v.ptr;
+        } else {
+            run_append(g, pages, table, layer, g->step_k.ptr, g->step_v.ptr);
+        }
         run_attend(g, p);
         cuda_check(cudaMemcpyAsync(out_host, g->step_out.ptr, q_bytes, cudaMemcpyDeviceToHost, ctx->stream), "D2H out");
         cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");

@@ -26,13 +26,13 @@ __global__ void __launch_bounds__(kGenericThreads) attend_generic_kernel(AttendP
     __shared__ uint32_t limit_s[kMaxRows];
 
     for (uint32_t index = p.cta_item_begin[cta]; index < p.cta_item_begin[cta + 1]; ++index) {
-        const ItemView v = view_item(p, p.items[index]);
+        const ItemView v = view_item(p, index);
         __syncwarp();
         for (uint32_t i = lane; i < v.rows * D; i += kGenericThreads) {
             const uint32_t r = i / D, d = i % D;
             q_s[r * D + d] = load_as_float(p.q, item_row_index(p, v, r) * D + d, p.dtype);
         }
-        if (lane < v.rows) limit_s[lane] = p.flat_token_indices[v.flat_begin + lane / v.num_heads] + 1;
+        if (lane < v.rows) limit_s[lane] = item_row_limit(v, lane);
         __syncwarp();
 
         float m[kMaxRows], l[kMaxRows], o[kMaxRows][DPL];
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kReduceThreads) attend_reduce_kernel(AttendPar
     const uint32_t unit = blockIdx.x;
     if (unit >= p.scalars[kScalarNumReduces]) return;
     const ReduceUnit ru = p.reduces[unit];
-    const ItemView v = view_item(p, p.items[ru.first_item]);
+    const ItemView v = view_item(p, ru.first_item);
     const uint32_t D = p.geo.head_dim;
     const uint32_t first_slot = v.partial_slot;  // slots of one unit are consecutive
     for (uint32_t i = threadIdx.x; i < v.rows * D; i += kReduceThreads) {

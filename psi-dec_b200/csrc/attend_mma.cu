@@ -157,30 +157,14 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     const uint32_t copy_src = copy_row * L::kRowBytes + copy_chunk * 16;
     const uint32_t copy_x = copy_chunk ^ copy_row;                  // copy_row < 8: XOR-able with the row step below
 
-    for (uint32_t index = p.cta_item_begin[cta]; index < p.cta_item_begin[cta + 1]; ++index) {
-        const ItemView v = view_item(p, p.items[index]);
-        __syncthreads();  // the previous item's merge is done with the ring and with q
+    const uint32_t item_begin = p.cta_item_begin[cta], item_end = p.cta_item_begin[cta + 1];
+    const bool fused = p.new_k != nullptr;
+    for (uint32_t index = item_begin; index < item_end; ++index) {
+        const ItemView v = view_item(p, index);
+        __syncthreads();  // the previous item's merge is done with the ring, with q and with limit_s
 
-        // ---- stage the query rows (zero rows beyond the item's) and the per-row causal limits ----------------------
-        for (uint32_t i = tid; i < kTile * kChunks; i += kThreads) {
-            const uint32_t r = i / kChunks, c = i % kChunks;
-            uint4 value = make_uint4(0, 0, 0, 0);
-            if (r < v.rows) {
-                const T* src = static_cast<const T*>(p.q) + item_row_index(p, v, r) * D + c * 8;
-                value = *reinterpret_cast<const uint4*>(src);
-            }
-            *reinterpret_cast<uint4*>(smem + swizzled(r, c, L::kRowBytes)) = value;
-        }
-        if (tid < kTile) {
-            uint32_t limit = v.kv_end;
-            if (tid < v.rows) limit = min(limit, p.flat_token_indices[v.flat_begin + tid / v.num_heads] + 1);
-            limit_s[tid] = limit;
-        }
-        __syncthreads();
-
-        const uint32_t limit0 = limit_s[quad_row], limit1 = limit_s[quad_row + 8];
-        uint32_t limit_min = v.kv_end;
-        for (uint32_t r = 0; r < v.rows; ++r) limit_min = min(limit_min, limit_s[r]);
+        // Keys at or beyond `paged_end` are this step's own tokens: in the fused step they are read from new_k/new_v.
+        const uint32_t paged_end = fused ? min(v.kv_end, v.new_begin) : v.kv_end;
 
         // ---- this warp's share of the item's KV tiles ----------------------------------------------------------------
         const uint32_t first_tile = v.kv_begin / kTile;
@@ -194,8 +178,8 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         // Page ids of the two 8-token halves of local tile i (equal when a page holds 16 tokens or more).
         auto lookup = [&](uint32_t i, uint32_t& id_lo, uint32_t& id_hi) {
             const uint32_t token = (first_tile + warp + i * kWarps) * kTile;
-            id_lo = token < v.kv_end ? row_ids[token >> page_shift] : 0u;
-            id_hi = token + 8 < v.kv_end ? row_ids[(token + 8) >> page_shift] : 0u;
+            id_lo = token < paged_end ? row_ids[token >> page_shift] : 0u;
+            id_hi = token + 8 < paged_end ? row_ids[(token + 8) >> page_shift] : 0u;
         };
         // Issues the copies of half-tile h (K of tile h/2 when h is even, else V) into ring slot `slot`.
         auto issue = [&](uint32_t h, uint32_t slot, uint32_t id_lo, uint32_t id_hi) {
@@ -206,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                 pages + static_cast<uint64_t>(id_lo) * page_bytes + region + (token0 & page_mask) * L::kRowBytes;
             const unsigned char* src_hi =
                 pages + static_cast<uint64_t>(id_hi) * page_bytes + region + ((token0 + 8) & page_mask) * L::kRowBytes;
-            if (token0 + kTile <= v.kv_end) {
+            if (token0 + kTile <= paged_end) {
 #pragma unroll
                 for (uint32_t it = 0; it < kTile / kRowsPerCopy; ++it) {
                     const uint32_t row0 = it * kRowsPerCopy;  // this lane's row is row0 + copy_row
@@ -214,13 +198,22 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                     cp_async_16(dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4), src, 16u);
                 }
             } else {
+                const unsigned char* fresh = static_cast<const unsigned char*>((h & 1) ? p.new_v : p.new_k);
 #pragma unroll
                 for (uint32_t it = 0; it < kTile / kRowsPerCopy; ++it) {
                     const uint32_t row0 = it * kRowsPerCopy;
-                    const bool valid = token0 + row0 + copy_row < v.kv_end;
+                    const uint32_t token = token0 + row0 + copy_row;
                     const unsigned char* src = row0 < 8 ? src_lo + row0 * L::kRowBytes : src_hi + (row0 - 8) * L::kRowBytes;
-                    cp_async_16(dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4), valid ? src : pages,
-                                valid ? 16u : 0u);
+                    uint32_t bytes = 16u;
+                    if (token >= v.kv_end) {
+                        src = pages;  // beyond the item: zero-fill
+                        bytes = 0u;
+                    } else if (token >= paged_end) {
+                        // one of this step's tokens: row (flat token, kv head) of the new K / V
+                        src = fresh + (static_cast<uint64_t>(v.flat_req_begin + (token - v.new_begin)) * p.geo.num_kv_heads +
+                                       v.kv_head) * L::kRowBytes + copy_chunk * 16;
+                    }
+                    cp_async_16(dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4), src, bytes);
                 }
             }
         };
@@ -246,6 +239,39 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             }
             cp_async_commit();
         }
+
+        // ---- with the first tiles in flight: stage the query rows (zero rows beyond the item's), the per-row
+        // causal limits, and in the fused step write this item's share of the step's K/V rows into their pages --------
+        for (uint32_t i = tid; i < kTile * kChunks; i += kThreads) {
+            const uint32_t r = i / kChunks, c = i % kChunks;
+            uint4 value = make_uint4(0, 0, 0, 0);
+            if (r < v.rows) {
+                const T* src = static_cast<const T*>(p.q) + item_row_index(p, v, r) * D + c * 8;
+                value = *reinterpret_cast<const uint4*>(src);
+            }
+            *reinterpret_cast<uint4*>(smem + swizzled(r, c, L::kRowBytes)) = value;
+        }
+        if (tid < kTile) limit_s[tid] = tid < v.rows ? item_row_limit(v, tid) : v.kv_end;
+        if (fused && v.writes_kv) {
+            for (uint32_t i = tid; i < v.num_tokens * 2 * kChunks; i += kThreads) {
+                const uint32_t c = i % kChunks, which = (i / kChunks) & 1, j = i / (2 * kChunks);
+                const uint32_t pos = v.first_pos + j;
+                if (pos >= v.kv_begin && pos < v.kv_end) {
+                    const unsigned char* fresh = static_cast<const unsigned char*>(which ? p.new_v : p.new_k);
+                    const uint4 value = *reinterpret_cast<const uint4*>(
+                        fresh + (static_cast<uint64_t>(v.flat_begin + j) * p.geo.num_kv_heads + v.kv_head) * L::kRowBytes + c * 16);
+                    unsigned char* dst = const_cast<unsigned char*>(pages) +
+                                         static_cast<uint64_t>(row_ids[pos >> page_shift]) * page_bytes + head_bytes +
+                                         (which ? v_region_bytes : 0) + (pos & page_mask) * L::kRowBytes + c * 16;
+                    *reinterpret_cast<uint4*>(dst) = value;
+                }
+            }
+        }
+        __syncthreads();
+
+        const uint32_t limit0 = limit_s[quad_row], limit1 = limit_s[quad_row + 8];
+        uint32_t limit_min = v.kv_end;
+        for (uint32_t r = 0; r < v.rows; ++r) limit_min = min(limit_min, limit_s[r]);
 
         float s[2][4];
         uint32_t pa[4];

@@ -51,46 +51,29 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 namespace psi {
 
-// What one work item means once its tile and head selection are resolved.
-struct ItemView {
-    uint32_t flat_begin;   // first flat query token of the tile
-    uint32_t num_tokens;   // query tokens in the tile
-    uint32_t kv_head;
-    uint32_t head0;        // first q head the item carries
-    uint32_t num_heads;    // q heads the item carries
-    uint32_t rows;         // num_tokens * num_heads (<= 16); row r = (token r / num_heads, head r % num_heads)
-    uint32_t kv_begin;
-    uint32_t kv_end;
-    uint32_t partial_slot;
-    uint32_t reduce_unit;
-    uint32_t unit_first_slot;
-    uint32_t unit_num_items;
-    uint32_t req_slot;
+// A work item as the kernels see it; `rows` = num_tokens * num_heads (<= 16).
+struct ItemView : DeviceItem {
+    uint32_t rows;
 };
 
-__device__ __forceinline__ ItemView view_item(const AttendParams& p, const WorkItem& item) {
+__device__ __forceinline__ ItemView view_item(const AttendParams& p, uint32_t index) {
     ItemView v;
-    const ExecTile tile = p.tiles[item.tile];
-    v.flat_begin = tile.flat_begin;
-    v.num_tokens = tile.flat_end - tile.flat_begin;
-    v.kv_head = item.head_sel / p.head_tiles;
-    const uint32_t head_tile = item.head_sel % p.head_tiles;
-    v.head0 = v.kv_head * p.group + head_tile * p.heads_per_tile;
-    v.num_heads = min(p.heads_per_tile, p.group - head_tile * p.heads_per_tile);
+    const uint4* src = reinterpret_cast<const uint4*>(p.items + index);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<DeviceItem*>(&v));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] = src[i];
     v.rows = v.num_tokens * v.num_heads;
-    v.kv_begin = item.kv_begin;
-    v.kv_end = item.kv_end;
-    v.partial_slot = item.partial_slot;
-    v.reduce_unit = item.reduce_unit;
-    v.unit_first_slot = item.unit_first_slot;
-    v.unit_num_items = item.unit_num_items;
-    v.req_slot = p.req_slots[tile.flat_begin];
     return v;
 }
 
 // Flat (token, head) row of q / out / ext_* that item row r stands for.
 __device__ __forceinline__ uint64_t item_row_index(const AttendParams& p, const ItemView& v, uint32_t r) {
     return static_cast<uint64_t>(v.flat_begin + r / v.num_heads) * p.num_q_heads + v.head0 + r % v.num_heads;
+}
+
+// Keys row r may see: [0, first_pos + token(r)] clipped to the item's range end.
+__device__ __forceinline__ uint32_t item_row_limit(const ItemView& v, uint32_t r) {
+    return min(v.kv_end, v.first_pos + r / v.num_heads + 1);
 }
 
 constexpr float kLn2 = 0.6931471805599453f;

@@ -278,14 +278,16 @@ void finish_plan(WorkPlan& plan) {
 
 }  // namespace
 
-WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* token_indices, const uint32_t* cu_tokens,
-                             uint32_t num_reqs, uint32_t max_ctas, uint32_t min_kv_tiles_per_cta) {
+WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
+                             const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
+                             uint32_t min_kv_tiles_per_cta) {
     WorkPlan plan;
     std::vector<uint32_t> tile_ctx;
     for (uint32_t r = 0; r < num_reqs; ++r) {
         for (uint32_t begin = cu_tokens[r]; begin < cu_tokens[r + 1];) {
             uint32_t end = std::min(cu_tokens[r + 1], begin + geo.tokens_per_tile);
-            plan.tiles.push_back({begin, end});
+            plan.tiles.push_back({begin, end, req_slots[r], token_indices[r] + (begin - cu_tokens[r]),
+                                  token_indices[r], cu_tokens[r]});
             tile_ctx.push_back(token_indices[r] + (end - cu_tokens[r]));
             begin = end;
         }
@@ -330,9 +332,11 @@ WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* token_indi
 }
 
 WorkPlan build_reference_plan(const PlanGeometry& geo, const ReferenceMetadata& md, const psi_replay_shape& shape,
-                              bool tiled_q) {
+                              bool tiled_q, const uint32_t* token_indices, const uint32_t* cu_tokens,
+                              uint32_t num_reqs) {
     WorkPlan plan;
     const uint32_t heads = geo.num_kv_heads * geo.head_tiles;
+    uint32_t req = 0;  // reference q tiles come in flat-token order, so the owning request only moves forward
     for (uint32_t rt = 0; rt < shape.num_q_token_tiles; ++rt) {
         const uint32_t flat_begin = tiled_q ? md.q_token_tiles[size_t(rt) * 2] : rt;
         const uint32_t flat_end = tiled_q ? md.q_token_tiles[size_t(rt) * 2 + 1] : rt + 1;
@@ -340,7 +344,9 @@ WorkPlan build_reference_plan(const PlanGeometry& geo, const ReferenceMetadata& 
         for (uint32_t begin = flat_begin; begin < flat_end;) {
             const uint32_t end = std::min(flat_end, begin + geo.tokens_per_tile);
             const uint32_t tile = static_cast<uint32_t>(plan.tiles.size());
-            plan.tiles.push_back({begin, end});
+            while (req + 1 < num_reqs && begin >= cu_tokens[req + 1]) ++req;
+            plan.tiles.push_back({begin, end, md.req_slots[begin], md.flat_token_indices[begin], token_indices[req],
+                                  cu_tokens[req]});
             const uint32_t ctx = md.flat_token_indices[end - 1] + 1;  // keys the sub-tile's last token sees
             for (uint32_t h = 0; h < heads; ++h) {
                 for (uint32_t s = s_begin; s < s_end; ++s) {
@@ -363,6 +369,33 @@ WorkPlan build_reference_plan(const PlanGeometry& geo, const ReferenceMetadata& 
     for (size_t i = 0; i <= plan.items.size(); ++i) plan.cta_item_begin[i] = static_cast<uint32_t>(i);
     finish_plan(plan);
     return plan;
+}
+
+std::vector<DeviceItem> flatten_plan(const WorkPlan& plan, const PlanGeometry& geo) {
+    std::vector<DeviceItem> out(plan.items.size());
+    for (size_t i = 0; i < plan.items.size(); ++i) {
+        const WorkItem& it = plan.items[i];
+        const ExecTile& tile = plan.tiles[it.tile];
+        const uint32_t head_tile = it.head_sel % geo.head_tiles;
+        DeviceItem& d = out[i];
+        d.kv_begin = it.kv_begin;
+        d.kv_end = it.kv_end;
+        d.partial_slot = it.partial_slot;
+        d.reduce_unit = it.reduce_unit;
+        d.unit_first_slot = it.unit_first_slot;
+        d.unit_num_items = it.unit_num_items;
+        d.flat_begin = tile.flat_begin;
+        d.num_tokens = tile.flat_end - tile.flat_begin;
+        d.req_slot = tile.req_slot;
+        d.kv_head = it.head_sel / geo.head_tiles;
+        d.head0 = d.kv_head * geo.group + head_tile * geo.heads_per_tile;
+        d.num_heads = std::min(geo.heads_per_tile, geo.group - head_tile * geo.heads_per_tile);
+        d.first_pos = tile.first_pos;
+        d.new_begin = tile.new_begin;
+        d.flat_req_begin = tile.flat_req_begin;
+        d.writes_kv = head_tile == 0 ? 1u : 0u;
+    }
+    return out;
 }
 
 // -------------------------------------------------------------------------------------------------------------------

@@ -77,9 +77,14 @@ struct ReferenceMetadata {
 struct ExecTile {
     uint32_t flat_begin;
     uint32_t flat_end;
+    uint32_t req_slot;
+    uint32_t first_pos;       // request-absolute position of the tile's first token
+    uint32_t new_begin;       // request-absolute position of the request's first token of this step
+    uint32_t flat_req_begin;  // flat index of that token
 };
 
-// One unit of map work: the rows of (tile, head_sel) against KV tokens [kv_begin, kv_end).  32 bytes on the device.
+// One unit of map work while the plan is being built: the rows of (tile, head_sel) against KV tokens
+// [kv_begin, kv_end).
 struct WorkItem {
     uint32_t tile;
     uint32_t head_sel;      // kv_head * head_tiles + head_tile
@@ -90,6 +95,27 @@ struct WorkItem {
     uint32_t unit_first_slot;  // partial slot of the unit's first item (slots of one unit are consecutive)
     uint32_t unit_num_items;   // items that share the unit
 };
+
+// The same item as the kernels read it: self-contained, 64 bytes, no further indirection.
+struct DeviceItem {
+    uint32_t kv_begin;
+    uint32_t kv_end;
+    uint32_t partial_slot;
+    uint32_t reduce_unit;
+    uint32_t unit_first_slot;
+    uint32_t unit_num_items;
+    uint32_t flat_begin;      // first flat query token of the tile
+    uint32_t num_tokens;      // query tokens in the tile
+    uint32_t req_slot;
+    uint32_t kv_head;
+    uint32_t head0;           // first q head the item carries
+    uint32_t num_heads;       // q heads the item carries; row r = (token r / num_heads, head r % num_heads)
+    uint32_t first_pos;       // position of the tile's first token: token j sees keys [0, first_pos + j]
+    uint32_t new_begin;       // positions at or beyond this belong to this step's appended tokens
+    uint32_t flat_req_begin;  // flat index of the token at position new_begin
+    uint32_t writes_kv;       // 1: the item appends its tile's K/V rows that fall into its KV range (fused step)
+};
+static_assert(sizeof(DeviceItem) == 64, "DeviceItem is read as four 16-byte words");
 
 struct ReduceUnit {
     uint32_t first_item;
@@ -118,13 +144,18 @@ struct WorkPlan {
 
 // Equal-share plan: the (tile, head_sel) units laid end to end in 16-token KV tiles, cut into `max_ctas` (or fewer)
 // contiguous shares.
-WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* token_indices, const uint32_t* cu_tokens,
-                             uint32_t num_reqs, uint32_t max_ctas, uint32_t min_kv_tiles_per_cta);
+WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
+                             const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
+                             uint32_t min_kv_tiles_per_cta);
 
 // One CTA per (reference KV split, head_sel); reference q tiles wider than tokens_per_tile are cut into sub-tiles
 // that share the split boundaries.
 WorkPlan build_reference_plan(const PlanGeometry& geo, const ReferenceMetadata& md, const psi_replay_shape& shape,
-                              bool tiled_q);
+                              bool tiled_q, const uint32_t* token_indices, const uint32_t* cu_tokens,
+                              uint32_t num_reqs);
+
+// Device form of a finished plan.
+std::vector<DeviceItem> flatten_plan(const WorkPlan& plan, const PlanGeometry& geo);
 
 // ---- page-ID allocator (crates/inference-runtime-core/src/memory/u32_id_allocator.rs) --------------------------------
 class IdAllocator {

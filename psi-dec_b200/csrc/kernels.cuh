@@ -56,10 +56,9 @@ struct AttendParams {
     float* ext_o;                 // [T][Hq][D] f32 normalised partial (attend_partial), else nullptr
     float* ext_m;                 // [T][Hq] natural-log max
     float* ext_l;                 // [T][Hq] exp-sum
-    const uint32_t* req_slots;
-    const uint32_t* flat_token_indices;
-    const ExecTile* tiles;
-    const WorkItem* items;
+    const void* new_k;            // fused step only: this step's K rows [T][Hkv][D], appended by the map kernel
+    const void* new_v;            //                  and read from here instead of from their pages; else nullptr
+    const DeviceItem* items;
     const uint32_t* cta_item_begin;
     const ReduceUnit* reduces;
     float* partial_o;             // [slots][16][D] normalised
@@ -68,9 +67,6 @@ struct AttendParams {
     uint32_t* unit_counters;      // [reduce units], zero between launches: arrivals of a unit's items (mma kernel)
     const uint32_t* scalars;
     uint32_t num_q_heads;
-    uint32_t group;
-    uint32_t heads_per_tile;
-    uint32_t head_tiles;
     uint32_t dtype;
     float scale_log2;             // scale * log2(e)
 };

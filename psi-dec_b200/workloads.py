@@ -211,7 +211,14 @@ class Session:
         self.gqa.attend(self.pages, self.table, self.spec.layer, self.q, self.out)
 
     def step(self):
-        """One pass of the hot path with inputs resident in HBM: append this step's K/V, then attend."""
+        """One pass of the hot path with inputs resident in HBM: append this step's K/V and attend, as one launch."""
+        if self.spec.do_append:
+            self.gqa.append_attend(self.pages, self.table, self.spec.layer, self.k, self.v, self.q, self.out)
+        else:
+            self.attend()
+
+    def step_unfused(self):
+        """The same step as the reference records it: KV page write, then attention, in stream order."""
         if self.spec.do_append:
             self.append()
         self.attend()

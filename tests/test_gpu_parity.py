@@ -408,6 +408,25 @@ def test_scaled_configs_full_parity(index, scale_down, plan_mode, _name):
     s.close()
 
 
+@pytest.mark.parametrize("index,scale_down", [(1, 1), (2, 8), (3, 16), (5, 64)])
+def test_fused_step_equals_append_then_attend(index, scale_down):
+    # one launch (the map kernel appends and reads this step's rows from k / v) against the two-stage order
+    import torch
+    spec = W.config(index, scale_down=scale_down)
+    a, b = W.Session(spec), W.Session(spec)
+    assert torch.equal(a.arena.view(torch.int16), b.arena.view(torch.int16))
+    a.step()
+    b.step_unfused()
+    a.ctx.sync()
+    b.ctx.sync()
+    assert torch.equal(a.arena.view(torch.int16), b.arena.view(torch.int16))
+    diff = (a.out.float() - b.out.float()).abs().max().item()
+    assert diff <= 1e-2, diff  # same math; partial sums may associate differently across launches
+    checks.assert_attention_close(a)
+    a.close()
+    b.close()
+
+
 def test_config2_full_size_parity_and_idempotence():
     import torch
     s = W.Session(W.config(2))
