@@ -311,6 +311,36 @@ PSI_API int32_t psi_gqa_decode_step_host(psi_gqa* gqa, psi_pages* pages, psi_tab
 PSI_API int32_t psi_page_gather(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t req_slot, uint32_t layer,
                                 uint32_t tok_begin, uint32_t tok_end, void* k_out, void* v_out);
 
+/* Attention for callers that must not allocate device memory (no counterpart in the reference, whose Metal buffers
+ * are all created up front).  A server that gave all remaining HBM to its KV arena, a host runtime that owns every
+ * device allocation through its own pool, or a decode loop that cannot take the device-wide stall of an allocation
+ * can still run the split-KV attention of psi_gqa_attend through this call: the plan, the arrival counters and the
+ * partial outputs live in one fixed device array of PSI_STATIC_SCRATCH_BYTES that each GPU loading the library holds
+ * until exit, and the call makes no cudaMalloc, cudaFree or other allocating CUDA call.
+ *
+ * Takes no psi_ctx / psi_gqa: `device` and `cuda_stream` name where to run, `config` the profile (plan_mode is
+ * ignored, the balanced plan is used; max_ctas may lower the CTA count further), `pages` the device arena,
+ * `page_table` the device table in the layout of config->layout, and the host arrays req_slots / token_indices /
+ * cu_tokens the batch exactly as for psi_gqa_prepare.  q and out are device [T][Hq][D].  The work is enqueued on the
+ * stream and the call returns; results equal psi_gqa_attend's.
+ *
+ * Limits: head_dim <= PSI_STATIC_MAX_HEAD_DIM, at most PSI_STATIC_MAX_CTAS CTAs (so less of a large GPU is used than
+ * by psi_gqa_attend) and PSI_STATIC_MAX_ITEMS work items - roughly (query tiles x KV heads) + PSI_STATIC_MAX_CTAS; a
+ * step beyond them returns PSI_ERR_INVALID_ARGUMENT with the reason in `error` and enqueues nothing.
+ * The first call on a device resolves the scratch address (cudaGetSymbolAddress); make that call outside any stream
+ * capture.  All calls on a device share the one scratch, which keeps the previous call's contents: each call
+ * rewrites its plan and clears the arrival counters itself, and two calls whose work overlaps on the GPU (different
+ * streams, or different host threads) race on it - serialise them on one stream.  `error` (may be NULL) receives a
+ * NUL-terminated message on failure. */
+#define PSI_STATIC_MAX_HEAD_DIM 256
+#define PSI_STATIC_MAX_CTAS 64
+#define PSI_STATIC_MAX_ITEMS 512
+#define PSI_STATIC_SCRATCH_BYTES 2148608
+PSI_API int32_t psi_gqa_attend_static(int32_t device, void* cuda_stream, const psi_gqa_config* config,
+                                      const void* pages, const uint32_t* page_table, const uint32_t* req_slots,
+                                      const uint32_t* token_indices, const uint32_t* cu_tokens, uint32_t num_reqs,
+                                      uint32_t layer, const void* q, void* out, char* error, size_t error_len);
+
 /* Number of kernels this library has launched on the context since creation (for launch accounting). */
 PSI_API int32_t psi_ctx_launch_count(psi_ctx* ctx, uint64_t* out);
 

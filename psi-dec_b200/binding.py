@@ -422,3 +422,26 @@ class GQA:
         _check(library().psi_page_gather(self._h, pages._h, table._h, C.c_uint32(req_slot), C.c_uint32(layer),
                                          C.c_uint32(tok_begin), C.c_uint32(tok_end), _ptr(k_out), _ptr(v_out)),
                self.ctx._h)
+
+
+def attend_static(device, stream, config: GQAConfig, pages, page_table, req_slots, token_indices, cu_tokens, layer, q,
+                  out):
+    """Split-KV attention without any device allocation (``psi_gqa_attend_static``).
+
+    For hosts that cannot call ``cudaMalloc`` while serving - all HBM already given to the KV arena, device memory
+    owned by the host runtime's own pool, or a decode loop that cannot stall on an allocation.  The scratch is one
+    fixed device array inside the library; ``pages`` and ``page_table`` are device addresses, the batch arrays are
+    host lists as for :meth:`GQA.prepare`.  Calls on one device share that scratch, so keep them on one stream.
+    Raises :class:`PsiError` with the library's message when the step exceeds the scratch limits.
+    """
+    rs, n = _u32_array(req_slots)
+    ti, n2 = _u32_array(token_indices)
+    cu, n3 = _u32_array(cu_tokens)
+    if n != n2 or n3 != n + 1:
+        raise PsiError(1, "req_slots, token_indices and cu_tokens lengths disagree")
+    err = C.create_string_buffer(512)
+    status = library().psi_gqa_attend_static(C.c_int32(device), C.c_void_p(int(stream or 0)), C.byref(config),
+                                             _ptr(pages), _ptr(page_table), rs, ti, cu, C.c_uint32(n),
+                                             C.c_uint32(layer), _ptr(q), _ptr(out), err, C.c_size_t(len(err)))
+    if status:
+        raise PsiError(status, err.value.decode("utf-8", "replace"))
