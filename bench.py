@@ -30,6 +30,9 @@ METRIC = "paged_gqa_decode_kv_read_bandwidth"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one attend_mma_kernel launch divided by the launch's algorithmic
+# bytes, from the ncu capture summarised in profiles/attend_mma_cfg2_ncu_full.md (301.27 MB for 296.76 MB).
+NCU_DRAM_BYTES_PER_ALGORITHMIC_BYTE = {"cfg2-a3b-layer-decode": 301.27 / 296.76}
 
 
 def measured_peak():
@@ -118,7 +121,7 @@ def bench_ours(args):
     alg = spec.algorithmic_bytes()
     # Larger than the 126 MB L2 and swept read-only between timed steps, so that the step's inputs are not resident
     # and no dirty lines are left for the timed kernels to write back.
-    flush = torch.zeros(64 << 20, dtype=torch.int32, device=session.device)
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=session.device)  # f32: summed without a cast copy
 
     def barrier():
         if world > 1:
@@ -219,14 +222,9 @@ def bench_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
-        traffic_file = ROOT / "profiles" / "traffic.json"
-        if traffic_file.exists():
-            try:
-                per_byte = json.loads(traffic_file.read_text()).get(base.name)
-                if per_byte:
-                    line["roofline"]["traffic"] = int(per_byte * alg["total"])
-            except Exception:
-                pass
+        per_byte = NCU_DRAM_BYTES_PER_ALGORITHMIC_BYTE.get(base.name)
+        if per_byte and stats["kernel"] == 2:
+            line["roofline"]["traffic"] = int(per_byte * alg["total"])
         if world == 1 and not args.no_cpu_baseline:
             import checks
             tok_s, bytes_s, desc, threads = checks.time_oracle_sample(session, seconds_target=12.0)

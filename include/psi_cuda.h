@@ -300,6 +300,21 @@ PSI_API int32_t psi_gqa_attend_partial(psi_gqa* gqa, psi_pages* pages, psi_table
 PSI_API int32_t psi_gqa_combine(psi_gqa* gqa, const float* const* o, const float* const* m, const float* const* l,
                                 uint32_t n, uint32_t num_tokens, void* out);
 
+/* KV ranges split across devices, exchange without a library collective: a producer runs psi_gqa_attend_partial with
+ * o/m/l pointing into the owner's receive buffers (peer memory) and then psi_gqa_signal, which release-stores `value`
+ * to `flag` (in the owner's memory) once everything enqueued before it is visible system-wide.  The owner runs
+ * psi_gqa_combine_wait: the merge of psi_gqa_combine, preceded by a BOUNDED wait until each of the n flags (device
+ * array in the owner's own memory) has reached flag_value.  If a producer never publishes, the wait gives up after
+ * max_polls polls (0 = default, roughly a fraction of a second), writes nothing to `out`, and records PSI_ERR_TIMEOUT,
+ * which psi_gqa_device_status returns (and clears) after waiting for the stream; the context stays usable.  Flag values
+ * should increase from step to step (a step counter), so flags never need resetting.  No reference counterpart: the
+ * reference has no multi-device path (crates/inference-runtime-core/src/network/mod.rs is empty). */
+PSI_API int32_t psi_gqa_signal(psi_gqa* gqa, uint32_t* flag, uint32_t value);
+PSI_API int32_t psi_gqa_combine_wait(psi_gqa* gqa, const float* const* o, const float* const* m, const float* const* l,
+                                     uint32_t n, uint32_t num_tokens, void* out, const uint32_t* flags,
+                                     uint32_t flag_value, uint32_t max_polls);
+PSI_API int32_t psi_gqa_device_status(psi_gqa* gqa, int32_t* out);
+
 /* One whole decode step through host memory: copies k, v [T][Hkv][D] and q [T][Hq][D] host->device, runs append then
  * attend, copies out [T][Hq][D] device->host and waits.  T is the prepared num_tokens. */
 PSI_API int32_t psi_gqa_decode_step_host(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,

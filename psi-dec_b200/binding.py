@@ -414,6 +414,25 @@ class GQA:
         _check(library().psi_gqa_combine(self._h, po, pm, pl, C.c_uint32(n), C.c_uint32(num_tokens), _ptr(out)),
                self.ctx._h)
 
+    def signal(self, flag, value: int):
+        """Release-store ``value`` to the u32 at device address ``flag`` after all earlier work of the stream."""
+        _check(library().psi_gqa_signal(self._h, _ptr(flag), C.c_uint32(value)), self.ctx._h)
+
+    def combine_wait(self, o_list, m_list, l_list, num_tokens, out, flags, flag_value: int, max_polls: int = 0):
+        """``combine`` preceded by a bounded device-side wait until each of the n flags reached ``flag_value``."""
+        n = len(o_list)
+        po = (C.c_void_p * n)(*[_ptr(x).value for x in o_list])
+        pm = (C.c_void_p * n)(*[_ptr(x).value for x in m_list])
+        pl = (C.c_void_p * n)(*[_ptr(x).value for x in l_list])
+        _check(library().psi_gqa_combine_wait(self._h, po, pm, pl, C.c_uint32(n), C.c_uint32(num_tokens), _ptr(out),
+                                              _ptr(flags), C.c_uint32(flag_value), C.c_uint32(max_polls)), self.ctx._h)
+
+    def device_status(self) -> int:
+        """Waits for the stream; returns 0, or the status a bounded device-side wait recorded (4 = timeout)."""
+        out = C.c_int32()
+        _check(library().psi_gqa_device_status(self._h, C.byref(out)), self.ctx._h)
+        return out.value
+
     def decode_step_host(self, pages, table, layer, k_host, v_host, q_host, out_host):
         _check(library().psi_gqa_decode_step_host(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(k_host),
                                                   _ptr(v_host), _ptr(q_host), _ptr(out_host)), self.ctx._h)

@@ -164,6 +164,7 @@ struct psi_gqa {
     uint64_t partial_slots_cap = 0;
     DeviceBuffer step_k, step_v, step_q, step_out;  // psi_gqa_decode_step_host staging
     DeviceBuffer combine_ptrs;
+    DeviceBuffer status_word;  // u32 written by bounded device-side waits
 };
 
 namespace {
@@ -876,6 +877,7 @@ int32_t psi_gqa_destroy(psi_gqa* g) {
         g->step_q.release();
         g->step_out.release();
         g->combine_ptrs.release();
+        g->status_word.release();
         if (g->staging != nullptr) (void)cudaFreeHost(g->staging);
         if (g->upload_done != nullptr) (void)cudaEventDestroy(g->upload_done);
     });
@@ -1122,8 +1124,9 @@ int32_t psi_gqa_attend_partial(psi_gqa* g, psi_pages* pages, psi_table* table, u
     });
 }
 
-int32_t psi_gqa_combine(psi_gqa* g, const float* const* o, const float* const* m, const float* const* l, uint32_t n,
-                        uint32_t num_tokens, void* out) {
+static int32_t combine_impl(psi_gqa* g, const float* const* o, const float* const* m, const float* const* l, uint32_t n,
+                            uint32_t num_tokens, void* out, const uint32_t* flags, uint32_t flag_value,
+                            uint32_t max_polls) {
     if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
     return guarded(g->ctx, [&] {
         require(o != nullptr && m != nullptr && l != nullptr && out != nullptr, "combine arguments must not be null");
@@ -1153,8 +1156,51 @@ int32_t psi_gqa_combine(psi_gqa* g, const float* const* o, const float* const* m
         p.head_dim = g->cfg.head_dim;
         p.dtype = g->cfg.dtype;
         p.out = out;
+        if (flags != nullptr) {
+            g->status_word.ensure(ctx, sizeof(uint32_t), true);
+            p.flags = flags;
+            p.flag_value = flag_value;
+            p.max_polls = max_polls == 0 ? 2000000u : max_polls;  // ~100 ns per poll: a fraction of a second by default
+            p.status = static_cast<uint32_t*>(g->status_word.ptr);
+        }
         LaunchScope scope(ctx, PSI_KERNEL_CLASS_COMBINE);
         cuda_check(launch_combine(p, ctx->stream), "combine launch");
+    });
+}
+
+int32_t psi_gqa_combine(psi_gqa* g, const float* const* o, const float* const* m, const float* const* l, uint32_t n,
+                        uint32_t num_tokens, void* out) {
+    return combine_impl(g, o, m, l, n, num_tokens, out, nullptr, 0, 0);
+}
+
+int32_t psi_gqa_combine_wait(psi_gqa* g, const float* const* o, const float* const* m, const float* const* l,
+                             uint32_t n, uint32_t num_tokens, void* out, const uint32_t* flags, uint32_t flag_value,
+                             uint32_t max_polls) {
+    if (flags == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return combine_impl(g, o, m, l, n, num_tokens, out, flags, flag_value, max_polls);
+}
+
+int32_t psi_gqa_signal(psi_gqa* g, uint32_t* flag, uint32_t value) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(flag != nullptr, "flag must not be null");
+        g->ctx->bind();
+        g->ctx->launches += 1;
+        cuda_check(launch_signal(flag, value, g->ctx->stream), "signal launch");
+    });
+}
+
+int32_t psi_gqa_device_status(psi_gqa* g, int32_t* out) {
+    if (g == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        g->ctx->bind();
+        cuda_check(cudaStreamSynchronize(g->ctx->stream), "cudaStreamSynchronize");
+        uint32_t word = 0;
+        if (g->status_word.ptr != nullptr) {
+            cuda_check(cudaMemcpy(&word, g->status_word.ptr, sizeof(word), cudaMemcpyDeviceToHost), "cudaMemcpy");
+            if (word != 0) cuda_check(cudaMemset(g->status_word.ptr, 0, sizeof(word)), "cudaMemset");
+        }
+        *out = static_cast<int32_t>(word);
     });
 }
 

@@ -159,24 +159,57 @@ __global__ void __launch_bounds__(kReduceThreads) attend_reduce_kernel(AttendPar
 
 // Cross-device merge of per-device partials in the natural-log domain (same algebra as above).
 __global__ void __launch_bounds__(kReduceThreads) combine_kernel(CombineParams p) {
+    if (p.flags != nullptr) {
+        // Partials arrive from other devices: wait, with a bound, until every producer has published this step.
+        __shared__ uint32_t ready_s;
+        if (threadIdx.x == 0) {
+            uint32_t ready = 1;
+            for (uint32_t i = 0; i < p.n && ready; ++i) {
+                uint32_t polls = 0, seen = 0;
+                for (;;) {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.flags + i) : "memory");
+                    if (static_cast<int32_t>(seen - p.flag_value) >= 0) break;
+                    if (++polls >= p.max_polls) {
+                        ready = 0;
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+            if (!ready) atomicExch(p.status, static_cast<uint32_t>(PSI_ERR_TIMEOUT));
+            ready_s = ready;
+        }
+        __syncthreads();
+        if (!ready_s) return;
+    }
     const uint64_t total = static_cast<uint64_t>(p.num_rows) * p.head_dim;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kReduceThreads + threadIdx.x; i < total;
          i += static_cast<uint64_t>(gridDim.x) * kReduceThreads) {
         const uint64_t row = i / p.head_dim;
         float global_max = -INFINITY;
-        for (uint32_t s = 0; s < p.n; ++s) global_max = fmaxf(global_max, p.m[s][row]);
+        for (uint32_t s = 0; s < p.n; ++s) global_max = fmaxf(global_max, __ldcg(p.m[s] + row));
         float sum = 0.0f, acc = 0.0f;
         for (uint32_t s = 0; s < p.n; ++s) {
-            const float pm = p.m[s][row];
-            const float w = isfinite(pm) ? expf(pm - global_max) * p.l[s][row] : 0.0f;
+            const float pm = __ldcg(p.m[s] + row);
+            const float w = isfinite(pm) ? expf(pm - global_max) * __ldcg(p.l[s] + row) : 0.0f;
             sum += w;
-            acc += w * p.o[s][i];
+            acc += w * __ldcg(p.o[s] + i);
         }
         store_from_float(p.out, i, p.dtype, sum > 0.0f ? acc / sum : 0.0f);
     }
 }
 
+__global__ void signal_kernel(uint32_t* flag, uint32_t value) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+
 }  // namespace
+
+cudaError_t launch_signal(uint32_t* flag, uint32_t value, cudaStream_t stream) {
+    signal_kernel<<<1, 1, 0, stream>>>(flag, value);
+    return cudaGetLastError();
+}
 
 uint32_t attend_generic_ctas_per_sm() { return 8; }
 

@@ -75,6 +75,10 @@ struct CombineParams {
     const float* const* o;        // device array of n pointers
     const float* const* m;
     const float* const* l;
+    const uint32_t* flags;        // nullptr, or n arrival flags in this device's memory: wait until each >= flag_value
+    uint32_t flag_value;
+    uint32_t max_polls;           // bound of the wait; on expiry *status = PSI_ERR_TIMEOUT and nothing is written
+    uint32_t* status;
     uint32_t n;
     uint32_t num_rows;            // num_tokens * Hq
     uint32_t head_dim;
@@ -94,5 +98,7 @@ cudaError_t launch_attend_generic(const AttendParams& p, uint32_t num_ctas, cuda
 cudaError_t launch_attend_mma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
 cudaError_t launch_attend_reduce(const AttendParams& p, uint32_t num_reduces, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
+// Release-stores `value` to *flag (local or peer memory) once all earlier work of the stream is visible system-wide.
+cudaError_t launch_signal(uint32_t* flag, uint32_t value, cudaStream_t stream);
 
 }  // namespace psi

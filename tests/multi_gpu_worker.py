@@ -1,0 +1,88 @@
+"""Worker of the multi-GPU tests: run under torch.distributed.run with one process per GPU.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29533 \
+        tests/multi_gpu_worker.py kv_range p2p
+
+Modes: ``kv_range p2p|nccl`` (configuration 4 scaled down, KV range split across the ranks, partial exchange, merged
+output checked against the CPU oracle's merge of per-rank oracle partials) and ``sequence`` (configuration 3 scaled
+down, sequence-sharded, every rank checked against the oracle on its own shard).
+"""
+import os
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+import __graft_entry__ as entry
+
+entry.load_package()
+import checks
+from oracle import psi_oracle as O
+from psi_dec_b200 import workloads as W
+from psi_dec_b200.distributed import KvRangeExchange
+
+
+def main():
+    kind = sys.argv[1]
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if kind == "sequence":
+        spec = W.config(3, scale_down=8).shard(rank, world)
+        s = W.Session(spec, device=local)
+        s.step()
+        s.ctx.sync()
+        checks.assert_attention_close(s)
+        s.close()
+    else:
+        mode = sys.argv[2]
+        whole = W.config(4, scale_down=32)
+        spec = whole.kv_range_shard(rank, world)
+        s = W.Session(spec, device=local)
+        # every rank uses the same queries
+        gen = torch.Generator(device=s.device)
+        gen.manual_seed(1234)
+        s.q.copy_(torch.randn(s.q.shape, generator=gen, device=s.device, dtype=torch.float32))
+        ex = KvRangeExchange(s, rank, world, mode=mode)
+        for _ in range(3):          # several steps: flags must work as a step counter
+            ex.step()
+        s.ctx.sync()
+        assert s.gqa.device_status() == 0
+        # per-rank oracle partial on the rank's own arena, gathered on the host
+        prob = checks.host_problem(s)
+        q = checks.to_numpy_bits(s.q)[prob["tok_rows"]]
+        eo, em, es = O.paged_attention(prob["arena"], spec.dtype, q, prob["req_slots"], prob["positions"],
+                                       prob["table"], 0, prob["layout"], spec.num_q_heads, spec.num_kv_heads,
+                                       spec.head_dim, spec.page_bytes, spec.scale, want_stats=True)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (eo, em, es))
+        dist.barrier()
+        if rank == ex.owner or mode == "nccl":
+            t, hq, d = spec.num_tokens, spec.num_q_heads, spec.head_dim
+            expected = np.zeros((t, hq, d), dtype=np.float32)
+            for i in range(t):
+                for h in range(hq):
+                    expected[i, h] = O.merge_partials(np.stack([g[0][i, h] for g in gathered]),
+                                                      [g[1][i, h] for g in gathered], [g[2][i, h] for g in gathered])
+            got = O.decode(checks.to_numpy_bits(s.out), spec.dtype)
+            diff = np.abs(got - expected)
+            assert diff.max() <= 2e-2 and diff.mean() <= 2e-3, (diff.max(), diff.mean())
+            for r, (po, pm, pl) in enumerate(ex.partials_on_owner()):
+                assert np.abs(po - gathered[r][0]).max() <= 2e-2
+                assert np.abs(pm - gathered[r][1]).max() <= 2e-3
+        dist.barrier()
+        s.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        print(f"multi-gpu worker ok: {' '.join(sys.argv[1:])} world={world}")
+
+
+if __name__ == "__main__":
+    main()

@@ -587,3 +587,42 @@ def test_host_side_contracts_on_the_component():
     for obj in (g, table, arena):
         obj.close()
     ctx.close()
+
+
+def test_flag_exchange_on_one_device_and_bounded_wait_timeout():
+    # Two emulated ranks on one GPU: partials land in "receive" slots, each followed by a flag; the merge waits on
+    # the flags (already set: same stream).  Then a flag that nothing sets: the bounded wait gives up, reports a
+    # timeout, writes nothing, and the context keeps working.
+    import torch
+    spec = W.config(4, scale_down=64)
+    t, hq, d = spec.num_tokens, spec.num_q_heads, spec.head_dim
+    shards = [W.Session(spec.kv_range_shard(r, 2)) for r in range(2)]
+    owner = shards[1]
+    recv_o = [torch.zeros((t, hq, d), dtype=torch.float32, device="cuda:0") for _ in range(2)]
+    recv_m = [torch.zeros((t, hq), dtype=torch.float32, device="cuda:0") for _ in range(2)]
+    recv_l = [torch.zeros((t, hq), dtype=torch.float32, device="cuda:0") for _ in range(2)]
+    flags = torch.zeros(4, dtype=torch.int32, device="cuda:0")
+    expect = torch.zeros_like(owner.q)
+    for step in (1, 2):
+        for r, sh in enumerate(shards):
+            sh.q.copy_(owner.q)
+            if sh.spec.do_append:
+                sh.append()
+            sh.gqa.attend_partial(sh.pages, sh.table, 0, sh.q, recv_o[r], recv_m[r], recv_l[r])
+            sh.gqa.signal(flags.data_ptr() + 4 * r, step)
+        out = torch.zeros_like(owner.q)
+        owner.gqa.combine_wait(recv_o, recv_m, recv_l, t, out, flags, step)
+        owner.gqa.combine(recv_o, recv_m, recv_l, t, expect)
+        assert owner.gqa.device_status() == 0
+        assert torch.equal(out.view(torch.int16), expect.view(torch.int16))
+        assert flags[:2].tolist() == [step, step]
+    canary = torch.full_like(owner.q, 7.0)
+    owner.gqa.combine_wait(recv_o, recv_m, recv_l, t, canary, flags, 3, max_polls=2000)   # nobody publishes step 3
+    assert owner.gqa.device_status() == 4                                               # PSI_ERR_TIMEOUT
+    assert bool((canary == 7.0).all())
+    assert owner.gqa.device_status() == 0                                               # cleared; still usable
+    owner.gqa.combine_wait(recv_o, recv_m, recv_l, t, canary, flags, 2)
+    assert owner.gqa.device_status() == 0
+    assert torch.equal(canary.view(torch.int16), expect.view(torch.int16))
+    for sh in shards:
+        sh.close()
