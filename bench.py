@@ -89,12 +89,14 @@ class ClockSampler:
 
 
 def bench_ours(args):
+    import numpy as np
     import torch
     import torch.distributed as dist
 
     import __graft_entry__ as entry
     pkg = entry.load_package()
     from psi_dec_b200 import workloads as W
+    from psi_dec_b200.distributed import KvRangeExchange
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -105,18 +107,32 @@ def bench_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    # Global batch = N x the single-GPU configuration, sequence-sharded (weak scaling, no collective in the step).
+    # How the job is spread over N GPUs.  The headline configuration (2) grows with N: the global batch is N x 32
+    # sequences, sequence-sharded, no collective in the step (weak scaling).  Configurations 3 and 5 shard their fixed
+    # batch by sequence, configuration 4 splits every sequence's KV range across the ranks and exchanges partials
+    # (strong scaling).
     base = W.config(args.config)
-    if world > 1:
-        import numpy as np
+    exchange = None
+    scaling, parallelism = "weak", f"sequence-sharded x{world}"
+    if world == 1:
+        spec = base
+    elif args.config == 4:
+        spec = base.kv_range_shard(rank, world)
+        scaling, parallelism = "strong", f"kv-range-split x{world} ({args.exchange} partial exchange)"
+    elif args.config in (3, 5):
+        spec = base.shard(rank, world)
+        scaling = "strong"
+    else:
         specs = [W.config(args.config, seed=base.seed + 100 * r) for r in range(world)]
         whole = W.Spec(base.name, base.dtype, base.num_q_heads, base.num_kv_heads, base.head_dim,
                        base.tokens_per_page, np.concatenate([s.context_lens for s in specs]),
                        np.concatenate([s.q_len for s in specs]), base.seed)
         spec = whole.shard(rank, world)
-    else:
-        spec = base
-    session = W.Session(spec, device=local_rank)
+    kernel_mode = {"auto": pkg.KERNEL_AUTO, "mma": pkg.KERNEL_MMA, "generic": pkg.KERNEL_GENERIC}[args.kernel]
+    session = W.Session(spec, device=local_rank, kernel_mode=kernel_mode)
+    if world > 1 and args.config == 4:
+        exchange = KvRangeExchange(session, rank, world, mode=args.exchange)
+    step = exchange.step if exchange else session.step
     ctx = session.ctx
     alg = spec.algorithmic_bytes()
     # Larger than the 126 MB L2 and swept read-only between timed steps, so that the step's inputs are not resident
@@ -128,12 +144,15 @@ def bench_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, prepare_each=False):
-        """Per-step CUDA-event durations (ms) with an L2 flush between steps, outside the timed windows."""
+    def timed(fn, steps):
+        """Per-step CUDA-event durations (ms) on the launching stream, L2 sweep between steps outside the windows.
+        With an exchange in the step every rank enters each step together (barrier), as a serving loop would."""
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         for i in range(steps):
             flush.sum()
+            if exchange:
+                barrier()
             starts[i].record(session.stream)
             fn()
             ends[i].record(session.stream)
@@ -141,21 +160,22 @@ def bench_ours(args):
         return [s.elapsed_time(e) for s, e in zip(starts, ends)]
 
     for _ in range(max(args.warmup, 3)):
-        session.step()
+        step()
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches_before = ctx.launch_count
     barrier()
-    step_ms = timed(session.step, args.steps)
+    step_ms = timed(step, args.steps)
     barrier()
     launches = ctx.launch_count - launches_before
     # The dominant kernel on its own clock: the same steps again with the library's per-launch event pairs switched
     # on (kept out of the pass above, where the extra events would sit inside the step time).
     ctx.enable_kernel_timing(True)
-    timed(session.step, args.steps)
+    timed(step, args.steps)
     map_ms, map_n = ctx.kernel_timing(1)
     append_ms, append_n = ctx.kernel_timing(0)
     reduce_ms, reduce_n = ctx.kernel_timing(2)
+    combine_ms, combine_n = ctx.kernel_timing(3)
     ctx.enable_kernel_timing(False)
     barrier()
 
@@ -166,7 +186,17 @@ def bench_ours(args):
 
     def e2e_step():
         session.gqa.prepare(*batch)
-        session.gqa.decode_step_host(session.pages, session.table, spec.layer, kh, vh, qh, oh)
+        if exchange:
+            session.q.copy_(qh, non_blocking=True)
+            if spec.do_append:
+                session.k.copy_(kh, non_blocking=True)
+                session.v.copy_(vh, non_blocking=True)
+            exchange.step()
+            if rank == exchange.owner or args.exchange == "nccl":
+                oh.copy_(session.out, non_blocking=True)
+            session.stream.synchronize()
+        else:
+            session.gqa.decode_step_host(session.pages, session.table, spec.layer, kh, vh, qh, oh)
 
     for _ in range(3):
         e2e_step()
@@ -177,13 +207,17 @@ def bench_ours(args):
 
     total_ms = sum(step_ms)
     e2e_total_ms = sum(e2e_ms)
-    sums = torch.tensor([float(alg["total"]), float(spec.num_tokens), float(alg["kv"])], dtype=torch.float64,
-                        device=session.device)
+    h2d = kh.numel() * kh.element_size() * 2 * (1 if spec.do_append else 0) + qh.numel() * qh.element_size()
+    d2h = oh.numel() * oh.element_size() if (exchange is None or rank == exchange.owner) else 0
+    sums = torch.tensor([float(alg["total"]), float(spec.num_tokens), float(alg["kv"]), float(h2d), float(d2h)],
+                        dtype=torch.float64, device=session.device)
     worst = torch.tensor([total_ms, e2e_total_ms], dtype=torch.float64, device=session.device)
     if world > 1:
         dist.all_reduce(sums, op=dist.ReduceOp.SUM)
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-    job_bytes, job_tokens, job_kv = (float(x) for x in sums.tolist())
+    job_bytes, job_tokens, job_kv, job_h2d, job_d2h = (float(x) for x in sums.tolist())
+    if exchange:
+        job_tokens = float(base.num_tokens)  # every rank works on the same query tokens
     total_ms, e2e_total_ms = (float(x) for x in worst.tolist())
 
     if rank == 0:
@@ -196,29 +230,30 @@ def bench_ours(args):
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if spec.dtype == pkg.BF16 else "f16/f32",
+            "scaling": scaling, "vs_baseline": None, "dtype": "bf16" if spec.dtype == pkg.BF16 else "f16/f32",
             "data": "synthetic",
-            "config": {"workload": base.name, "sequences_per_gpu": base.num_seqs, "q_heads": spec.num_q_heads,
+            "config": {"workload": base.name, "sequences_rank0": spec.num_seqs, "q_heads": spec.num_q_heads,
                        "kv_heads": spec.num_kv_heads, "head_dim": spec.head_dim,
                        "tokens_per_page": spec.tokens_per_page, "visible_tokens_rank0": int(spec.visible.sum()),
-                       "seed": base.seed, "parallelism": f"sequence-sharded x{world}",
-                       "l2": "256 MB read-only sweep between timed steps", "kernel": "mma" if stats["kernel"] == 2 else "generic",
+                       "seed": base.seed, "parallelism": parallelism,
+                       "l2": "256 MB read-only sweep between timed steps",
+                       "kernel": "mma" if stats["kernel"] == 2 else "generic",
                        "ctas": stats["ctas"], "items": stats["items"], "reduce_units": stats["reduce_units"]},
             "tokens_per_s": round(job_tokens / (ms_per_step * 1e-3), 1),
             "kv_gbs": round(job_kv / (ms_per_step * 1e-3) / 1e9, 1),
             "frac_of_nominal_8tbs_per_gpu": round(value / world / NOMINAL_HBM_GBS, 4),
-            "roofline": {"bound": "hbm", "kernel": "attend_map", "achieved": round(achieved, 1), "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "attend_map (rank 0)", "achieved": round(achieved, 1), "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                          "traffic": None, "algorithmic_bytes_per_launch": alg["total"],
                          "avg_launch_ms": round(map_avg_ms, 5), "launches": map_n},
             "kernel_ms_per_step": {"append": round(append_ms / max(append_n, 1), 5),
                                    "attend_map": round(map_avg_ms, 5),
-                                   "attend_reduce": round(reduce_ms / max(reduce_n, 1), 5)},
+                                   "attend_reduce": round(reduce_ms / max(reduce_n, 1), 5),
+                                   "combine": round(combine_ms / max(combine_n, 1), 5)},
             "e2e": {"value": round(job_bytes / (e2e_total_ms / args.steps * 1e-3) / 1e9, 1), "unit": UNIT,
                     "ms_per_step": round(e2e_total_ms / args.steps, 5),
                     "tokens_per_s": round(job_tokens / (e2e_total_ms / args.steps * 1e-3), 1),
-                    "h2d_bytes_per_step": int(kh.numel() * kh.element_size() * 2 + qh.numel() * qh.element_size()),
-                    "d2h_bytes_per_step": int(oh.numel() * oh.element_size())},
+                    "h2d_bytes_per_step": int(job_h2d), "d2h_bytes_per_step": int(job_d2h)},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
@@ -231,6 +266,7 @@ def bench_ours(args):
             line["cpu_baseline"] = {"value": round(bytes_s / 1e9, 4), "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": desc, "tokens_per_s": round(tok_s, 2)}
         print(json.dumps(line), flush=True)
+    barrier()
     session.close()
     if world > 1:
         dist.barrier()
@@ -317,6 +353,10 @@ def main():
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--config", type=int, default=2, help="benchmark configuration (2 = the headline)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--kernel", choices=["auto", "mma", "generic"], default="auto",
+                        help="attention kernel: tensor-core mma (default where supported) or the CUDA-core kernel")
+    parser.add_argument("--exchange", choices=["p2p", "nccl"], default="p2p",
+                        help="partial exchange of the KV-range-split configuration 4")
     args = parser.parse_args()
     if args.impl == "reference":
         bench_reference(args)

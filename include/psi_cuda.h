@@ -262,7 +262,7 @@ PSI_API int32_t psi_gqa_metadata_write(psi_gqa* gqa, uint32_t which, uint64_t of
 
 /* Plan statistics of the last prepare: out[0]=CTAs launched by the map kernel, out[1]=work items, out[2]=partial
  * slots, out[3]=reduce units, out[4]=exec q tiles, out[5]=kernel (1 generic, 2 mma), out[6]=total 16-token KV tiles,
- * out[7]=rows per q tile. */
+ * out[7]=rows per q tile, out[8]=CTAs of the long-query (chunk) kernel, out[9]=its work items. */
 PSI_API int32_t psi_gqa_plan_stats(psi_gqa* gqa, uint32_t* out, uint32_t n);
 
 /* KV append: GQAKVPageWrite::invoke_bucketed (crates/inference-backend-metal/src/components/gqa_kv_page_write.rs:
@@ -368,7 +368,8 @@ typedef enum psi_kernel_class {
     PSI_KERNEL_CLASS_ATTEND_MAP = 1,
     PSI_KERNEL_CLASS_ATTEND_REDUCE = 2,
     PSI_KERNEL_CLASS_COMBINE = 3,
-    PSI_KERNEL_CLASS_GATHER = 4
+    PSI_KERNEL_CLASS_GATHER = 4,
+    PSI_KERNEL_CLASS_ATTEND_CHUNK = 5
 } psi_kernel_class;
 PSI_API int32_t psi_ctx_enable_kernel_timing(psi_ctx* ctx, int32_t enable);
 PSI_API int32_t psi_ctx_kernel_timing(psi_ctx* ctx, uint32_t kernel_class, float* out_total_ms, uint64_t* out_launches);

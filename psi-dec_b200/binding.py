@@ -384,9 +384,10 @@ class GQA:
                self.ctx._h)
 
     def plan_stats(self) -> dict:
-        out = (C.c_uint32 * 8)()
-        _check(library().psi_gqa_plan_stats(self._h, out, C.c_uint32(8)), self.ctx._h)
-        keys = ("ctas", "items", "partial_slots", "reduce_units", "q_tiles", "kernel", "kv_tiles", "rows_per_tile")
+        out = (C.c_uint32 * 10)()
+        _check(library().psi_gqa_plan_stats(self._h, out, C.c_uint32(10)), self.ctx._h)
+        keys = ("ctas", "items", "partial_slots", "reduce_units", "q_tiles", "kernel", "kv_tiles", "rows_per_tile",
+                "chunk_ctas", "chunk_items")
         return dict(zip(keys, out))
 
     def kv_page_write(self, pages: PageArena, table: GQARequestPageTable, layer: int, k, v):

@@ -34,7 +34,7 @@ uint64_t pad_words(uint64_t n) { return (n + kWordAlign - 1) / kWordAlign * kWor
 
 }  // namespace
 
-constexpr uint32_t kKernelClasses = 5;
+constexpr uint32_t kKernelClasses = 6;
 
 struct psi_ctx {
     int device = 0;
@@ -150,6 +150,8 @@ struct psi_gqa {
     psi_replay_shape shape{};
     psi_split_kv_variant variant{};
     WorkPlan plan;
+    ChunkPlan chunk;            // long query runs (balanced plan + mma kernel only)
+    bool chunk_supported = false;
     bool prepared = false;
 
     DeviceBuffer block;       // device metadata block
@@ -158,6 +160,7 @@ struct psi_gqa {
     cudaEvent_t upload_done = nullptr;
     // section offsets (in words) of the block uploaded by the last prepare
     uint64_t off_req_slots = 0, off_token_indices = 0, off_cta = 0, off_reduces = 0, off_items = 0;
+    uint64_t off_chunk_cta = 0, off_chunk_items = 0;
 
     DeviceBuffer partial_o, partial_ml;  // [slots][16][D] and [2][slots][16]
     DeviceBuffer unit_counters;          // [slots] u32, zero between launches
@@ -262,6 +265,7 @@ AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* 
     p.unit_counters = static_cast<uint32_t*>(g->unit_counters.ptr);
     p.scalars = block_words(g, 0);
     p.num_q_heads = g->cfg.num_q_heads;
+    p.tokens_per_tile = g->geo.tokens_per_tile;
     p.dtype = g->cfg.dtype;
     p.scale_log2 = g->cfg.scale * 1.4426950408889634f;
     return p;
@@ -277,6 +281,13 @@ void run_attend(psi_gqa* g, const AttendParams& p) {
         } else {
             cuda_check(launch_attend_generic(p, num_ctas, ctx->stream), "attend (generic) launch");
         }
+    }
+    if (g->chunk.num_ctas() > 0) {
+        AttendParams c = p;
+        c.items = reinterpret_cast<const DeviceItem*>(block_words(g, g->off_chunk_items));
+        c.cta_item_begin = block_words(g, g->off_chunk_cta);
+        LaunchScope scope(ctx, PSI_KERNEL_CLASS_ATTEND_CHUNK);
+        cuda_check(launch_attend_chunk(c, g->chunk.num_ctas(), ctx->stream), "attend (chunk) launch");
     }
     // The mma kernel merges a unit's partials in the CTA that delivers the last one; the generic kernel needs the
     // separate reduce pass.
@@ -853,6 +864,8 @@ int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out
         const uint32_t per_sm =
             g->kernel == PSI_KERNEL_MMA ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm();
         g->grid_cap = c.max_ctas > 0 ? c.max_ctas : static_cast<uint32_t>(ctx->sm_count) * per_sm;
+        g->chunk_supported = g->kernel == PSI_KERNEL_MMA && c.plan_mode == PSI_PLAN_BALANCED &&
+                             attend_chunk_supported(c.dtype, c.head_dim, g->tokens_per_page);
         if (c.dtype != PSI_DTYPE_F16) {
             g->selector = std::make_unique<SplitKvSelector>(c.dtype, c.page_bytes, c.num_q_heads, c.num_kv_heads,
                                                             c.head_dim, false);
@@ -939,13 +952,28 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         if (g->cfg.plan_mode == PSI_PLAN_REFERENCE) {
             g->plan = build_reference_plan(g->geo, *g->md, shape, variant.tiled_q != 0, token_indices, cu_tokens,
                                            num_reqs);
+            g->chunk = ChunkPlan{};
         } else {
+            // Requests with a long run of query tokens go to the chunk kernel (one pass over their KV for eight query
+            // tiles at a time); the rest are decode rows.
+            constexpr uint32_t kChunkMinTiles = 5;
+            std::vector<uint32_t> decode_reqs, chunk_reqs;
+            for (uint32_t r = 0; r < num_reqs; ++r) {
+                const uint32_t tiles = (cu_tokens[r + 1] - cu_tokens[r] + g->geo.tokens_per_tile - 1) / g->geo.tokens_per_tile;
+                if (tiles == 0) continue;
+                (g->chunk_supported && tiles >= kChunkMinTiles ? chunk_reqs : decode_reqs).push_back(r);
+            }
             const uint32_t min_tiles = g->kernel == PSI_KERNEL_MMA ? 16u : 4u;
-            g->plan = build_balanced_plan(g->geo, req_slots, token_indices, cu_tokens, num_reqs, g->grid_cap,
+            g->plan = build_balanced_plan(g->geo, req_slots, token_indices, cu_tokens, decode_reqs, g->grid_cap,
                                           min_tiles);
+            g->chunk = build_chunk_plan(g->geo, req_slots, token_indices, cu_tokens, chunk_reqs, g->grid_cap,
+                                        g->plan.num_partial_slots, static_cast<uint32_t>(g->plan.reduces.size()));
         }
         const WorkPlan& plan = g->plan;
+        const ChunkPlan& chunk = g->chunk;
         const std::vector<DeviceItem> device_items = flatten_plan(plan, g->geo);
+        const uint32_t total_slots = plan.num_partial_slots + chunk.num_partial_slots;
+        const uint32_t total_counters = static_cast<uint32_t>(plan.reduces.size()) + chunk.num_counters;
 
         // Pack the device block: scalars | req_slots | flat_token_indices | cta ranges | reduces | items.
         uint64_t cursor = pad_words(kScalarCount);
@@ -959,6 +987,10 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         cursor += pad_words(plan.reduces.size() * 2);
         g->off_items = cursor;
         cursor += pad_words(device_items.size() * (sizeof(DeviceItem) / sizeof(uint32_t)));
+        g->off_chunk_cta = cursor;
+        cursor += pad_words(chunk.cta_item_begin.size());
+        g->off_chunk_items = cursor;
+        cursor += pad_words(chunk.items.size() * (sizeof(DeviceItem) / sizeof(uint32_t)));
         const uint64_t words = cursor;
 
         if (g->staging_words < words) {
@@ -974,17 +1006,17 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
             cuda_check(cudaEventSynchronize(g->upload_done), "cudaEventSynchronize");  // previous upload left staging
         }
         g->block.ensure(ctx, g->staging_words * sizeof(uint32_t), false);
-        if (plan.num_partial_slots > g->partial_slots_cap) {
-            const uint64_t slots = std::max<uint64_t>(plan.num_partial_slots, 2ull * g->grid_cap);
+        if (total_slots > g->partial_slots_cap) {
+            const uint64_t slots = std::max<uint64_t>(total_slots, 2ull * g->grid_cap);
             g->partial_o.ensure(ctx, slots * kMaxRows * g->cfg.head_dim * sizeof(float), false);
             g->partial_ml.ensure(ctx, 2 * slots * kMaxRows * sizeof(float), false);
             g->unit_counters.ensure(ctx, slots * sizeof(uint32_t), true);
             g->partial_slots_cap = slots;
         }
-        if (g->kernel == PSI_KERNEL_MMA && !plan.reduces.empty()) {
+        if (g->kernel == PSI_KERNEL_MMA && total_counters > 0) {
             // Arrival counters return to zero by themselves; clearing them here keeps one aborted launch from
             // poisoning the next step.
-            cuda_check(cudaMemsetAsync(g->unit_counters.ptr, 0, plan.reduces.size() * sizeof(uint32_t), ctx->stream),
+            cuda_check(cudaMemsetAsync(g->unit_counters.ptr, 0, total_counters * sizeof(uint32_t), ctx->stream),
                        "cudaMemsetAsync");
         }
 
@@ -993,6 +1025,7 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         s[kScalarNumActiveTokens] = num_tokens;
         s[kScalarNumCtas] = plan.num_ctas();
         s[kScalarNumReduces] = static_cast<uint32_t>(plan.reduces.size());
+        s[kScalarNumChunkCtas] = chunk.num_ctas();
         std::copy(g->md->req_slots.begin(), g->md->req_slots.begin() + num_tokens, s + g->off_req_slots);
         std::copy(g->md->flat_token_indices.begin(), g->md->flat_token_indices.begin() + num_tokens,
                   s + g->off_token_indices);
@@ -1001,6 +1034,9 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
             std::memcpy(s + g->off_reduces, plan.reduces.data(), plan.reduces.size() * sizeof(ReduceUnit));
         if (!device_items.empty())
             std::memcpy(s + g->off_items, device_items.data(), device_items.size() * sizeof(DeviceItem));
+        std::copy(chunk.cta_item_begin.begin(), chunk.cta_item_begin.end(), s + g->off_chunk_cta);
+        if (!chunk.items.empty())
+            std::memcpy(s + g->off_chunk_items, chunk.items.data(), chunk.items.size() * sizeof(DeviceItem));
         cuda_check(cudaMemcpyAsync(g->block.ptr, s, words * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream),
                    "cudaMemcpyAsync");
         cuda_check(cudaEventRecord(g->upload_done, ctx->stream), "cudaEventRecord");
@@ -1055,15 +1091,17 @@ int32_t psi_gqa_plan_stats(psi_gqa* g, uint32_t* out, uint32_t n) {
     if (g == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
     return guarded(g->ctx, [&] {
         require(g->prepared, "GQA batch metadata must be updated before recording");
-        const uint32_t stats[8] = {g->plan.num_ctas(),
+        const uint32_t stats[10] = {g->plan.num_ctas(),
                                    static_cast<uint32_t>(g->plan.items.size()),
                                    g->plan.num_partial_slots,
                                    static_cast<uint32_t>(g->plan.reduces.size()),
                                    static_cast<uint32_t>(g->plan.tiles.size()),
                                    g->kernel,
                                    static_cast<uint32_t>(std::min<uint64_t>(g->plan.total_kv_tiles, kU32Max)),
-                                   g->geo.tokens_per_tile * g->geo.heads_per_tile};
-        for (uint32_t i = 0; i < n && i < 8; ++i) out[i] = stats[i];
+                                   g->geo.tokens_per_tile * g->geo.heads_per_tile,
+                                   g->chunk.num_ctas(),
+                                   static_cast<uint32_t>(g->chunk.items.size())};
+        for (uint32_t i = 0; i < n && i < 10; ++i) out[i] = stats[i];
     });
 }
 

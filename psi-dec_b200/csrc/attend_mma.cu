@@ -17,86 +17,11 @@
 // The arithmetic this replaces: crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_map.metal
 // (decode rows) and metal/gqa_split_kv_tiled_q.metal:161-319 (several query tokens of one request with the in-kernel
 // causal limit).
-#include <cmath>
-
-#include "device_common.cuh"
+#include "mma_common.cuh"
 
 namespace psi {
 
 namespace {
-
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
-constexpr int kTile = 16;  // KV tokens per tile == query rows per item
-
-template <typename T>
-struct Mma;
-
-template <>
-struct Mma<__nv_bfloat16> {
-    __device__ static __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    }
-    __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-        return *reinterpret_cast<uint32_t*>(&v);
-    }
-    __device__ static __forceinline__ void store4(void* dst, float4 v) {
-        uint2 packed = make_uint2(pack(v.x, v.y), pack(v.z, v.w));
-        *reinterpret_cast<uint2*>(dst) = packed;
-    }
-};
-
-template <>
-struct Mma<__half> {
-    __device__ static __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    }
-    __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
-        __half2 v = __floats2half2_rn(lo, hi);
-        return *reinterpret_cast<uint32_t*>(&v);
-    }
-    __device__ static __forceinline__ void store4(void* dst, float4 v) {
-        uint2 packed = make_uint2(pack(v.x, v.y), pack(v.z, v.w));
-        *reinterpret_cast<uint2*>(dst) = packed;
-    }
-};
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-
-// 16-byte global->shared copy; src_bytes == 0 zero-fills the destination without reading the source.
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
-// Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold `row_bytes` bytes: the chunk index is
-// XOR-ed with the low row bits so that the eight rows one ldmatrix phase reads fall into distinct banks.
-__device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk, uint32_t row_bytes) {
-    return row * row_bytes + ((chunk ^ (row & 7u)) << 4);
-}
 
 template <int D, int NSLOT>
 struct SmemLayout {
@@ -143,14 +68,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     const uint64_t page_bytes = p.geo.page_elems * 2;
     const uint64_t v_region_bytes = v_region_offset(p.geo) * 2;
 
-    // ldmatrix lane roles (constant for the whole kernel), pre-folded into byte offsets
-    const uint32_t mat = lane >> 3, mat_row = lane & 7;
-    const uint32_t q_row = mat_row + 8 * (mat & 1);                 // A operand: rows x k-halves
-    const uint32_t k_row = mat_row + 8 * (mat >> 1);                // B operand of Q K^T
-    const uint32_t v_row = mat_row + 8 * (mat & 1);                 // B operand of P V (transposed)
-    const uint32_t q_lane = q_base + q_row * L::kRowBytes, q_x = ((mat >> 1) ^ (q_row & 7)) << 4;
-    const uint32_t k_lane = k_row * L::kRowBytes, k_x = ((mat & 1) ^ (k_row & 7)) << 4;
-    const uint32_t v_lane = v_row * L::kRowBytes, v_x = ((mat >> 1) ^ (v_row & 7)) << 4;
+    const FragmentLanes frag(lane, L::kRowBytes);
 
     // copy lane roles: this lane moves chunk copy_chunk of rows copy_row, copy_row + kRowsPerCopy, ...
     const uint32_t copy_row = lane / kChunks, copy_chunk = lane % kChunks;
@@ -218,10 +136,8 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             }
         };
 
-        float o[D / 8][4];
-#pragma unroll
-        for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
-        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+        RowState<D> st;
+        st.clear();
 
         // ids of the tile whose halves are issued next, and of the tile after it
         uint32_t cur_lo = 0, cur_hi = 0, next_lo = 0, next_hi = 0;
@@ -273,7 +189,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         uint32_t limit_min = v.kv_end;
         for (uint32_t r = 0; r < v.rows; ++r) limit_min = min(limit_min, limit_s[r]);
 
-        float s[2][4];
         uint32_t pa[4];
         for (uint32_t h = 0; h < my_halves; ++h) {
             cp_async_wait<NSLOT - 2>();
@@ -291,108 +206,35 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
 
             const uint32_t slot_base = ring_base + (h % NSLOT) * L::kTileBytes;
             if ((h & 1) == 0) {
-                // ---- S = Q K^T: two 8-token column tiles, even and odd k-steps in separate accumulators ----------------
                 const uint32_t token0 = (first_tile + warp + (h >> 1) * kWarps) * kTile;
-                float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-                for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
-#pragma unroll
-                for (int ks = 0; ks < kKSteps; ++ks) {
-                    uint32_t a[4], b[4];
-                    ldmatrix_x4(a, q_lane + (q_x ^ (32u * ks)));
-                    ldmatrix_x4(b, slot_base + k_lane + (k_x ^ (32u * ks)));
-                    if (ks & 1) {
-                        Mma<T>::run(s_odd[0], a, b[0], b[1]);
-                        Mma<T>::run(s_odd[1], a, b[2], b[3]);
-                    } else {
-                        Mma<T>::run(s[0], a, b[0], b[1]);
-                        Mma<T>::run(s[1], a, b[2], b[3]);
-                    }
-                }
-#pragma unroll
-                for (int n = 0; n < 2; ++n)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) s[n][e] = (s[n][e] + s_odd[n][e]) * p.scale_log2;
-
-                // ---- visibility: keys at or beyond a row's limit, or before the item's range, do not count ------------
-                if (token0 < v.kv_begin || token0 + kTile > limit_min) {
-#pragma unroll
-                    for (int n = 0; n < 2; ++n)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const uint32_t token = token0 + 8 * n + 2 * quad_col + (e & 1);
-                            const uint32_t limit = e < 2 ? limit0 : limit1;
-                            if (token >= limit || token < v.kv_begin) s[n][e] = -INFINITY;
-                        }
-                }
-
-                // ---- online softmax on the fragments ---------------------------------------------------------------
-                float max0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-                float max1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-                max0 = fmaxf(max0, __shfl_xor_sync(0xFFFFFFFFu, max0, 1));
-                max0 = fmaxf(max0, __shfl_xor_sync(0xFFFFFFFFu, max0, 2));
-                max1 = fmaxf(max1, __shfl_xor_sync(0xFFFFFFFFu, max1, 1));
-                max1 = fmaxf(max1, __shfl_xor_sync(0xFFFFFFFFu, max1, 2));
-                const float new0 = fmaxf(m0, max0), new1 = fmaxf(m1, max1);
-                const bool moved = new0 > m0 || new1 > m1;
-                if (__any_sync(0xFFFFFFFFu, moved)) {
-                    const float corr0 = new0 == -INFINITY ? 1.0f : exp2f(m0 - new0);
-                    const float corr1 = new1 == -INFINITY ? 1.0f : exp2f(m1 - new1);
-                    l0 *= corr0;
-                    l1 *= corr1;
-#pragma unroll
-                    for (int j = 0; j < D / 8; ++j) {
-                        o[j][0] *= corr0;
-                        o[j][1] *= corr0;
-                        o[j][2] *= corr1;
-                        o[j][3] *= corr1;
-                    }
-                    m0 = new0;
-                    m1 = new1;
-                }
-                const float base0 = m0 == -INFINITY ? 0.0f : m0, base1 = m1 == -INFINITY ? 0.0f : m1;
-                const float p00 = exp2f(s[0][0] - base0), p01 = exp2f(s[0][1] - base0);
-                const float p02 = exp2f(s[0][2] - base1), p03 = exp2f(s[0][3] - base1);
-                const float p10 = exp2f(s[1][0] - base0), p11 = exp2f(s[1][1] - base0);
-                const float p12 = exp2f(s[1][2] - base1), p13 = exp2f(s[1][3] - base1);
-                l0 += (p00 + p01) + (p10 + p11);
-                l1 += (p02 + p03) + (p12 + p13);
-                pa[0] = Mma<T>::pack(p00, p01);
-                pa[1] = Mma<T>::pack(p02, p03);
-                pa[2] = Mma<T>::pack(p10, p11);
-                pa[3] = Mma<T>::pack(p12, p13);
+                const bool masked = token0 < v.kv_begin || token0 + kTile > limit_min;
+                TileMath<T, D>::scores(frag, q_base, slot_base, p.scale_log2, masked, token0, limit0, limit1,
+                                       v.kv_begin, st, pa);
             } else {
-                // ---- O += P V ----------------------------------------------------------------------------------------------
-#pragma unroll
-                for (int j = 0; j < D / 16; ++j) {
-                    uint32_t b[4];
-                    ldmatrix_x4_trans(b, slot_base + v_lane + (v_x ^ (32u * j)));
-                    Mma<T>::run(o[2 * j], pa, b[0], b[1]);
-                    Mma<T>::run(o[2 * j + 1], pa, b[2], b[3]);
-                }
+                TileMath<T, D>::values(frag, slot_base, pa, st);
             }
         }
 
         // ---- merge the warps' partial results --------------------------------------------------------------------------
         cp_async_wait<0>();
         __syncthreads();  // every warp is done with its ring: the merge buffer may overwrite it
-        l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1);
-        l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
-        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1);
-        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+        st.l0 += __shfl_xor_sync(0xFFFFFFFFu, st.l0, 1);
+        st.l0 += __shfl_xor_sync(0xFFFFFFFFu, st.l0, 2);
+        st.l1 += __shfl_xor_sync(0xFFFFFFFFu, st.l1, 1);
+        st.l1 += __shfl_xor_sync(0xFFFFFFFFu, st.l1, 2);
         if (quad_col == 0) {
-            merge_m[warp][quad_row] = m0;
-            merge_m[warp][quad_row + 8] = m1;
-            merge_l[warp][quad_row] = l0;
-            merge_l[warp][quad_row + 8] = l1;
+            merge_m[warp][quad_row] = st.m0;
+            merge_m[warp][quad_row + 8] = st.m1;
+            merge_l[warp][quad_row] = st.l0;
+            merge_l[warp][quad_row + 8] = st.l1;
         }
         {
             float* mine = merge_o + warp * kTile * L::kMergeStride;
 #pragma unroll
             for (int j = 0; j < D / 8; ++j) {
                 const uint32_t col = 8 * j + 2 * quad_col;
-                *reinterpret_cast<float2*>(mine + quad_row * L::kMergeStride + col) = make_float2(o[j][0], o[j][1]);
-                *reinterpret_cast<float2*>(mine + (quad_row + 8) * L::kMergeStride + col) = make_float2(o[j][2], o[j][3]);
+                *reinterpret_cast<float2*>(mine + quad_row * L::kMergeStride + col) = make_float2(st.o[j][0], st.o[j][1]);
+                *reinterpret_cast<float2*>(mine + (quad_row + 8) * L::kMergeStride + col) = make_float2(st.o[j][2], st.o[j][3]);
             }
         }
         __syncthreads();

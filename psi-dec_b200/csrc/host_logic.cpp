@@ -281,9 +281,17 @@ void finish_plan(WorkPlan& plan) {
 WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
                              const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
                              uint32_t min_kv_tiles_per_cta) {
+    std::vector<uint32_t> all(num_reqs);
+    for (uint32_t r = 0; r < num_reqs; ++r) all[r] = r;
+    return build_balanced_plan(geo, req_slots, token_indices, cu_tokens, all, max_ctas, min_kv_tiles_per_cta);
+}
+
+WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
+                             const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,
+                             uint32_t min_kv_tiles_per_cta) {
     WorkPlan plan;
     std::vector<uint32_t> tile_ctx;
-    for (uint32_t r = 0; r < num_reqs; ++r) {
+    for (uint32_t r : requests) {
         for (uint32_t begin = cu_tokens[r]; begin < cu_tokens[r + 1];) {
             uint32_t end = std::min(cu_tokens[r + 1], begin + geo.tokens_per_tile);
             plan.tiles.push_back({begin, end, req_slots[r], token_indices[r] + (begin - cu_tokens[r]),
@@ -368,6 +376,81 @@ WorkPlan build_reference_plan(const PlanGeometry& geo, const ReferenceMetadata& 
     plan.cta_item_begin.resize(plan.items.size() + 1);
     for (size_t i = 0; i <= plan.items.size(); ++i) plan.cta_item_begin[i] = static_cast<uint32_t>(i);
     finish_plan(plan);
+    return plan;
+}
+
+ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
+                           const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,
+                           uint32_t slot_base, uint32_t counter_base) {
+    ChunkPlan plan;
+    struct SuperTile {
+        uint32_t req, flat_begin, flat_end, ctx_end;
+    };
+    std::vector<SuperTile> supers;
+    const uint32_t tokens_per_item = geo.tokens_per_tile * kChunkTilesPerItem;
+    for (uint32_t r : requests) {
+        for (uint32_t begin = cu_tokens[r]; begin < cu_tokens[r + 1];) {
+            const uint32_t end = std::min(cu_tokens[r + 1], begin + tokens_per_item);
+            supers.push_back({r, begin, end, token_indices[r] + (end - cu_tokens[r])});
+            begin = end;
+        }
+    }
+    const uint32_t heads = geo.num_kv_heads * geo.head_tiles;
+    uint64_t total = 0;
+    for (const auto& s : supers) total += div_ceil(s.ctx_end, kKvTile) * heads;
+    plan.total_kv_tiles = total;
+    if (total == 0) return plan;
+    const uint64_t num_ctas = std::min<uint64_t>(std::max(1u, max_ctas), std::max<uint64_t>(1, total / 4));
+    auto share_end = [&](uint64_t c) { return total * (c + 1) / num_ctas; };
+    uint64_t cursor = 0;
+    uint32_t cta = 0;
+    plan.cta_item_begin.assign(1, 0);
+    for (const auto& s : supers) {
+        const uint64_t unit_tiles = div_ceil(s.ctx_end, kKvTile);
+        for (uint32_t h = 0; h < heads; ++h) {
+            const size_t unit_first_item = plan.items.size();
+            uint64_t done = 0;
+            while (done < unit_tiles) {
+                while (cursor + done >= share_end(cta)) {
+                    ++cta;
+                    plan.cta_item_begin.push_back(static_cast<uint32_t>(plan.items.size()));
+                }
+                const uint64_t take = std::min(unit_tiles - done, share_end(cta) - (cursor + done));
+                const uint32_t head_tile = h % geo.head_tiles;
+                DeviceItem d{};
+                d.kv_begin = static_cast<uint32_t>(done * kKvTile);
+                d.kv_end = static_cast<uint32_t>(std::min<uint64_t>((done + take) * kKvTile, s.ctx_end));
+                d.partial_slot = kU32Max;
+                d.flat_begin = s.flat_begin;
+                d.num_tokens = s.flat_end - s.flat_begin;
+                d.req_slot = req_slots[s.req];
+                d.kv_head = h / geo.head_tiles;
+                d.head0 = d.kv_head * geo.group + head_tile * geo.heads_per_tile;
+                d.num_heads = std::min(geo.heads_per_tile, geo.group - head_tile * geo.heads_per_tile);
+                d.first_pos = token_indices[s.req] + (s.flat_begin - cu_tokens[s.req]);
+                d.new_begin = token_indices[s.req];
+                d.flat_req_begin = cu_tokens[s.req];
+                d.writes_kv = head_tile == 0 ? 1u : 0u;
+                plan.items.push_back(d);
+                done += take;
+            }
+            cursor += unit_tiles;
+            const uint32_t n = static_cast<uint32_t>(plan.items.size() - unit_first_item);
+            if (n > 1) {  // the unit is shared between CTAs: partial slots 8 apart, eight arrival counters
+                const uint32_t first_slot = slot_base + plan.num_partial_slots;
+                for (uint32_t k = 0; k < n; ++k) {
+                    DeviceItem& d = plan.items[unit_first_item + k];
+                    d.partial_slot = first_slot + k * kChunkTilesPerItem;
+                    d.reduce_unit = counter_base + plan.num_counters;
+                    d.unit_first_slot = first_slot;
+                    d.unit_num_items = n;
+                }
+                plan.num_partial_slots += n * kChunkTilesPerItem;
+                plan.num_counters += kChunkTilesPerItem;
+            }
+        }
+    }
+    while (plan.cta_item_begin.size() < num_ctas + 1) plan.cta_item_begin.push_back(static_cast<uint32_t>(plan.items.size()));
     return plan;
 }
 

@@ -147,12 +147,33 @@ struct WorkPlan {
 WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
                              const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
                              uint32_t min_kv_tiles_per_cta);
+// The same over a subset of the batch's requests (indices into the request arrays, ascending).
+WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
+                             const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,
+                             uint32_t min_kv_tiles_per_cta);
 
 // One CTA per (reference KV split, head_sel); reference q tiles wider than tokens_per_tile are cut into sub-tiles
 // that share the split boundaries.
 WorkPlan build_reference_plan(const PlanGeometry& geo, const ReferenceMetadata& md, const psi_replay_shape& shape,
                               bool tiled_q, const uint32_t* token_indices, const uint32_t* cu_tokens,
                               uint32_t num_reqs);
+
+// Plan of the long-query (chunk) kernel: items are super-tiles of up to eight consecutive query tiles of one request
+// and KV head; the warp w of a CTA owns tile w of the super-tile, its partial slot is `partial_slot + w` and its arrival
+// counter `reduce_unit + w`; the slots of one unit lie 8 apart (`unit_first_slot + ordinal * 8 + w`).
+struct ChunkPlan {
+    std::vector<DeviceItem> items;
+    std::vector<uint32_t> cta_item_begin;
+    uint32_t num_partial_slots = 0;   // slots used beyond slot_base
+    uint32_t num_counters = 0;        // counters used beyond counter_base
+    uint64_t total_kv_tiles = 0;
+    uint32_t num_ctas() const { return cta_item_begin.empty() ? 0u : static_cast<uint32_t>(cta_item_begin.size() - 1); }
+};
+constexpr uint32_t kChunkTilesPerItem = 8;  // one query tile per warp
+
+ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
+                           const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,
+                           uint32_t slot_base, uint32_t counter_base);
 
 // Device form of a finished plan.
 std::vector<DeviceItem> flatten_plan(const WorkPlan& plan, const PlanGeometry& geo);

@@ -14,6 +14,7 @@ enum ScalarSlot : uint32_t {
     kScalarNumActiveTokens = 0,
     kScalarNumCtas = 1,
     kScalarNumReduces = 2,
+    kScalarNumChunkCtas = 3,
     kScalarCount = 8
 };
 
@@ -67,6 +68,7 @@ struct AttendParams {
     uint32_t* unit_counters;      // [reduce units], zero between launches: arrivals of a unit's items (mma kernel)
     const uint32_t* scalars;
     uint32_t num_q_heads;
+    uint32_t tokens_per_tile;     // query tokens of one 16-row tile (plan geometry)
     uint32_t dtype;
     float scale_log2;             // scale * log2(e)
 };
@@ -96,6 +98,9 @@ uint32_t attend_mma_ctas_per_sm(uint32_t head_dim);
 uint32_t attend_generic_ctas_per_sm();
 cudaError_t launch_attend_generic(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
 cudaError_t launch_attend_mma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
+// Long query runs: one CTA = up to eight query tiles of one request sharing one pass over the KV range.
+bool attend_chunk_supported(uint32_t dtype, uint32_t head_dim, uint32_t tokens_per_page);
+cudaError_t launch_attend_chunk(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
 cudaError_t launch_attend_reduce(const AttendParams& p, uint32_t num_reduces, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
 // Release-stores `value` to *flag (local or peer memory) once all earlier work of the stream is visible system-wide.

@@ -1,0 +1,117 @@
+"""Continuous-batching churn on one GPU: page IDs come from the allocator, finished sequences free their pages, new
+sequences reuse them (contents are never cleared), and every step's attention is checked against the CPU oracle on a
+host-side shadow of each sequence's K/V that knows nothing about paging.
+
+Scaled-down version of the churn configuration: 24 live sequences, 16/2 heads, head_dim 128, 16-token pages, 30 % of
+the sequences append a 40-token chunk per step and the rest one token, 10 % finish per step.  The cache-ownership side
+follows crates/inference-runtime-core/src/memory/u32_id_allocator.rs (free IDs first) and
+crates/inference-executor-metal/src/attn/gqa/request_page_table.rs (reset on slot reuse)."""
+import numpy as np
+import pytest
+
+import checks
+import gpuharness as G
+from oracle import psi_oracle as O
+
+pkg = G.pkg
+pytestmark = pytest.mark.gpu
+
+
+def test_allocator_driven_page_reuse_over_many_steps():
+    import torch
+    rng = np.random.default_rng(5)
+    hq, hkv, d, p = 16, 2, 128, 16
+    slots, max_ctx, chunk, steps = 24, 640, 40, 14
+    blocks = -(-(max_ctx + chunk) // p)
+    pool = slots * blocks // 2                      # tight pool: reuse is the rule, not the exception
+    scale = 1.0 / np.sqrt(d)
+    rig = G.Rig(pkg.BF16, hq, hkv, d, p, float(scale), (slots, 1, blocks, 1), slots * chunk, num_pages=pool)
+    rig.arena.copy_(torch.randn(rig.arena.shape, device="cuda").to(torch.bfloat16))   # stale garbage everywhere
+    alloc = pkg.U32IDAllocator(pool)
+    shadow_k = [np.zeros((0, hkv, d), np.uint16) for _ in range(slots)]
+    shadow_v = [np.zeros((0, hkv, d), np.uint16) for _ in range(slots)]
+    pages = [[] for _ in range(slots)]
+    reused = 0
+    ever_freed = set()
+
+    def grow(slot, new_len):
+        nonlocal reused
+        while len(pages[slot]) * p < new_len:
+            pid = alloc.alloc_one()
+            reused += pid in ever_freed
+            rig.table.write_page_ids(slot, 0, len(pages[slot]), [pid])
+            pages[slot].append(pid)
+
+    def admit(slot):
+        """A new sequence arrives with a cached prompt: its K/V rows are appended in bulk, without attention."""
+        length = int(min(max_ctx - 200, 16 + rng.zipf(1.3)))
+        grow(slot, length)
+        k = rng.integers(0, 1 << 16, size=(length, hkv, d)).astype(np.uint16) & 0xBFFF | 0x3000  # finite bf16 values
+        v = rng.integers(0, 1 << 16, size=(length, hkv, d)).astype(np.uint16) & 0xBFFF | 0x3000
+        shadow_k[slot], shadow_v[slot] = k, v
+        for start in range(0, length, slots * chunk):
+            n = min(slots * chunk, length - start)
+            rig.gqa.prepare([slot], [start], [0, n])
+            kd = torch.from_numpy(k[start:start + n].view(np.int16)).cuda()
+            vd = torch.from_numpy(v[start:start + n].view(np.int16)).cuda()
+            rig.gqa.kv_page_write(rig.pages, rig.table, 0, kd, vd)
+            rig.ctx.sync()
+
+    for slot in range(slots):
+        admit(slot)
+
+    for step in range(steps):
+        # 10 % of the sequences finish: pages go back to the allocator, the slot's table rows are zeroed, a new
+        # sequence moves in
+        for slot in rng.choice(slots, size=max(1, slots // 10), replace=False):
+            slot = int(slot)
+            alloc.free_many(pages[slot])
+            ever_freed.update(pages[slot])
+            pages[slot] = []
+            rig.table.reset_req_slot(slot)
+            admit(slot)
+        q_len = np.where(rng.random(slots) < 0.3, chunk, 1)
+        active = [s for s in range(slots) if len(shadow_k[s]) + q_len[s] <= max_ctx + chunk]
+        token_indices = [len(shadow_k[s]) for s in active]
+        cu = np.concatenate([[0], np.cumsum(q_len[active])]).tolist()
+        t = cu[-1]
+        for s in active:
+            grow(s, len(shadow_k[s]) + int(q_len[s]))
+        kq = rng.standard_normal((t, hkv, d)).astype(np.float32)
+        vq = rng.standard_normal((t, hkv, d)).astype(np.float32)
+        qq = rng.standard_normal((t, hq, d)).astype(np.float32)
+        kd, vd, qd = G.to_device(kq, pkg.BF16), G.to_device(vq, pkg.BF16), G.to_device(qq, pkg.BF16)
+        out = torch.zeros_like(qd)
+        rig.gqa.prepare(active, token_indices, cu)
+        if step % 2 == 0:
+            rig.gqa.append_attend(rig.pages, rig.table, 0, kd, vd, qd, out)      # one launch
+        else:
+            rig.gqa.kv_page_write(rig.pages, rig.table, 0, kd, vd)               # the two-stage order
+            rig.gqa.attend(rig.pages, rig.table, 0, qd, out)
+        rig.ctx.sync()
+        kb, vb = G.bits_of(kd), G.bits_of(vd)
+        for i, s in enumerate(active):
+            shadow_k[s] = np.concatenate([shadow_k[s], kb[cu[i]:cu[i + 1]]])
+            shadow_v[s] = np.concatenate([shadow_v[s], vb[cu[i]:cu[i + 1]]])
+        # oracle on the shadows of a sample of sequences (always including a chunk when there is one)
+        sample = sorted(set([int(np.argmax(q_len[active]))] + rng.choice(len(active), size=4, replace=False).tolist()))
+        got = O.decode(G.bits_of(out), O.BF16)
+        for i in sample:
+            s = active[i]
+            n = cu[i + 1] - cu[i]
+            expected = O.projected_gqa_reference(hq, hkv, d, float(scale), [0, n], [token_indices[i]],
+                                                 O.decode(G.bits_of(qd)[cu[i]:cu[i + 1]], O.BF16),
+                                                 [O.decode(shadow_k[s], O.BF16)], [O.decode(shadow_v[s], O.BF16)])
+            diff = np.abs(got[cu[i]:cu[i + 1]].reshape(-1) - expected)
+            assert diff.max() <= 2e-2 and diff.mean() <= 2e-3, (step, s, diff.max(), diff.mean())
+        # gather returns exactly the shadow (bit-exact), across reused pages
+        s = active[sample[0]]
+        n = len(shadow_k[s])
+        kout = torch.zeros((n, hkv, d), dtype=torch.bfloat16, device="cuda")
+        vout = torch.zeros_like(kout)
+        rig.gqa.page_gather(rig.pages, rig.table, s, 0, 0, n, kout, vout)
+        rig.ctx.sync()
+        assert np.array_equal(G.bits_of(kout), shadow_k[s]) and np.array_equal(G.bits_of(vout), shadow_v[s])
+    assert reused > 50, "the trace must actually recycle page IDs"
+    assert alloc.used() == sum(len(x) for x in pages)
+    rig.close()

@@ -427,6 +427,30 @@ def test_fused_step_equals_append_then_attend(index, scale_down):
     b.close()
 
 
+@pytest.mark.parametrize("max_ctas", [1, 5, 148])
+@pytest.mark.parametrize("heads,head_dim,page", [((16, 2), 256, 16), ((24, 4), 128, 8), ((8, 8), 128, 32)])
+def test_long_query_runs_through_the_chunk_kernel(heads, head_dim, page, max_ctas):
+    # chunked prefill mixed with decode rows: requests with long query runs take the chunk kernel (one pass over the
+    # history for eight query tiles), units cut across CTAs leave partials that the last-arriving warp merges
+    hq, hkv = heads
+    spec = W.Spec("chunks", pkg.BF16, hq, hkv, head_dim, page, [700, 37, 0, 1500, 260], [96, 1, 40, 33, 2], seed=11)
+    s = W.Session(spec, max_ctas=max_ctas)
+    stats = s.gqa.plan_stats()
+    assert stats["chunk_ctas"] >= 1 and stats["chunk_items"] >= 1
+    before = checks.to_numpy_bits(s.arena)
+    s.step()
+    s.ctx.sync()
+    expected = checks.expected_arena_after_append(s, before)
+    assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), expected)
+    checks.assert_attention_close(s)
+    # the unfused order and the partial (o, m, l) outputs take the same kernels
+    fused = s.out.clone()
+    s.step_unfused()
+    s.ctx.sync()
+    assert float((s.out.float() - fused.float()).abs().max()) <= 1e-2
+    s.close()
+
+
 def test_config2_full_size_parity_and_idempotence():
     import torch
     s = W.Session(W.config(2))
