@@ -216,12 +216,14 @@ __global__ void __launch_bounds__(kThreads, 1) attend_chunk_kernel(AttendParams 
                 for (uint32_t i = lane; i < my_rows * (D / 4); i += 32) {
                     const uint32_t r = i / (D / 4), c4 = i % (D / 4);
                     float global_max = -INFINITY;
+#pragma unroll 4
                     for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
                         const uint64_t prow = static_cast<uint64_t>(v.unit_first_slot + s_i * kWarps + warp) * kMaxRows + r;
                         global_max = fmaxf(global_max, __ldcg(p.partial_m + prow));
                     }
                     float sum = 0.0f;
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
                     for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
                         const uint64_t prow = static_cast<uint64_t>(v.unit_first_slot + s_i * kWarps + warp) * kMaxRows + r;
                         const float pm = __ldcg(p.partial_m + prow);

@@ -293,25 +293,47 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             __syncthreads();
             if (arrival_s == v.unit_num_items - 1) {
                 __threadfence();
-                for (uint32_t i = tid; i < v.rows * (D / 4); i += kThreads) {
-                    const uint32_t r = i / (D / 4), c4 = i % (D / 4);
+                // All statistics of the unit first (one round trip for every thread), then the weights per row, then
+                // the weighted sum with several partial rows in flight per thread.
+                const uint32_t n = v.unit_num_items, rows = v.rows;
+                float* stat_m = merge_o;                 // [n][rows] max, overwritten by the weights
+                float* stat_l = merge_o + n * rows;      // [n][rows] sum
+                float* row_max = stat_l + n * rows;      // [rows]
+                float* row_sum = row_max + kTile;        // [rows]
+                for (uint32_t i = tid; i < n * rows; i += kThreads) {
+                    const uint64_t prow = static_cast<uint64_t>(v.unit_first_slot + i / rows) * kMaxRows + i % rows;
+                    stat_m[i] = __ldcg(p.partial_m + prow);
+                    stat_l[i] = __ldcg(p.partial_l + prow);
+                }
+                __syncthreads();
+                if (tid < rows) {
                     float global_max = -INFINITY;
-                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
-                        global_max = fmaxf(global_max, __ldcg(p.partial_m + static_cast<uint64_t>(v.unit_first_slot + s_i) * kMaxRows + r));
-                    }
+                    for (uint32_t s_i = 0; s_i < n; ++s_i) global_max = fmaxf(global_max, stat_m[s_i * rows + tid]);
                     float sum = 0.0f;
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
-                        const uint64_t prow = static_cast<uint64_t>(v.unit_first_slot + s_i) * kMaxRows + r;
-                        const float pm = __ldcg(p.partial_m + prow);
-                        const float weight = pm == -INFINITY ? 0.0f : exp2f(pm - global_max) * __ldcg(p.partial_l + prow);
-                        const float4 part = __ldcg(reinterpret_cast<const float4*>(p.partial_o + prow * D + 4 * c4));
+                    for (uint32_t s_i = 0; s_i < n; ++s_i) {
+                        const float pm = stat_m[s_i * rows + tid];
+                        const float weight = pm == -INFINITY ? 0.0f : exp2f(pm - global_max) * stat_l[s_i * rows + tid];
+                        stat_m[s_i * rows + tid] = weight;
                         sum += weight;
+                    }
+                    row_max[tid] = global_max;
+                    row_sum[tid] = sum;
+                }
+                __syncthreads();
+                for (uint32_t i = tid; i < rows * (D / 4); i += kThreads) {
+                    const uint32_t r = i / (D / 4), c4 = i % (D / 4);
+                    const float* src = p.partial_o + (static_cast<uint64_t>(v.unit_first_slot) * kMaxRows + r) * D + 4 * c4;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                    for (uint32_t s_i = 0; s_i < n; ++s_i) {
+                        const float4 part = __ldcg(reinterpret_cast<const float4*>(src + static_cast<uint64_t>(s_i) * kMaxRows * D));
+                        const float weight = stat_m[s_i * rows + r];
                         acc.x += weight * part.x;
                         acc.y += weight * part.y;
                         acc.z += weight * part.z;
                         acc.w += weight * part.w;
                     }
+                    const float sum = row_sum[r];
                     const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
                     acc.x *= inv;
                     acc.y *= inv;
@@ -321,7 +343,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                     if (p.ext_o != nullptr) {
                         *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc;
                         if (c4 == 0) {
-                            p.ext_m[row] = global_max * kLn2;
+                            p.ext_m[row] = row_max[r] * kLn2;
                             p.ext_l[row] = sum;
                         }
                     } else {
