@@ -212,11 +212,13 @@ PSI_API int32_t psi_metadata_update_host(uint32_t max_tokens, const uint32_t* re
 /* The balanced device work plan of a batch, computed on the host (what psi_gqa_prepare uploads in
  * PSI_PLAN_BALANCED).  out_items receives 6 u32 per item {q tile, head selection, kv_begin, kv_end, partial slot or
  * 0xFFFFFFFF, flat token begin of the tile}; out_cta_item_begin receives num_ctas+1 entries; out_counts receives
- * {items, ctas, partial slots, reduce units, q tiles, total 16-token KV tiles (saturated)}.  No reference counterpart:
+ * {items, ctas, partial slots, reduce units, q tiles, total 16-token KV tiles (saturated)}.  item_start_cost is the
+ * number of KV tiles one additional item is charged when the shares are balanced.  No reference counterpart:
  * the reference's planner is psi_metadata_update_host. */
 PSI_API int32_t psi_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint32_t* token_indices,
                                  const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
-                                 uint32_t min_kv_tiles_per_cta, uint32_t* out_items, uint64_t items_cap,
+                                 uint32_t min_kv_tiles_per_cta, uint32_t item_start_cost, uint32_t* out_items,
+                                 uint64_t items_cap,
                                  uint32_t* out_cta_item_begin, uint64_t cta_cap, uint32_t* out_counts);
 
 /* U32IDAllocator (crates/inference-runtime-core/src/memory/u32_id_allocator.rs:69-172): freed IDs first, in the order

@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <new>
@@ -143,6 +144,7 @@ struct psi_gqa {
     uint32_t tokens_per_page = 0;
     uint32_t kernel = PSI_KERNEL_GENERIC;  // resolved kernel
     uint32_t grid_cap = 1;
+    uint32_t item_start_cost = 0;  // KV tiles one item switch is worth when shares are balanced
     PlanGeometry geo{};
     std::unique_ptr<SplitKvSelector> selector;  // null when the profile is outside the reference selector's domain
     std::unique_ptr<ReferenceMetadata> md;
@@ -747,7 +749,7 @@ int32_t psi_metadata_update_host(uint32_t max_tokens, const uint32_t* req_slots,
 
 int32_t psi_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint32_t* token_indices,
                          const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas, uint32_t min_kv_tiles_per_cta,
-                         uint32_t* out_items, uint64_t items_cap, uint32_t* out_cta_item_begin, uint64_t cta_cap,
+                         uint32_t item_start_cost, uint32_t* out_items, uint64_t items_cap, uint32_t* out_cta_item_begin, uint64_t cta_cap,
                          uint32_t* out_counts) {
     return guarded(nullptr, [&] {
         require(token_indices && cu_tokens && out_counts, "plan inputs must not be null");
@@ -758,7 +760,7 @@ int32_t psi_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint
             require(cu_tokens[r] <= cu_tokens[r + 1], "GQA batch cu_tokens must be nondecreasing");
         const std::vector<uint32_t> slots(num_reqs, 0u);
         const WorkPlan plan = build_balanced_plan(plan_geometry(num_q_heads, num_kv_heads), slots.data(), token_indices,
-                                                  cu_tokens, num_reqs, max_ctas, min_kv_tiles_per_cta);
+                                                  cu_tokens, num_reqs, max_ctas, min_kv_tiles_per_cta, item_start_cost);
         out_counts[0] = static_cast<uint32_t>(plan.items.size());
         out_counts[1] = plan.num_ctas();
         out_counts[2] = plan.num_partial_slots;
@@ -864,6 +866,7 @@ int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out
         const uint32_t per_sm =
             g->kernel == PSI_KERNEL_MMA ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm();
         g->grid_cap = c.max_ctas > 0 ? c.max_ctas : static_cast<uint32_t>(ctx->sm_count) * per_sm;
+        g->item_start_cost = g->kernel == PSI_KERNEL_MMA ? 16u : 0u;
         g->chunk_supported = g->kernel == PSI_KERNEL_MMA && c.plan_mode == PSI_PLAN_BALANCED &&
                              attend_chunk_supported(c.dtype, c.head_dim, g->tokens_per_page);
         if (c.dtype != PSI_DTYPE_F16) {
@@ -965,7 +968,7 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
             }
             const uint32_t min_tiles = g->kernel == PSI_KERNEL_MMA ? 16u : 4u;
             g->plan = build_balanced_plan(g->geo, req_slots, token_indices, cu_tokens, decode_reqs, g->grid_cap,
-                                          min_tiles);
+                                          min_tiles, g->item_start_cost);
             g->chunk = build_chunk_plan(g->geo, req_slots, token_indices, cu_tokens, chunk_reqs, g->grid_cap,
                                         g->plan.num_partial_slots, static_cast<uint32_t>(g->plan.reduces.size()));
         }

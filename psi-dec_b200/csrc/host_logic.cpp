@@ -280,15 +280,16 @@ void finish_plan(WorkPlan& plan) {
 
 WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
                              const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
-                             uint32_t min_kv_tiles_per_cta) {
+                             uint32_t min_kv_tiles_per_cta, uint32_t item_start_cost) {
     std::vector<uint32_t> all(num_reqs);
     for (uint32_t r = 0; r < num_reqs; ++r) all[r] = r;
-    return build_balanced_plan(geo, req_slots, token_indices, cu_tokens, all, max_ctas, min_kv_tiles_per_cta);
+    return build_balanced_plan(geo, req_slots, token_indices, cu_tokens, all, max_ctas, min_kv_tiles_per_cta,
+                               item_start_cost);
 }
 
 WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
                              const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,
-                             uint32_t min_kv_tiles_per_cta) {
+                             uint32_t min_kv_tiles_per_cta, uint32_t item_start_cost) {
     WorkPlan plan;
     std::vector<uint32_t> tile_ctx;
     for (uint32_t r : requests) {
@@ -308,30 +309,39 @@ WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots,
 
     uint64_t wanted = std::max<uint64_t>(1, total / std::max(1u, min_kv_tiles_per_cta));
     const uint64_t num_ctas = std::min<uint64_t>(std::max(1u, max_ctas), wanted);
-    // Share c covers linear KV tiles [total*c/n, total*(c+1)/n): shares differ by at most one tile.
-    uint64_t cursor = 0;  // linear position of the current unit's first KV tile
+    // Every unit is laid out as `start_cost` virtual tiles (what opening a new item costs a CTA: pipeline drain,
+    // merge, first-load latency) followed by its KV tiles; share c covers positions [span*c/n, span*(c+1)/n) of that
+    // line, so CTAs that open several items get correspondingly fewer KV tiles.
+    const uint64_t start_cost = item_start_cost;
+    const uint64_t span = total + start_cost * plan.tiles.size() * heads;
+    uint64_t cursor = 0;  // position of the current unit's first (virtual) tile
     uint32_t cta = 0;
     plan.cta_item_begin.assign(1, 0);
-    auto share_end = [&](uint64_t c) { return total * (c + 1) / num_ctas; };
+    auto share_end = [&](uint64_t c) { return span * (c + 1) / num_ctas; };
     for (uint32_t tile = 0; tile < plan.tiles.size(); ++tile) {
         const uint64_t unit_tiles = div_ceil(tile_ctx[tile], kKvTile);
+        const uint64_t unit_span = start_cost + unit_tiles;
         for (uint32_t h = 0; h < heads; ++h) {
             uint64_t done = 0;
-            while (done < unit_tiles) {
+            while (done < unit_span) {
                 while (cursor + done >= share_end(cta)) {
                     ++cta;
                     plan.cta_item_begin.push_back(static_cast<uint32_t>(plan.items.size()));
                 }
-                uint64_t take = std::min(unit_tiles - done, share_end(cta) - (cursor + done));
-                WorkItem item{};
-                item.tile = tile;
-                item.head_sel = h;
-                item.kv_begin = static_cast<uint32_t>(done * kKvTile);
-                item.kv_end = static_cast<uint32_t>(std::min<uint64_t>((done + take) * kKvTile, tile_ctx[tile]));
-                plan.items.push_back(item);
+                const uint64_t take = std::min(unit_span - done, share_end(cta) - (cursor + done));
+                const uint64_t real_begin = std::max(done, start_cost) - start_cost;
+                const uint64_t real_end = std::max(done + take, start_cost) - start_cost;
+                if (real_end > real_begin) {
+                    WorkItem item{};
+                    item.tile = tile;
+                    item.head_sel = h;
+                    item.kv_begin = static_cast<uint32_t>(real_begin * kKvTile);
+                    item.kv_end = static_cast<uint32_t>(std::min<uint64_t>(real_end * kKvTile, tile_ctx[tile]));
+                    plan.items.push_back(item);
+                }
                 done += take;
             }
-            cursor += unit_tiles;
+            cursor += unit_span;
         }
     }
     while (plan.cta_item_begin.size() < num_ctas + 1) plan.cta_item_begin.push_back(static_cast<uint32_t>(plan.items.size()));

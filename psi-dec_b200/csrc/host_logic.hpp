@@ -143,14 +143,15 @@ struct WorkPlan {
 };
 
 // Equal-share plan: the (tile, head_sel) units laid end to end in 16-token KV tiles, cut into `max_ctas` (or fewer)
-// contiguous shares.
+// contiguous shares.  `item_start_cost` (in KV tiles) is what opening one more item costs a CTA; shares are equal in
+// KV tiles plus that cost per unit start.
 WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
                              const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
-                             uint32_t min_kv_tiles_per_cta);
+                             uint32_t min_kv_tiles_per_cta, uint32_t item_start_cost = 0);
 // The same over a subset of the batch's requests (indices into the request arrays, ascending).
 WorkPlan build_balanced_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
                              const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,
-                             uint32_t min_kv_tiles_per_cta);
+                             uint32_t min_kv_tiles_per_cta, uint32_t item_start_cost = 0);
 
 // One CTA per (reference KV split, head_sel); reference q tiles wider than tokens_per_tile are cut into sub-tiles
 // that share the split boundaries.

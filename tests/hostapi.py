@@ -49,19 +49,19 @@ def tiled_q(q_tile, kv_tile, head_tile=1):
     return pkg.GQASplitKVVariant(1, q_tile, kv_tile, 0, head_tile)
 
 
-def plan_preview(num_q_heads, num_kv_heads, token_indices, cu_tokens, max_ctas, min_tiles=8):
+def plan_preview(num_q_heads, num_kv_heads, token_indices, cu_tokens, max_ctas, min_tiles=8, start_cost=0):
     p = lambda a: a.ctypes.data_as(C.POINTER(C.c_uint32))
     ti = np.ascontiguousarray(token_indices, dtype=np.uint32)
     cu = np.ascontiguousarray(cu_tokens, dtype=np.uint32)
     counts = np.zeros(6, dtype=np.uint32)
     status = lib().psi_plan_preview(C.c_uint32(num_q_heads), C.c_uint32(num_kv_heads), p(ti), p(cu), C.c_uint32(len(ti)),
-                                    C.c_uint32(max_ctas), C.c_uint32(min_tiles), None, C.c_uint64(0), None,
+                                    C.c_uint32(max_ctas), C.c_uint32(min_tiles), C.c_uint32(start_cost), None, C.c_uint64(0), None,
                                     C.c_uint64(0), p(counts))
     assert status == 0
     items = np.zeros((int(counts[0]), 6), dtype=np.uint32)
     ctas = np.zeros(int(counts[1]) + 1, dtype=np.uint32)
     status = lib().psi_plan_preview(C.c_uint32(num_q_heads), C.c_uint32(num_kv_heads), p(ti), p(cu), C.c_uint32(len(ti)),
-                                    C.c_uint32(max_ctas), C.c_uint32(min_tiles), p(items), C.c_uint64(len(items)),
+                                    C.c_uint32(max_ctas), C.c_uint32(min_tiles), C.c_uint32(start_cost), p(items), C.c_uint64(len(items)),
                                     p(ctas), C.c_uint64(len(ctas)), p(counts))
     assert status == 0
     return items, ctas, counts
