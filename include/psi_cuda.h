@@ -109,6 +109,20 @@ typedef enum psi_capacity_mode {
     PSI_CAPACITY_CALLER_TOKENS = 2
 } psi_capacity_mode;
 
+/* RMSNormRopeConfig + RopeScaling (crates/inference-backend-metal/src/components/rms_norm_rope.rs:42-165). */
+typedef struct psi_norm_rope_config {
+    uint32_t rope_dim; /* rotated leading dims of each head (even, <= head_dim) */
+    float eps;
+    float rope_theta;
+    uint32_t yarn_enabled; /* 0 = RopeScaling::Default */
+    float yarn_factor;
+    float yarn_attention_factor;
+    float yarn_beta_fast;
+    float yarn_beta_slow;
+    uint32_t yarn_original_max_position_embeddings;
+    uint32_t yarn_truncate;
+} psi_norm_rope_config;
+
 /* GQA::new + GQAMetalConfig + GQAScratch sizing (crates/inference-executor-metal/src/attn/gqa/backend.rs:253-282,
  * scratch.rs:49-92). */
 typedef struct psi_gqa_config {
@@ -289,6 +303,28 @@ PSI_API int32_t psi_gqa_attend(psi_gqa* gqa, psi_pages* pages, psi_table* table,
 PSI_API int32_t psi_gqa_append_attend(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer, const void* k,
                                       const void* v, const void* q, void* out);
 
+/* ---- neighbours of the path that the reference records around it ---------------------------------------------------- */
+
+/* RopeScaling::kernel_parameters (rms_norm_rope.rs:167-230), host only: rope_dim/2 inverse frequencies, the attention
+ * factor, and Yarn's correction range (0, 0 without Yarn; either pointer may be NULL). */
+PSI_API int32_t psi_rope_parameters(const psi_norm_rope_config* config, float* out_inverse_frequencies,
+                                    float* out_attention_factor, float* out_correction_low,
+                                    float* out_correction_high);
+/* Fixes the q / k RMSNorm + RoPE profile of the component: the bf16 norm weights (host arrays of head_dim values,
+ * RMSNormRopeBuffers::norm_weight) and the rope parameters are uploaded once. */
+PSI_API int32_t psi_gqa_set_norm_rope(psi_gqa* gqa, const psi_norm_rope_config* config,
+                                      const uint16_t* q_norm_weight_bf16, const uint16_t* k_norm_weight_bf16);
+/* The three stages GQA::record puts before the attention (backend.rs:465-513: q norm/rope, k norm/rope,
+ * kv_page_write; shaders metal/rms_norm_rope.metal, metal/gqa_kv_page_write.metal) as ONE launch: q_out receives the
+ * normalised, rotated queries, the normalised, rotated keys go straight into their pages (no k scratch), the values
+ * are copied into theirs.  q_in/q_out [T][Hq][D], k_in/v_in [T][Hkv][D], device, positions = the prepared batch. */
+PSI_API int32_t psi_gqa_norm_rope_append(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
+                                         const void* q_in, const void* k_in, const void* v_in, void* q_out);
+/* psi_gqa_attend with the stage the reference records after it fused into the epilogue: out = attention *
+ * sigmoid(gates) (backend.rs:613-624, metal/gqa_activation_gate.metal).  gates: device [T][Hq][D] in the I/O dtype. */
+PSI_API int32_t psi_gqa_attend_gated(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer, const void* q,
+                                     const void* gates, void* out);
+
 /* The same map + reduce, stopping before normalisation to the output dtype: f32 o [T][Hq][D] (normalised within the
  * local KV), m [T][Hq] (natural-log running max of scale*q.k), l [T][Hq] (sum of exp(logit - m)).  This is the
  * reference's partial-output ABI (gqa_split_kv_single_q_map.metal:231-252) lifted to one partial per device, for KV
@@ -371,7 +407,8 @@ typedef enum psi_kernel_class {
     PSI_KERNEL_CLASS_ATTEND_REDUCE = 2,
     PSI_KERNEL_CLASS_COMBINE = 3,
     PSI_KERNEL_CLASS_GATHER = 4,
-    PSI_KERNEL_CLASS_ATTEND_CHUNK = 5
+    PSI_KERNEL_CLASS_ATTEND_CHUNK = 5,
+    PSI_KERNEL_CLASS_NORM_ROPE_APPEND = 6
 } psi_kernel_class;
 PSI_API int32_t psi_ctx_enable_kernel_timing(psi_ctx* ctx, int32_t enable);
 PSI_API int32_t psi_ctx_kernel_timing(psi_ctx* ctx, uint32_t kernel_class, float* out_total_ms, uint64_t* out_launches);

@@ -888,3 +888,127 @@ PSI_ORACLE_API uint64_t psi_oracle_allocator_bitmap(const psi_oracle_allocator* 
 PSI_ORACLE_API uint64_t psi_oracle_allocator_free_count(const psi_oracle_allocator* a) {
     return a->q_len + (a->capacity - a->counter);
 }
+
+/* ------------------------------------------------------------------ */
+/* Neighbours of the path: q/k RMSNorm + RoPE, attention-output gate   */
+/* ------------------------------------------------------------------ */
+
+typedef struct {
+    uint32_t enabled;  /* 0 = RopeScaling::Default */
+    float factor;
+    float attention_factor;
+    float beta_fast;
+    float beta_slow;
+    uint32_t original_max_position_embeddings;
+    uint32_t truncate;
+} psi_oracle_yarn;
+
+/* RopeScaling::kernel_parameters / yarn_kernel_parameters,
+ * crates/inference-backend-metal/src/components/rms_norm_rope.rs:167-230.  Writes rope_dim/2 inverse frequencies,
+ * the attention factor and (when yarn is on) the correction range. */
+PSI_ORACLE_API int psi_oracle_rope_parameters(uint32_t rope_dim, float rope_theta, const psi_oracle_yarn* yarn,
+                                              float* inverse_frequencies, float* attention_factor,
+                                              float* correction_low, float* correction_high) {
+    uint32_t rope_half = rope_dim / 2;
+    float low = 0.0f, high = 0.0f;
+    int on = yarn != NULL && yarn->enabled;
+    if (on) {
+        double dimension = (double)rope_dim, base = (double)rope_theta;
+        double original = (double)yarn->original_max_position_embeddings;
+        float c_fast = (float)(dimension * log(original / ((double)yarn->beta_fast * 6.283185307179586)) / (2.0 * log(base)));
+        float c_slow = (float)(dimension * log(original / ((double)yarn->beta_slow * 6.283185307179586)) / (2.0 * log(base)));
+        low = c_fast > 0.0f ? c_fast : 0.0f;
+        float cap = rope_dim > 0 ? (float)(rope_dim - 1) : 0.0f;
+        high = c_slow < cap ? c_slow : cap;
+        if (yarn->truncate) {
+            low = floorf(low);
+            high = ceilf(high);
+        }
+        if (!(low <= high)) return 1;
+        if (low == high) high += 0.001f;
+    }
+    for (uint32_t d = 0; d < rope_half; ++d) {
+        float inv = powf(rope_theta, -((float)d / (float)rope_half));
+        if (on) {
+            float ramp = ((float)d - low) / (high - low);
+            ramp = ramp < 0.0f ? 0.0f : (ramp > 1.0f ? 1.0f : ramp);
+            inv *= 1.0f + ramp * (1.0f / yarn->factor - 1.0f);
+        }
+        if (!(inv > 0.0f) || !isfinite(inv)) return 2;
+        inverse_frequencies[d] = inv;
+    }
+    *attention_factor = on ? yarn->attention_factor : 1.0f;
+    if (correction_low) *correction_low = low;
+    if (correction_high) *correction_high = high;
+    return 0;
+}
+
+/* Round-trip through the storage dtype T (identity for f32): the shader's T(...) casts. */
+static inline float round_to(float v, int dtype) {
+    if (dtype == PSI_O_F32) return v;
+    if (dtype == PSI_O_BF16) return psi_oracle_bf16_to_f32(psi_oracle_f32_to_bf16(v));
+    return psi_oracle_f16_to_f32(psi_oracle_f32_to_f16(v));
+}
+
+static inline void store_elem(void* base, size_t index, int dtype, float v) {
+    if (dtype == PSI_O_F32) ((float*)base)[index] = v;
+    else if (dtype == PSI_O_BF16) ((uint16_t*)base)[index] = psi_oracle_f32_to_bf16(v);
+    else ((uint16_t*)base)[index] = psi_oracle_f32_to_f16(v);
+}
+
+/* Per (token, head) row: RMS-normalise, scale by the bf16 weight with the shader's rounding order
+ * (T(weight) * T(x * inv_rms)), rotate the first rope_dim dims by position * inverse_frequency.
+ * crates/inference-backend-metal/src/components/metal/rms_norm_rope.metal:7-82; the row sum is taken sequentially in
+ * f32 as the reference's own CPU expectations do (rms_norm_rope.rs:448-450,500-507). */
+PSI_ORACLE_API void psi_oracle_rms_norm_rope(const void* input, int dtype, const uint16_t* norm_weight_bf16,
+                                             const uint32_t* flat_token_indices, uint32_t num_tokens,
+                                             uint32_t num_heads, uint32_t head_dim, uint32_t rope_dim, float eps,
+                                             const float* inverse_frequencies, float attention_factor, void* output) {
+    uint32_t rope_half = rope_dim / 2;
+    for (uint32_t row = 0; row < num_tokens * num_heads; ++row) {
+        size_t base = (size_t)row * head_dim;
+        float acc = 0.0f;
+        for (uint32_t d = 0; d < head_dim; ++d) {
+            float x = load_elem(input, base + d, dtype);
+            acc += x * x;
+        }
+        float inv_rms = 1.0f / sqrtf(acc / (float)head_dim + eps);
+        float position = (float)flat_token_indices[row / num_heads];
+        for (uint32_t d = 0; d < head_dim; ++d) {
+            float w = round_to(psi_oracle_bf16_to_f32(norm_weight_bf16[d]), dtype);
+            float xn = round_to(w * round_to(load_elem(input, base + d, dtype) * inv_rms, dtype), dtype);
+            if (d < rope_half) {
+                uint32_t d2 = d + rope_half;
+                float w2 = round_to(psi_oracle_bf16_to_f32(norm_weight_bf16[d2]), dtype);
+                float x2 = round_to(w2 * round_to(load_elem(input, base + d2, dtype) * inv_rms, dtype), dtype);
+                float theta = position * inverse_frequencies[d];
+                float c = cosf(theta), s = sinf(theta);
+                store_elem(output, base + d, dtype, attention_factor * (xn * c - x2 * s));
+                store_elem(output, base + d2, dtype, attention_factor * (xn * s + x2 * c));
+            } else if (d >= rope_dim) {
+                store_elem(output, base + d, dtype, xn);
+            }
+        }
+    }
+}
+
+/* out = attention_output * sigmoid(gate) with the shader's per-dtype arithmetic: f32 throughout, or every step
+ * rounded to bf16.  crates/inference-backend-metal/src/components/metal/gqa_activation_gate.metal:5-39 */
+PSI_ORACLE_API void psi_oracle_activation_gate(const void* attention_output, const void* gates, int dtype, size_t n,
+                                               void* output) {
+    for (size_t i = 0; i < n; ++i) {
+        float a = load_elem(attention_output, i, dtype), x = load_elem(gates, i, dtype);
+        float sig;
+        if (dtype == PSI_O_F32) {
+            float y = 1.0f / (1.0f + expf(-fabsf(x)));
+            sig = x < 0.0f ? 1.0f - y : y;
+        } else {
+            float abs_x = round_to(fabsf(x), dtype);
+            float exp_x = round_to(expf(round_to(-abs_x, dtype)), dtype);
+            float denom = round_to(1.0f + exp_x, dtype);
+            float y = round_to(1.0f / denom, dtype);
+            sig = x < 0.0f ? round_to(1.0f - y, dtype) : y;
+        }
+        store_elem(output, i, dtype, a * sig);
+    }
+}

@@ -297,3 +297,42 @@ class Allocator:
 
     def free_count(self):
         return int(lib().psi_oracle_allocator_free_count(self._h))
+
+
+class Yarn(C.Structure):
+    _fields_ = [("enabled", C.c_uint32), ("factor", C.c_float), ("attention_factor", C.c_float),
+                ("beta_fast", C.c_float), ("beta_slow", C.c_float), ("original_max_position_embeddings", C.c_uint32),
+                ("truncate", C.c_uint32)]
+
+
+def rope_parameters(rope_dim, rope_theta, yarn: Yarn | None = None):
+    """(inverse_frequencies[rope_dim/2], attention_factor, correction_low, correction_high)."""
+    inv = np.zeros(rope_dim // 2, dtype=np.float32)
+    factor, low, high = C.c_float(), C.c_float(), C.c_float()
+    y = yarn if yarn is not None else Yarn(0, 1.0, 1.0, 1.0, 1.0, 1, 0)
+    rc = lib().psi_oracle_rope_parameters(C.c_uint32(rope_dim), C.c_float(rope_theta), C.byref(y), _p(inv),
+                                          C.byref(factor), C.byref(low), C.byref(high))
+    if rc:
+        raise AssertionError("invalid rope parameters")
+    return inv, factor.value, low.value, high.value
+
+
+def rms_norm_rope(values_bits, dtype, norm_weight_bf16, positions, num_heads, head_dim, rope_dim, eps, inv_freq,
+                  attention_factor=1.0):
+    x = np.ascontiguousarray(values_bits, dtype=np_dtype(dtype))
+    w = np.ascontiguousarray(norm_weight_bf16, dtype=np.uint16)
+    pos = _u32(positions)
+    f = np.ascontiguousarray(inv_freq, dtype=np.float32)
+    out = np.zeros_like(x)
+    lib().psi_oracle_rms_norm_rope(_p(x), C.c_int(dtype), _p(w), _p(pos), C.c_uint32(len(pos)), C.c_uint32(num_heads),
+                                   C.c_uint32(head_dim), C.c_uint32(rope_dim), C.c_float(eps), _p(f),
+                                   C.c_float(attention_factor), _p(out))
+    return out
+
+
+def activation_gate(attention_bits, gate_bits, dtype):
+    a = np.ascontiguousarray(attention_bits, dtype=np_dtype(dtype))
+    g = np.ascontiguousarray(gate_bits, dtype=np_dtype(dtype))
+    out = np.zeros_like(a)
+    lib().psi_oracle_activation_gate(_p(a), _p(g), C.c_int(dtype), C.c_size_t(a.size), _p(out))
+    return out

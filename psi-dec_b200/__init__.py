@@ -6,5 +6,5 @@ registered as ``psi_dec_b200``.
 from .binding import (  # noqa: F401
     BF16, F16, F32, CAPACITY_BUCKETED, CAPACITY_CALLER_TOKENS, CAPACITY_EXACT, KERNEL_AUTO, KERNEL_GENERIC, KERNEL_MMA,
     PLAN_BALANCED, PLAN_REFERENCE, Context, GQA, GQAConfig, GQAPageTableLayout, GQAReplayShape, GQARequestPageTable,
-    GQASplitKV, GQASplitKVVariant, PageArena, PsiError, ReplayBucketPolicy, U32IDAllocator, attend_static, library, library_path,
+    GQASplitKV, GQASplitKVVariant, NormRopeConfig, PageArena, PsiError, ReplayBucketPolicy, U32IDAllocator, attend_static, library, library_path, rope_parameters,
 )

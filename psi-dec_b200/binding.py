@@ -52,6 +52,21 @@ class GQASplitKVVariant(C.Structure):
         return tuple(getattr(self, n) for n, _ in self._fields_)
 
 
+class NormRopeConfig(C.Structure):
+    _fields_ = [("rope_dim", C.c_uint32), ("eps", C.c_float), ("rope_theta", C.c_float), ("yarn_enabled", C.c_uint32),
+                ("yarn_factor", C.c_float), ("yarn_attention_factor", C.c_float), ("yarn_beta_fast", C.c_float),
+                ("yarn_beta_slow", C.c_float), ("yarn_original_max_position_embeddings", C.c_uint32),
+                ("yarn_truncate", C.c_uint32)]
+
+
+def rope_parameters(config: "NormRopeConfig"):
+    """(inverse_frequencies, attention_factor, correction_low, correction_high) of a RoPE profile (host only)."""
+    inv = (C.c_float * max(config.rope_dim // 2, 1))()
+    factor, low, high = C.c_float(), C.c_float(), C.c_float()
+    _check(library().psi_rope_parameters(C.byref(config), inv, C.byref(factor), C.byref(low), C.byref(high)))
+    return list(inv[: config.rope_dim // 2]), factor.value, low.value, high.value
+
+
 class GQAConfig(C.Structure):
     _fields_ = [("num_q_heads", C.c_uint32), ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32),
                 ("scale", C.c_float), ("page_bytes", C.c_uint32), ("dtype", C.c_uint32),
@@ -402,6 +417,24 @@ class GQA:
         """KV append and attention as one launch (same results as ``kv_page_write`` then ``attend``)."""
         _check(library().psi_gqa_append_attend(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(k), _ptr(v),
                                                _ptr(q), _ptr(out)), self.ctx._h)
+
+    def set_norm_rope(self, config: NormRopeConfig, q_norm_weight_bf16, k_norm_weight_bf16):
+        """Fix the q / k RMSNorm + RoPE profile; weights are sequences of ``head_dim`` bf16 bit patterns."""
+        qw, nq = (C.c_uint16 * len(q_norm_weight_bf16))(*[int(x) for x in q_norm_weight_bf16]), len(q_norm_weight_bf16)
+        kw, nk = (C.c_uint16 * len(k_norm_weight_bf16))(*[int(x) for x in k_norm_weight_bf16]), len(k_norm_weight_bf16)
+        if nq != self.config.head_dim or nk != self.config.head_dim:
+            raise PsiError(1, "norm weights must hold head_dim values")
+        _check(library().psi_gqa_set_norm_rope(self._h, C.byref(config), qw, kw), self.ctx._h)
+
+    def norm_rope_append(self, pages, table, layer, q_in, k_in, v_in, q_out):
+        """q norm/rope -> q_out, k norm/rope -> pages, v -> pages: the three stages before attention as one launch."""
+        _check(library().psi_gqa_norm_rope_append(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(q_in),
+                                                  _ptr(k_in), _ptr(v_in), _ptr(q_out)), self.ctx._h)
+
+    def attend_gated(self, pages, table, layer, q, gates, out):
+        """Attention with ``out = attention * sigmoid(gates)`` fused into the epilogue."""
+        _check(library().psi_gqa_attend_gated(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(q), _ptr(gates),
+                                              _ptr(out)), self.ctx._h)
 
     def attend_partial(self, pages, table, layer, q, o, m, l):
         _check(library().psi_gqa_attend_partial(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(q), _ptr(o),

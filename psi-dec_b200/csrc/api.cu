@@ -35,7 +35,7 @@ uint64_t pad_words(uint64_t n) { return (n + kWordAlign - 1) / kWordAlign * kWor
 
 }  // namespace
 
-constexpr uint32_t kKernelClasses = 6;
+constexpr uint32_t kKernelClasses = 7;
 
 struct psi_ctx {
     int device = 0;
@@ -170,6 +170,10 @@ struct psi_gqa {
     DeviceBuffer step_k, step_v, step_q, step_out;  // psi_gqa_decode_step_host staging
     DeviceBuffer combine_ptrs;
     DeviceBuffer status_word;  // u32 written by bounded device-side waits
+    DeviceBuffer norm_rope;    // q weight bf16[D] | k weight bf16[D] | inverse frequencies f32[rope_dim/2]
+    psi_norm_rope_config norm_rope_cfg{};
+    float norm_rope_attention_factor = 1.0f;
+    bool has_norm_rope = false;
 };
 
 namespace {
@@ -894,6 +898,7 @@ int32_t psi_gqa_destroy(psi_gqa* g) {
         g->step_out.release();
         g->combine_ptrs.release();
         g->status_word.release();
+        g->norm_rope.release();
         if (g->staging != nullptr) (void)cudaFreeHost(g->staging);
         if (g->upload_done != nullptr) (void)cudaEventDestroy(g->upload_done);
     });
@@ -1146,6 +1151,92 @@ int32_t psi_gqa_append_attend(psi_gqa* g, psi_pages* pages, psi_table* table, ui
         p.out = out;
         p.new_k = k;
         p.new_v = v;
+        run_attend(g, p);
+    });
+}
+
+int32_t psi_rope_parameters(const psi_norm_rope_config* config, float* out_inverse_frequencies,
+                            float* out_attention_factor, float* out_correction_low, float* out_correction_high) {
+    return guarded(nullptr, [&] {
+        require(config != nullptr && out_inverse_frequencies != nullptr && out_attention_factor != nullptr,
+                "rope parameter outputs must not be null");
+        const RopeParameters params = rope_parameters(*config);
+        std::copy(params.inverse_frequencies.begin(), params.inverse_frequencies.end(), out_inverse_frequencies);
+        *out_attention_factor = params.attention_factor;
+        if (out_correction_low != nullptr) *out_correction_low = params.correction_low;
+        if (out_correction_high != nullptr) *out_correction_high = params.correction_high;
+    });
+}
+
+int32_t psi_gqa_set_norm_rope(psi_gqa* g, const psi_norm_rope_config* config, const uint16_t* q_weight,
+                              const uint16_t* k_weight) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(config != nullptr && q_weight != nullptr && k_weight != nullptr, "norm/rope arguments must not be null");
+        require(config->rope_dim <= g->cfg.head_dim, "RoPE dimension exceeds head_dim");
+        require(std::isfinite(config->eps) && config->eps >= 0.0f, "RMSNorm eps must be finite and non-negative");
+        const RopeParameters params = rope_parameters(*config);
+        psi_ctx* ctx = g->ctx;
+        ctx->bind();
+        const uint32_t d = g->cfg.head_dim;
+        const uint64_t weight_bytes = (uint64_t(d) * 2 + 15) / 16 * 16;
+        std::vector<unsigned char> host(2 * weight_bytes + params.inverse_frequencies.size() * sizeof(float), 0);
+        std::memcpy(host.data(), q_weight, size_t(d) * 2);
+        std::memcpy(host.data() + weight_bytes, k_weight, size_t(d) * 2);
+        std::memcpy(host.data() + 2 * weight_bytes, params.inverse_frequencies.data(),
+                    params.inverse_frequencies.size() * sizeof(float));
+        g->norm_rope.ensure(ctx, host.size(), false);
+        cuda_check(cudaMemcpyAsync(g->norm_rope.ptr, host.data(), host.size(), cudaMemcpyHostToDevice, ctx->stream),
+                   "cudaMemcpyAsync");  // pageable source: staged before the call returns
+        g->norm_rope_cfg = *config;
+        g->norm_rope_attention_factor = params.attention_factor;
+        g->has_norm_rope = true;
+    });
+}
+
+int32_t psi_gqa_norm_rope_append(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* q_in,
+                                 const void* k_in, const void* v_in, void* q_out) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(g->prepared, "GQA batch metadata must be updated before recording");
+        require(g->has_norm_rope, "psi_gqa_set_norm_rope must be called before psi_gqa_norm_rope_append");
+        require(q_in != nullptr && k_in != nullptr && v_in != nullptr && q_out != nullptr, "buffers must not be null");
+        g->ctx->bind();
+        PrepParams p{};
+        p.geo = page_geometry(g, pages, table, layer);
+        p.q_in = q_in;
+        p.k_in = k_in;
+        p.v_in = v_in;
+        p.q_out = q_out;
+        const uint64_t weight_bytes = (uint64_t(g->cfg.head_dim) * 2 + 15) / 16 * 16;
+        const auto* base = static_cast<const unsigned char*>(g->norm_rope.ptr);
+        p.q_weight = base;
+        p.k_weight = base + weight_bytes;
+        p.inverse_frequencies = reinterpret_cast<const float*>(base + 2 * weight_bytes);
+        p.attention_factor = g->norm_rope_attention_factor;
+        p.eps = g->norm_rope_cfg.eps;
+        p.rope_dim = g->norm_rope_cfg.rope_dim;
+        p.num_q_heads = g->cfg.num_q_heads;
+        p.dtype = g->cfg.dtype;
+        p.req_slots = block_words(g, g->off_req_slots);
+        p.flat_token_indices = block_words(g, g->off_token_indices);
+        p.scalars = block_words(g, 0);
+        p.num_total_tokens = g->shape.num_total_tokens;
+        LaunchScope scope(g->ctx, PSI_KERNEL_CLASS_NORM_ROPE_APPEND);
+        cuda_check(launch_norm_rope_append(p, g->ctx->stream), "norm/rope/append launch");
+    });
+}
+
+int32_t psi_gqa_attend_gated(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* q,
+                             const void* gates, void* out) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(out != nullptr && gates != nullptr, "gates and out must not be null");
+        require((reinterpret_cast<uintptr_t>(gates) & 7u) == 0, "gates must be 8-byte aligned");
+        g->ctx->bind();
+        AttendParams p = attend_params(g, pages, table, layer, q);
+        p.out = out;
+        p.gates = gates;
         run_attend(g, p);
     });
 }

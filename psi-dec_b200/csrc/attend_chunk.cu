@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_chunk_kernel(AttendParams 
                             p.ext_l[row] = sum;
                         }
                     } else {
-                        Mma<T>::store4(static_cast<T*>(p.out) + row * D + 4 * c4, acc);
+                        store_out4<T>(p, row * D + 4 * c4, acc);
                     }
                 }
                 if (lane == 0) p.unit_counters[v.reduce_unit + warp] = 0;  // ready for the next launch
@@ -271,13 +271,12 @@ __global__ void __launch_bounds__(kThreads, 1) attend_chunk_kernel(AttendParams 
                 }
             }
         } else {
-            T* out = static_cast<T*>(p.out);
             const uint64_t row0 = r0 < my_rows ? out_row(r0) : 0, row1 = r1 < my_rows ? out_row(r1) : 0;
 #pragma unroll
             for (int j = 0; j < D / 8; ++j) {
                 const uint32_t col = 8 * j + 2 * frag.quad_col;
-                if (r0 < my_rows) *reinterpret_cast<uint32_t*>(out + row0 * D + col) = Mma<T>::pack(st.o[j][0] * inv0, st.o[j][1] * inv0);
-                if (r1 < my_rows) *reinterpret_cast<uint32_t*>(out + row1 * D + col) = Mma<T>::pack(st.o[j][2] * inv1, st.o[j][3] * inv1);
+                if (r0 < my_rows) store_out2<T>(p, row0 * D + col, st.o[j][0] * inv0, st.o[j][1] * inv0);
+                if (r1 < my_rows) store_out2<T>(p, row1 * D + col, st.o[j][2] * inv1, st.o[j][3] * inv1);
             }
         }
     }

@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(kGenericThreads) attend_generic_kernel(AttendP
 #pragma unroll
                     for (int i = 0; i < DPL; ++i) {
                         const uint32_t d = lane + 32 * i;
-                        if (d < D) store_from_float(p.out, row * D + d, p.dtype, o[r][i] * inv);
+                        if (d < D) store_from_float(p.out, row * D + d, p.dtype, o[r][i] * inv * gate_factor(p, row * D + d));
                     }
                 }
             }
@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(kReduceThreads) attend_reduce_kernel(AttendPar
                 p.ext_l[row] = sum;
             }
         } else {
-            store_from_float(p.out, row * D + d, p.dtype, value);
+            store_from_float(p.out, row * D + d, p.dtype, value * gate_factor(p, row * D + d));
         }
     }
 }

@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                         p.ext_l[row] = sum;
                     }
                 } else {
-                    Mma<T>::store4(static_cast<T*>(p.out) + row * D + 4 * c4, acc);
+                    store_out4<T>(p, row * D + 4 * c4, acc);
                 }
             }
         }
@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                             p.ext_l[row] = sum;
                         }
                     } else {
-                        Mma<T>::store4(static_cast<T*>(p.out) + row * D + 4 * c4, acc);
+                        store_out4<T>(p, row * D + 4 * c4, acc);
                     }
                 }
                 if (tid == 0) p.unit_counters[v.reduce_unit] = 0;  // ready for the next launch

@@ -41,6 +41,13 @@ __device__ __forceinline__ uint64_t v_region_offset(const PageGeometry& g) {
     return static_cast<uint64_t>(g.num_kv_heads) * g.tokens_per_page * g.head_dim;
 }
 
+// sigmoid as the reference's gate computes it: 1 / (1 + exp(-|x|)), mirrored for negative x
+// (crates/inference-backend-metal/src/components/metal/gqa_activation_gate.metal:13-16).
+__device__ __forceinline__ float gate_sigmoid(float x) {
+    const float y = 1.0f / (1.0f + __expf(-fabsf(x)));
+    return x < 0.0f ? 1.0f - y : y;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);
@@ -77,5 +84,14 @@ __device__ __forceinline__ uint32_t item_row_limit(const ItemView& v, uint32_t r
 }
 
 constexpr float kLn2 = 0.6931471805599453f;
+
+}  // namespace psi
+
+namespace psi {
+
+// sigmoid(gate) of output element `index`, or 1 when the launch has no gate.
+__device__ __forceinline__ float gate_factor(const AttendParams& p, uint64_t index) {
+    return p.gates == nullptr ? 1.0f : gate_sigmoid(load_as_float(p.gates, index, p.dtype));
+}
 
 }  // namespace psi

@@ -1,6 +1,7 @@
 #include "host_logic.hpp"
 
 #include <algorithm>
+#include <cmath>
 #include <limits>
 
 namespace psi {
@@ -487,6 +488,54 @@ std::vector<DeviceItem> flatten_plan(const WorkPlan& plan, const PlanGeometry& g
         d.new_begin = tile.new_begin;
         d.flat_req_begin = tile.flat_req_begin;
         d.writes_kv = head_tile == 0 ? 1u : 0u;
+    }
+    return out;
+}
+
+// -------------------------------------------------------------------------------------------------------------------
+// RoPE inverse frequencies, with the Yarn ramp when scaling is on.
+// -------------------------------------------------------------------------------------------------------------------
+RopeParameters rope_parameters(const psi_norm_rope_config& c) {
+    require(c.rope_dim > 0 && c.rope_dim % 2 == 0, "RoPE dimension must be positive and even");
+    require(std::isfinite(c.rope_theta) && c.rope_theta > 0.0f, "rope_theta must be finite and positive");
+    RopeParameters out;
+    const uint32_t rope_half = c.rope_dim / 2;
+    const bool yarn = c.yarn_enabled != 0;
+    if (yarn) {
+        require(std::isfinite(c.yarn_factor) && c.yarn_factor >= 1.0f, "Yarn factor must be at least 1");
+        require(std::isfinite(c.yarn_attention_factor) && c.yarn_attention_factor > 0.0f, "Yarn attention factor must be positive");
+        require(c.yarn_beta_fast > 0.0f && c.yarn_beta_slow > 0.0f && c.yarn_beta_fast >= c.yarn_beta_slow,
+                "Yarn beta_fast must be at least beta_slow, both positive");
+        require(c.yarn_original_max_position_embeddings > 0, "Yarn original context length must be positive");
+        require(c.rope_theta > 1.0f, "Yarn rope_theta must be greater than 1");
+        auto correction = [&](float rotations) {
+            const double two_pi = 6.283185307179586;
+            return static_cast<float>(double(c.rope_dim) *
+                                      std::log(double(c.yarn_original_max_position_embeddings) / (double(rotations) * two_pi)) /
+                                      (2.0 * std::log(double(c.rope_theta))));
+        };
+        float low = std::max(correction(c.yarn_beta_fast), 0.0f);
+        float high = std::min(correction(c.yarn_beta_slow), static_cast<float>(c.rope_dim - 1));
+        if (c.yarn_truncate) {
+            low = std::floor(low);
+            high = std::ceil(high);
+        }
+        require(low <= high, "Yarn correction range must be ordered");
+        if (low == high) high += 0.001f;
+        out.correction_low = low;
+        out.correction_high = high;
+        out.attention_factor = c.yarn_attention_factor;
+    }
+    out.inverse_frequencies.resize(rope_half);
+    for (uint32_t d = 0; d < rope_half; ++d) {
+        float inv = std::pow(c.rope_theta, -(static_cast<float>(d) / static_cast<float>(rope_half)));
+        if (yarn) {
+            float ramp = (static_cast<float>(d) - out.correction_low) / (out.correction_high - out.correction_low);
+            ramp = std::min(std::max(ramp, 0.0f), 1.0f);
+            inv *= 1.0f + ramp * (1.0f / c.yarn_factor - 1.0f);
+        }
+        require(std::isfinite(inv) && inv > 0.0f, "RMSNorm/RoPE inverse frequency must be finite and positive");
+        out.inverse_frequencies[d] = inv;
     }
     return out;
 }

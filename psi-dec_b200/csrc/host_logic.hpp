@@ -179,6 +179,14 @@ ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, c
 // Device form of a finished plan.
 std::vector<DeviceItem> flatten_plan(const WorkPlan& plan, const PlanGeometry& geo);
 
+// ---- RoPE parameters (crates/inference-backend-metal/src/components/rms_norm_rope.rs:126-230) ---------------------
+struct RopeParameters {
+    std::vector<float> inverse_frequencies;  // rope_dim / 2
+    float attention_factor = 1.0f;
+    float correction_low = 0.0f, correction_high = 0.0f;  // Yarn only
+};
+RopeParameters rope_parameters(const psi_norm_rope_config& config);
+
 // ---- page-ID allocator (crates/inference-runtime-core/src/memory/u32_id_allocator.rs) --------------------------------
 class IdAllocator {
 public:

@@ -41,6 +41,26 @@ struct AppendParams {
     uint32_t num_total_tokens;    // launch capacity; rows >= scalars[kScalarNumActiveTokens] do nothing
 };
 
+struct PrepParams {
+    PageGeometry geo;
+    const void* q_in;             // [T][Hq][D] projected, not yet normalised
+    const void* k_in;             // [T][Hkv][D]
+    const void* v_in;             // [T][Hkv][D]
+    void* q_out;                  // [T][Hq][D] normalised + rotated
+    const void* q_weight;         // bf16 [D]
+    const void* k_weight;         // bf16 [D]
+    const float* inverse_frequencies;  // [rope_dim / 2]
+    float attention_factor;
+    float eps;
+    uint32_t rope_dim;
+    uint32_t num_q_heads;
+    uint32_t dtype;
+    const uint32_t* req_slots;
+    const uint32_t* flat_token_indices;
+    const uint32_t* scalars;
+    uint32_t num_total_tokens;
+};
+
 struct GatherParams {
     PageGeometry geo;
     uint32_t req_slot;
@@ -57,6 +77,7 @@ struct AttendParams {
     float* ext_o;                 // [T][Hq][D] f32 normalised partial (attend_partial), else nullptr
     float* ext_m;                 // [T][Hq] natural-log max
     float* ext_l;                 // [T][Hq] exp-sum
+    const void* gates;            // nullptr, or [T][Hq][D] in the I/O dtype: out = attention * sigmoid(gate)
     const void* new_k;            // fused step only: this step's K rows [T][Hkv][D], appended by the map kernel
     const void* new_v;            //                  and read from here instead of from their pages; else nullptr
     const DeviceItem* items;
@@ -90,6 +111,7 @@ struct CombineParams {
 
 cudaError_t launch_kv_append(const AppendParams& p, cudaStream_t stream);
 cudaError_t launch_page_gather(const GatherParams& p, cudaStream_t stream);
+cudaError_t launch_norm_rope_append(const PrepParams& p, cudaStream_t stream);
 
 // Map kernels.  `num_ctas` CTAs walk cta_item_begin.  The generic kernel takes any profile with head_dim <= 256; the
 // mma kernel needs bf16/f16, head_dim in {64,128,256} and tokens_per_page % 8 == 0.

@@ -82,6 +82,31 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk, uint3
     return row * row_bytes + ((chunk ^ (row & 7u)) << 4);
 }
 
+// Final output stores: optional gate (out = attention * sigmoid(gate)), then one rounding to the I/O dtype.
+template <typename T>
+__device__ __forceinline__ void store_out4(const AttendParams& p, uint64_t index, float4 v) {
+    if (p.gates != nullptr) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.gates) + index);
+        const T* g = reinterpret_cast<const T*>(&raw);
+        v.x *= gate_sigmoid(static_cast<float>(g[0]));
+        v.y *= gate_sigmoid(static_cast<float>(g[1]));
+        v.z *= gate_sigmoid(static_cast<float>(g[2]));
+        v.w *= gate_sigmoid(static_cast<float>(g[3]));
+    }
+    Mma<T>::store4(static_cast<T*>(p.out) + index, v);
+}
+
+template <typename T>
+__device__ __forceinline__ void store_out2(const AttendParams& p, uint64_t index, float a, float b) {
+    if (p.gates != nullptr) {
+        const uint32_t raw = *reinterpret_cast<const uint32_t*>(static_cast<const T*>(p.gates) + index);
+        const T* g = reinterpret_cast<const T*>(&raw);
+        a *= gate_sigmoid(static_cast<float>(g[0]));
+        b *= gate_sigmoid(static_cast<float>(g[1]));
+    }
+    *reinterpret_cast<uint32_t*>(static_cast<T*>(p.out) + index) = Mma<T>::pack(a, b);
+}
+
 // Lane roles of the ldmatrix fetches, pre-folded into byte offsets (constant for a whole kernel).
 struct FragmentLanes {
     uint32_t q_lane, q_x;   // A operand (query rows x k halves): address = q_tile_base + q_lane + (q_x ^ 32*ks)

@@ -1,0 +1,124 @@
+"""GPU parity of the stages the reference records next to the path and this library fuses into it: q/k RMSNorm + RoPE
+with the KV page write (one launch), and the sigmoid gate in the attention epilogue."""
+import math
+
+import numpy as np
+import pytest
+
+import checks
+import gpuharness as G
+import workloads as W
+from oracle import psi_oracle as O
+
+pkg = G.pkg
+pytestmark = pytest.mark.gpu
+
+
+def test_bf16_norm_rounding_order_is_bit_exact_for_q_and_k():
+    # crates/inference-backend-metal/src/components/rms_norm_rope.rs:476-519 through the fused launch
+    import torch
+    x = O.encode(np.array([0.73046875, -1.171875, 0.43945313, 2.03125], dtype=np.float32), O.BF16)
+    w = O.encode(np.array([1.296875, 0.8984375, 1.1015625, 0.703125], dtype=np.float32), O.BF16)
+    rig = G.Rig(pkg.BF16, 1, 1, 4, 2, 0.5, (1, 1, 1, 1), 1, num_pages=1)
+    rig.set_pages(0, 0, [0])
+    rig.gqa.set_norm_rope(pkg.NormRopeConfig(2, 1e-6, 1_000_000.0, 0, 1, 1, 1, 1, 1, 0), w.tolist(), w.tolist())
+    rig.gqa.prepare([0], [0], [0, 1])
+    xin = torch.from_numpy(x.view(np.int16).copy()).cuda().view(torch.bfloat16).reshape(1, 1, 4)
+    q_out = torch.zeros_like(xin)
+    rig.gqa.norm_rope_append(rig.pages, rig.table, 0, xin, xin, xin, q_out)
+    rig.ctx.sync()
+    inv, factor, _, _ = O.rope_parameters(2, 1_000_000.0)
+    expected = O.rms_norm_rope(x, O.BF16, w, [0], 1, 4, 2, 1e-6, inv, factor)
+    assert G.bits_of(q_out).reshape(-1).tolist() == expected.tolist()
+    arena = rig.arena_bits()       # page = [K: 2 tokens x 4][V: 2 tokens x 4]; token 0
+    assert arena[:4].tolist() == expected.tolist() and arena[8:12].tolist() == x.tolist()
+    rig.close()
+
+
+def test_f32_yarn_rotation_at_long_context():
+    # rms_norm_rope.rs:414-474: position 262,143, tolerance 1e-3 against the CPU expectation
+    import torch
+    factor = float(np.float32(1.0) + np.float32(0.1) * np.log(np.float32(32.0)))
+    x = np.array([((i * 37 % 29) - 14.0) / 8.0 for i in range(128)], dtype=np.float32)
+    w = O.encode(np.array([0.75 + (i % 11) / 20.0 for i in range(128)], dtype=np.float32), O.BF16)
+    blocks = 262144 // 16
+    rig = G.Rig(pkg.F32, 1, 1, 128, 16, 0.1, (1, 1, blocks, 1), 1, num_pages=1)
+    rig.gqa.set_norm_rope(pkg.NormRopeConfig(128, 1e-6, 10_000_000.0, 1, 32.0, factor, 32.0, 1.0, 8192, 1), w.tolist(),
+                          w.tolist())
+    rig.gqa.prepare([0], [262143], [0, 1])
+    xin = torch.from_numpy(x.copy()).cuda().reshape(1, 1, 128)
+    q_out = torch.zeros_like(xin)
+    rig.gqa.norm_rope_append(rig.pages, rig.table, 0, xin, xin, xin, q_out)
+    rig.ctx.sync()
+    inv, f, _, _ = O.rope_parameters(128, 10_000_000.0, O.Yarn(1, 32.0, factor, 32.0, 1.0, 8192, 1))
+    expected = O.rms_norm_rope(x, O.F32, w, [262143], 1, 128, 128, 1e-6, inv, f)
+    assert np.max(np.abs(q_out.cpu().numpy().reshape(-1) - expected)) < 1e-3
+    rig.close()
+
+
+@pytest.mark.parametrize("dtype,head_dim,rope_dim", [(pkg.BF16, 256, 64), (pkg.BF16, 128, 128), (pkg.F16, 128, 64),
+                                                     (pkg.F32, 64, 32)])
+def test_fused_norm_rope_append_then_attention_matches_the_staged_oracle(dtype, head_dim, rope_dim):
+    import torch
+    rng = np.random.default_rng(head_dim + rope_dim)
+    spec = W.Spec("norm-rope", dtype, 8, 2, head_dim, 16, [300, 41, 0, 1000], [3, 1, 20, 2], seed=21)
+    s = W.Session(spec)
+    wq = O.encode(1.0 + 0.1 * rng.standard_normal(head_dim).astype(np.float32), O.BF16)
+    wk = O.encode(1.0 + 0.1 * rng.standard_normal(head_dim).astype(np.float32), O.BF16)
+    cfg = pkg.NormRopeConfig(rope_dim, 1e-6, 1_000_000.0, 0, 1, 1, 1, 1, 1, 0)
+    s.gqa.set_norm_rope(cfg, wq.tolist(), wk.tolist())
+    q_raw, k_raw = s.q.clone(), s.k.clone()
+    before = checks.to_numpy_bits(s.arena)
+    s.gqa.norm_rope_append(s.pages, s.table, 0, q_raw, k_raw, s.v, s.q)     # s.q now holds the normalised queries
+    s.attend()
+    s.ctx.sync()
+    # oracle: the same three stages one after the other
+    positions = [int(c) + j for c, n in zip(spec.context_lens, spec.q_len) for j in range(int(n))]
+    inv, factor, _, _ = O.rope_parameters(rope_dim, 1_000_000.0)
+    q_ref = O.rms_norm_rope(checks.to_numpy_bits(q_raw), dtype, wq, positions, spec.num_q_heads, head_dim, rope_dim,
+                            1e-6, inv, factor)
+    k_ref = O.rms_norm_rope(checks.to_numpy_bits(k_raw), dtype, wk, positions, spec.num_kv_heads, head_dim, rope_dim,
+                            1e-6, inv, factor)
+    ulp = 2.0 ** -7 if dtype == pkg.BF16 else (2.0 ** -10 if dtype == pkg.F16 else 1e-5)
+    q_got = O.decode(checks.to_numpy_bits(s.q), dtype)
+    q_exp = O.decode(q_ref, dtype)
+    assert np.max(np.abs(q_got - q_exp) / np.maximum(1.0, np.abs(q_exp))) <= 2 * ulp     # sin/cos differ by an ulp at most
+    if dtype != pkg.F32:   # f32 keeps every bit of the row sum, whose summation order differs between the two sides
+        assert np.mean(checks.to_numpy_bits(s.q) == q_ref) > 0.98
+    # pages: the oracle's page write of its own normalised keys, compared through the decoded values
+    s2_k = s.k.clone()
+    s.k.copy_(G.to_device(O.decode(k_ref, dtype), dtype).reshape(s.k.shape))
+    expected_arena = checks.expected_arena_after_append(s, before)
+    s.k.copy_(s2_k)
+    got_arena = checks.to_numpy_bits(s.arena).reshape(-1)
+    diff = np.abs(O.decode(got_arena, dtype) - O.decode(expected_arena, dtype))
+    assert np.max(diff / np.maximum(1.0, np.abs(O.decode(expected_arena, dtype)))) <= 2 * ulp
+    if dtype != pkg.F32:
+        assert np.mean(got_arena == expected_arena) > 0.9999  # everything but a few rotated elements is bit-identical
+    # attention over the pages the GPU wrote, with the GPU's normalised queries, against the oracle
+    checks.assert_attention_close(s)
+    s.close()
+
+
+@pytest.mark.parametrize("index,scale_down,kernel_mode", [(2, 8, pkg.KERNEL_AUTO), (5, 64, pkg.KERNEL_AUTO),
+                                                          (3, 16, pkg.KERNEL_GENERIC)])
+def test_gate_fused_into_the_attention_epilogue(index, scale_down, kernel_mode):
+    import torch
+    s = W.Session(W.config(index, scale_down=scale_down), kernel_mode=kernel_mode)
+    s.append()
+    gates = (2.0 * torch.randn(s.q.shape, device=s.device)).to(s.tdtype)
+    s.attend()
+    s.ctx.sync()
+    plain = checks.to_numpy_bits(s.out)
+    s.gqa.attend_gated(s.pages, s.table, 0, s.q, gates, s.out)
+    s.ctx.sync()
+    expected = O.decode(O.activation_gate(plain, checks.to_numpy_bits(gates), s.spec.dtype), s.spec.dtype)
+    got = O.decode(checks.to_numpy_bits(s.out), s.spec.dtype)
+    diff = np.abs(got - expected)
+    assert diff.max() <= 2e-2 and diff.mean() <= 2e-3, (diff.max(), diff.mean())
+    # and against the f32 oracle attention gated in f64
+    attn, rows = checks.oracle_attention(s)
+    g64 = O.decode(checks.to_numpy_bits(gates), s.spec.dtype).astype(np.float64)[rows]
+    exact = attn.astype(np.float64) / (1.0 + np.exp(-g64))
+    assert np.abs(got[rows] - exact).max() <= 2e-2
+    s.close()

@@ -279,3 +279,20 @@ def test_balanced_plan_properties():
         g = int(rng.choice([1, 2, 4, 6, 8, 16, 24]))
         _check_plan(hkv * g, hkv, rng.integers(0, 5000, size=reqs), cu, int(rng.integers(1, 300)),
                     int(rng.choice([1, 4, 8])), int(rng.choice([0, 3, 10])))
+
+
+def test_rope_parameters_yarn_golden_and_oracle():
+    # crates/inference-backend-metal/src/components/rms_norm_rope.rs:394-412 (correction range 14, 29)
+    import math
+    factor = float(np.float32(1.0) + np.float32(0.1) * np.log(np.float32(32.0)))
+    cfg = pkg.NormRopeConfig(128, 1e-6, 10_000_000.0, 1, 32.0, factor, 32.0, 1.0, 8192, 1)
+    inv, f, low, high = pkg.rope_parameters(cfg)
+    assert (low, high) == (14.0, 29.0) and f == pytest.approx(1.0 + 0.1 * math.log(32.0), abs=1e-6)
+    ref_inv, ref_f, ref_low, ref_high = O.rope_parameters(128, 10_000_000.0, O.Yarn(1, 32.0, factor, 32.0, 1.0, 8192, 1))
+    assert np.allclose(inv, ref_inv, rtol=1e-6) and (low, high) == (ref_low, ref_high)
+    plain = pkg.NormRopeConfig(64, 1e-6, 1_000_000.0, 0, 1.0, 1.0, 1.0, 1.0, 1, 0)
+    inv, f, low, high = pkg.rope_parameters(plain)
+    assert f == 1.0 and (low, high) == (0.0, 0.0)
+    assert np.allclose(inv, O.rope_parameters(64, 1_000_000.0)[0], rtol=1e-6)
+    with pytest.raises(pkg.PsiError, match="Yarn rope_theta must be greater than 1"):
+        pkg.rope_parameters(pkg.NormRopeConfig(64, 1e-6, 1.0, 1, 2.0, 1.0, 2.0, 1.0, 4096, 0))

@@ -228,3 +228,47 @@ def test_paged_attention_matches_contiguous_reference_and_merge():
     for h in range(hq):
         merged = O.merge_partials(np.stack([o_a[0, h], o_b[0, h]]), [m_a[0, h], m_b[0, h]], [s_a[0, h], s_b[0, h]])
         assert np.max(np.abs(merged - out[0, h])) <= 1e-6
+
+
+def test_yarn_correction_range_and_long_context_rotation():
+    # crates/inference-backend-metal/src/components/rms_norm_rope.rs:394-474
+    yarn = O.Yarn(1, 32.0, float(np.float32(1.0) + np.float32(0.1) * np.log(np.float32(32.0))), 32.0, 1.0, 8192, 1)
+    inv, factor, low, high = O.rope_parameters(128, 10_000_000.0, yarn)
+    assert (low, high) == (14.0, 29.0) and abs(factor - (1.0 + 0.1 * math.log(32.0))) < 1e-6
+    x = np.array([((i * 37 % 29) - 14.0) / 8.0 for i in range(128)], dtype=np.float32)
+    w = O.encode(np.array([0.75 + (i % 11) / 20.0 for i in range(128)], dtype=np.float32), O.BF16)
+    position = 262143
+    out = O.rms_norm_rope(x, O.F32, w, [position], 1, 128, 128, 1e-6, inv, factor)
+    f = np.float32
+    inv_rms = f(1.0) / np.sqrt(f(np.sum(x * x, dtype=np.float32) / f(128) + f(1e-6)))
+    wf = O.decode(w, O.BF16)
+    for d in range(64):
+        ramp = min(max((d - 14.0) / (29.0 - 14.0), 0.0), 1.0)
+        inv_freq = f(f(10_000_000.0) ** f(-(d / 64.0))) * f(1.0 + ramp * (1.0 / 32.0 - 1.0))
+        theta = f(position) * inv_freq
+        first, second = wf[d] * x[d] * inv_rms, wf[d + 64] * x[d + 64] * inv_rms
+        assert abs(out[d] - factor * (first * math.cos(theta) - second * math.sin(theta))) < 1e-3
+        assert abs(out[d + 64] - factor * (first * math.sin(theta) + second * math.cos(theta))) < 1e-3
+
+
+def test_bf16_norm_rounding_order_is_bit_exact():
+    # rms_norm_rope.rs:476-519: position 0, rope_dim 2 of head_dim 4
+    x = O.encode(np.array([0.73046875, -1.171875, 0.43945313, 2.03125], dtype=np.float32), O.BF16)
+    w = O.encode(np.array([1.296875, 0.8984375, 1.1015625, 0.703125], dtype=np.float32), O.BF16)
+    inv, factor, _, _ = O.rope_parameters(2, 1_000_000.0)
+    out = O.rms_norm_rope(x, O.BF16, w, [0], 1, 4, 2, 1e-6, inv, factor)
+    xf, wf = O.decode(x, O.BF16), O.decode(w, O.BF16)
+    inv_rms = np.float32(1.0) / np.sqrt(np.float32(np.float32(np.sum(xf * xf, dtype=np.float32)) / np.float32(4) + np.float32(1e-6)))
+    expected = O.encode(wf * O.decode(O.encode(xf * inv_rms, O.BF16), O.BF16), O.BF16)
+    assert out.tolist() == expected.tolist()
+
+
+def test_activation_gate_sigmoid():
+    # crates/inference-backend-metal/src/components/metal/gqa_activation_gate.metal:13-38
+    a = np.array([1.0, -2.0, 0.5, 3.0], dtype=np.float32)
+    g = np.array([0.0, 2.0, -2.0, 30.0], dtype=np.float32)
+    out = O.activation_gate(a, g, O.F32)
+    expected = a / (1.0 + np.exp(-g.astype(np.float64)))
+    assert np.max(np.abs(out - expected)) < 1e-6
+    out16 = O.decode(O.activation_gate(O.encode(a, O.BF16), O.encode(g, O.BF16), O.BF16), O.BF16)
+    assert np.max(np.abs(out16 - expected)) < 2e-2
