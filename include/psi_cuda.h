@@ -353,8 +353,10 @@ PSI_API int32_t psi_gqa_combine_wait(psi_gqa* gqa, const float* const* o, const 
                                      uint32_t flag_value, uint32_t max_polls);
 PSI_API int32_t psi_gqa_device_status(psi_gqa* gqa, int32_t* out);
 
-/* One whole decode step through host memory: copies k, v [T][Hkv][D] and q [T][Hq][D] host->device, runs append then
- * attend, copies out [T][Hq][D] device->host and waits.  T is the prepared num_tokens. */
+/* One whole decode step through host memory: k, v [T][Hkv][D] and q [T][Hq][D] come from host buffers, out [T][Hq][D]
+ * lands in a host buffer, and the call waits for it.  T is the prepared num_tokens.  With pinned (page-locked,
+ * device-mapped) buffers the attention launch reads and writes them in place over the host link; with pageable
+ * buffers the inputs are staged through device copies first. */
 PSI_API int32_t psi_gqa_decode_step_host(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
                                          const void* k_host, const void* v_host, const void* q_host, void* out_host);
 

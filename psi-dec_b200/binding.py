@@ -97,6 +97,10 @@ def _ptr(x):
 
 
 def _u32_array(values):
+    """(pointer, length) of a u32 sequence; a contiguous numpy uint32 array is passed without a copy."""
+    if hasattr(values, "ctypes") and getattr(values, "dtype", None) is not None and values.dtype.itemsize == 4 \
+            and values.dtype.kind == "u" and values.flags["C_CONTIGUOUS"]:
+        return values.ctypes.data_as(C.POINTER(C.c_uint32)), int(values.size)
     values = [int(v) for v in values]
     return (C.c_uint32 * max(len(values), 1))(*values), len(values)
 

@@ -1021,12 +1021,8 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
             g->unit_counters.ensure(ctx, slots * sizeof(uint32_t), true);
             g->partial_slots_cap = slots;
         }
-        if (g->kernel == PSI_KERNEL_MMA && total_counters > 0) {
-            // Arrival counters return to zero by themselves; clearing them here keeps one aborted launch from
-            // poisoning the next step.
-            cuda_check(cudaMemsetAsync(g->unit_counters.ptr, 0, total_counters * sizeof(uint32_t), ctx->stream),
-                       "cudaMemsetAsync");
-        }
+        // Arrival counters start at zero (cleared when allocated) and every launch returns them to zero itself.
+        (void)total_counters;
 
         uint32_t* s = g->staging;
         std::fill(s, s + kScalarCount, 0u);
@@ -1348,12 +1344,44 @@ int32_t psi_gqa_decode_step_host(psi_gqa* g, psi_pages* pages, psi_table* table,
         const uint64_t esz = dtype_bytes(g->cfg.dtype);
         const uint64_t kv_cap = uint64_t(g->cfg.max_tokens) * g->cfg.num_kv_heads * g->cfg.head_dim * esz;
         const uint64_t q_cap = uint64_t(g->cfg.max_tokens) * g->cfg.num_q_heads * g->cfg.head_dim * esz;
+        const uint64_t kv_bytes = uint64_t(g->shape.num_tokens) * g->cfg.num_kv_heads * g->cfg.head_dim * esz;
+        const uint64_t q_bytes = uint64_t(g->shape.num_tokens) * g->cfg.num_q_heads * g->cfg.head_dim * esz;
         g->step_k.ensure(ctx, kv_cap, false);
         g->step_v.ensure(ctx, kv_cap, false);
         g->step_q.ensure(ctx, q_cap, false);
+        // Pinned, device-mapped host buffers: one launch pulls q/k/v over the host link into device staging (every
+        // work item re-reads its query rows, so they should be read from HBM, not from the host), and the attention
+        // launch stores `out` straight into the host buffer.  Two launches and one wait, no copy engine round trips.
+        auto mapped = [](const void* host) -> void* {
+            cudaPointerAttributes attr{};
+            if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+                attr.devicePointer != nullptr && (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15u) == 0) {
+                return attr.devicePointer;
+            }
+            (void)cudaGetLastError();
+            return nullptr;
+        };
+        if (g->kernel == PSI_KERNEL_MMA && kv_bytes % 16 == 0 && q_bytes % 16 == 0) {
+            void* dk = mapped(k_host);
+            void* dv = mapped(v_host);
+            void* dq = mapped(q_host);
+            void* dout = mapped(out_host);
+            if (dk != nullptr && dv != nullptr && dq != nullptr && dout != nullptr) {
+                const void* const src[3] = {dq, dk, dv};
+                void* const dst[3] = {g->step_q.ptr, g->step_k.ptr, g->step_v.ptr};
+                const uint64_t bytes[3] = {q_bytes, kv_bytes, kv_bytes};
+                ctx->launches += 1;
+                cuda_check(launch_host_pull(src, dst, bytes, ctx->stream), "host pull launch");
+                AttendParams p = attend_params(g, pages, table, layer, g->step_q.ptr);
+                p.out = dout;
+                p.new_k = g->step_k.ptr;
+                p.new_v = g->step_v.ptr;
+                run_attend(g, p);
+                cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+                return;
+            }
+        }
         g->step_out.ensure(ctx, q_cap, false);
-        const uint64_t kv_bytes = uint64_t(g->shape.num_tokens) * g->cfg.num_kv_heads * g->cfg.head_dim * esz;
-        const uint64_t q_bytes = uint64_t(g->shape.num_tokens) * g->cfg.num_q_heads * g->cfg.head_dim * esz;
         cuda_check(cudaMemcpyAsync(g->step_k.ptr, k_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D k");
         cuda_check(cudaMemcpyAsync(g->step_v.ptr, v_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D v");
         cuda_check(cudaMemcpyAsync(g->step_q.ptr, q_host, q_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D q");

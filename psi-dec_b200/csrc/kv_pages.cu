@@ -4,6 +4,8 @@
 // aligned, one thread moves one 16-byte chunk (a warp covers 512 contiguous bytes on both sides); otherwise one thread
 // moves one element.  The address algebra follows the reference shader
 // crates/inference-backend-metal/src/components/metal/gqa_kv_page_write.metal:20-52.
+#include <algorithm>
+
 #include "device_common.cuh"
 
 namespace psi {
@@ -60,6 +62,22 @@ __global__ void page_gather_kernel(GatherParams p, uint32_t units_per_row) {
         pages[(src_elem + v_region_offset(p.geo)) * scale / sizeof(Unit) + unit];
 }
 
+// Pulls up to three host-mapped buffers into device memory in one launch (16-byte chunks, grid-stride).
+struct PullParams {
+    const uint4* src[3];
+    uint4* dst[3];
+    uint64_t chunks[3];
+};
+
+__global__ void host_pull_kernel(PullParams p) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (int b = 0; b < 3; ++b) {
+        for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.chunks[b]; i += stride) {
+            p.dst[b][i] = p.src[b][i];
+        }
+    }
+}
+
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
 constexpr int kCopyThreads = 256;
@@ -97,6 +115,22 @@ cudaError_t launch_page_gather(const GatherParams& p, cudaStream_t stream) {
     } else {
         page_gather_kernel<uint16_t><<<static_cast<unsigned>(blocks), kCopyThreads, 0, stream>>>(p, units);
     }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_host_pull(const void* const src[3], void* const dst[3], const uint64_t bytes[3],
+                             cudaStream_t stream) {
+    PullParams p{};
+    uint64_t total = 0;
+    for (int b = 0; b < 3; ++b) {
+        p.src[b] = static_cast<const uint4*>(src[b]);
+        p.dst[b] = static_cast<uint4*>(dst[b]);
+        p.chunks[b] = bytes[b] / 16;
+        total += p.chunks[b];
+    }
+    if (total == 0) return cudaSuccess;
+    const uint64_t blocks = std::min<uint64_t>((total + kCopyThreads - 1) / kCopyThreads, 592);
+    host_pull_kernel<<<static_cast<unsigned>(blocks), kCopyThreads, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -81,11 +81,10 @@ class Spec:
 
     # -- batch description in the reference's request-level form ---------------------------------------------------------
     def batch(self):
-        req_slots = list(range(self.num_seqs))
-        token_indices = [int(c) for c in self.context_lens]
-        cu = [0]
-        for n in self.q_len:
-            cu.append(cu[-1] + int(n))
+        """(req_slots, token_indices, cu_tokens) as contiguous uint32 arrays."""
+        req_slots = np.arange(self.num_seqs, dtype=np.uint32)
+        token_indices = self.context_lens.astype(np.uint32)
+        cu = np.concatenate([[0], np.cumsum(self.q_len)]).astype(np.uint32)
         return req_slots, token_indices, cu
 
     def algorithmic_bytes(self) -> dict:

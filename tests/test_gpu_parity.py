@@ -539,13 +539,16 @@ def test_partials_and_combine_match_full_attention():
     full.close()
 
 
-def test_decode_step_through_host_buffers():
+@pytest.mark.parametrize("pinned", [True, False])
+def test_decode_step_through_host_buffers(pinned):
+    # pinned buffers are read and written in place by the launch; pageable ones are staged through device copies
     import torch
     spec = W.config(2, scale_down=8)
     s = W.Session(spec)
     before = checks.to_numpy_bits(s.arena)
-    kh, vh, qh = s.k.cpu().pin_memory(), s.v.cpu().pin_memory(), s.q.cpu().pin_memory()
-    oh = torch.zeros_like(qh).pin_memory()
+    pin = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
+    kh, vh, qh = pin(s.k.cpu()), pin(s.v.cpu()), pin(s.q.cpu())
+    oh = pin(torch.zeros_like(qh))
     s.gqa.decode_step_host(s.pages, s.table, 0, kh, vh, qh, oh)
     expected = checks.expected_arena_after_append(s, before)
     assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), expected)
