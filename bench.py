@@ -128,7 +128,8 @@ def bench_ours(args):
                        base.tokens_per_page, np.concatenate([s.context_lens for s in specs]),
                        np.concatenate([s.q_len for s in specs]), base.seed)
         spec = whole.shard(rank, world)
-    kernel_mode = {"auto": pkg.KERNEL_AUTO, "mma": pkg.KERNEL_MMA, "generic": pkg.KERNEL_GENERIC}[args.kernel]
+    kernel_mode = {"auto": pkg.KERNEL_AUTO, "mma": pkg.KERNEL_MMA, "generic": pkg.KERNEL_GENERIC,
+                   "mma_sync": pkg.KERNEL_MMA_SYNC}[args.kernel]
     session = W.Session(spec, device=local_rank, kernel_mode=kernel_mode)
     if world > 1 and args.config == 4:
         exchange = KvRangeExchange(session, rank, world, mode=args.exchange)
@@ -353,8 +354,9 @@ def main():
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--config", type=int, default=2, help="benchmark configuration (2 = the headline)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--kernel", choices=["auto", "mma", "generic"], default="auto",
-                        help="attention kernel: tensor-core mma (default where supported) or the CUDA-core kernel")
+    parser.add_argument("--kernel", choices=["auto", "mma", "generic", "mma_sync"], default="auto",
+                        help="attention kernel: tensor-core kernels (default where supported), the CUDA-core kernel, or "
+                             "mma_sync = tensor-core kernels with long query runs kept off the tcgen05 kernel")
     parser.add_argument("--exchange", choices=["p2p", "nccl"], default="p2p",
                         help="partial exchange of the KV-range-split configuration 4")
     args = parser.parse_args()

@@ -4,7 +4,7 @@ The directory name carries a hyphen, so the package is loaded by path (``__graft
 registered as ``psi_dec_b200``.
 """
 from .binding import (  # noqa: F401
-    BF16, F16, F32, CAPACITY_BUCKETED, CAPACITY_CALLER_TOKENS, CAPACITY_EXACT, KERNEL_AUTO, KERNEL_GENERIC, KERNEL_MMA,
+    BF16, F16, F32, CAPACITY_BUCKETED, CAPACITY_CALLER_TOKENS, CAPACITY_EXACT, KERNEL_AUTO, KERNEL_GENERIC, KERNEL_MMA, KERNEL_MMA_SYNC,
     PLAN_BALANCED, PLAN_REFERENCE, Context, GQA, GQAConfig, GQAPageTableLayout, GQAReplayShape, GQARequestPageTable,
     GQASplitKV, GQASplitKVVariant, NormRopeConfig, PageArena, PsiError, ReplayBucketPolicy, U32IDAllocator, attend_static, library, library_path, rope_parameters,
 )

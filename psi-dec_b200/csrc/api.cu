@@ -170,6 +170,7 @@ struct psi_gqa {
     DeviceBuffer step_k, step_v, step_q, step_out;  // psi_gqa_decode_step_host staging
     DeviceBuffer combine_ptrs;
     DeviceBuffer status_word;  // u32 written by bounded device-side waits
+    bool chunk_umma = false;   // long query runs on the tcgen05 kernel (else the mma.sync chunk kernel)
     DeviceBuffer norm_rope;    // q weight bf16[D] | k weight bf16[D] | inverse frequencies f32[rope_dim/2]
     psi_norm_rope_config norm_rope_cfg{};
     float norm_rope_attention_factor = 1.0f;
@@ -293,7 +294,12 @@ void run_attend(psi_gqa* g, const AttendParams& p) {
         c.items = reinterpret_cast<const DeviceItem*>(block_words(g, g->off_chunk_items));
         c.cta_item_begin = block_words(g, g->off_chunk_cta);
         LaunchScope scope(ctx, PSI_KERNEL_CLASS_ATTEND_CHUNK);
-        cuda_check(launch_attend_chunk(c, g->chunk.num_ctas(), ctx->stream), "attend (chunk) launch");
+        if (g->chunk_umma) {
+            c.status = static_cast<uint32_t*>(g->status_word.ptr);
+            cuda_check(launch_attend_chunk_umma(c, g->chunk.num_ctas(), ctx->stream), "attend (chunk, tcgen05) launch");
+        } else {
+            cuda_check(launch_attend_chunk(c, g->chunk.num_ctas(), ctx->stream), "attend (chunk) launch");
+        }
     }
     // The mma kernel merges a unit's partials in the CTA that delivers the last one; the generic kernel needs the
     // separate reduce pass.
@@ -848,7 +854,7 @@ int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out
         require(c.scale > 0.0f && std::isfinite(c.scale), "GQA scale must be positive");
         require(c.dtype <= PSI_DTYPE_F16, "unsupported GQA dtype");
         require(c.max_tokens > 0, "GQA batch metadata requires tokens");
-        require(c.plan_mode <= PSI_PLAN_REFERENCE && c.kernel_mode <= PSI_KERNEL_MMA, "unknown plan or kernel mode");
+        require(c.plan_mode <= PSI_PLAN_REFERENCE && c.kernel_mode <= PSI_KERNEL_MMA_SYNC, "unknown plan or kernel mode");
         validate_layout(c.layout);
         const uint64_t per_token = uint64_t(c.num_kv_heads) * c.head_dim * 2u * dtype_bytes(c.dtype);
         require(per_token <= kU32Max, "GQA K/V bytes per token must fit u32");
@@ -865,7 +871,7 @@ int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out
         g->tokens_per_page = c.page_bytes / static_cast<uint32_t>(per_token);
         g->geo = plan_geometry(c.num_q_heads, c.num_kv_heads);
         const bool mma_ok = attend_mma_supported(c.dtype, c.head_dim, g->tokens_per_page);
-        if (c.kernel_mode == PSI_KERNEL_MMA) require(mma_ok, "the mma kernel does not support this profile");
+        if (c.kernel_mode >= PSI_KERNEL_MMA) require(mma_ok, "the mma kernel does not support this profile");
         g->kernel = (c.kernel_mode == PSI_KERNEL_GENERIC || !mma_ok) ? PSI_KERNEL_GENERIC : PSI_KERNEL_MMA;
         const uint32_t per_sm =
             g->kernel == PSI_KERNEL_MMA ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm();
@@ -873,6 +879,8 @@ int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out
         g->item_start_cost = g->kernel == PSI_KERNEL_MMA ? 16u : 0u;
         g->chunk_supported = g->kernel == PSI_KERNEL_MMA && c.plan_mode == PSI_PLAN_BALANCED &&
                              attend_chunk_supported(c.dtype, c.head_dim, g->tokens_per_page);
+        g->chunk_umma = g->chunk_supported && c.kernel_mode != PSI_KERNEL_MMA_SYNC;
+        if (g->chunk_umma) g->status_word.ensure(ctx, sizeof(uint32_t), true);
         if (c.dtype != PSI_DTYPE_F16) {
             g->selector = std::make_unique<SplitKvSelector>(c.dtype, c.page_bytes, c.num_q_heads, c.num_kv_heads,
                                                             c.head_dim, false);

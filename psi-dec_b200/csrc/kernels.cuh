@@ -92,6 +92,7 @@ struct AttendParams {
     uint32_t tokens_per_tile;     // query tokens of one 16-row tile (plan geometry)
     uint32_t dtype;
     float scale_log2;             // scale * log2(e)
+    uint32_t* status;             // nullptr, or the word a bounded device-side wait writes PSI_ERR_TIMEOUT to
 };
 
 struct CombineParams {
@@ -125,6 +126,8 @@ cudaError_t launch_attend_mma(const AttendParams& p, uint32_t num_ctas, cudaStre
 // Long query runs: one CTA = up to eight query tiles of one request sharing one pass over the KV range.
 bool attend_chunk_supported(uint32_t dtype, uint32_t head_dim, uint32_t tokens_per_page);
 cudaError_t launch_attend_chunk(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
+// The same work items on the tcgen05 tensor cores (accumulators in TMEM); same profiles as launch_attend_chunk.
+cudaError_t launch_attend_chunk_umma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
 cudaError_t launch_attend_reduce(const AttendParams& p, uint32_t num_reduces, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
 // Release-stores `value` to *flag (local or peer memory) once all earlier work of the stream is visible system-wide.

@@ -427,14 +427,15 @@ def test_fused_step_equals_append_then_attend(index, scale_down):
     b.close()
 
 
+@pytest.mark.parametrize("engine", ["tcgen05", "mma_sync"])
 @pytest.mark.parametrize("max_ctas", [1, 5, 148])
 @pytest.mark.parametrize("heads,head_dim,page", [((16, 2), 256, 16), ((24, 4), 128, 8), ((8, 8), 128, 32)])
-def test_long_query_runs_through_the_chunk_kernel(heads, head_dim, page, max_ctas):
+def test_long_query_runs_through_the_chunk_kernel(heads, head_dim, page, max_ctas, engine):
     # chunked prefill mixed with decode rows: requests with long query runs take the chunk kernel (one pass over the
     # history for eight query tiles), units cut across CTAs leave partials that the last-arriving warp merges
     hq, hkv = heads
     spec = W.Spec("chunks", pkg.BF16, hq, hkv, head_dim, page, [700, 37, 0, 1500, 260], [96, 1, 40, 33, 2], seed=11)
-    s = W.Session(spec, max_ctas=max_ctas)
+    s = W.Session(spec, max_ctas=max_ctas, kernel_mode=pkg.KERNEL_MMA if engine == "tcgen05" else pkg.KERNEL_MMA_SYNC)
     stats = s.gqa.plan_stats()
     assert stats["chunk_ctas"] >= 1 and stats["chunk_items"] >= 1
     before = checks.to_numpy_bits(s.arena)
@@ -448,6 +449,7 @@ def test_long_query_runs_through_the_chunk_kernel(heads, head_dim, page, max_cta
     s.step_unfused()
     s.ctx.sync()
     assert float((s.out.float() - fused.float()).abs().max()) <= 1e-2
+    assert s.gqa.device_status() == 0  # no bounded wait of the tcgen05 kernel ran out
     s.close()
 
 
