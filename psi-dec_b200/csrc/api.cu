@@ -244,6 +244,7 @@ PageGeometry page_geometry(const psi_gqa* g, const psi_pages* pages, const psi_t
     geo.page_ids = table->dev;
     geo.elem_bytes = dtype_bytes(g->cfg.dtype);
     geo.page_elems = g->cfg.page_bytes / geo.elem_bytes;
+    geo.num_pages = pages->num_pages;
     geo.layer = layer;
     geo.num_layers = b.num_gqa_layers;
     geo.pages_per_req = static_cast<uint32_t>(table->row_words());
@@ -294,12 +295,14 @@ void run_attend(psi_gqa* g, const AttendParams& p) {
         c.items = reinterpret_cast<const DeviceItem*>(block_words(g, g->off_chunk_items));
         c.cta_item_begin = block_words(g, g->off_chunk_cta);
         LaunchScope scope(ctx, PSI_KERNEL_CLASS_ATTEND_CHUNK);
+        cudaError_t launched = cudaErrorNotSupported;
         if (g->chunk_umma) {
             c.status = static_cast<uint32_t*>(g->status_word.ptr);
-            cuda_check(launch_attend_chunk_umma(c, g->chunk.num_ctas(), ctx->stream), "attend (chunk, tcgen05) launch");
-        } else {
-            cuda_check(launch_attend_chunk(c, g->chunk.num_ctas(), ctx->stream), "attend (chunk) launch");
+            launched = launch_attend_chunk_umma(c, g->chunk.num_ctas(), ctx->stream);
         }
+        // an arena the TMA unit cannot address (alignment, size) keeps the mma.sync kernel
+        if (launched == cudaErrorNotSupported) launched = launch_attend_chunk(c, g->chunk.num_ctas(), ctx->stream);
+        cuda_check(launched, "attend (chunk) launch");
     }
     // The mma kernel merges a unit's partials in the CTA that delivers the last one; the generic kernel needs the
     // separate reduce pass.

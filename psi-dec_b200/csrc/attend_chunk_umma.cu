@@ -1,17 +1,26 @@
-// Multi-query attention for long query runs on the 5th-generation tensor cores (tcgen05 / TMEM).
+// Multi-query attention for long query runs on the 5th-generation tensor cores (tcgen05 / TMEM), K/V staged by TMA.
 //
 // Same work items as attend_chunk.cu (a super-tile of up to eight 16-row query tiles of one request and KV head: 128
-// rows = one native UMMA M tile), different engine: the 128 query rows sit in shared memory once, K and V tiles of 64
-// tokens are staged with 16-byte cp.async into 128-byte-swizzled operand layouts, one elected thread issues
-//   S[128x64]  = Q[128xD] . K^T      (tcgen05.mma, both operands K-major from shared memory, accumulator in TMEM)
-//   O[128xD]  += P[128x64] . V       (P from shared memory, V as an MN-major operand, accumulator in TMEM)
-// and the 128 threads own one accumulator row each: they read their S row from TMEM (tcgen05.ld), apply the causal
-// limit and the online softmax without any cross-thread traffic, write P back as an MMA operand, and rescale their O
-// row in TMEM only when a running max moved.  Completion of the MMAs is tracked with mbarriers (tcgen05.commit); every
-// wait is bounded and reports PSI_ERR_TIMEOUT through the status word instead of hanging.  The epilogue (direct
-// output, per-tile partial slots, last-arriver merge) matches attend_chunk.cu.
+// rows = one native UMMA M tile), different engine.  The 128 query rows sit in shared memory once per item; K and V
+// tiles of 64 tokens are brought from their pages by TMA (one box of min(tokens_per_page, 64) rows x 64 elements per
+// copy, written with the 128-byte swizzle the MMA descriptors expect) into two K and two V slots.  Roles:
+//   warps 0-3 (128 threads): one accumulator row each.  Read the S row from TMEM (tcgen05.ld), apply the causal limit
+//       and the online softmax without any cross-thread traffic, write P back to shared memory as an MMA operand,
+//       rescale their O row in TMEM only when a running max moved; epilogue, partial slots and last-arriver merge as
+//       in attend_chunk.cu.
+//   warp 4: lane 0 issues the TMA copies and the MMAs
+//         S[128x64]  = Q[128xD] . K^T    (both operands K-major from shared memory, accumulator in TMEM, two buffers)
+//         O[128xD]  += P[128x64] . V     (V as an MN-major operand, accumulator in TMEM)
+//       so that Q K^T of tile i+1 runs under the softmax of tile i and P V of tile i under the softmax of tile i+1.
+//       Tiles that touch this step's not-yet-paged rows (fused step) or end beyond the item are copied by the whole
+//       warp with zero-filling 16-byte cp.async instead.
+// All hand-offs are mbarriers (TMA byte counts, tcgen05.commit, thread arrivals); every wait is bounded and reports
+// PSI_ERR_TIMEOUT through the status word instead of hanging, and the kernel frees its TMEM on every path.
 //
 // Arithmetic replaced: crates/inference-backend-metal/src/components/metal/gqa_split_kv_tiled_q.metal:49-378.
+#include <cuda.h>
+
+#include <mutex>
 #include <type_traits>
 
 #include "mma_common.cuh"
@@ -20,7 +29,8 @@ namespace psi {
 
 namespace {
 
-constexpr uint32_t kUmmaThreads = 128;
+constexpr uint32_t kRowThreads = 128;   // warps 0-3: one accumulator row per thread
+constexpr uint32_t kUmmaThreads = 192;  // + warp 4: MMA issue, warp 5: K/V tiles into the shared-memory ring
 constexpr uint32_t kUmmaM = 128;   // query rows per CTA = TMEM lanes
 constexpr uint32_t kUmmaN = 64;    // KV tokens per tile
 constexpr uint32_t kMaxPolls = 200000;
@@ -41,14 +51,6 @@ __device__ __forceinline__ uint32_t umma_idesc(uint32_t n, bool b_mn_major) {
     const uint32_t format = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
     return (1u << 4) | (format << 7) | (format << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) |
            ((kUmmaM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_issue(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
-        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-        : "memory");
 }
 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -112,29 +114,91 @@ __device__ __forceinline__ uint32_t operand_offset(uint32_t rows, uint32_t row, 
     return (chunk >> 3) * rows * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// One TMA box of the page arena (viewed as [page][row in page][element]) into shared memory; completion is counted
+// in bytes on `bar`.  c0 (elements) is always a multiple of 64, i.e. of 128 bytes.
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, uint32_t bar, uint32_t c0, uint32_t c1,
+                                             uint32_t c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void row_threads_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_issue_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_store32_bits(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+        "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+        "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+        "r"(v[31])
+        : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared-memory ring slots of one K or V tile, and how far the lazily kept softmax reference may lag the running max
+// (log2 domain): P then stays below 2^8, well inside bf16/f16, and O is rescaled only on a real jump.
+template <int D>
+struct Ring {
+    static constexpr uint32_t kSlots = D == 256 ? 7u : 12u;
+};
+constexpr float kRescaleThreshold = 8.0f;
+
 template <typename T, int D>
-__global__ void __launch_bounds__(kUmmaThreads, 1) attend_chunk_umma_kernel(AttendParams p) {
-    constexpr uint32_t kChunks = D / 8;                       // 16-byte chunks per row of Q / K / V
-    constexpr uint32_t kQBytes = D * 2 * kUmmaM;              // [D/64][128][64]
-    constexpr uint32_t kTileBytes = D * 2 * kUmmaN;           // one K or V tile: [D/64][64][64]
-    constexpr uint32_t kStageBytes = 2 * kTileBytes;          // K then V
-    constexpr uint32_t kPOffset = kQBytes + 2 * kStageBytes;  // P: [1][128][64]
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+    attend_chunk_umma_kernel(const AttendParams p, const __grid_constant__ CUtensorMap kv_map, const uint32_t box_rows) {
+    constexpr uint32_t kChunks = D / 8;               // 16-byte chunks per row of K / V
+    constexpr uint32_t kTileBytes = D * 2 * kUmmaN;   // one K or V tile: [D/64][64][64]
+    constexpr uint32_t kSlots = Ring<D>::kSlots;
     constexpr uint32_t kTmemColumns = 512;
-    constexpr uint32_t kColS = 0, kColO = kUmmaN;
+    // TMEM columns: Q as an MMA A operand (two 16-bit elements per column), two S buffers whose first half is
+    // overwritten by P (again two elements per column), O
+    constexpr uint32_t kColQ = 0, kColS = D / 2, kColO = D / 2 + 2 * kUmmaN;
+    static_assert(kColO + D <= kTmemColumns, "Q, S and O share one TMEM allocation");
+    // barriers
+    constexpr uint32_t kBarFull = 0, kBarEmpty = kSlots, kBarS = 2 * kSlots, kBarO = kBarS + 2, kBarP = kBarO + 2,
+                       kBarQ = kBarP + 2, kNumBarriers = kBarQ + 1;
 
     const uint32_t cta = blockIdx.x;
     if (cta >= p.scalars[kScalarNumChunkCtas]) return;
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_s, bar_o;
-    __shared__ uint32_t tmem_base_s, abort_s, last_s[kWarps];
+    __shared__ __align__(8) uint64_t bars[kNumBarriers];
+    __shared__ uint32_t tmem_base_s, abort_s, last_s[8];
 
-    const uint32_t tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // the swizzled operand layouts repeat every 1024 bytes: place them on that boundary whatever the toolchain did
-    const uint32_t smem_pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
-    unsigned char* smem = smem_raw + smem_pad;
-    const uint32_t smem_base = smem_u32(smem);
-    const uint32_t bar_s_addr = smem_u32(&bar_s), bar_o_addr = smem_u32(&bar_o);
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](uint32_t which) { return bar0 + which * 8; };
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
@@ -143,8 +207,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) attend_chunk_umma_kernel(Atte
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_s_addr), "r"(1u) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_o_addr), "r"(1u) : "memory");
+        for (uint32_t b = 0; b < kBarP; ++b) mbar_init(bar(b), 1);
+        for (uint32_t b = kBarP; b < kNumBarriers; ++b) mbar_init(bar(b), kRowThreads);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         abort_s = 0;
     }
@@ -152,12 +216,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) attend_chunk_umma_kernel(Atte
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
-    const uint32_t lane_base = (warp * 32u) << 16;            // this warp's TMEM lanes
-    const uint32_t tmem_s = tmem + kColS, tmem_o = tmem + kColO;
-    uint32_t phase_s = 0, phase_o = 0;
-
-    const uint32_t idesc_qk = umma_idesc<T>(kUmmaN, false);
-    const uint32_t idesc_pv = umma_idesc<T>(D, true);
 
     const uint32_t page_mask = p.geo.tokens_per_page - 1;
     const uint32_t page_shift = 31 - __clz(p.geo.tokens_per_page);
@@ -168,285 +226,396 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) attend_chunk_umma_kernel(Atte
 
     // A wait that ran out flags the launch and lets every later wait fall through: results are then garbage, the
     // status word says so, and the kernel still frees its TMEM and returns.
-    auto wait = [&](uint32_t bar, uint32_t parity) {
-        if (*reinterpret_cast<volatile uint32_t*>(&abort_s)) return;
-        if (!mbar_wait(bar, parity)) {
+    auto wait = [&](uint32_t which, uint32_t parity) {
+        if (*reinterpret_cast<volatile uint32_t*>(&abort_s) == 0 && !mbar_wait(bar(which), parity & 1)) {
             abort_s = 1;
             if (p.status != nullptr) atomicExch(p.status, static_cast<uint32_t>(PSI_ERR_TIMEOUT));
         }
+        __syncwarp();  // whole warps wait together; the TMEM accesses that follow are warp-collective
     };
 
+    // Tiles, ring fills (K of tile t = fill 2t, V = fill 2t + 1) and items are counted over the whole launch, the
+    // same way in every role: ring slot = fill % kSlots with barrier phase fill / kSlots; the S, O and P barriers come
+    // in pairs indexed by tile % 2 with phase tile / 2, so that a barrier cannot complete a second time before its
+    // waiter has seen the first (a parity wait cannot tell two completions from none); Q takes the item count.
+    uint32_t tile_base = 0, item_count = 0;
     const uint32_t item_begin = p.cta_item_begin[cta], item_end = p.cta_item_begin[cta + 1];
-    for (uint32_t index = item_begin; index < item_end; ++index) {
-        const ItemView v = view_item(p, index);
-        __syncthreads();  // the previous item is done with shared memory
 
-        // row of this thread: 16-row tile w, row rr inside it -> (token, head) of the super-tile
-        const uint32_t w = tid >> 4, rr = tid & 15;
-        const uint32_t token_off = w * p.tokens_per_tile + rr / v.num_heads;
-        const bool row_valid = rr < p.tokens_per_tile * v.num_heads && token_off < v.num_tokens;
-        const uint32_t limit = row_valid ? min(v.kv_end, v.first_pos + token_off + 1) : v.kv_end;
-        const uint32_t min_limit = min(v.kv_end, v.first_pos + 1);
-        const uint64_t out_row =
-            static_cast<uint64_t>(v.flat_begin + (row_valid ? token_off : 0)) * p.num_q_heads + v.head0 + rr % v.num_heads;
-        const uint32_t paged_end = fused ? min(v.kv_end, v.new_begin) : v.kv_end;
-        const uint32_t* row_ids = table_row(p.geo, v.req_slot);
-        const uint64_t head_bytes = static_cast<uint64_t>(v.kv_head) * p.geo.tokens_per_page * (D * 2);
-        const uint32_t first_tile = v.kv_begin / kUmmaN;
-        const uint32_t num_tiles = (v.kv_end + kUmmaN - 1) / kUmmaN - first_tile;
-
-        // K and V tile i -> stage i % 2, 16 bytes per cp.async, rows = tokens, swizzled operand layout
-        auto issue = [&](uint32_t i) {
-            const uint32_t stage = smem_base + kQBytes + (i & 1) * kStageBytes;
-            const uint32_t token0 = (first_tile + i) * kUmmaN;
-            for (uint32_t c = tid; c < kUmmaN * kChunks; c += kUmmaThreads) {
-                const uint32_t row = c / kChunks, chunk = c % kChunks;
-                const uint32_t token = token0 + row;
-                const unsigned char* k_src = pages;
-                const unsigned char* v_src = pages;
-                uint32_t bytes = 16u;
-                if (token >= v.kv_end) {
-                    bytes = 0u;  // beyond the item: zero-fill
-                } else if (token >= paged_end) {
-                    const uint64_t fresh = (static_cast<uint64_t>(v.flat_req_begin + (token - v.new_begin)) * p.geo.num_kv_heads +
-                                            v.kv_head) * (D * 2) + chunk * 16;
-                    k_src = static_cast<const unsigned char*>(p.new_k) + fresh;
-                    v_src = static_cast<const unsigned char*>(p.new_v) + fresh;
-                } else {
-                    k_src = pages + static_cast<uint64_t>(row_ids[token >> page_shift]) * page_bytes + head_bytes +
-                            (token & page_mask) * (D * 2) + chunk * 16;
-                    v_src = k_src + v_region_bytes;
-                }
-                const uint32_t dst = stage + operand_offset(kUmmaN, row, chunk);
-                cp_async_16(dst, k_src, bytes);
-                cp_async_16(dst + kTileBytes, v_src, bytes);
-            }
-        };
-
-        if (num_tiles > 0) issue(0);
-        cp_async_commit();
-
-        // query rows (zero for rows the super-tile does not have), and in the fused step this item's K/V page writes
-        for (uint32_t c = tid; c < kUmmaM * kChunks; c += kUmmaThreads) {
-            const uint32_t row = c / kChunks, chunk = c % kChunks;
-            const uint32_t rw = row >> 4, rrr = row & 15;
-            const uint32_t tok = rw * p.tokens_per_tile + rrr / v.num_heads;
-            uint4 value = make_uint4(0, 0, 0, 0);
-            if (rrr < p.tokens_per_tile * v.num_heads && tok < v.num_tokens) {
-                const uint64_t grow = static_cast<uint64_t>(v.flat_begin + tok) * p.num_q_heads + v.head0 + rrr % v.num_heads;
-                value = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + grow * D + chunk * 8);
-            }
-            *reinterpret_cast<uint4*>(smem + operand_offset(kUmmaM, row, chunk)) = value;
-        }
-        if (fused && v.writes_kv) {
-            for (uint32_t i = tid; i < v.num_tokens * 2 * kChunks; i += kUmmaThreads) {
-                const uint32_t c = i % kChunks, which = (i / kChunks) & 1, j = i / (2 * kChunks);
-                const uint32_t pos = v.first_pos + j;
-                if (pos >= v.kv_begin && pos < v.kv_end) {
-                    const unsigned char* fresh = static_cast<const unsigned char*>(which ? p.new_v : p.new_k);
-                    const uint4 value = *reinterpret_cast<const uint4*>(
-                        fresh + (static_cast<uint64_t>(v.flat_begin + j) * p.geo.num_kv_heads + v.kv_head) * (D * 2) + c * 16);
-                    unsigned char* dst = const_cast<unsigned char*>(pages) +
-                                         static_cast<uint64_t>(row_ids[pos >> page_shift]) * page_bytes + head_bytes +
-                                         (which ? v_region_bytes : 0) + (pos & page_mask) * (D * 2) + c * 16;
-                    *reinterpret_cast<uint4*>(dst) = value;
-                }
-            }
-        }
-
-        float row_max = -INFINITY, row_sum = 0.0f;
-        for (uint32_t i = 0; i < num_tiles; ++i) {
-            if (i + 1 < num_tiles) issue(i + 1);  // its stage was released when P V of tile i-1 completed
-            cp_async_commit();
-            cp_async_wait<1>();                   // tile i (and, for i == 0, the query rows) have landed
-            fence_async_smem();
-            tc_fence_before();
-            __syncthreads();
-            tc_fence_after();
-            const uint32_t stage = smem_base + kQBytes + (i & 1) * kStageBytes;
-            const uint32_t token0 = (first_tile + i) * kUmmaN;
-
-            // ---- S = Q K^T --------------------------------------------------------------------------------------------
-            if (tid == 0) {
-#pragma unroll
-                for (uint32_t ks = 0; ks < D / 16; ++ks) {
-                    const uint64_t a = umma_desc(smem_base + (ks >> 2) * (kUmmaM * 128) + (ks & 3) * 32, 16, 1024);
-                    const uint64_t b = umma_desc(stage + (ks >> 2) * (kUmmaN * 128) + (ks & 3) * 32, 16, 1024);
-                    umma_issue(tmem_s, a, b, idesc_qk, ks > 0);
-                }
-                umma_commit(bar_s_addr);
-            }
-            __syncwarp();
-            wait(bar_s_addr, phase_s);
-            phase_s ^= 1;
-            tc_fence_after();
-
-            // ---- this thread's row: scale, visibility, online softmax ------------------------------------------------------
-            float s[kUmmaN];
-            {
-                float part[32];
-                tmem_load32(tmem_s + lane_base, part);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) s[c] = part[c] * p.scale_log2;
-                tmem_load32(tmem_s + lane_base + 32, part);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) s[32 + c] = part[c] * p.scale_log2;
-            }
-            if (token0 < v.kv_begin || token0 + kUmmaN > min_limit) {
-#pragma unroll
-                for (int c = 0; c < int(kUmmaN); ++c) {
-                    const uint32_t token = token0 + c;
-                    if (token >= limit || token < v.kv_begin) s[c] = -INFINITY;
-                }
-            }
-            float tile_max = s[0];
-#pragma unroll
-            for (int c = 1; c < int(kUmmaN); ++c) tile_max = fmaxf(tile_max, s[c]);
-            const float new_max = fmaxf(row_max, tile_max);
-            const bool moved = new_max > row_max;
-            if (i > 0 && __any_sync(0xFFFFFFFFu, moved)) {
-                // rescale this warp's O rows in TMEM (P V of the previous tile has completed: waited below)
-                const float corr = new_max == -INFINITY ? 1.0f : exp2f(row_max - new_max);
-                row_sum *= corr;
-#pragma unroll 1
-                for (uint32_t c = 0; c < uint32_t(D); c += 32) {
-                    float o[32];
-                    tmem_load32(tmem_o + lane_base + c, o);
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) o[e] *= corr;
-                    tmem_store32(tmem_o + lane_base + c, o);
-                }
-                tmem_store_wait();
-            }
-            row_max = new_max;
-            const float base = row_max == -INFINITY ? 0.0f : row_max;
-            float tile_sum = 0.0f;
-#pragma unroll
-            for (int c8 = 0; c8 < int(kUmmaN) / 8; ++c8) {
-                float e[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    e[k] = exp2f(s[c8 * 8 + k] - base);
-                    tile_sum += e[k];
-                }
-                const uint4 packed = make_uint4(Mma<T>::pack(e[0], e[1]), Mma<T>::pack(e[2], e[3]), Mma<T>::pack(e[4], e[5]),
-                                                Mma<T>::pack(e[6], e[7]));
-                *reinterpret_cast<uint4*>(smem + kPOffset + operand_offset(kUmmaM, tid, c8)) = packed;
-            }
-            row_sum += tile_sum;
-            fence_async_smem();
-            tc_fence_before();
-            __syncthreads();
-            tc_fence_after();
-
-            // ---- O += P V ------------------------------------------------------------------------------------------------
-            if (tid == 0) {
-#pragma unroll
-                for (uint32_t ks = 0; ks < kUmmaN / 16; ++ks) {
-                    const uint64_t a = umma_desc(smem_base + kPOffset + ks * 32, 16, 1024);
-                    const uint64_t b = umma_desc(stage + kTileBytes + ks * 2048, kUmmaN * 128, 1024);
-                    umma_issue(tmem_o, a, b, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
-                }
-                umma_commit(bar_o_addr);
-            }
-            __syncwarp();
-            wait(bar_o_addr, phase_o);  // O, P and this tile's stage are free again
-            phase_o ^= 1;
-            tc_fence_after();
-        }
-        cp_async_wait<0>();
-
-        // ---- epilogue: every thread finishes its own row ---------------------------------------------------------------
-        const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
-        const bool is_partial = v.partial_slot != kU32Max;
-        const uint64_t prow = is_partial ? static_cast<uint64_t>(v.partial_slot + w) * kMaxRows + rr : 0;
-#pragma unroll 1
-        for (uint32_t c = 0; c < uint32_t(D); c += 32) {
-            float o[32];
-            if (num_tiles > 0) {
-                tmem_load32(tmem_o + lane_base + c, o);
-            } else {
-#pragma unroll
-                for (int e = 0; e < 32; ++e) o[e] = 0.0f;
-            }
-            if (!row_valid) continue;  // after the warp-collective load
-#pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-                const float4 value = make_float4(o[e] * inv, o[e + 1] * inv, o[e + 2] * inv, o[e + 3] * inv);
-                if (is_partial) {
-                    *reinterpret_cast<float4*>(p.partial_o + prow * D + c + e) = value;
-                } else if (p.ext_o != nullptr) {
-                    *reinterpret_cast<float4*>(p.ext_o + out_row * D + c + e) = value;
-                } else {
-                    store_out4<T>(p, out_row * D + c + e, value);
-                }
-            }
-        }
-        if (row_valid) {
-            if (is_partial) {
-                p.partial_m[prow] = row_max;
-                p.partial_l[prow] = row_sum;
-            } else if (p.ext_o != nullptr) {
-                p.ext_m[out_row] = row_max * kLn2;
-                p.ext_l[out_row] = row_sum;
-            }
-        }
-        tc_fence_before();
-
-        // ---- units shared with other CTAs: whoever delivers a tile's last partial merges it ---------------------------
-        if (is_partial) {
-            __threadfence();
-            __syncthreads();
-            if (tid < kWarps) {
-                const bool has_rows = tid * p.tokens_per_tile < v.num_tokens;
-                last_s[tid] = has_rows && atomicAdd(p.unit_counters + v.reduce_unit + tid, 1u) == v.unit_num_items - 1;
-            }
-            __syncthreads();
-            for (uint32_t tile = 0; tile < uint32_t(kWarps); ++tile) {
-                if (!last_s[tile]) continue;
-                __threadfence();
-                const uint32_t tile_tokens = min(p.tokens_per_tile, v.num_tokens - tile * p.tokens_per_tile);
-                const uint32_t tile_rows = tile_tokens * v.num_heads;
-                for (uint32_t i = tid; i < tile_rows * (D / 4); i += kUmmaThreads) {
-                    const uint32_t r = i / (D / 4), c4 = i % (D / 4);
-                    float global_max = -INFINITY;
-#pragma unroll 4
-                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
-                        const uint64_t row = static_cast<uint64_t>(v.unit_first_slot + s_i * kWarps + tile) * kMaxRows + r;
-                        global_max = fmaxf(global_max, __ldcg(p.partial_m + row));
+    if (warp == 5) {
+        // ================================ producer: K/V tiles into the ring ==========================================
+        const uint32_t v_rows = p.geo.num_kv_heads * p.geo.tokens_per_page;  // rows of a page's K region
+        for (uint32_t index = item_begin; index < item_end; ++index) {
+            const ItemView v = view_item(p, index);
+            const uint32_t paged_end = fused ? min(v.kv_end, v.new_begin) : v.kv_end;
+            const uint32_t* row_ids = table_row(p.geo, v.req_slot);
+            const uint64_t head_bytes = static_cast<uint64_t>(v.kv_head) * p.geo.tokens_per_page * (D * 2);
+            const uint32_t head_row = v.kv_head * p.geo.tokens_per_page;
+            const uint32_t first_tile = v.kv_begin / kUmmaN;
+            const uint32_t num_tiles = (v.kv_end + kUmmaN - 1) / kUmmaN - first_tile;
+            uint32_t window_base = kU32Max, window_ids = 0;  // 32 page ids of the request, one per lane
+            for (uint32_t i = 0; i < num_tiles; ++i) {
+                const uint32_t token0 = (first_tile + i) * kUmmaN;
+                const bool whole = token0 + kUmmaN <= paged_end;
+                if (whole) {
+                    const uint32_t first_page = token0 >> page_shift, last_page = (token0 + kUmmaN - 1) >> page_shift;
+                    if (first_page < window_base || last_page >= window_base + 32) {
+                        window_base = first_page;
+                        const uint32_t page_index = first_page + lane;
+                        window_ids = page_index <= ((paged_end - 1) >> page_shift) ? row_ids[page_index] : 0u;
                     }
-                    float sum = 0.0f;
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
-                        const uint64_t row = static_cast<uint64_t>(v.unit_first_slot + s_i * kWarps + tile) * kMaxRows + r;
-                        const float pm = __ldcg(p.partial_m + row);
-                        const float weight = pm == -INFINITY ? 0.0f : exp2f(pm - global_max) * __ldcg(p.partial_l + row);
-                        const float4 part = __ldcg(reinterpret_cast<const float4*>(p.partial_o + row * D + 4 * c4));
-                        sum += weight;
-                        acc.x += weight * part.x;
-                        acc.y += weight * part.y;
-                        acc.z += weight * part.z;
-                        acc.w += weight * part.w;
-                    }
-                    const float scale = sum > 0.0f ? 1.0f / sum : 0.0f;
-                    acc.x *= scale;
-                    acc.y *= scale;
-                    acc.z *= scale;
-                    acc.w *= scale;
-                    const uint64_t row = static_cast<uint64_t>(v.flat_begin + tile * p.tokens_per_tile + r / v.num_heads) * p.num_q_heads +
-                                         v.head0 + r % v.num_heads;
-                    if (p.ext_o != nullptr) {
-                        *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc;
-                        if (c4 == 0) {
-                            p.ext_m[row] = global_max * kLn2;
-                            p.ext_l[row] = sum;
+                }
+                for (uint32_t which = 0; which < 2; ++which) {
+                    const uint32_t fill = 2 * (tile_base + i) + which, slot = fill % kSlots, use = fill / kSlots;
+                    const uint32_t dst = smem_base + slot * kTileBytes;
+                    if (use > 0) wait(kBarEmpty + slot, use - 1);  // the MMAs that read the slot's previous tile are done
+                    if (whole) {
+                        if (lane == 0) mbar_expect_tx(bar(kBarFull + slot), kTileBytes);
+                        for (uint32_t row = 0; row < kUmmaN; row += box_rows) {
+                            const uint32_t token = token0 + row;
+                            const uint32_t page = __shfl_sync(0xFFFFFFFFu, window_ids, (token >> page_shift) - window_base);
+                            const uint32_t page_row = which * v_rows + head_row + (token & page_mask);
+                            if (lane == 0) {
+#pragma unroll
+                                for (uint32_t kb = 0; kb < uint32_t(D) / 64; ++kb)
+                                    tma_load_box(dst + kb * (kUmmaN * 128) + row * 128, &kv_map, bar(kBarFull + slot), kb * 64,
+                                                 page_row, page);
+                            }
                         }
                     } else {
-                        store_out4<T>(p, row * D + 4 * c4, acc);
+                        // ragged tile: rows beyond the item are zero, rows of this step come from the step's K/V arrays
+                        for (uint32_t c = lane; c < kUmmaN * kChunks; c += 32) {
+                            const uint32_t row = c / kChunks, chunk = c % kChunks;
+                            const uint32_t token = token0 + row;
+                            const unsigned char* src = pages;
+                            uint32_t bytes = 16u;
+                            if (token >= v.kv_end) {
+                                bytes = 0u;
+                            } else if (token >= paged_end) {
+                                src = static_cast<const unsigned char*>(which ? p.new_v : p.new_k) +
+                                      (static_cast<uint64_t>(v.flat_req_begin + (token - v.new_begin)) * p.geo.num_kv_heads +
+                                       v.kv_head) * (D * 2) + chunk * 16;
+                            } else {
+                                src = pages + static_cast<uint64_t>(row_ids[token >> page_shift]) * page_bytes + head_bytes +
+                                      (which ? v_region_bytes : 0) + (token & page_mask) * (D * 2) + chunk * 16;
+                            }
+                            cp_async_16(dst + operand_offset(kUmmaN, row, chunk), src, bytes);
+                        }
+                        cp_async_commit();
+                        cp_async_wait<0>();
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(kBarFull + slot));
+                    }
+                    __syncwarp();
+                }
+            }
+            tile_base += num_tiles;
+        }
+        // the CTA does not go away with its own bulk copies in flight: every slot's last fill has landed (a bounded
+        // wait of its own, also after an earlier wait gave up)
+        const uint32_t fills = 2 * tile_base;
+        for (uint32_t back = 1; back <= kSlots && back <= fills; ++back) {
+            const uint32_t fill = fills - back;
+            mbar_wait(bar(kBarFull + fill % kSlots), (fill / kSlots) & 1);
+        }
+    } else if (warp == 4) {
+        // ================================ MMA issue ========================================================================
+        const uint32_t idesc_qk = umma_idesc<T>(kUmmaN, false);
+        const uint32_t idesc_pv = umma_idesc<T>(D, true);
+        for (uint32_t index = item_begin; index < item_end; ++index, ++item_count) {
+            const ItemView v = view_item(p, index);
+            const uint32_t first_tile = v.kv_begin / kUmmaN;
+            const uint32_t num_tiles = (v.kv_end + kUmmaN - 1) / kUmmaN - first_tile;
+
+            // S[tile % 2] = Q K^T of local tile i; frees the K slot when done
+            auto issue_qk = [&](uint32_t i) {
+                const uint32_t tile = tile_base + i, fill = 2 * tile, slot = fill % kSlots;
+                wait(kBarFull + slot, fill / kSlots);
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t k_slot = smem_base + slot * kTileBytes;
+#pragma unroll
+                    for (uint32_t ks = 0; ks < uint32_t(D) / 16; ++ks) {
+                        const uint64_t b = umma_desc(k_slot + (ks >> 2) * (kUmmaN * 128) + (ks & 3) * 32, 16, 1024);
+                        umma_issue_ts(tmem + kColS + (tile & 1) * kUmmaN, tmem + kColQ + ks * 8, b, idesc_qk, ks > 0);
+                    }
+                    umma_commit(bar(kBarS + (tile & 1)));
+                    umma_commit(bar(kBarEmpty + slot));
+                }
+                __syncwarp();
+            };
+
+            wait(kBarQ, item_count);  // the item's query rows are in TMEM; the rows are done with the previous item
+            if (num_tiles > 0) issue_qk(0);
+            for (uint32_t i = 0; i < num_tiles; ++i) {
+                const uint32_t tile = tile_base + i, fill = 2 * tile + 1, slot = fill % kSlots;
+                if (i + 1 < num_tiles) issue_qk(i + 1);  // runs under the softmax of tile i
+                wait(kBarP + (tile & 1), tile >> 1);      // P of tile i is in TMEM (over the first half of its S buffer)
+                wait(kBarFull + slot, fill / kSlots);
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t v_slot = smem_base + slot * kTileBytes;
+#pragma unroll
+                    for (uint32_t ks = 0; ks < kUmmaN / 16; ++ks) {
+                        const uint64_t b = umma_desc(v_slot + ks * 2048, kUmmaN * 128, 1024);
+                        umma_issue_ts(tmem + kColO, tmem + kColS + (tile & 1) * kUmmaN + ks * 8, b, idesc_pv,
+                                      (i > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(bar(kBarO + (tile & 1)));
+                    umma_commit(bar(kBarEmpty + slot));
+                }
+                __syncwarp();
+            }
+            tile_base += num_tiles;
+        }
+    } else {
+        // ================================ one accumulator row per thread ===============================================
+        const uint32_t lane_base = (warp * 32u) << 16;  // this warp's TMEM lanes
+        const uint32_t tmem_o = tmem + kColO;
+        for (uint32_t index = item_begin; index < item_end; ++index, ++item_count) {
+            const ItemView v = view_item(p, index);
+
+            // row of this thread: 16-row tile w, row rr inside it -> (token, head) of the super-tile
+            const uint32_t w = tid >> 4, rr = tid & 15;
+            const uint32_t token_off = w * p.tokens_per_tile + rr / v.num_heads;
+            const bool row_valid = rr < p.tokens_per_tile * v.num_heads && token_off < v.num_tokens;
+            const uint32_t limit = row_valid ? min(v.kv_end, v.first_pos + token_off + 1) : v.kv_end;
+            const uint32_t min_limit = min(v.kv_end, v.first_pos + 1);
+            const uint64_t out_row = static_cast<uint64_t>(v.flat_begin + (row_valid ? token_off : 0)) * p.num_q_heads +
+                                     v.head0 + rr % v.num_heads;
+            const uint32_t first_tile = v.kv_begin / kUmmaN;
+            const uint32_t num_tiles = (v.kv_end + kUmmaN - 1) / kUmmaN - first_tile;
+
+            // this thread's query row into its TMEM lane (zero for rows the super-tile does not have); every Q K^T of
+            // the previous item has completed
+            {
+                const uint4* q_row = reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + out_row * D);
+#pragma unroll 1
+                for (uint32_t c = 0; c < uint32_t(D) / 2; c += 32) {
+                    uint32_t regs[32];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 value = row_valid ? q_row[c / 4 + j] : make_uint4(0, 0, 0, 0);
+                        regs[4 * j] = value.x;
+                        regs[4 * j + 1] = value.y;
+                        regs[4 * j + 2] = value.z;
+                        regs[4 * j + 3] = value.w;
+                    }
+                    __syncwarp();
+                    tmem_store32_bits(tmem + kColQ + lane_base + c, regs);
+                }
+                tmem_store_wait();
+                tc_fence_before();
+                mbar_arrive(bar(kBarQ));
+            }
+
+            // in the fused step: this item's share of the step's K/V rows into their pages
+            if (fused && v.writes_kv) {
+                const uint32_t* row_ids = table_row(p.geo, v.req_slot);
+                const uint64_t head_bytes = static_cast<uint64_t>(v.kv_head) * p.geo.tokens_per_page * (D * 2);
+                for (uint32_t i = tid; i < v.num_tokens * 2 * kChunks; i += kRowThreads) {
+                    const uint32_t c = i % kChunks, which = (i / kChunks) & 1, j = i / (2 * kChunks);
+                    const uint32_t pos = v.first_pos + j;
+                    if (pos >= v.kv_begin && pos < v.kv_end) {
+                        const unsigned char* fresh = static_cast<const unsigned char*>(which ? p.new_v : p.new_k);
+                        const uint4 value = *reinterpret_cast<const uint4*>(
+                            fresh + (static_cast<uint64_t>(v.flat_begin + j) * p.geo.num_kv_heads + v.kv_head) * (D * 2) + c * 16);
+                        unsigned char* dst = const_cast<unsigned char*>(pages) +
+                                             static_cast<uint64_t>(row_ids[pos >> page_shift]) * page_bytes + head_bytes +
+                                             (which ? v_region_bytes : 0) + (pos & page_mask) * (D * 2) + c * 16;
+                        *reinterpret_cast<uint4*>(dst) = value;
                     }
                 }
-                if (tid == 0) p.unit_counters[v.reduce_unit + tile] = 0;  // ready for the next launch
+                __syncwarp();
+            }
+
+            // softmax state in the log2 domain: `row_ref` is the reference the exponentials are taken against (it
+            // trails the true running max `row_max` by at most kRescaleThreshold), `row_sum` is relative to it
+            float row_ref = -INFINITY, row_max = -INFINITY, row_sum = 0.0f;
+            for (uint32_t i = 0; i < num_tiles; ++i) {
+                const uint32_t tile = tile_base + i, buf = tile & 1;
+                const uint32_t token0 = (first_tile + i) * kUmmaN;
+                const uint32_t tmem_s = tmem + kColS + buf * kUmmaN + lane_base;
+                wait(kBarS + buf, tile >> 1);
+                tc_fence_after();
+
+                float s[kUmmaN];
+                {
+                    float part[32];
+                    tmem_load32(tmem_s, part);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) s[c] = part[c];
+                    tmem_load32(tmem_s + 32, part);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) s[32 + c] = part[c];
+                }
+                if (token0 < v.kv_begin || token0 + kUmmaN > min_limit) {
+#pragma unroll
+                    for (int c = 0; c < int(kUmmaN); ++c) {
+                        const uint32_t token = token0 + c;
+                        if (token >= limit || token < v.kv_begin) s[c] = -INFINITY;
+                    }
+                }
+                float m4[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+                for (int c = 4; c < int(kUmmaN); c += 4) {
+                    m4[0] = fmaxf(m4[0], s[c]);
+                    m4[1] = fmaxf(m4[1], s[c + 1]);
+                    m4[2] = fmaxf(m4[2], s[c + 2]);
+                    m4[3] = fmaxf(m4[3], s[c + 3]);
+                }
+                const float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;  // scale > 0
+                row_max = fmaxf(row_max, tile_max);
+                const bool moved = row_max > row_ref + kRescaleThreshold;  // also the first visible key (-inf reference)
+                float corr = 1.0f;
+                if (moved) {
+                    corr = row_ref == -INFINITY ? 0.0f : fast_exp2(row_ref - row_max);
+                    row_ref = row_max;
+                }
+                const float base = row_ref == -INFINITY ? 0.0f : row_ref;
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t packed[kUmmaN / 2];
+#pragma unroll
+                for (int c = 0; c < int(kUmmaN); c += 4) {
+                    const float e0 = fast_exp2(fmaf(s[c], p.scale_log2, -base));
+                    const float e1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -base));
+                    const float e2 = fast_exp2(fmaf(s[c + 2], p.scale_log2, -base));
+                    const float e3 = fast_exp2(fmaf(s[c + 3], p.scale_log2, -base));
+                    sum4[0] += e0;
+                    sum4[1] += e1;
+                    sum4[2] += e2;
+                    sum4[3] += e3;
+                    packed[c / 2] = Mma<T>::pack(e0, e1);
+                    packed[c / 2 + 1] = Mma<T>::pack(e2, e3);
+                }
+                row_sum = row_sum * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+
+                // O is touched only when a reference moved (per warp: each warp owns its 32 rows), and only then does
+                // P wait for the previous P V; otherwise P goes out first and the wait just keeps the phases in step
+                const bool rescale = i > 0 && __any_sync(0xFFFFFFFFu, moved);
+                if (rescale) {
+                    wait(kBarO + ((tile - 1) & 1), (tile - 1) >> 1);
+                    tc_fence_after();
+#pragma unroll 1
+                    for (uint32_t c = 0; c < uint32_t(D); c += 32) {
+                        float o[32];
+                        tmem_load32(tmem_o + lane_base + c, o);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] *= corr;
+                        tmem_store32(tmem_o + lane_base + c, o);
+                    }
+                }
+                tmem_store32_bits(tmem_s, packed);  // P over the first 32 columns of this S buffer
+                tmem_store_wait();
+                tc_fence_before();
+                mbar_arrive(bar(kBarP + buf));
+                if (i > 0 && !rescale) wait(kBarO + ((tile - 1) & 1), (tile - 1) >> 1);
+            }
+            if (num_tiles > 0) {
+                const uint32_t last = tile_base + num_tiles - 1;
+                wait(kBarO + (last & 1), last >> 1);
+                tc_fence_after();
+            }
+            tile_base += num_tiles;
+
+            // ---- epilogue: every thread finishes its own row ---------------------------------------------------------------
+            // back to the true max as the reference: l' = l * 2^(ref - max); O / l is unchanged by the shift
+            const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
+            const float sum_at_max = row_max == -INFINITY ? row_sum : row_sum * fast_exp2(row_ref - row_max);
+            const bool is_partial = v.partial_slot != kU32Max;
+            const uint64_t prow = is_partial ? static_cast<uint64_t>(v.partial_slot + w) * kMaxRows + rr : 0;
+#pragma unroll 1
+            for (uint32_t c = 0; c < uint32_t(D); c += 32) {
+                float o[32];
+                if (num_tiles > 0) {
+                    tmem_load32(tmem_o + lane_base + c, o);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] = 0.0f;
+                }
+                if (row_valid) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4) {
+                        const float4 value = make_float4(o[e] * inv, o[e + 1] * inv, o[e + 2] * inv, o[e + 3] * inv);
+                        if (is_partial) {
+                            *reinterpret_cast<float4*>(p.partial_o + prow * D + c + e) = value;
+                        } else if (p.ext_o != nullptr) {
+                            *reinterpret_cast<float4*>(p.ext_o + out_row * D + c + e) = value;
+                        } else {
+                            store_out4<T>(p, out_row * D + c + e, value);
+                        }
+                    }
+                }
+                __syncwarp();  // the TMEM load of the next pass is warp-collective
+            }
+            if (row_valid) {
+                if (is_partial) {
+                    p.partial_m[prow] = row_max;
+                    p.partial_l[prow] = sum_at_max;
+                } else if (p.ext_o != nullptr) {
+                    p.ext_m[out_row] = row_max * kLn2;
+                    p.ext_l[out_row] = sum_at_max;
+                }
+            }
+            tc_fence_before();
+
+            // ---- units shared with other CTAs: whoever delivers a tile's last partial merges it ---------------------------
+            if (is_partial) {
+                __threadfence();
+                row_threads_sync();
+                if (tid < 8) {
+                    const bool has_rows = tid * p.tokens_per_tile < v.num_tokens;
+                    last_s[tid] = has_rows && atomicAdd(p.unit_counters + v.reduce_unit + tid, 1u) == v.unit_num_items - 1;
+                }
+                row_threads_sync();
+                for (uint32_t tile = 0; tile < 8; ++tile) {
+                    if (!last_s[tile]) continue;
+                    __threadfence();
+                    const uint32_t tile_tokens = min(p.tokens_per_tile, v.num_tokens - tile * p.tokens_per_tile);
+                    const uint32_t tile_rows = tile_tokens * v.num_heads;
+                    for (uint32_t i = tid; i < tile_rows * (D / 4); i += kRowThreads) {
+                        const uint32_t r = i / (D / 4), c4 = i % (D / 4);
+                        float global_max = -INFINITY;
+#pragma unroll 4
+                        for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
+                            const uint64_t row = static_cast<uint64_t>(v.unit_first_slot + s_i * 8 + tile) * kMaxRows + r;
+                            global_max = fmaxf(global_max, __ldcg(p.partial_m + row));
+                        }
+                        float sum = 0.0f;
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                        for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
+                            const uint64_t row = static_cast<uint64_t>(v.unit_first_slot + s_i * 8 + tile) * kMaxRows + r;
+                            const float pm = __ldcg(p.partial_m + row);
+                            const float weight = pm == -INFINITY ? 0.0f : exp2f(pm - global_max) * __ldcg(p.partial_l + row);
+                            const float4 part = __ldcg(reinterpret_cast<const float4*>(p.partial_o + row * D + 4 * c4));
+                            sum += weight;
+                            acc.x += weight * part.x;
+                            acc.y += weight * part.y;
+                            acc.z += weight * part.z;
+                            acc.w += weight * part.w;
+                        }
+                        const float scale = sum > 0.0f ? 1.0f / sum : 0.0f;
+                        acc.x *= scale;
+                        acc.y *= scale;
+                        acc.z *= scale;
+                        acc.w *= scale;
+                        const uint64_t row =
+                            static_cast<uint64_t>(v.flat_begin + tile * p.tokens_per_tile + r / v.num_heads) * p.num_q_heads +
+                            v.head0 + r % v.num_heads;
+                        if (p.ext_o != nullptr) {
+                            *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc;
+                            if (c4 == 0) {
+                                p.ext_m[row] = global_max * kLn2;
+                                p.ext_l[row] = sum;
+                            }
+                        } else {
+                            store_out4<T>(p, row * D + 4 * c4, acc);
+                        }
+                    }
+                    if (tid == 0) p.unit_counters[v.reduce_unit + tile] = 0;  // ready for the next launch
+                }
+                row_threads_sync();  // the flags are read before the next item overwrites them
             }
         }
     }
@@ -458,9 +627,47 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) attend_chunk_umma_kernel(Atte
     }
 }
 
+// The page arena as a TMA tensor [page][row in page][element]: rows are the 2 * Hkv * tokens_per_page K and V rows of
+// a page, a box is `box_rows` consecutive rows of 64 elements (128 bytes), written with the 128-byte swizzle.
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            entry = nullptr;
+        return reinterpret_cast<EncodeTiled>(entry);
+    }();
+    return fn;
+}
+
+bool make_kv_map(const AttendParams& p, uint32_t box_rows, CUtensorMap* map) {
+    const EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const uint64_t page_bytes = p.geo.page_elems * 2;
+    const uint64_t rows_per_page = 2ull * p.geo.num_kv_heads * p.geo.tokens_per_page;
+    if (reinterpret_cast<uintptr_t>(p.geo.pages) % 16 != 0 || page_bytes % 16 != 0 || p.geo.num_pages == 0 ||
+        p.geo.num_pages > 0x7FFFFFFFull || rows_per_page * p.geo.head_dim * 2 > page_bytes)
+        return false;
+    const cuuint64_t dims[3] = {p.geo.head_dim, rows_per_page, p.geo.num_pages};
+    const cuuint64_t strides[2] = {p.geo.head_dim * 2ull, page_bytes};
+    const cuuint32_t box[3] = {64, box_rows, 1};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    const CUtensorMapDataType type = p.dtype == PSI_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    return encode(map, type, 3, const_cast<void*>(p.geo.pages), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <typename T, int D>
 cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
-    constexpr uint32_t kSmem = D * 2 * kUmmaM + 2 * (2 * D * 2 * kUmmaN) + kUmmaM * 128 + 1024;
+    constexpr uint32_t kSmem = Ring<D>::kSlots * (D * 2 * kUmmaN) + 1024;
+    const uint32_t box_rows = p.geo.tokens_per_page < kUmmaN ? p.geo.tokens_per_page : kUmmaN;
+    CUtensorMap map;
+    if (!make_kv_map(p, box_rows, &map)) return cudaErrorNotSupported;
     auto kernel = attend_chunk_umma_kernel<T, D>;
     static int configured_device = -1;
     int device = 0;
@@ -471,7 +678,7 @@ cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t st
         if (err != cudaSuccess) return err;
         configured_device = device;
     }
-    kernel<<<num_ctas, kUmmaThreads, kSmem, stream>>>(p);
+    kernel<<<num_ctas, kUmmaThreads, kSmem, stream>>>(p, map, box_rows);
     return cudaGetLastError();
 }
 
@@ -486,6 +693,8 @@ cudaError_t launch_for_dim(const AttendParams& p, uint32_t num_ctas, cudaStream_
 
 }  // namespace
 
+// cudaErrorNotSupported: the arena cannot be described to the TMA unit (alignment, size); nothing was launched and
+// the caller takes launch_attend_chunk instead.
 cudaError_t launch_attend_chunk_umma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     if (num_ctas == 0) return cudaSuccess;
     return p.dtype == PSI_DTYPE_BF16 ? launch_for_dim<__nv_bfloat16>(p, num_ctas, stream)

@@ -22,6 +22,7 @@ struct PageGeometry {
     const void* pages;
     const uint32_t* page_ids;     // whole table
     uint64_t page_elems;          // elements per page
+    uint64_t num_pages;           // pages of the arena (bounds of the TMA view; 0 where no kernel needs it)
     uint32_t layer;
     uint32_t num_layers;
     uint32_t pages_per_req;       // num_blocks * num_page_ids_per_block: one (slot, layer) row of the table
