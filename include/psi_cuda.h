@@ -280,7 +280,9 @@ PSI_API int32_t psi_gqa_metadata_write(psi_gqa* gqa, uint32_t which, uint64_t of
 
 /* Plan statistics of the last prepare: out[0]=CTAs launched by the map kernel, out[1]=work items, out[2]=partial
  * slots, out[3]=reduce units, out[4]=exec q tiles, out[5]=kernel (1 generic, 2 mma), out[6]=total 16-token KV tiles,
- * out[7]=rows per q tile, out[8]=CTAs of the long-query (chunk) kernel, out[9]=its work items. */
+ * out[7]=rows per q tile, out[8]=CTAs of the long-query (chunk) kernel, out[9]=its work items, out[10]=launches of
+ * the tcgen05 chunk kernel since the object was created, out[11]=launches of the mma.sync chunk kernel (the fallback
+ * when PSI_KERNEL_MMA_SYNC asks for it or the page arena cannot be described to the TMA unit). */
 PSI_API int32_t psi_gqa_plan_stats(psi_gqa* gqa, uint32_t* out, uint32_t n);
 
 /* KV append: GQAKVPageWrite::invoke_bucketed (crates/inference-backend-metal/src/components/gqa_kv_page_write.rs:

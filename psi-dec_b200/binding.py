@@ -403,10 +403,10 @@ class GQA:
                self.ctx._h)
 
     def plan_stats(self) -> dict:
-        out = (C.c_uint32 * 10)()
-        _check(library().psi_gqa_plan_stats(self._h, out, C.c_uint32(10)), self.ctx._h)
+        out = (C.c_uint32 * 12)()
+        _check(library().psi_gqa_plan_stats(self._h, out, C.c_uint32(12)), self.ctx._h)
         keys = ("ctas", "items", "partial_slots", "reduce_units", "q_tiles", "kernel", "kv_tiles", "rows_per_tile",
-                "chunk_ctas", "chunk_items")
+                "chunk_ctas", "chunk_items", "chunk_tcgen05_launches", "chunk_mma_sync_launches")
         return dict(zip(keys, out))
 
     def kv_page_write(self, pages: PageArena, table: GQARequestPageTable, layer: int, k, v):

@@ -171,6 +171,7 @@ struct psi_gqa {
     DeviceBuffer combine_ptrs;
     DeviceBuffer status_word;  // u32 written by bounded device-side waits
     bool chunk_umma = false;   // long query runs on the tcgen05 kernel (else the mma.sync chunk kernel)
+    uint32_t chunk_launches[2] = {0, 0};  // tcgen05, mma.sync
     DeviceBuffer norm_rope;    // q weight bf16[D] | k weight bf16[D] | inverse frequencies f32[rope_dim/2]
     psi_norm_rope_config norm_rope_cfg{};
     float norm_rope_attention_factor = 1.0f;
@@ -279,8 +280,27 @@ AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* 
     return p;
 }
 
-void run_attend(psi_gqa* g, const AttendParams& p) {
+void run_attend(psi_gqa* g, const AttendParams& params) {
     psi_ctx* ctx = g->ctx;
+    AttendParams p = params;
+    if (p.new_k != nullptr && g->chunk.num_ctas() > 0) {
+        // A fused step that carries long query runs: their K/V tiles are fetched page-wise by TMA, so the step's rows
+        // go to their pages first (one more launch, against milliseconds of attention) and both kernels read pages only.
+        AppendParams a{};
+        a.geo = p.geo;
+        a.flat_k = p.new_k;
+        a.flat_v = p.new_v;
+        a.req_slots = block_words(g, g->off_req_slots);
+        a.flat_token_indices = block_words(g, g->off_token_indices);
+        a.scalars = block_words(g, 0);
+        a.num_total_tokens = g->shape.num_total_tokens;
+        {
+            LaunchScope scope(ctx, PSI_KERNEL_CLASS_APPEND);
+            cuda_check(launch_kv_append(a, ctx->stream), "kv append launch");
+        }
+        p.new_k = nullptr;
+        p.new_v = nullptr;
+    }
     const uint32_t num_ctas = g->plan.num_ctas();
     if (num_ctas > 0) {
         LaunchScope scope(ctx, PSI_KERNEL_CLASS_ATTEND_MAP);
@@ -301,7 +321,12 @@ void run_attend(psi_gqa* g, const AttendParams& p) {
             launched = launch_attend_chunk_umma(c, g->chunk.num_ctas(), ctx->stream);
         }
         // an arena the TMA unit cannot address (alignment, size) keeps the mma.sync kernel
-        if (launched == cudaErrorNotSupported) launched = launch_attend_chunk(c, g->chunk.num_ctas(), ctx->stream);
+        if (launched == cudaErrorNotSupported) {
+            launched = launch_attend_chunk(c, g->chunk.num_ctas(), ctx->stream);
+            g->chunk_launches[1] += 1;
+        } else {
+            g->chunk_launches[0] += 1;
+        }
         cuda_check(launched, "attend (chunk) launch");
     }
     // The mma kernel merges a unit's partials in the CTA that delivers the last one; the generic kernel needs the
@@ -1106,7 +1131,7 @@ int32_t psi_gqa_plan_stats(psi_gqa* g, uint32_t* out, uint32_t n) {
     if (g == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
     return guarded(g->ctx, [&] {
         require(g->prepared, "GQA batch metadata must be updated before recording");
-        const uint32_t stats[10] = {g->plan.num_ctas(),
+        const uint32_t stats[12] = {g->plan.num_ctas(),
                                    static_cast<uint32_t>(g->plan.items.size()),
                                    g->plan.num_partial_slots,
                                    static_cast<uint32_t>(g->plan.reduces.size()),
@@ -1115,8 +1140,10 @@ int32_t psi_gqa_plan_stats(psi_gqa* g, uint32_t* out, uint32_t n) {
                                    static_cast<uint32_t>(std::min<uint64_t>(g->plan.total_kv_tiles, kU32Max)),
                                    g->geo.tokens_per_tile * g->geo.heads_per_tile,
                                    g->chunk.num_ctas(),
-                                   static_cast<uint32_t>(g->chunk.items.size())};
-        for (uint32_t i = 0; i < n && i < 10; ++i) out[i] = stats[i];
+                                   static_cast<uint32_t>(g->chunk.items.size()),
+                                   g->chunk_launches[0],
+                                   g->chunk_launches[1]};
+        for (uint32_t i = 0; i < n && i < 12; ++i) out[i] = stats[i];
     });
 }
 

@@ -62,15 +62,19 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // Bounded wait on one phase of an mbarrier; false when the bound ran out.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < kMaxPolls; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done) return true;
+        if (mbar_try(bar, parity)) return true;
     }
     return false;
 }
@@ -108,10 +112,11 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const float (&v)[32
 
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
-// Byte offset of the 16-byte chunk `chunk` (8 elements) of row `row` in a stack of [blocks][rows][64 elements] tiles
-// with the 128-byte swizzle the descriptors above announce (chunk index XOR row % 8 inside each 128-byte row).
-__device__ __forceinline__ uint32_t operand_offset(uint32_t rows, uint32_t row, uint32_t chunk) {
-    return (chunk >> 3) * rows * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+// Byte offset of the 16-byte chunk `chunk` (8 elements) of token row `row` in a K or V tile.  A tile is a stack of
+// [row / 8][element block of 64][row % 8][64 elements]: every (8 rows x 128 bytes) block is one swizzle atom (chunk
+// index XOR row % 8), the `blocks` atoms of an 8-row group follow one another, groups are blocks * 1024 bytes apart.
+__device__ __forceinline__ uint32_t operand_offset(uint32_t blocks, uint32_t row, uint32_t chunk) {
+    return ((row >> 3) * blocks + (chunk >> 3)) * 1024 + (row & 7) * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
 
@@ -127,13 +132,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-// One TMA box of the page arena (viewed as [page][row in page][element]) into shared memory; completion is counted
-// in bytes on `bar`.  c0 (elements) is always a multiple of 64, i.e. of 128 bytes.
-__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, uint32_t bar, uint32_t c0, uint32_t c1,
-                                             uint32_t c2) {
+// One TMA box of the page arena into shared memory; completion is counted in bytes on `bar`.  The arena is viewed as
+// [page][8-row group][element block][row in group][64 elements], a box takes whole groups of one page (all element
+// blocks), so the only coordinates that vary are the group and the page; the innermost one is always 0.
+__device__ __forceinline__ void tma_load_groups(uint32_t dst, const CUtensorMap* map, uint32_t bar, uint32_t group, uint32_t page) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
-        "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(0u), "r"(group), "r"(page)
         : "memory");
 }
 
@@ -176,6 +181,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
     attend_chunk_umma_kernel(const AttendParams p, const __grid_constant__ CUtensorMap kv_map, const uint32_t box_rows) {
     constexpr uint32_t kChunks = D / 8;               // 16-byte chunks per row of K / V
+    constexpr uint32_t kBlocks = D / 64;              // 64-element (128-byte) blocks per row
     constexpr uint32_t kTileBytes = D * 2 * kUmmaN;   // one K or V tile: [D/64][64][64]
     constexpr uint32_t kSlots = Ring<D>::kSlots;
     constexpr uint32_t kTmemColumns = 512;
@@ -222,16 +228,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     const unsigned char* pages = static_cast<const unsigned char*>(p.geo.pages);
     const uint64_t page_bytes = p.geo.page_elems * 2;
     const uint64_t v_region_bytes = v_region_offset(p.geo) * 2;
-    const bool fused = p.new_k != nullptr;
 
     // A wait that ran out flags the launch and lets every later wait fall through: results are then garbage, the
     // status word says so, and the kernel still frees its TMEM and returns.
     auto wait = [&](uint32_t which, uint32_t parity) {
+        if (mbar_try(bar(which), parity & 1)) return;  // the usual case: already complete, or completes within one try
         if (*reinterpret_cast<volatile uint32_t*>(&abort_s) == 0 && !mbar_wait(bar(which), parity & 1)) {
             abort_s = 1;
             if (p.status != nullptr) atomicExch(p.status, static_cast<uint32_t>(PSI_ERR_TIMEOUT));
         }
-        __syncwarp();  // whole warps wait together; the TMEM accesses that follow are warp-collective
     };
 
     // Tiles, ring fills (K of tile t = fill 2t, V = fill 2t + 1) and items are counted over the whole launch, the
@@ -243,62 +248,52 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
     if (warp == 5) {
         // ================================ producer: K/V tiles into the ring ==========================================
-        const uint32_t v_rows = p.geo.num_kv_heads * p.geo.tokens_per_page;  // rows of a page's K region
+        const uint32_t v_groups = p.geo.num_kv_heads * p.geo.tokens_per_page / 8;  // 8-row groups of a page's K region
         for (uint32_t index = item_begin; index < item_end; ++index) {
             const ItemView v = view_item(p, index);
-            const uint32_t paged_end = fused ? min(v.kv_end, v.new_begin) : v.kv_end;
             const uint32_t* row_ids = table_row(p.geo, v.req_slot);
             const uint64_t head_bytes = static_cast<uint64_t>(v.kv_head) * p.geo.tokens_per_page * (D * 2);
-            const uint32_t head_row = v.kv_head * p.geo.tokens_per_page;
+            const uint32_t head_group = v.kv_head * p.geo.tokens_per_page / 8;
             const uint32_t first_tile = v.kv_begin / kUmmaN;
             const uint32_t num_tiles = (v.kv_end + kUmmaN - 1) / kUmmaN - first_tile;
+            const uint32_t last_page = (v.kv_end - 1) >> page_shift;
             uint32_t window_base = kU32Max, window_ids = 0;  // 32 page ids of the request, one per lane
             for (uint32_t i = 0; i < num_tiles; ++i) {
                 const uint32_t token0 = (first_tile + i) * kUmmaN;
-                const bool whole = token0 + kUmmaN <= paged_end;
-                if (whole) {
-                    const uint32_t first_page = token0 >> page_shift, last_page = (token0 + kUmmaN - 1) >> page_shift;
-                    if (first_page < window_base || last_page >= window_base + 32) {
+                const bool whole = token0 + kUmmaN <= v.kv_end;
+                {
+                    const uint32_t first_page = token0 >> page_shift;
+                    const uint32_t end_page = min(last_page, (token0 + kUmmaN - 1) >> page_shift);
+                    if (first_page < window_base || end_page >= window_base + 32) {
                         window_base = first_page;
-                        const uint32_t page_index = first_page + lane;
-                        window_ids = page_index <= ((paged_end - 1) >> page_shift) ? row_ids[page_index] : 0u;
+                        window_ids = first_page + lane <= last_page ? row_ids[first_page + lane] : 0u;
                     }
                 }
                 for (uint32_t which = 0; which < 2; ++which) {
                     const uint32_t fill = 2 * (tile_base + i) + which, slot = fill % kSlots, use = fill / kSlots;
                     const uint32_t dst = smem_base + slot * kTileBytes;
                     if (use > 0) wait(kBarEmpty + slot, use - 1);  // the MMAs that read the slot's previous tile are done
+                    __syncwarp();
                     if (whole) {
                         if (lane == 0) mbar_expect_tx(bar(kBarFull + slot), kTileBytes);
                         for (uint32_t row = 0; row < kUmmaN; row += box_rows) {
                             const uint32_t token = token0 + row;
                             const uint32_t page = __shfl_sync(0xFFFFFFFFu, window_ids, (token >> page_shift) - window_base);
-                            const uint32_t page_row = which * v_rows + head_row + (token & page_mask);
-                            if (lane == 0) {
-#pragma unroll
-                                for (uint32_t kb = 0; kb < uint32_t(D) / 64; ++kb)
-                                    tma_load_box(dst + kb * (kUmmaN * 128) + row * 128, &kv_map, bar(kBarFull + slot), kb * 64,
-                                                 page_row, page);
-                            }
+                            const uint32_t group = which * v_groups + head_group + (token & page_mask) / 8;
+                            if (lane == 0)
+                                tma_load_groups(dst + (row / 8) * (kBlocks * 1024), &kv_map, bar(kBarFull + slot), group, page);
                         }
                     } else {
-                        // ragged tile: rows beyond the item are zero, rows of this step come from the step's K/V arrays
+                        // the item's last tile: rows at and beyond its end are zero
                         for (uint32_t c = lane; c < kUmmaN * kChunks; c += 32) {
                             const uint32_t row = c / kChunks, chunk = c % kChunks;
                             const uint32_t token = token0 + row;
-                            const unsigned char* src = pages;
-                            uint32_t bytes = 16u;
-                            if (token >= v.kv_end) {
-                                bytes = 0u;
-                            } else if (token >= paged_end) {
-                                src = static_cast<const unsigned char*>(which ? p.new_v : p.new_k) +
-                                      (static_cast<uint64_t>(v.flat_req_begin + (token - v.new_begin)) * p.geo.num_kv_heads +
-                                       v.kv_head) * (D * 2) + chunk * 16;
-                            } else {
-                                src = pages + static_cast<uint64_t>(row_ids[token >> page_shift]) * page_bytes + head_bytes +
-                                      (which ? v_region_bytes : 0) + (token & page_mask) * (D * 2) + chunk * 16;
-                            }
-                            cp_async_16(dst + operand_offset(kUmmaN, row, chunk), src, bytes);
+                            const bool valid = token < v.kv_end;
+                            const uint32_t page =
+                                __shfl_sync(0xFFFFFFFFu, window_ids, valid ? (token >> page_shift) - window_base : 0u);
+                            const unsigned char* src = pages + static_cast<uint64_t>(page) * page_bytes + head_bytes +
+                                                       (which ? v_region_bytes : 0) + (token & page_mask) * (D * 2) + chunk * 16;
+                            cp_async_16(dst + operand_offset(kBlocks, row, chunk), valid ? src : pages, valid ? 16u : 0u);
                         }
                         cp_async_commit();
                         cp_async_wait<0>();
@@ -319,54 +314,53 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             mbar_wait(bar(kBarFull + fill % kSlots), (fill / kSlots) & 1);
         }
     } else if (warp == 4) {
-        // ================================ MMA issue ========================================================================
-        const uint32_t idesc_qk = umma_idesc<T>(kUmmaN, false);
-        const uint32_t idesc_pv = umma_idesc<T>(D, true);
-        for (uint32_t index = item_begin; index < item_end; ++index, ++item_count) {
-            const ItemView v = view_item(p, index);
-            const uint32_t first_tile = v.kv_begin / kUmmaN;
-            const uint32_t num_tiles = (v.kv_end + kUmmaN - 1) / kUmmaN - first_tile;
+        // ================================ MMA issue (one thread) =========================================================
+        if (lane == 0) {
+            const uint32_t idesc_qk = umma_idesc<T>(kUmmaN, false);
+            const uint32_t idesc_pv = umma_idesc<T>(D, true);
+            for (uint32_t index = item_begin; index < item_end; ++index, ++item_count) {
+                const ItemView v = view_item(p, index);
+                const uint32_t first_tile = v.kv_begin / kUmmaN;
+                const uint32_t num_tiles = (v.kv_end + kUmmaN - 1) / kUmmaN - first_tile;
 
-            // S[tile % 2] = Q K^T of local tile i; frees the K slot when done
-            auto issue_qk = [&](uint32_t i) {
-                const uint32_t tile = tile_base + i, fill = 2 * tile, slot = fill % kSlots;
-                wait(kBarFull + slot, fill / kSlots);
-                tc_fence_after();
-                if (lane == 0) {
+                // S[tile % 2] = Q K^T of local tile i; frees the K slot when done
+                auto issue_qk = [&](uint32_t i) {
+                    const uint32_t tile = tile_base + i, fill = 2 * tile, slot = fill % kSlots;
+                    wait(kBarFull + slot, fill / kSlots);
+                    tc_fence_after();
                     const uint32_t k_slot = smem_base + slot * kTileBytes;
 #pragma unroll
                     for (uint32_t ks = 0; ks < uint32_t(D) / 16; ++ks) {
-                        const uint64_t b = umma_desc(k_slot + (ks >> 2) * (kUmmaN * 128) + (ks & 3) * 32, 16, 1024);
+                        // K-major operand: 8-row groups kBlocks KiB apart, element block ks / 4, 32 bytes per k-step
+                        const uint64_t b = umma_desc(k_slot + (ks >> 2) * 1024 + (ks & 3) * 32, 16, kBlocks * 1024);
                         umma_issue_ts(tmem + kColS + (tile & 1) * kUmmaN, tmem + kColQ + ks * 8, b, idesc_qk, ks > 0);
                     }
                     umma_commit(bar(kBarS + (tile & 1)));
                     umma_commit(bar(kBarEmpty + slot));
-                }
-                __syncwarp();
-            };
+                };
 
-            wait(kBarQ, item_count);  // the item's query rows are in TMEM; the rows are done with the previous item
-            if (num_tiles > 0) issue_qk(0);
-            for (uint32_t i = 0; i < num_tiles; ++i) {
-                const uint32_t tile = tile_base + i, fill = 2 * tile + 1, slot = fill % kSlots;
-                if (i + 1 < num_tiles) issue_qk(i + 1);  // runs under the softmax of tile i
-                wait(kBarP + (tile & 1), tile >> 1);      // P of tile i is in TMEM (over the first half of its S buffer)
-                wait(kBarFull + slot, fill / kSlots);
-                tc_fence_after();
-                if (lane == 0) {
+                wait(kBarQ, item_count);  // the item's query rows are in TMEM; the rows are done with the previous item
+                if (num_tiles > 0) issue_qk(0);
+                for (uint32_t i = 0; i < num_tiles; ++i) {
+                    const uint32_t tile = tile_base + i, fill = 2 * tile + 1, slot = fill % kSlots;
+                    if (i + 1 < num_tiles) issue_qk(i + 1);  // runs under the softmax of tile i
+                    wait(kBarFull + slot, fill / kSlots);
+                    wait(kBarP + (tile & 1), tile >> 1);      // P of tile i is in TMEM (over the first half of its S buffer)
+                    tc_fence_after();
                     const uint32_t v_slot = smem_base + slot * kTileBytes;
 #pragma unroll
                     for (uint32_t ks = 0; ks < kUmmaN / 16; ++ks) {
-                        const uint64_t b = umma_desc(v_slot + ks * 2048, kUmmaN * 128, 1024);
+                        // MN-major operand: 64-element blocks 1 KiB apart, 8-token groups kBlocks KiB apart, two groups
+                        // per k-step
+                        const uint64_t b = umma_desc(v_slot + ks * 2 * (kBlocks * 1024), 1024, kBlocks * 1024);
                         umma_issue_ts(tmem + kColO, tmem + kColS + (tile & 1) * kUmmaN + ks * 8, b, idesc_pv,
                                       (i > 0 || ks > 0) ? 1u : 0u);
                     }
                     umma_commit(bar(kBarO + (tile & 1)));
                     umma_commit(bar(kBarEmpty + slot));
                 }
-                __syncwarp();
+                tile_base += num_tiles;
             }
-            tile_base += num_tiles;
         }
     } else {
         // ================================ one accumulator row per thread ===============================================
@@ -409,26 +403,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 mbar_arrive(bar(kBarQ));
             }
 
-            // in the fused step: this item's share of the step's K/V rows into their pages
-            if (fused && v.writes_kv) {
-                const uint32_t* row_ids = table_row(p.geo, v.req_slot);
-                const uint64_t head_bytes = static_cast<uint64_t>(v.kv_head) * p.geo.tokens_per_page * (D * 2);
-                for (uint32_t i = tid; i < v.num_tokens * 2 * kChunks; i += kRowThreads) {
-                    const uint32_t c = i % kChunks, which = (i / kChunks) & 1, j = i / (2 * kChunks);
-                    const uint32_t pos = v.first_pos + j;
-                    if (pos >= v.kv_begin && pos < v.kv_end) {
-                        const unsigned char* fresh = static_cast<const unsigned char*>(which ? p.new_v : p.new_k);
-                        const uint4 value = *reinterpret_cast<const uint4*>(
-                            fresh + (static_cast<uint64_t>(v.flat_begin + j) * p.geo.num_kv_heads + v.kv_head) * (D * 2) + c * 16);
-                        unsigned char* dst = const_cast<unsigned char*>(pages) +
-                                             static_cast<uint64_t>(row_ids[pos >> page_shift]) * page_bytes + head_bytes +
-                                             (which ? v_region_bytes : 0) + (pos & page_mask) * (D * 2) + c * 16;
-                        *reinterpret_cast<uint4*>(dst) = value;
-                    }
-                }
-                __syncwarp();
-            }
-
             // softmax state in the log2 domain: `row_ref` is the reference the exponentials are taken against (it
             // trails the true running max `row_max` by at most kRescaleThreshold), `row_sum` is relative to it
             float row_ref = -INFINITY, row_max = -INFINITY, row_sum = 0.0f;
@@ -437,6 +411,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 const uint32_t token0 = (first_tile + i) * kUmmaN;
                 const uint32_t tmem_s = tmem + kColS + buf * kUmmaN + lane_base;
                 wait(kBarS + buf, tile >> 1);
+                __syncwarp();  // the TMEM accesses below are warp-collective
                 tc_fence_after();
 
                 float s[kUmmaN];
@@ -495,6 +470,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 const bool rescale = i > 0 && __any_sync(0xFFFFFFFFu, moved);
                 if (rescale) {
                     wait(kBarO + ((tile - 1) & 1), (tile - 1) >> 1);
+                    __syncwarp();
                     tc_fence_after();
 #pragma unroll 1
                     for (uint32_t c = 0; c < uint32_t(D); c += 32) {
@@ -505,6 +481,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                         tmem_store32(tmem_o + lane_base + c, o);
                     }
                 }
+                __syncwarp();
                 tmem_store32_bits(tmem_s, packed);  // P over the first 32 columns of this S buffer
                 tmem_store_wait();
                 tc_fence_before();
@@ -514,6 +491,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             if (num_tiles > 0) {
                 const uint32_t last = tile_base + num_tiles - 1;
                 wait(kBarO + (last & 1), last >> 1);
+                __syncwarp();
                 tc_fence_after();
             }
             tile_base += num_tiles;
@@ -627,8 +605,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     }
 }
 
-// The page arena as a TMA tensor [page][row in page][element]: rows are the 2 * Hkv * tokens_per_page K and V rows of
-// a page, a box is `box_rows` consecutive rows of 64 elements (128 bytes), written with the 128-byte swizzle.
+// The page arena as a TMA tensor [page][8-row group][element block][row in group][64 elements]: a page holds
+// 2 * Hkv * tokens_per_page K and V rows of head_dim elements, a box is `box_rows / 8` consecutive groups with all their
+// element blocks, written with the 128-byte swizzle in exactly the order the MMA descriptors read a tile in.
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -649,16 +628,17 @@ bool make_kv_map(const AttendParams& p, uint32_t box_rows, CUtensorMap* map) {
     const EncodeTiled encode = encode_tiled();
     if (encode == nullptr) return false;
     const uint64_t page_bytes = p.geo.page_elems * 2;
+    const uint64_t row_bytes = p.geo.head_dim * 2ull;
     const uint64_t rows_per_page = 2ull * p.geo.num_kv_heads * p.geo.tokens_per_page;
     if (reinterpret_cast<uintptr_t>(p.geo.pages) % 16 != 0 || page_bytes % 16 != 0 || p.geo.num_pages == 0 ||
-        p.geo.num_pages > 0x7FFFFFFFull || rows_per_page * p.geo.head_dim * 2 > page_bytes)
+        p.geo.num_pages > 0x7FFFFFFFull || rows_per_page * row_bytes > page_bytes || p.geo.tokens_per_page % 8 != 0)
         return false;
-    const cuuint64_t dims[3] = {p.geo.head_dim, rows_per_page, p.geo.num_pages};
-    const cuuint64_t strides[2] = {p.geo.head_dim * 2ull, page_bytes};
-    const cuuint32_t box[3] = {64, box_rows, 1};
-    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    const cuuint64_t dims[5] = {64, 8, p.geo.head_dim / 64, rows_per_page / 8, p.geo.num_pages};
+    const cuuint64_t strides[4] = {row_bytes, 128, 8 * row_bytes, page_bytes};
+    const cuuint32_t box[5] = {64, 8, p.geo.head_dim / 64, box_rows / 8, 1};
+    const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
     const CUtensorMapDataType type = p.dtype == PSI_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    return encode(map, type, 3, const_cast<void*>(p.geo.pages), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    return encode(map, type, 5, const_cast<void*>(p.geo.pages), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

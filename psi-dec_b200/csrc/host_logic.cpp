@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cmath>
 #include <limits>
+#include <queue>
 
 namespace psi {
 
@@ -394,74 +395,85 @@ ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, c
                            const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,
                            uint32_t slot_base, uint32_t counter_base) {
     ChunkPlan plan;
-    struct SuperTile {
-        uint32_t req, flat_begin, flat_end, ctx_end;
+    // Units in stream order: all super-tiles of one (request, KV head) follow one another, so that CTAs working on
+    // neighbouring units at the same time read the same K/V pages (once from HBM, then from L2).
+    struct Unit {
+        uint32_t req, flat_begin, flat_end, ctx_end, head;
     };
-    std::vector<SuperTile> supers;
+    std::vector<Unit> units;
     const uint32_t tokens_per_item = geo.tokens_per_tile * kChunkTilesPerItem;
-    for (uint32_t r : requests) {
-        for (uint32_t begin = cu_tokens[r]; begin < cu_tokens[r + 1];) {
-            const uint32_t end = std::min(cu_tokens[r + 1], begin + tokens_per_item);
-            supers.push_back({r, begin, end, token_indices[r] + (end - cu_tokens[r])});
-            begin = end;
-        }
-    }
     const uint32_t heads = geo.num_kv_heads * geo.head_tiles;
     uint64_t total = 0;
-    for (const auto& s : supers) total += div_ceil(s.ctx_end, kKvTile) * heads;
+    for (uint32_t r : requests) {
+        for (uint32_t h = 0; h < heads; ++h) {
+            for (uint32_t begin = cu_tokens[r]; begin < cu_tokens[r + 1];) {
+                const uint32_t end = std::min(cu_tokens[r + 1], begin + tokens_per_item);
+                units.push_back({r, begin, end, token_indices[r] + (end - cu_tokens[r]), h});
+                total += div_ceil(units.back().ctx_end, kKvTile);
+                begin = end;
+            }
+        }
+    }
     plan.total_kv_tiles = total;
     if (total == 0) return plan;
     const uint64_t num_ctas = std::min<uint64_t>(std::max(1u, max_ctas), std::max<uint64_t>(1, total / 4));
-    auto share_end = [&](uint64_t c) { return total * (c + 1) / num_ctas; };
-    uint64_t cursor = 0;
-    uint32_t cta = 0;
-    plan.cta_item_begin.assign(1, 0);
-    for (const auto& s : supers) {
-        const uint64_t unit_tiles = div_ceil(s.ctx_end, kKvTile);
-        for (uint32_t h = 0; h < heads; ++h) {
-            const size_t unit_first_item = plan.items.size();
-            uint64_t done = 0;
-            while (done < unit_tiles) {
-                while (cursor + done >= share_end(cta)) {
-                    ++cta;
-                    plan.cta_item_begin.push_back(static_cast<uint32_t>(plan.items.size()));
-                }
-                const uint64_t take = std::min(unit_tiles - done, share_end(cta) - (cursor + done));
-                const uint32_t head_tile = h % geo.head_tiles;
-                DeviceItem d{};
-                d.kv_begin = static_cast<uint32_t>(done * kKvTile);
-                d.kv_end = static_cast<uint32_t>(std::min<uint64_t>((done + take) * kKvTile, s.ctx_end));
-                d.partial_slot = kU32Max;
-                d.flat_begin = s.flat_begin;
-                d.num_tokens = s.flat_end - s.flat_begin;
-                d.req_slot = req_slots[s.req];
-                d.kv_head = h / geo.head_tiles;
-                d.head0 = d.kv_head * geo.group + head_tile * geo.heads_per_tile;
-                d.num_heads = std::min(geo.heads_per_tile, geo.group - head_tile * geo.heads_per_tile);
-                d.first_pos = token_indices[s.req] + (s.flat_begin - cu_tokens[s.req]);
-                d.new_begin = token_indices[s.req];
-                d.flat_req_begin = cu_tokens[s.req];
-                d.writes_kv = head_tile == 0 ? 1u : 0u;
-                plan.items.push_back(d);
-                done += take;
-            }
-            cursor += unit_tiles;
-            const uint32_t n = static_cast<uint32_t>(plan.items.size() - unit_first_item);
+    // A unit longer than 1/8 of a CTA's fair share is cut along its KV range into equal pieces (partial slots, merged
+    // by the last arriver), which bounds how far the last CTA can trail the others.
+    const uint64_t piece_cap = std::max<uint64_t>(kChunkMinPieceTiles, div_ceil(total, num_ctas * 8));
+
+    // Pieces are dealt in order to whichever CTA is free first under the cost model (KV tiles + a fixed start
+    // cost): the static equivalent of CTAs pulling work from a queue.
+    struct Slot {
+        uint64_t load;
+        uint32_t cta;
+        bool operator>(const Slot& o) const { return load != o.load ? load > o.load : cta > o.cta; }
+    };
+    std::priority_queue<Slot, std::vector<Slot>, std::greater<Slot>> free_first;
+    for (uint32_t c = 0; c < num_ctas; ++c) free_first.push({0, c});
+    std::vector<std::vector<DeviceItem>> per_cta(num_ctas);
+    for (const Unit& u : units) {
+        const uint64_t unit_tiles = div_ceil(u.ctx_end, kKvTile);
+        const uint32_t n = static_cast<uint32_t>(div_ceil(unit_tiles, piece_cap));
+        const uint32_t head_tile = u.head % geo.head_tiles;
+        const uint32_t first_slot = slot_base + plan.num_partial_slots;
+        for (uint32_t k = 0; k < n; ++k) {
+            const uint64_t tile_begin = unit_tiles * k / n, tile_end = unit_tiles * (k + 1) / n;
+            DeviceItem d{};
+            d.kv_begin = static_cast<uint32_t>(tile_begin * kKvTile);
+            d.kv_end = static_cast<uint32_t>(std::min<uint64_t>(tile_end * kKvTile, u.ctx_end));
+            d.partial_slot = kU32Max;
+            d.flat_begin = u.flat_begin;
+            d.num_tokens = u.flat_end - u.flat_begin;
+            d.req_slot = req_slots[u.req];
+            d.kv_head = u.head / geo.head_tiles;
+            d.head0 = d.kv_head * geo.group + head_tile * geo.heads_per_tile;
+            d.num_heads = std::min(geo.heads_per_tile, geo.group - head_tile * geo.heads_per_tile);
+            d.first_pos = token_indices[u.req] + (u.flat_begin - cu_tokens[u.req]);
+            d.new_begin = token_indices[u.req];
+            d.flat_req_begin = cu_tokens[u.req];
+            d.writes_kv = head_tile == 0 ? 1u : 0u;
             if (n > 1) {  // the unit is shared between CTAs: partial slots 8 apart, eight arrival counters
-                const uint32_t first_slot = slot_base + plan.num_partial_slots;
-                for (uint32_t k = 0; k < n; ++k) {
-                    DeviceItem& d = plan.items[unit_first_item + k];
-                    d.partial_slot = first_slot + k * kChunkTilesPerItem;
-                    d.reduce_unit = counter_base + plan.num_counters;
-                    d.unit_first_slot = first_slot;
-                    d.unit_num_items = n;
-                }
-                plan.num_partial_slots += n * kChunkTilesPerItem;
-                plan.num_counters += kChunkTilesPerItem;
+                d.partial_slot = first_slot + k * kChunkTilesPerItem;
+                d.reduce_unit = counter_base + plan.num_counters;
+                d.unit_first_slot = first_slot;
+                d.unit_num_items = n;
             }
+            Slot slot = free_first.top();
+            free_first.pop();
+            per_cta[slot.cta].push_back(d);
+            slot.load += (tile_end - tile_begin) + kChunkStartCostTiles;
+            free_first.push(slot);
+        }
+        if (n > 1) {
+            plan.num_partial_slots += n * kChunkTilesPerItem;
+            plan.num_counters += kChunkTilesPerItem;
         }
     }
-    while (plan.cta_item_begin.size() < num_ctas + 1) plan.cta_item_begin.push_back(static_cast<uint32_t>(plan.items.size()));
+    plan.cta_item_begin.assign(1, 0);
+    for (const auto& list : per_cta) {
+        plan.items.insert(plan.items.end(), list.begin(), list.end());
+        plan.cta_item_begin.push_back(static_cast<uint32_t>(plan.items.size()));
+    }
     return plan;
 }
 

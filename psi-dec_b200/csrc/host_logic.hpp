@@ -171,6 +171,8 @@ struct ChunkPlan {
     uint32_t num_ctas() const { return cta_item_begin.empty() ? 0u : static_cast<uint32_t>(cta_item_begin.size() - 1); }
 };
 constexpr uint32_t kChunkTilesPerItem = 8;  // one query tile per warp
+constexpr uint32_t kChunkMinPieceTiles = 64;   // a KV piece of a cut unit is at least this many 16-token tiles
+constexpr uint32_t kChunkStartCostTiles = 8;   // fixed cost of a work item (query load, epilogue) in KV tiles
 
 ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
                            const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,

@@ -450,6 +450,11 @@ def test_long_query_runs_through_the_chunk_kernel(heads, head_dim, page, max_cta
     s.ctx.sync()
     assert float((s.out.float() - fused.float()).abs().max()) <= 1e-2
     assert s.gqa.device_status() == 0  # no bounded wait of the tcgen05 kernel ran out
+    stats = s.gqa.plan_stats()
+    if engine == "tcgen05":
+        assert stats["chunk_tcgen05_launches"] >= 2 and stats["chunk_mma_sync_launches"] == 0
+    else:
+        assert stats["chunk_tcgen05_launches"] == 0 and stats["chunk_mma_sync_launches"] >= 2
     s.close()
 
 
