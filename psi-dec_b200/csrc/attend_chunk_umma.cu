@@ -328,13 +328,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     const uint32_t tile = tile_base + i, fill = 2 * tile, slot = fill % kSlots;
                     wait(kBarFull + slot, fill / kSlots);
                     tc_fence_after();
-                    const uint32_t k_slot = smem_base + slot * kTileBytes;
+                    // K-major operand: 8-row groups kBlocks KiB apart; per k-step the start moves to element block ks / 4
+                    // and 32 bytes on inside it (the start-address field counts 16-byte units)
+                    const uint64_t k_desc = umma_desc(smem_base + slot * kTileBytes, 16, kBlocks * 1024);
+                    const uint32_t s_tmem = tmem + kColS + (tile & 1) * kUmmaN;
 #pragma unroll
-                    for (uint32_t ks = 0; ks < uint32_t(D) / 16; ++ks) {
-                        // K-major operand: 8-row groups kBlocks KiB apart, element block ks / 4, 32 bytes per k-step
-                        const uint64_t b = umma_desc(k_slot + (ks >> 2) * 1024 + (ks & 3) * 32, 16, kBlocks * 1024);
-                        umma_issue_ts(tmem + kColS + (tile & 1) * kUmmaN, tmem + kColQ + ks * 8, b, idesc_qk, ks > 0);
-                    }
+                    for (uint32_t ks = 0; ks < uint32_t(D) / 16; ++ks)
+                        umma_issue_ts(s_tmem, tmem + kColQ + ks * 8, k_desc + ((ks >> 2) * 1024 + (ks & 3) * 32) / 16, idesc_qk, ks > 0);
                     umma_commit(bar(kBarS + (tile & 1)));
                     umma_commit(bar(kBarEmpty + slot));
                 };
@@ -347,15 +347,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     wait(kBarFull + slot, fill / kSlots);
                     wait(kBarP + (tile & 1), tile >> 1);      // P of tile i is in TMEM (over the first half of its S buffer)
                     tc_fence_after();
-                    const uint32_t v_slot = smem_base + slot * kTileBytes;
+                    // MN-major operand: 64-element blocks 1 KiB apart, 8-token groups kBlocks KiB apart, two groups per
+                    // k-step
+                    const uint64_t v_desc = umma_desc(smem_base + slot * kTileBytes, 1024, kBlocks * 1024);
+                    const uint32_t p_tmem = tmem + kColS + (tile & 1) * kUmmaN;
 #pragma unroll
-                    for (uint32_t ks = 0; ks < kUmmaN / 16; ++ks) {
-                        // MN-major operand: 64-element blocks 1 KiB apart, 8-token groups kBlocks KiB apart, two groups
-                        // per k-step
-                        const uint64_t b = umma_desc(v_slot + ks * 2 * (kBlocks * 1024), 1024, kBlocks * 1024);
-                        umma_issue_ts(tmem + kColO, tmem + kColS + (tile & 1) * kUmmaN + ks * 8, b, idesc_pv,
+                    for (uint32_t ks = 0; ks < kUmmaN / 16; ++ks)
+                        umma_issue_ts(tmem + kColO, p_tmem + ks * 8, v_desc + ks * 2 * (kBlocks * 1024) / 16, idesc_pv,
                                       (i > 0 || ks > 0) ? 1u : 0u);
-                    }
                     umma_commit(bar(kBarO + (tile & 1)));
                     umma_commit(bar(kBarEmpty + slot));
                 }
@@ -366,42 +365,49 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         // ================================ one accumulator row per thread ===============================================
         const uint32_t lane_base = (warp * 32u) << 16;  // this warp's TMEM lanes
         const uint32_t tmem_o = tmem + kColO;
+        // Row of this thread in an item: 16-row tile w = tid / 16, row rr inside it -> (token, head) of the super-tile.
+        const uint32_t w = tid >> 4, rr = tid & 15;
+        auto row_of = [&](const ItemView& v, bool& valid) {
+            const uint32_t token_off = w * p.tokens_per_tile + rr / v.num_heads;
+            valid = rr < p.tokens_per_tile * v.num_heads && token_off < v.num_tokens;
+            return static_cast<uint64_t>(v.flat_begin + (valid ? token_off : 0)) * p.num_q_heads + v.head0 + rr % v.num_heads;
+        };
+        // This thread's query row of an item into its TMEM lane (zero for rows the super-tile does not have).  Called
+        // when every Q K^T of the previous item has completed; 16 loads in flight at a time.
+        auto load_q = [&](const ItemView& v) {
+            bool valid;
+            const uint64_t row = row_of(v, valid);
+            const uint4* q_row = reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + row * D);
+#pragma unroll 1
+            for (uint32_t c = 0; c < uint32_t(D) / 2; c += 64) {
+                uint32_t regs[2][32];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const uint4 value = valid ? q_row[c / 4 + j] : make_uint4(0, 0, 0, 0);
+                    regs[j / 8][4 * (j % 8)] = value.x;
+                    regs[j / 8][4 * (j % 8) + 1] = value.y;
+                    regs[j / 8][4 * (j % 8) + 2] = value.z;
+                    regs[j / 8][4 * (j % 8) + 3] = value.w;
+                }
+                __syncwarp();
+                tmem_store32_bits(tmem + kColQ + lane_base + c, regs[0]);
+                tmem_store32_bits(tmem + kColQ + lane_base + c + 32, regs[1]);
+            }
+            tmem_store_wait();
+            tc_fence_before();
+            mbar_arrive(bar(kBarQ));
+        };
+
+        if (item_begin < item_end) load_q(view_item(p, item_begin));
         for (uint32_t index = item_begin; index < item_end; ++index, ++item_count) {
             const ItemView v = view_item(p, index);
-
-            // row of this thread: 16-row tile w, row rr inside it -> (token, head) of the super-tile
-            const uint32_t w = tid >> 4, rr = tid & 15;
+            bool row_valid;
+            const uint64_t out_row = row_of(v, row_valid);
             const uint32_t token_off = w * p.tokens_per_tile + rr / v.num_heads;
-            const bool row_valid = rr < p.tokens_per_tile * v.num_heads && token_off < v.num_tokens;
             const uint32_t limit = row_valid ? min(v.kv_end, v.first_pos + token_off + 1) : v.kv_end;
             const uint32_t min_limit = min(v.kv_end, v.first_pos + 1);
-            const uint64_t out_row = static_cast<uint64_t>(v.flat_begin + (row_valid ? token_off : 0)) * p.num_q_heads +
-                                     v.head0 + rr % v.num_heads;
             const uint32_t first_tile = v.kv_begin / kUmmaN;
             const uint32_t num_tiles = (v.kv_end + kUmmaN - 1) / kUmmaN - first_tile;
-
-            // this thread's query row into its TMEM lane (zero for rows the super-tile does not have); every Q K^T of
-            // the previous item has completed
-            {
-                const uint4* q_row = reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + out_row * D);
-#pragma unroll 1
-                for (uint32_t c = 0; c < uint32_t(D) / 2; c += 32) {
-                    uint32_t regs[32];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint4 value = row_valid ? q_row[c / 4 + j] : make_uint4(0, 0, 0, 0);
-                        regs[4 * j] = value.x;
-                        regs[4 * j + 1] = value.y;
-                        regs[4 * j + 2] = value.z;
-                        regs[4 * j + 3] = value.w;
-                    }
-                    __syncwarp();
-                    tmem_store32_bits(tmem + kColQ + lane_base + c, regs);
-                }
-                tmem_store_wait();
-                tc_fence_before();
-                mbar_arrive(bar(kBarQ));
-            }
 
             // softmax state in the log2 domain: `row_ref` is the reference the exponentials are taken against (it
             // trails the true running max `row_max` by at most kRescaleThreshold), `row_sum` is relative to it
@@ -495,6 +501,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 tc_fence_after();
             }
             tile_base += num_tiles;
+            // The next item's query rows go to TMEM before this item's output is written: its first Q K^T products then
+            // run under the epilogue (O is not touched before P of that item's first tile exists).
+            if (index + 1 < item_end) load_q(view_item(p, index + 1));
 
             // ---- epilogue: every thread finishes its own row ---------------------------------------------------------------
             // back to the true max as the reference: l' = l * 2^(ref - max); O / l is unchanged by the shift
@@ -513,15 +522,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 }
                 if (row_valid) {
 #pragma unroll
-                    for (int e = 0; e < 32; e += 4) {
-                        const float4 value = make_float4(o[e] * inv, o[e + 1] * inv, o[e + 2] * inv, o[e + 3] * inv);
-                        if (is_partial) {
-                            *reinterpret_cast<float4*>(p.partial_o + prow * D + c + e) = value;
-                        } else if (p.ext_o != nullptr) {
-                            *reinterpret_cast<float4*>(p.ext_o + out_row * D + c + e) = value;
-                        } else {
-                            store_out4<T>(p, out_row * D + c + e, value);
-                        }
+                    for (int e = 0; e < 32; ++e) o[e] *= inv;
+                    if (is_partial || p.ext_o != nullptr) {
+                        float* dst = is_partial ? p.partial_o + prow * D + c : p.ext_o + out_row * D + c;
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4)
+                            *reinterpret_cast<float4*>(dst + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8) store_out8<T>(p, out_row * D + c + e, o + e);
                     }
                 }
                 __syncwarp();  // the TMEM load of the next pass is warp-collective

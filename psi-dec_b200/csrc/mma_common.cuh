@@ -96,6 +96,21 @@ __device__ __forceinline__ void store_out4(const AttendParams& p, uint64_t index
     Mma<T>::store4(static_cast<T*>(p.out) + index, v);
 }
 
+// Eight consecutive outputs as one 16-byte store.
+template <typename T>
+__device__ __forceinline__ void store_out8(const AttendParams& p, uint64_t index, const float* v) {
+    float g[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+    if (p.gates != nullptr) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.gates) + index);
+        const T* gate = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) g[i] = gate_sigmoid(static_cast<float>(gate[i]));
+    }
+    const uint4 packed = make_uint4(Mma<T>::pack(v[0] * g[0], v[1] * g[1]), Mma<T>::pack(v[2] * g[2], v[3] * g[3]),
+                                    Mma<T>::pack(v[4] * g[4], v[5] * g[5]), Mma<T>::pack(v[6] * g[6], v[7] * g[7]));
+    *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + index) = packed;
+}
+
 template <typename T>
 __device__ __forceinline__ void store_out2(const AttendParams& p, uint64_t index, float a, float b) {
     if (p.gates != nullptr) {
