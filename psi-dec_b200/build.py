@@ -44,6 +44,8 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
               "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden", f"-I{ROOT / 'include'}", f"-I{CSRC}"]
     if verbose:
         common += ["-Xptxas", "-v"]
+    # extra -D flags for tracing builds, e.g. PSI_CUDA_DEFINES="PSI_UMMA_TRACE"
+    common += [f"-D{name}" for name in os.environ.get("PSI_CUDA_DEFINES", "").split() if name]
     procs = []
     objects = []
     for src in SOURCES:

@@ -27,6 +27,12 @@
 
 namespace psi {
 
+#ifdef PSI_UMMA_TRACE
+// Build-time tracing (-DPSI_UMMA_TRACE): per CTA its cycles in the kernel, the 64-token tiles it processed and the
+// cycles its row threads spent waiting for S; read back with psi_debug_umma_cta.
+__device__ unsigned long long g_umma_cta[148 * 4];
+#endif
+
 namespace {
 
 constexpr uint32_t kRowThreads = 128;   // warps 0-3: one accumulator row per thread
@@ -66,6 +72,17 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Non-blocking test of one phase.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(done)
         : "r"(bar), "r"(parity)
         : "memory");
@@ -195,6 +212,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
     const uint32_t cta = blockIdx.x;
     if (cta >= p.scalars[kScalarNumChunkCtas]) return;
+#ifdef PSI_UMMA_TRACE
+    const long long trace_t0 = clock64();
+    long long trace_wait_s = 0, trace_item = 0;
+#endif
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bars[kNumBarriers];
@@ -232,7 +253,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     // A wait that ran out flags the launch and lets every later wait fall through: results are then garbage, the
     // status word says so, and the kernel still frees its TMEM and returns.
     auto wait = [&](uint32_t which, uint32_t parity) {
-        if (mbar_try(bar(which), parity & 1)) return;  // the usual case: already complete, or completes within one try
+        if (mbar_test(bar(which), parity & 1)) return;  // the usual case: already complete
         if (*reinterpret_cast<volatile uint32_t*>(&abort_s) == 0 && !mbar_wait(bar(which), parity & 1)) {
             abort_s = 1;
             if (p.status != nullptr) atomicExch(p.status, static_cast<uint32_t>(PSI_ERR_TIMEOUT));
@@ -416,7 +437,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 const uint32_t tile = tile_base + i, buf = tile & 1;
                 const uint32_t token0 = (first_tile + i) * kUmmaN;
                 const uint32_t tmem_s = tmem + kColS + buf * kUmmaN + lane_base;
+#ifdef PSI_UMMA_TRACE
+                const long long trace_w0 = clock64();
+#endif
                 wait(kBarS + buf, tile >> 1);
+#ifdef PSI_UMMA_TRACE
+                trace_wait_s += clock64() - trace_w0;
+#endif
                 __syncwarp();  // the TMEM accesses below are warp-collective
                 tc_fence_after();
 
@@ -501,6 +528,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 tc_fence_after();
             }
             tile_base += num_tiles;
+#ifdef PSI_UMMA_TRACE
+            const long long trace_e0 = clock64();
+#endif
             // The next item's query rows go to TMEM before this item's output is written: its first Q K^T products then
             // run under the epilogue (O is not touched before P of that item's first tile exists).
             if (index + 1 < item_end) load_q(view_item(p, index + 1));
@@ -558,55 +588,90 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 for (uint32_t tile = 0; tile < 8; ++tile) {
                     if (!last_s[tile]) continue;
                     __threadfence();
+                    // 16 rows x D / 4 float4 outputs per tile, 8 per thread (row 2 j + tid / (D / 4) ... for D = 256);
+                    // the loads of one pass are independent of one another, so each pass costs one round trip per two
+                    // pieces rather than one per output
                     const uint32_t tile_tokens = min(p.tokens_per_tile, v.num_tokens - tile * p.tokens_per_tile);
                     const uint32_t tile_rows = tile_tokens * v.num_heads;
-                    for (uint32_t i = tid; i < tile_rows * (D / 4); i += kRowThreads) {
-                        const uint32_t r = i / (D / 4), c4 = i % (D / 4);
-                        float global_max = -INFINITY;
-#pragma unroll 4
-                        for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
-                            const uint64_t row = static_cast<uint64_t>(v.unit_first_slot + s_i * 8 + tile) * kMaxRows + r;
-                            global_max = fmaxf(global_max, __ldcg(p.partial_m + row));
+                    constexpr uint32_t kPerThread = kMaxRows * (D / 4) / kRowThreads;
+                    constexpr uint32_t kRowStep = kRowThreads / (D / 4);  // rows between a thread's consecutive outputs
+                    const uint32_t c4 = tid % (D / 4), r0 = tid / (D / 4);
+                    const uint64_t slot_rows = static_cast<uint64_t>(v.unit_first_slot + tile) * kMaxRows;
+                    float row_top[kPerThread];
+#pragma unroll
+                    for (uint32_t j = 0; j < kPerThread; ++j) row_top[j] = -INFINITY;
+#pragma unroll 2
+                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
+#pragma unroll
+                        for (uint32_t j = 0; j < kPerThread; ++j) {
+                            const uint32_t r = r0 + j * kRowStep;
+                            if (r < tile_rows)
+                                row_top[j] = fmaxf(row_top[j], __ldcg(p.partial_m + slot_rows + static_cast<uint64_t>(s_i) * 8 * kMaxRows + r));
                         }
-                        float sum = 0.0f;
-                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-                        for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
-                            const uint64_t row = static_cast<uint64_t>(v.unit_first_slot + s_i * 8 + tile) * kMaxRows + r;
-                            const float pm = __ldcg(p.partial_m + row);
-                            const float weight = pm == -INFINITY ? 0.0f : exp2f(pm - global_max) * __ldcg(p.partial_l + row);
-                            const float4 part = __ldcg(reinterpret_cast<const float4*>(p.partial_o + row * D + 4 * c4));
-                            sum += weight;
-                            acc.x += weight * part.x;
-                            acc.y += weight * part.y;
-                            acc.z += weight * part.z;
-                            acc.w += weight * part.w;
+                    }
+                    float sum[kPerThread];
+                    float4 acc[kPerThread];
+#pragma unroll
+                    for (uint32_t j = 0; j < kPerThread; ++j) {
+                        sum[j] = 0.0f;
+                        acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll 2
+                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
+#pragma unroll
+                        for (uint32_t j = 0; j < kPerThread; ++j) {
+                            const uint32_t r = r0 + j * kRowStep;
+                            if (r < tile_rows) {
+                                const uint64_t row = slot_rows + static_cast<uint64_t>(s_i) * 8 * kMaxRows + r;
+                                const float pm = __ldcg(p.partial_m + row);
+                                const float pl = __ldcg(p.partial_l + row);
+                                const float4 part = __ldcg(reinterpret_cast<const float4*>(p.partial_o + row * D + 4 * c4));
+                                const float weight = pm == -INFINITY ? 0.0f : exp2f(pm - row_top[j]) * pl;
+                                sum[j] += weight;
+                                acc[j].x += weight * part.x;
+                                acc[j].y += weight * part.y;
+                                acc[j].z += weight * part.z;
+                                acc[j].w += weight * part.w;
+                            }
                         }
-                        const float scale = sum > 0.0f ? 1.0f / sum : 0.0f;
-                        acc.x *= scale;
-                        acc.y *= scale;
-                        acc.z *= scale;
-                        acc.w *= scale;
+                    }
+#pragma unroll
+                    for (uint32_t j = 0; j < kPerThread; ++j) {
+                        const uint32_t r = r0 + j * kRowStep;
+                        if (r >= tile_rows) continue;
+                        const float scale = sum[j] > 0.0f ? 1.0f / sum[j] : 0.0f;
+                        const float4 value = make_float4(acc[j].x * scale, acc[j].y * scale, acc[j].z * scale, acc[j].w * scale);
                         const uint64_t row =
                             static_cast<uint64_t>(v.flat_begin + tile * p.tokens_per_tile + r / v.num_heads) * p.num_q_heads +
                             v.head0 + r % v.num_heads;
                         if (p.ext_o != nullptr) {
-                            *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc;
+                            *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = value;
                             if (c4 == 0) {
-                                p.ext_m[row] = global_max * kLn2;
-                                p.ext_l[row] = sum;
+                                p.ext_m[row] = row_top[j] * kLn2;
+                                p.ext_l[row] = sum[j];
                             }
                         } else {
-                            store_out4<T>(p, row * D + 4 * c4, acc);
+                            store_out4<T>(p, row * D + 4 * c4, value);
                         }
                     }
                     if (tid == 0) p.unit_counters[v.reduce_unit + tile] = 0;  // ready for the next launch
                 }
                 row_threads_sync();  // the flags are read before the next item overwrites them
             }
+#ifdef PSI_UMMA_TRACE
+            trace_item += clock64() - trace_e0;
+#endif
         }
     }
 
+#ifdef PSI_UMMA_TRACE
+    if (tid == 0 && cta < 148) {
+        g_umma_cta[cta * 4] = clock64() - trace_t0;
+        g_umma_cta[cta * 4 + 1] = tile_base;
+        g_umma_cta[cta * 4 + 2] = trace_wait_s;
+        g_umma_cta[cta * 4 + 3] = trace_item;
+    }
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {
@@ -684,6 +749,13 @@ cudaError_t launch_for_dim(const AttendParams& p, uint32_t num_ctas, cudaStream_
 
 // cudaErrorNotSupported: the arena cannot be described to the TMA unit (alignment, size); nothing was launched and
 // the caller takes launch_attend_chunk instead.
+#ifdef PSI_UMMA_TRACE
+extern "C" __attribute__((visibility("default"))) int psi_debug_umma_cta(unsigned long long* out) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+    return cudaMemcpyFromSymbol(out, g_umma_cta, sizeof(g_umma_cta)) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 cudaError_t launch_attend_chunk_umma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     if (num_ctas == 0) return cudaSuccess;
     return p.dtype == PSI_DTYPE_BF16 ? launch_for_dim<__nv_bfloat16>(p, num_ctas, stream)

@@ -404,7 +404,12 @@ ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, c
     const uint32_t tokens_per_item = geo.tokens_per_tile * kChunkTilesPerItem;
     const uint32_t heads = geo.num_kv_heads * geo.head_tiles;
     uint64_t total = 0;
-    for (uint32_t r : requests) {
+    // longest requests first: the work dealt last, which decides how far the last CTA trails, is the cheapest
+    std::vector<uint32_t> by_length(requests);
+    std::stable_sort(by_length.begin(), by_length.end(), [&](uint32_t a, uint32_t b) {
+        return token_indices[a] + (cu_tokens[a + 1] - cu_tokens[a]) > token_indices[b] + (cu_tokens[b + 1] - cu_tokens[b]);
+    });
+    for (uint32_t r : by_length) {
         for (uint32_t h = 0; h < heads; ++h) {
             for (uint32_t begin = cu_tokens[r]; begin < cu_tokens[r + 1];) {
                 const uint32_t end = std::min(cu_tokens[r + 1], begin + tokens_per_item);
@@ -417,9 +422,10 @@ ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, c
     plan.total_kv_tiles = total;
     if (total == 0) return plan;
     const uint64_t num_ctas = std::min<uint64_t>(std::max(1u, max_ctas), std::max<uint64_t>(1, total / 4));
-    // A unit longer than 1/8 of a CTA's fair share is cut along its KV range into equal pieces (partial slots, merged
-    // by the last arriver), which bounds how far the last CTA can trail the others.
-    const uint64_t piece_cap = std::max<uint64_t>(kChunkMinPieceTiles, div_ceil(total, num_ctas * 8));
+    // A unit longer than 1/4 of a CTA's fair share is cut along its KV range into equal pieces (partial slots, merged
+    // by the last arriver), which bounds how far the last CTA can trail the others; shorter units stay whole, since a
+    // cut costs a partial write, a fence and a merge.
+    const uint64_t piece_cap = std::max<uint64_t>(kChunkMinPieceTiles, div_ceil(total, num_ctas * 4));
 
     // Pieces are dealt in order to whichever CTA is free first under the cost model (KV tiles + a fixed start
     // cost): the static equivalent of CTAs pulling work from a queue.
