@@ -60,7 +60,10 @@ __device__ __forceinline__ uint32_t umma_idesc(uint32_t n, bool b_mn_major) {
 }
 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile(
+        "{\n\t.reg .pred e;\n\telect.sync _|e, 0xFFFFFFFF;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(bar)
+        : "memory");
 }
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -161,10 +164,11 @@ __device__ __forceinline__ void tma_load_groups(uint32_t dst, const CUtensorMap*
 
 __device__ __forceinline__ void row_threads_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// Executed by a whole converged warp; one elected lane (always the same one for a full warp) issues.
 __device__ __forceinline__ void umma_issue_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "{\n\t.reg .pred p, e;\n\tsetp.ne.b32 p, %4, 0;\n\telect.sync _|e, 0xFFFFFFFF;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
         "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -335,8 +339,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             mbar_wait(bar(kBarFull + fill % kSlots), (fill / kSlots) & 1);
         }
     } else if (warp == 4) {
-        // ================================ MMA issue (one thread) =========================================================
-        if (lane == 0) {
+        // ================================ MMA issue (converged warp, one elected lane) ================================
+        {
             const uint32_t idesc_qk = umma_idesc<T>(kUmmaN, false);
             const uint32_t idesc_pv = umma_idesc<T>(D, true);
             for (uint32_t index = item_begin; index < item_end; ++index, ++item_count) {
