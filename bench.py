@@ -30,6 +30,7 @@ METRIC = "paged_gqa_decode_kv_read_bandwidth"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1400.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one attend_mma_kernel launch divided by the launch's algorithmic
 # bytes, from the ncu capture summarised in profiles/attend_mma_cfg2_ncu_full.md (301.27 MB for 296.76 MB).
 NCU_DRAM_BYTES_PER_ALGORITHMIC_BYTE = {"cfg2-a3b-layer-decode": 301.27 / 296.76}
@@ -43,6 +44,18 @@ def measured_peak():
         except Exception:
             pass
     return FALLBACK_HBM_GBS, "fallback"
+
+
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s of a library GEMM timed inside a seconds-long loop (the chunk kernel runs for milliseconds
+    per launch under the power cap), else the stated fallback."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["bf16_tflops_sustained"]), "measured (sustained)"
+        except Exception:
+            pass
+    return FALLBACK_BF16_TFLOPS, "fallback"
 
 
 class ClockSampler:
@@ -111,7 +124,7 @@ def bench_ours(args):
     # sequences, sequence-sharded, no collective in the step (weak scaling).  Configurations 3 and 5 shard their fixed
     # batch by sequence, configuration 4 splits every sequence's KV range across the ranks and exchanges partials
     # (strong scaling).
-    base = W.config(args.config)
+    base = W.config(args.config, scale_down=args.scale_down)
     exchange = None
     scaling, parallelism = "weak", f"sequence-sharded x{world}"
     if world == 1:
@@ -123,7 +136,7 @@ def bench_ours(args):
         spec = base.shard(rank, world)
         scaling = "strong"
     else:
-        specs = [W.config(args.config, seed=base.seed + 100 * r) for r in range(world)]
+        specs = [W.config(args.config, scale_down=args.scale_down, seed=base.seed + 100 * r) for r in range(world)]
         whole = W.Spec(base.name, base.dtype, base.num_q_heads, base.num_kv_heads, base.head_dim,
                        base.tokens_per_page, np.concatenate([s.context_lens for s in specs]),
                        np.concatenate([s.q_len for s in specs]), base.seed)
@@ -177,6 +190,7 @@ def bench_ours(args):
     append_ms, append_n = ctx.kernel_timing(0)
     reduce_ms, reduce_n = ctx.kernel_timing(2)
     combine_ms, combine_n = ctx.kernel_timing(3)
+    chunk_ms, chunk_n = ctx.kernel_timing(5)
     ctx.enable_kernel_timing(False)
     barrier()
 
@@ -233,7 +247,8 @@ def bench_ours(args):
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
             "scaling": scaling, "vs_baseline": None, "dtype": "bf16" if spec.dtype == pkg.BF16 else "f16/f32",
             "data": "synthetic",
-            "config": {"workload": base.name, "sequences_rank0": spec.num_seqs, "q_heads": spec.num_q_heads,
+            "config": {"workload": base.name if args.scale_down == 1 else f"{base.name}/scaled-down-{args.scale_down}",
+                       "sequences_rank0": spec.num_seqs, "q_heads": spec.num_q_heads,
                        "kv_heads": spec.num_kv_heads, "head_dim": spec.head_dim,
                        "tokens_per_page": spec.tokens_per_page, "visible_tokens_rank0": int(spec.visible.sum()),
                        "seed": base.seed, "parallelism": parallelism,
@@ -250,7 +265,8 @@ def bench_ours(args):
             "kernel_ms_per_step": {"append": round(append_ms / max(append_n, 1), 5),
                                    "attend_map": round(map_avg_ms, 5),
                                    "attend_reduce": round(reduce_ms / max(reduce_n, 1), 5),
-                                   "combine": round(combine_ms / max(combine_n, 1), 5)},
+                                   "combine": round(combine_ms / max(combine_n, 1), 5),
+                                   "attend_chunk": round(chunk_ms / max(chunk_n, 1), 5)},
             "e2e": {"value": round(job_bytes / (e2e_total_ms / args.steps * 1e-3) / 1e9, 1), "unit": UNIT,
                     "ms_per_step": round(e2e_total_ms / args.steps, 5),
                     "tokens_per_s": round(job_tokens / (e2e_total_ms / args.steps * 1e-3), 1),
@@ -258,8 +274,22 @@ def bench_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if chunk_n and chunk_ms > map_ms:
+            # long query runs dominate the step: the chunk kernel is a contraction, bounded by the tensor pipe
+            flops = spec.long_run_flops(16 // min(16, spec.num_q_heads // spec.num_kv_heads))
+            tensor_peak, tensor_kind = measured_tensor_peak()
+            chunk_avg_ms = chunk_ms / chunk_n
+            tflops = flops / (chunk_avg_ms * 1e-3) / 1e12
+            engine = "tcgen05" if stats["chunk_tcgen05_launches"] else "mma.sync"
+            line["roofline"] = {"bound": "tensor", "kernel": f"attend_chunk ({engine}, rank 0)",
+                                "achieved": round(tflops, 1), "peak": tensor_peak, "peak_kind": tensor_kind,
+                                "unit": "TFLOP/s", "frac": round(tflops / tensor_peak, 4), "traffic": None,
+                                "flops_per_launch": flops, "avg_launch_ms": round(chunk_avg_ms, 5),
+                                "launches": chunk_n}
+            line["config"]["chunk_ctas"] = stats["chunk_ctas"]
+            line["config"]["chunk_items"] = stats["chunk_items"]
         per_byte = NCU_DRAM_BYTES_PER_ALGORITHMIC_BYTE.get(base.name)
-        if per_byte and stats["kernel"] == 2:
+        if per_byte and stats["kernel"] == 2 and line["roofline"]["bound"] == "hbm":
             line["roofline"]["traffic"] = int(per_byte * alg["total"])
         if world == 1 and not args.no_cpu_baseline:
             import checks
@@ -287,7 +317,7 @@ def bench_reference(args):
     from oracle import psi_oracle as O
     from psi_dec_b200 import workloads as W
 
-    base = W.config(args.config)
+    base = W.config(args.config, scale_down=args.scale_down)
     order = np.argsort(base.visible, kind="stable")
     budget = 400_000 * max(1, O.num_threads()) // 8  # visible tokens per step: a step of roughly a second
     chosen, total = [], 0
@@ -353,6 +383,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--config", type=int, default=2, help="benchmark configuration (2 = the headline)")
+    parser.add_argument("--scale-down", type=int, default=1,
+                        help="divide batch and context sizes (small cases for profiler captures; not a bench value)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--kernel", choices=["auto", "mma", "generic", "mma_sync"], default="auto",
                         help="attention kernel: tensor-core kernels (default where supported), the CUDA-core kernel, or "

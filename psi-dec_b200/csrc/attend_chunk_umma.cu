@@ -1,21 +1,23 @@
 // Multi-query attention for long query runs on the 5th-generation tensor cores (tcgen05 / TMEM), K/V staged by TMA.
 //
 // Same work items as attend_chunk.cu (a super-tile of up to eight 16-row query tiles of one request and KV head: 128
-// rows = one native UMMA M tile), different engine.  The 128 query rows sit in shared memory once per item; K and V
-// tiles of 64 tokens are brought from their pages by TMA (one box of min(tokens_per_page, 64) rows x 64 elements per
-// copy, written with the 128-byte swizzle the MMA descriptors expect) into two K and two V slots.  Roles:
-//   warps 0-3 (128 threads): one accumulator row each.  Read the S row from TMEM (tcgen05.ld), apply the causal limit
-//       and the online softmax without any cross-thread traffic, write P back to shared memory as an MMA operand,
-//       rescale their O row in TMEM only when a running max moved; epilogue, partial slots and last-arriver merge as
-//       in attend_chunk.cu.
-//   warp 4: lane 0 issues the TMA copies and the MMAs
-//         S[128x64]  = Q[128xD] . K^T    (both operands K-major from shared memory, accumulator in TMEM, two buffers)
-//         O[128xD]  += P[128x64] . V     (V as an MN-major operand, accumulator in TMEM)
+// rows = one native UMMA M tile), different engine.  Per CTA (224 threads, 512 TMEM columns, a shared-memory ring of
+// K/V tiles of 64 tokens):
+//   warps 0-3 (128 threads): one accumulator row each.  Stage their query row in TMEM as an MMA A operand (the next
+//       item's row goes in before the current item's output is written), read the S row from TMEM (tcgen05.ld), apply
+//       the causal limit and the online softmax without any cross-thread traffic, write P back over the S buffer as
+//       the A operand of P V, rescale their O row in TMEM only when the running max ran away from the reference the
+//       exponentials are taken against; epilogue, partial slots and last-arriver merge as in attend_chunk.cu.
+//   warp 4: issues the MMAs from converged code with one elected lane (operands then stay in uniform registers)
+//         S[128x64]  = Q[128xD] . K^T    (Q from TMEM, K as a K-major shared-memory operand, two S buffers)
+//         O[128xD]  += P[128x64] . V     (P from TMEM, V as an MN-major shared-memory operand)
 //       so that Q K^T of tile i+1 runs under the softmax of tile i and P V of tile i under the softmax of tile i+1.
-//       Tiles that touch this step's not-yet-paged rows (fused step) or end beyond the item are copied by the whole
-//       warp with zero-filling 16-byte cp.async instead.
+//   warps 5 and 6: bring the K and the V tiles from their pages by TMA, one 5-D box per page segment that lands in
+//       exactly the order the MMA descriptors read ([8-row group][64-element block][8 rows][64 elements], 128-byte
+//       swizzle); an item's last, ragged tile is copied with zero-filling 16-byte cp.async instead.
 // All hand-offs are mbarriers (TMA byte counts, tcgen05.commit, thread arrivals); every wait is bounded and reports
-// PSI_ERR_TIMEOUT through the status word instead of hanging, and the kernel frees its TMEM on every path.
+// PSI_ERR_TIMEOUT through the status word instead of hanging, and the kernel frees its TMEM on every path.  The kernel
+// reads pages only: a step that appends and attends runs the append launch first.
 //
 // Arithmetic replaced: crates/inference-backend-metal/src/components/metal/gqa_split_kv_tiled_q.metal:49-378.
 #include <cuda.h>
@@ -29,14 +31,15 @@ namespace psi {
 
 #ifdef PSI_UMMA_TRACE
 // Build-time tracing (-DPSI_UMMA_TRACE): per CTA its cycles in the kernel, the 64-token tiles it processed and the
-// cycles its row threads spent waiting for S; read back with psi_debug_umma_cta.
-__device__ unsigned long long g_umma_cta[148 * 4];
+// cycles its row threads spent waiting for S, at item ends, in merges of cut units (with their count and pieces) and
+// from an item's end to the start of its merge; read back with psi_debug_umma_cta.
+__device__ unsigned long long g_umma_cta[148 * 8];
 #endif
 
 namespace {
 
 constexpr uint32_t kRowThreads = 128;   // warps 0-3: one accumulator row per thread
-constexpr uint32_t kUmmaThreads = 192;  // + warp 4: MMA issue, warp 5: K/V tiles into the shared-memory ring
+constexpr uint32_t kUmmaThreads = 224;  // + warp 4: MMA issue, warps 5 and 6: K and V tiles into the shared-memory ring
 constexpr uint32_t kUmmaM = 128;   // query rows per CTA = TMEM lanes
 constexpr uint32_t kUmmaN = 64;    // KV tokens per tile
 constexpr uint32_t kMaxPolls = 200000;
@@ -155,9 +158,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // One TMA box of the page arena into shared memory; completion is counted in bytes on `bar`.  The arena is viewed as
 // [page][8-row group][element block][row in group][64 elements], a box takes whole groups of one page (all element
 // blocks), so the only coordinates that vary are the group and the page; the innermost one is always 0.
+// Executed by a whole converged warp; one elected lane issues the copy.
 __device__ __forceinline__ void tma_load_groups(uint32_t dst, const CUtensorMap* map, uint32_t bar, uint32_t group, uint32_t page) {
     asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %4, %5}], [%2];" ::"r"(dst),
+        "{\n\t.reg .pred e;\n\telect.sync _|e, 0xFFFFFFFF;\n\t"
+        "@e cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %4, %5}], [%2];\n\t}\n" ::"r"(dst),
         "l"(map), "r"(bar), "r"(0u), "r"(group), "r"(page)
         : "memory");
 }
@@ -218,7 +223,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     if (cta >= p.scalars[kScalarNumChunkCtas]) return;
 #ifdef PSI_UMMA_TRACE
     const long long trace_t0 = clock64();
-    long long trace_wait_s = 0, trace_item = 0;
+    long long trace_wait_s = 0, trace_item = 0, trace_merge = 0, trace_merges = 0, trace_pieces = 0, trace_partial = 0;
 #endif
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -271,8 +276,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     uint32_t tile_base = 0, item_count = 0;
     const uint32_t item_begin = p.cta_item_begin[cta], item_end = p.cta_item_begin[cta + 1];
 
-    if (warp == 5) {
-        // ================================ producer: K/V tiles into the ring ==========================================
+    if (warp >= 5) {
+        // ================================ producers: K (warp 5) and V (warp 6) tiles into the ring ====================
         const uint32_t v_groups = p.geo.num_kv_heads * p.geo.tokens_per_page / 8;  // 8-row groups of a page's K region
         for (uint32_t index = item_begin; index < item_end; ++index) {
             const ItemView v = view_item(p, index);
@@ -294,7 +299,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                         window_ids = first_page + lane <= last_page ? row_ids[first_page + lane] : 0u;
                     }
                 }
-                for (uint32_t which = 0; which < 2; ++which) {
+                {
+                    const uint32_t which = warp - 5;  // warp 5 brings the K tiles, warp 6 the V tiles
                     const uint32_t fill = 2 * (tile_base + i) + which, slot = fill % kSlots, use = fill / kSlots;
                     const uint32_t dst = smem_base + slot * kTileBytes;
                     if (use > 0) wait(kBarEmpty + slot, use - 1);  // the MMAs that read the slot's previous tile are done
@@ -305,8 +311,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                             const uint32_t token = token0 + row;
                             const uint32_t page = __shfl_sync(0xFFFFFFFFu, window_ids, (token >> page_shift) - window_base);
                             const uint32_t group = which * v_groups + head_group + (token & page_mask) / 8;
-                            if (lane == 0)
-                                tma_load_groups(dst + (row / 8) * (kBlocks * 1024), &kv_map, bar(kBarFull + slot), group, page);
+                            tma_load_groups(dst + (row / 8) * (kBlocks * 1024), &kv_map, bar(kBarFull + slot), group, page);
                         }
                     } else {
                         // the item's last tile: rows at and beyond its end are zero
@@ -589,8 +594,16 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     last_s[tid] = has_rows && atomicAdd(p.unit_counters + v.reduce_unit + tid, 1u) == v.unit_num_items - 1;
                 }
                 row_threads_sync();
+#ifdef PSI_UMMA_TRACE
+                const long long trace_m0 = clock64();
+                trace_partial += trace_m0 - trace_e0;
+#endif
                 for (uint32_t tile = 0; tile < 8; ++tile) {
                     if (!last_s[tile]) continue;
+#ifdef PSI_UMMA_TRACE
+                    trace_merges += 1;
+                    trace_pieces += v.unit_num_items;
+#endif
                     __threadfence();
                     // 16 rows x D / 4 float4 outputs per tile, 8 per thread (row 2 j + tid / (D / 4) ... for D = 256);
                     // the loads of one pass are independent of one another, so each pass costs one round trip per two
@@ -601,17 +614,22 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     constexpr uint32_t kRowStep = kRowThreads / (D / 4);  // rows between a thread's consecutive outputs
                     const uint32_t c4 = tid % (D / 4), r0 = tid / (D / 4);
                     const uint64_t slot_rows = static_cast<uint64_t>(v.unit_first_slot + tile) * kMaxRows;
+                    // rows beyond the tile's last one are computed on the last row and dropped at the end: the loops
+                    // below are then straight-line code whose loads all go out before the first one is used
+                    uint64_t row_off[kPerThread];
+#pragma unroll
+                    for (uint32_t j = 0; j < kPerThread; ++j) row_off[j] = slot_rows + min(r0 + j * kRowStep, tile_rows - 1);
                     float row_top[kPerThread];
 #pragma unroll
                     for (uint32_t j = 0; j < kPerThread; ++j) row_top[j] = -INFINITY;
-#pragma unroll 2
+#pragma unroll 4
                     for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
+                        float pm[kPerThread];
 #pragma unroll
-                        for (uint32_t j = 0; j < kPerThread; ++j) {
-                            const uint32_t r = r0 + j * kRowStep;
-                            if (r < tile_rows)
-                                row_top[j] = fmaxf(row_top[j], __ldcg(p.partial_m + slot_rows + static_cast<uint64_t>(s_i) * 8 * kMaxRows + r));
-                        }
+                        for (uint32_t j = 0; j < kPerThread; ++j)
+                            pm[j] = __ldcg(p.partial_m + row_off[j] + static_cast<uint64_t>(s_i) * 8 * kMaxRows);
+#pragma unroll
+                        for (uint32_t j = 0; j < kPerThread; ++j) row_top[j] = fmaxf(row_top[j], pm[j]);
                     }
                     float sum[kPerThread];
                     float4 acc[kPerThread];
@@ -622,21 +640,23 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     }
 #pragma unroll 2
                     for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
+                        float pm[kPerThread], pl[kPerThread];
+                        float4 part[kPerThread];
 #pragma unroll
                         for (uint32_t j = 0; j < kPerThread; ++j) {
-                            const uint32_t r = r0 + j * kRowStep;
-                            if (r < tile_rows) {
-                                const uint64_t row = slot_rows + static_cast<uint64_t>(s_i) * 8 * kMaxRows + r;
-                                const float pm = __ldcg(p.partial_m + row);
-                                const float pl = __ldcg(p.partial_l + row);
-                                const float4 part = __ldcg(reinterpret_cast<const float4*>(p.partial_o + row * D + 4 * c4));
-                                const float weight = pm == -INFINITY ? 0.0f : exp2f(pm - row_top[j]) * pl;
-                                sum[j] += weight;
-                                acc[j].x += weight * part.x;
-                                acc[j].y += weight * part.y;
-                                acc[j].z += weight * part.z;
-                                acc[j].w += weight * part.w;
-                            }
+                            const uint64_t row = row_off[j] + static_cast<uint64_t>(s_i) * 8 * kMaxRows;
+                            pm[j] = __ldcg(p.partial_m + row);
+                            pl[j] = __ldcg(p.partial_l + row);
+                            part[j] = __ldcg(reinterpret_cast<const float4*>(p.partial_o + row * D + 4 * c4));
+                        }
+#pragma unroll
+                        for (uint32_t j = 0; j < kPerThread; ++j) {
+                            const float weight = pm[j] == -INFINITY ? 0.0f : exp2f(pm[j] - row_top[j]) * pl[j];
+                            sum[j] += weight;
+                            acc[j].x += weight * part[j].x;
+                            acc[j].y += weight * part[j].y;
+                            acc[j].z += weight * part[j].z;
+                            acc[j].w += weight * part[j].w;
                         }
                     }
 #pragma unroll
@@ -661,6 +681,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     if (tid == 0) p.unit_counters[v.reduce_unit + tile] = 0;  // ready for the next launch
                 }
                 row_threads_sync();  // the flags are read before the next item overwrites them
+#ifdef PSI_UMMA_TRACE
+                trace_merge += clock64() - trace_m0;
+#endif
             }
 #ifdef PSI_UMMA_TRACE
             trace_item += clock64() - trace_e0;
@@ -670,10 +693,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
 #ifdef PSI_UMMA_TRACE
     if (tid == 0 && cta < 148) {
-        g_umma_cta[cta * 4] = clock64() - trace_t0;
-        g_umma_cta[cta * 4 + 1] = tile_base;
-        g_umma_cta[cta * 4 + 2] = trace_wait_s;
-        g_umma_cta[cta * 4 + 3] = trace_item;
+        g_umma_cta[cta * 8] = clock64() - trace_t0;
+        g_umma_cta[cta * 8 + 1] = tile_base;
+        g_umma_cta[cta * 8 + 2] = trace_wait_s;
+        g_umma_cta[cta * 8 + 3] = trace_item;
+        g_umma_cta[cta * 8 + 4] = trace_merge;
+        g_umma_cta[cta * 8 + 5] = trace_merges;
+        g_umma_cta[cta * 8 + 6] = trace_pieces;
+        g_umma_cta[cta * 8 + 7] = trace_partial;
     }
 #endif
     tc_fence_before();

@@ -422,10 +422,10 @@ ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, c
     plan.total_kv_tiles = total;
     if (total == 0) return plan;
     const uint64_t num_ctas = std::min<uint64_t>(std::max(1u, max_ctas), std::max<uint64_t>(1, total / 4));
-    // A unit longer than 1/4 of a CTA's fair share is cut along its KV range into equal pieces (partial slots, merged
-    // by the last arriver), which bounds how far the last CTA can trail the others; shorter units stay whole, since a
-    // cut costs a partial write, a fence and a merge.
-    const uint64_t piece_cap = std::max<uint64_t>(kChunkMinPieceTiles, div_ceil(total, num_ctas * 4));
+    // A unit longer than half a CTA's fair share is cut along its KV range into equal pieces (partial slots, merged
+    // by the last arriver), which bounds how far the last CTA can trail the others; shorter units stay whole, since
+    // every piece costs a partial write and a fence, and the merge reads all of them.
+    const uint64_t piece_cap = std::max<uint64_t>(kChunkMinPieceTiles, div_ceil(total, num_ctas * 2));
 
     // Pieces are dealt in order to whichever CTA is free first under the cost model (KV tiles + a fixed start
     // cost): the static equivalent of CTAs pulling work from a queue.

@@ -98,6 +98,16 @@ class Spec:
         table = int(self.pages_per_seq().sum()) * 4
         return {"kv": kv, "q_o": q_o, "append": app, "table": table, "total": kv + q_o + app + table}
 
+    def long_run_flops(self, tokens_per_tile: int, min_tiles: int = 5) -> int:
+        """Multiply-add work (2 flops each, Q K^T and P V) of the requests whose query run is long enough for the
+        chunk kernel: query token j of a request sees its context plus the j + 1 tokens appended so far."""
+        total = 0
+        for ctx, n in zip(self.context_lens.tolist(), self.q_len.tolist()):
+            if -(-n // tokens_per_tile) >= min_tiles:
+                keys = n * ctx + n * (n + 1) // 2
+                total += 4 * self.head_dim * self.num_q_heads * keys
+        return total
+
     def shard(self, rank: int, world: int) -> "Spec":
         """Sequence shard ``rank`` of ``world``: longest-first round robin, so every rank carries a similar KV load.
         Each rank owns its sequences' pages in an arena of its own."""
