@@ -109,10 +109,22 @@ class Spec:
         return total
 
     def shard(self, rank: int, world: int) -> "Spec":
-        """Sequence shard ``rank`` of ``world``: longest-first round robin, so every rank carries a similar KV load.
-        Each rank owns its sequences' pages in an arena of its own."""
-        order = np.argsort(-self.visible, kind="stable")
-        mine = np.sort(order[rank::world])
+        """Sequence shard ``rank`` of ``world``: sequences are dealt most-expensive-first to the rank with the least
+        work so far, where a sequence costs its K/V bytes at HBM speed plus, for a long query run, its attention
+        flops at tensor speed, so every rank carries a similar load.  Each rank owns its sequences' pages in an arena
+        of its own."""
+        kv_bytes = self.visible * (2 * self.num_kv_heads * self.head_dim * self.elem_bytes)
+        tokens_per_tile = max(1, 16 // min(16, self.num_q_heads // self.num_kv_heads))
+        long_run = -(-self.q_len // tokens_per_tile) >= 5
+        keys = self.q_len * self.context_lens + self.q_len * (self.q_len + 1) // 2
+        flops = np.where(long_run, 4 * self.head_dim * self.num_q_heads * keys, 0)
+        cost = kv_bytes / 6.5e12 + flops / 1.2e15
+        loads = np.zeros(world)
+        owner = np.empty(self.num_seqs, dtype=np.int64)
+        for seq in np.argsort(-cost, kind="stable"):
+            owner[seq] = int(np.argmin(loads))
+            loads[owner[seq]] += cost[seq]
+        mine = np.flatnonzero(owner == rank)
         return Spec(name=f"{self.name}/shard{rank}of{world}", dtype=self.dtype, num_q_heads=self.num_q_heads,
                     num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, tokens_per_page=self.tokens_per_page,
                     context_lens=self.context_lens[mine], q_len=self.q_len[mine], seed=self.seed * 1000 + rank,
