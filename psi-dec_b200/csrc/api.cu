@@ -163,6 +163,7 @@ struct psi_gqa {
     // section offsets (in words) of the block uploaded by the last prepare
     uint64_t off_req_slots = 0, off_token_indices = 0, off_cta = 0, off_reduces = 0, off_items = 0;
     uint64_t off_chunk_cta = 0, off_chunk_items = 0;
+    uint64_t off_first_items = 0;  // copies of every CTA's first item (mma kernel)
 
     DeviceBuffer partial_o, partial_ml;  // [slots][16][D] and [2][slots][16]
     DeviceBuffer unit_counters;          // [slots] u32, zero between launches
@@ -267,6 +268,7 @@ AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* 
     p.q = q;
     p.items = reinterpret_cast<const DeviceItem*>(block_words(g, g->off_items));
     p.cta_item_begin = block_words(g, g->off_cta);
+    if (g->kernel == PSI_KERNEL_MMA) p.cta_first_items = reinterpret_cast<const DeviceItem*>(block_words(g, g->off_first_items));
     p.reduces = reinterpret_cast<const ReduceUnit*>(block_words(g, g->off_reduces));
     p.partial_o = static_cast<float*>(g->partial_o.ptr);
     p.partial_m = static_cast<float*>(g->partial_ml.ptr);
@@ -904,7 +906,7 @@ int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out
         const uint32_t per_sm =
             g->kernel == PSI_KERNEL_MMA ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm();
         g->grid_cap = c.max_ctas > 0 ? c.max_ctas : static_cast<uint32_t>(ctx->sm_count) * per_sm;
-        g->item_start_cost = g->kernel == PSI_KERNEL_MMA ? 16u : 0u;
+        g->item_start_cost = g->kernel == PSI_KERNEL_MMA ? 32u : 0u;
         g->chunk_supported = g->kernel == PSI_KERNEL_MMA && c.plan_mode == PSI_PLAN_BALANCED &&
                              attend_chunk_supported(c.dtype, c.head_dim, g->tokens_per_page);
         g->chunk_umma = g->chunk_supported && c.kernel_mode != PSI_KERNEL_MMA_SYNC;
@@ -1031,6 +1033,8 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         cursor += pad_words(plan.reduces.size() * 2);
         g->off_items = cursor;
         cursor += pad_words(device_items.size() * (sizeof(DeviceItem) / sizeof(uint32_t)));
+        g->off_first_items = cursor;
+        cursor += pad_words(static_cast<uint64_t>(plan.num_ctas()) * (sizeof(DeviceItem) / sizeof(uint32_t)));
         g->off_chunk_cta = cursor;
         cursor += pad_words(chunk.cta_item_begin.size());
         g->off_chunk_items = cursor;
@@ -1074,6 +1078,14 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
             std::memcpy(s + g->off_reduces, plan.reduces.data(), plan.reduces.size() * sizeof(ReduceUnit));
         if (!device_items.empty())
             std::memcpy(s + g->off_items, device_items.data(), device_items.size() * sizeof(DeviceItem));
+        // a copy of every CTA's first item at a place the CTA can read without knowing its range (zeros for a CTA
+        // without items, which its empty range tells it not to use)
+        for (uint32_t c = 0; c < plan.num_ctas(); ++c) {
+            DeviceItem first{};
+            if (plan.cta_item_begin[c] < plan.cta_item_begin[c + 1]) first = device_items[plan.cta_item_begin[c]];
+            std::memcpy(s + g->off_first_items + static_cast<uint64_t>(c) * (sizeof(DeviceItem) / sizeof(uint32_t)), &first,
+                        sizeof(DeviceItem));
+        }
         std::copy(chunk.cta_item_begin.begin(), chunk.cta_item_begin.end(), s + g->off_chunk_cta);
         if (!chunk.items.empty())
             std::memcpy(s + g->off_chunk_items, chunk.items.data(), chunk.items.size() * sizeof(DeviceItem));

@@ -35,6 +35,18 @@ struct SmemLayout {
     static constexpr uint32_t kTotal = kRingOffset + (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes);
 };
 
+#ifdef PSI_MMA_TRACE
+// Build-time tracing (-DPSI_MMA_TRACE): per CTA the global-timer stamps (ns) of kernel entry, first K/V tile landed,
+// end of the last tile loop and exit, how many units it merged, and the prologue's stages (metadata read, page ids
+// read, first copies issued, query rows staged); read back with psi_debug_mma_cta.
+__device__ unsigned long long g_mma_cta[148 * 10];
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#endif
+
 template <typename T, int D, int NSLOT>
 __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p) {
     using L = SmemLayout<D, NSLOT>;
@@ -43,7 +55,21 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     constexpr int kKSteps = D / 16;
 
     const uint32_t cta = blockIdx.x;
-    if (cta >= p.scalars[kScalarNumCtas]) return;
+#ifdef PSI_MMA_TRACE
+    const unsigned long long trace_t0 = trace_now();
+    unsigned long long trace_first = 0, trace_loop_end = 0, trace_merged = 0, trace_items = 0;
+    unsigned long long trace_meta = 0, trace_ids = 0, trace_issued = 0, trace_staged = 0;
+#endif
+    // One round trip for everything the first tile copies depend on: the CTA count, this CTA's item range and a copy
+    // of its first item all go out before the first of them is needed.
+    const uint32_t num_ctas = p.scalars[kScalarNumCtas];
+    const uint32_t item_begin = p.cta_item_begin[cta], item_end = p.cta_item_begin[cta + 1];
+    const bool have_first = p.cta_first_items != nullptr;
+    const ItemView first_item = view_item(have_first ? p.cta_first_items + cta : p.items);
+    if (cta >= num_ctas) return;
+#ifdef PSI_MMA_TRACE
+    trace_meta = trace_now();
+#endif
 
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint32_t limit_s[kTile];
@@ -75,10 +101,9 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     const uint32_t copy_src = copy_row * L::kRowBytes + copy_chunk * 16;
     const uint32_t copy_x = copy_chunk ^ copy_row;                  // copy_row < 8: XOR-able with the row step below
 
-    const uint32_t item_begin = p.cta_item_begin[cta], item_end = p.cta_item_begin[cta + 1];
     const bool fused = p.new_k != nullptr;
     for (uint32_t index = item_begin; index < item_end; ++index) {
-        const ItemView v = view_item(p, index);
+        const ItemView v = (have_first && index == item_begin) ? first_item : view_item(p, index);
         __syncthreads();  // the previous item's merge is done with the ring, with q and with limit_s
 
         // Keys at or beyond `paged_end` are this step's own tokens: in the fused step they are read from new_k/new_v.
@@ -139,10 +164,23 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         RowState<D> st;
         st.clear();
 
+        // The query rows go straight into shared memory (zero rows beyond the item's) as the item's oldest copy group:
+        // they need nothing but the item, so they are under way before the first page id is known.
+        for (uint32_t i = tid; i < kTile * kChunks; i += kThreads) {
+            const uint32_t r = i / kChunks, c = i % kChunks;
+            const bool present = r < v.rows;
+            const T* src = static_cast<const T*>(p.q) + (present ? item_row_index(p, v, r) * D + c * 8 : 0);
+            cp_async_16(q_base + swizzled(r, c, L::kRowBytes), src, present ? 16u : 0u);
+        }
+        cp_async_commit();
+
         // ids of the tile whose halves are issued next, and of the tile after it
         uint32_t cur_lo = 0, cur_hi = 0, next_lo = 0, next_hi = 0;
         if (my_tiles > 0) lookup(0, cur_lo, cur_hi);
         if (my_tiles > 1) lookup(1, next_lo, next_hi);
+#ifdef PSI_MMA_TRACE
+        if (trace_ids == 0) trace_ids = (cur_lo == 0xFFFFFFFFu ? 1 : 0) + trace_now();
+#endif
 #pragma unroll
         for (uint32_t h = 0; h < NSLOT - 1; ++h) {
             if (h < my_halves) {
@@ -156,17 +194,11 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             cp_async_commit();
         }
 
-        // ---- with the first tiles in flight: stage the query rows (zero rows beyond the item's), the per-row
-        // causal limits, and in the fused step write this item's share of the step's K/V rows into their pages --------
-        for (uint32_t i = tid; i < kTile * kChunks; i += kThreads) {
-            const uint32_t r = i / kChunks, c = i % kChunks;
-            uint4 value = make_uint4(0, 0, 0, 0);
-            if (r < v.rows) {
-                const T* src = static_cast<const T*>(p.q) + item_row_index(p, v, r) * D + c * 8;
-                value = *reinterpret_cast<const uint4*>(src);
-            }
-            *reinterpret_cast<uint4*>(smem + swizzled(r, c, L::kRowBytes)) = value;
-        }
+#ifdef PSI_MMA_TRACE
+        if (trace_issued == 0) trace_issued = trace_now();
+#endif
+        // ---- with the first tiles in flight: the per-row causal limits, and in the fused step this item's share of the
+        // step's K/V rows into their pages -------------------------------------------------------------------------------
         if (tid < kTile) limit_s[tid] = tid < v.rows ? item_row_limit(v, tid) : v.kv_end;
         if (fused && v.writes_kv) {
             for (uint32_t i = tid; i < v.num_tokens * 2 * kChunks; i += kThreads) {
@@ -183,8 +215,12 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                 }
             }
         }
+        cp_async_wait<NSLOT - 1>();  // the query rows (the oldest group) have landed; the K/V tiles stay in flight
         __syncthreads();
 
+#ifdef PSI_MMA_TRACE
+        if (trace_staged == 0) trace_staged = trace_now();
+#endif
         const uint32_t limit0 = limit_s[quad_row], limit1 = limit_s[quad_row + 8];
         uint32_t limit_min = v.kv_end;
         for (uint32_t r = 0; r < v.rows; ++r) limit_min = min(limit_min, limit_s[r]);
@@ -193,6 +229,9 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         for (uint32_t h = 0; h < my_halves; ++h) {
             cp_async_wait<NSLOT - 2>();
             __syncwarp();
+#ifdef PSI_MMA_TRACE
+            if (trace_first == 0) trace_first = trace_now();
+#endif
             const uint32_t ahead = h + NSLOT - 1;
             if (ahead < my_halves) {
                 issue(ahead, ahead % NSLOT, cur_lo, cur_hi);
@@ -215,6 +254,10 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             }
         }
 
+#ifdef PSI_MMA_TRACE
+        trace_loop_end = trace_now();
+        trace_items += 1;
+#endif
         // ---- merge the warps' partial results --------------------------------------------------------------------------
         cp_async_wait<0>();
         __syncthreads();  // every warp is done with its ring: the merge buffer may overwrite it
@@ -292,48 +335,51 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             if (tid == 0) arrival_s = atomicAdd(p.unit_counters + v.reduce_unit, 1u);
             __syncthreads();
             if (arrival_s == v.unit_num_items - 1) {
+#ifdef PSI_MMA_TRACE
+                trace_merged += 1;
+#endif
                 __threadfence();
-                // All statistics of the unit first (one round trip for every thread), then the weights per row, then
-                // the weighted sum with several partial rows in flight per thread.
+                // Every thread merges its own outputs (row r, four columns) from all pieces: the pieces' statistics of
+                // row r and their O values go out together, four pieces at a time, so a unit of up to four pieces costs
+                // one round trip.
                 const uint32_t n = v.unit_num_items, rows = v.rows;
-                float* stat_m = merge_o;                 // [n][rows] max, overwritten by the weights
-                float* stat_l = merge_o + n * rows;      // [n][rows] sum
-                float* row_max = stat_l + n * rows;      // [rows]
-                float* row_sum = row_max + kTile;        // [rows]
-                for (uint32_t i = tid; i < n * rows; i += kThreads) {
-                    const uint64_t prow = static_cast<uint64_t>(v.unit_first_slot + i / rows) * kMaxRows + i % rows;
-                    stat_m[i] = __ldcg(p.partial_m + prow);
-                    stat_l[i] = __ldcg(p.partial_l + prow);
-                }
-                __syncthreads();
-                if (tid < rows) {
-                    float global_max = -INFINITY;
-                    for (uint32_t s_i = 0; s_i < n; ++s_i) global_max = fmaxf(global_max, stat_m[s_i * rows + tid]);
-                    float sum = 0.0f;
-                    for (uint32_t s_i = 0; s_i < n; ++s_i) {
-                        const float pm = stat_m[s_i * rows + tid];
-                        const float weight = pm == -INFINITY ? 0.0f : exp2f(pm - global_max) * stat_l[s_i * rows + tid];
-                        stat_m[s_i * rows + tid] = weight;
-                        sum += weight;
-                    }
-                    row_max[tid] = global_max;
-                    row_sum[tid] = sum;
-                }
-                __syncthreads();
                 for (uint32_t i = tid; i < rows * (D / 4); i += kThreads) {
                     const uint32_t r = i / (D / 4), c4 = i % (D / 4);
-                    const float* src = p.partial_o + (static_cast<uint64_t>(v.unit_first_slot) * kMaxRows + r) * D + 4 * c4;
+                    const uint64_t prow0 = static_cast<uint64_t>(v.unit_first_slot) * kMaxRows + r;
+                    float run_max = -INFINITY, sum = 0.0f;
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-                    for (uint32_t s_i = 0; s_i < n; ++s_i) {
-                        const float4 part = __ldcg(reinterpret_cast<const float4*>(src + static_cast<uint64_t>(s_i) * kMaxRows * D));
-                        const float weight = stat_m[s_i * rows + r];
-                        acc.x += weight * part.x;
-                        acc.y += weight * part.y;
-                        acc.z += weight * part.z;
-                        acc.w += weight * part.w;
+                    for (uint32_t s0 = 0; s0 < n; s0 += 4) {
+                        float pm[4], pl[4];
+                        float4 part[4];
+#pragma unroll
+                        for (uint32_t k = 0; k < 4; ++k) {
+                            const uint64_t prow = prow0 + static_cast<uint64_t>(min(s0 + k, n - 1)) * kMaxRows;
+                            pm[k] = __ldcg(p.partial_m + prow);
+                            pl[k] = __ldcg(p.partial_l + prow);
+                            part[k] = __ldcg(reinterpret_cast<const float4*>(p.partial_o + prow * D + 4 * c4));
+                        }
+                        float group_max = run_max;
+#pragma unroll
+                        for (uint32_t k = 0; k < 4; ++k)
+                            if (s0 + k < n) group_max = fmaxf(group_max, pm[k]);
+                        const float carry = run_max == -INFINITY ? 0.0f : exp2f(run_max - group_max);
+                        sum *= carry;
+                        acc.x *= carry;
+                        acc.y *= carry;
+                        acc.z *= carry;
+                        acc.w *= carry;
+#pragma unroll
+                        for (uint32_t k = 0; k < 4; ++k) {
+                            const float weight =
+                                (s0 + k < n && pm[k] != -INFINITY) ? exp2f(pm[k] - group_max) * pl[k] : 0.0f;
+                            sum += weight;
+                            acc.x += weight * part[k].x;
+                            acc.y += weight * part[k].y;
+                            acc.z += weight * part[k].z;
+                            acc.w += weight * part[k].w;
+                        }
+                        run_max = group_max;
                     }
-                    const float sum = row_sum[r];
                     const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
                     acc.x *= inv;
                     acc.y *= inv;
@@ -343,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                     if (p.ext_o != nullptr) {
                         *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc;
                         if (c4 == 0) {
-                            p.ext_m[row] = row_max[r] * kLn2;
+                            p.ext_m[row] = run_max * kLn2;
                             p.ext_l[row] = sum;
                         }
                     } else {
@@ -354,6 +400,20 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             }
         }
     }
+#ifdef PSI_MMA_TRACE
+    if (tid == 0 && cta < 148) {
+        g_mma_cta[cta * 10] = trace_t0;
+        g_mma_cta[cta * 10 + 1] = trace_first;
+        g_mma_cta[cta * 10 + 2] = trace_loop_end;
+        g_mma_cta[cta * 10 + 3] = trace_now();
+        g_mma_cta[cta * 10 + 4] = trace_merged;
+        g_mma_cta[cta * 10 + 5] = trace_items;
+        g_mma_cta[cta * 10 + 6] = trace_meta;
+        g_mma_cta[cta * 10 + 7] = trace_ids;
+        g_mma_cta[cta * 10 + 8] = trace_issued;
+        g_mma_cta[cta * 10 + 9] = trace_staged;
+    }
+#endif
 }
 
 template <int D>
@@ -401,6 +461,13 @@ bool attend_mma_supported(uint32_t dtype, uint32_t head_dim, uint32_t tokens_per
 }
 
 uint32_t attend_mma_ctas_per_sm(uint32_t /*head_dim*/) { return 1; }
+
+#ifdef PSI_MMA_TRACE
+extern "C" __attribute__((visibility("default"))) int psi_debug_mma_cta(unsigned long long* out) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+    return cudaMemcpyFromSymbol(out, g_mma_cta, sizeof(g_mma_cta)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 cudaError_t launch_attend_mma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     if (num_ctas == 0) return cudaSuccess;

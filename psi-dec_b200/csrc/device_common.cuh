@@ -63,6 +63,16 @@ struct ItemView : DeviceItem {
     uint32_t rows;
 };
 
+__device__ __forceinline__ ItemView view_item(const DeviceItem* item) {
+    ItemView v;
+    const uint4* src = reinterpret_cast<const uint4*>(item);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<DeviceItem*>(&v));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] = src[i];
+    v.rows = v.num_tokens * v.num_heads;
+    return v;
+}
+
 __device__ __forceinline__ ItemView view_item(const AttendParams& p, uint32_t index) {
     ItemView v;
     const uint4* src = reinterpret_cast<const uint4*>(p.items + index);

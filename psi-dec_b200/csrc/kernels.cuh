@@ -83,6 +83,7 @@ struct AttendParams {
     const void* new_v;            //                  and read from here instead of from their pages; else nullptr
     const DeviceItem* items;
     const uint32_t* cta_item_begin;
+    const DeviceItem* cta_first_items;  // nullptr, or [num_ctas]: a copy of each CTA's first item, readable before its range
     const ReduceUnit* reduces;
     float* partial_o;             // [slots][16][D] normalised
     float* partial_m;             // [slots][16] log2-domain max
