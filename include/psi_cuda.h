@@ -174,6 +174,59 @@ PSI_API int32_t psi_pages_allocate(psi_pages* pages);
 PSI_API int32_t psi_pages_export_range(psi_pages* pages, uint64_t page_begin, uint64_t page_end, void* host_out);
 PSI_API int32_t psi_pages_import_range(psi_pages* pages, uint64_t page_begin, uint64_t page_end, const void* host_in);
 
+/* ---- hibernation snapshots (crates/inference-executor-metal/src/model/state_snapshot.rs:40-881) --------------------
+ * A snapshot is a directory: one raw payload file per buffer ("page-arena", "main-gqa-request-page-table", ...) and a
+ * "manifest" (magic "PSISTATE", version 3, the hibernation plan, the sorted file list with payload lengths), written
+ * into a temporary sibling directory and published by rename.  StateSnapshotWriter::{new, write_full_buffer,
+ * write_selected_buffer, write_metadata, commit} and StateSnapshotReader::{open, read_full_buffer,
+ * read_selected_buffer, read_metadata, finish} keep their validation rules and messages.  With a selected plan the
+ * page arena is written / read by the plan's page-ID ranges (entry = one page) and a page table by its request-slot
+ * ranges (entry = one slot row), as PageArena and GQARequestPageTable do in
+ * crates/inference-executor-metal/src/attn/gqa/request_page_table/file_io.rs:14-60.  All calls block. */
+typedef struct psi_snapshot_writer psi_snapshot_writer;
+typedef struct psi_snapshot_reader psi_snapshot_reader;
+typedef struct psi_u32_range {
+    uint32_t begin, end; /* [begin, end) */
+} psi_u32_range;
+typedef struct psi_hibernation_plan { /* ExecutorHibernationPlan: All (selected = 0) or Selected */
+    uint32_t selected;
+    const psi_u32_range* request_slot_ranges;
+    uint64_t num_request_slot_ranges;
+    const psi_u32_range* page_id_ranges;
+    uint64_t num_page_id_ranges;
+} psi_hibernation_plan;
+typedef enum psi_snapshot_file { /* StateSnapshotFile, in manifest order */
+    PSI_SNAPSHOT_PAGE_ARENA = 0,
+    PSI_SNAPSHOT_MAIN_GQA_REQUEST_PAGE_TABLE = 1,
+    PSI_SNAPSHOT_MAIN_GDN_REQUEST_STATE_TABLE = 2, /* the one metadata (not buffer) file */
+    PSI_SNAPSHOT_MAIN_GDN_RECURRENT_STATE = 3,
+    PSI_SNAPSHOT_MAIN_GDN_CONV_STATE = 4,
+    PSI_SNAPSHOT_MTP_GQA_REQUEST_PAGE_TABLE = 5,
+    PSI_SNAPSHOT_DSPARK_GQA_REQUEST_PAGE_TABLE = 6
+} psi_snapshot_file;
+PSI_API int32_t psi_snapshot_writer_create(const char* destination, const uint32_t* expected_files, uint64_t num_files,
+                                           const psi_hibernation_plan* plan, psi_snapshot_writer** out);
+/* Whole arena / table under the All plan, the plan's page-ID / request-slot ranges under a Selected plan. */
+PSI_API int32_t psi_snapshot_write_pages(psi_snapshot_writer* writer, uint32_t file, psi_pages* pages);
+PSI_API int32_t psi_snapshot_write_table(psi_snapshot_writer* writer, uint32_t file, psi_table* table);
+/* A caller-held host buffer: whole (entry_ranges == NULL) or the given entry ranges of entry_bytes each. */
+PSI_API int32_t psi_snapshot_write_host_buffer(psi_snapshot_writer* writer, uint32_t file, const void* host, uint64_t bytes,
+                                               const psi_u32_range* entry_ranges, uint64_t num_ranges, uint64_t entry_bytes);
+PSI_API int32_t psi_snapshot_write_metadata(psi_snapshot_writer* writer, uint32_t file, const void* bytes, uint64_t n);
+PSI_API int32_t psi_snapshot_writer_commit(psi_snapshot_writer* writer);
+/* Also abandons an uncommitted snapshot (its temporary directory is removed). */
+PSI_API int32_t psi_snapshot_writer_destroy(psi_snapshot_writer* writer);
+PSI_API int32_t psi_snapshot_reader_open(const char* path, const uint32_t* expected_files, uint64_t num_files,
+                                         const psi_hibernation_plan* plan, psi_snapshot_reader** out);
+PSI_API int32_t psi_snapshot_read_pages(psi_snapshot_reader* reader, uint32_t file, psi_pages* pages);
+PSI_API int32_t psi_snapshot_read_table(psi_snapshot_reader* reader, uint32_t file, psi_table* table);
+PSI_API int32_t psi_snapshot_read_host_buffer(psi_snapshot_reader* reader, uint32_t file, void* host, uint64_t bytes,
+                                              const psi_u32_range* entry_ranges, uint64_t num_ranges, uint64_t entry_bytes);
+/* Copies the metadata payload into out (capacity cap) and stores its length in *out_n. */
+PSI_API int32_t psi_snapshot_read_metadata(psi_snapshot_reader* reader, uint32_t file, void* out, uint64_t cap, uint64_t* out_n);
+PSI_API int32_t psi_snapshot_reader_finish(psi_snapshot_reader* reader);
+PSI_API int32_t psi_snapshot_reader_destroy(psi_snapshot_reader* reader);
+
 /* ---- request page table (crates/inference-executor-metal/src/attn/gqa/request_page_table.rs:13-122) --------------- */
 
 /* GQARequestPageTable::new: zero-initialised u32 table on the device with a host mirror. */

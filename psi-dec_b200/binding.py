@@ -305,6 +305,136 @@ class GQASplitKV:
         return self._call(1, 1)[1]
 
 
+class _U32Range(C.Structure):
+    _fields_ = [("begin", C.c_uint32), ("end", C.c_uint32)]
+
+
+class _HibernationPlan(C.Structure):
+    _fields_ = [("selected", C.c_uint32), ("request_slot_ranges", C.POINTER(_U32Range)),
+                ("num_request_slot_ranges", C.c_uint64), ("page_id_ranges", C.POINTER(_U32Range)),
+                ("num_page_id_ranges", C.c_uint64)]
+
+
+def _ranges(ranges):
+    ranges = [(int(b), int(e)) for b, e in ranges]
+    arr = (_U32Range * max(len(ranges), 1))(*[_U32Range(b, e) for b, e in ranges])
+    return arr, len(ranges)
+
+
+class ExecutorHibernationPlan:
+    """``ExecutorHibernationPlan``: ``all()`` or ``selected(request_slot_ranges, page_id_ranges)`` (half-open ranges)."""
+
+    def __init__(self, selected: bool, request_slot_ranges=(), page_id_ranges=()):
+        self.is_selected = selected
+        self.request_slot_ranges = [tuple(r) for r in request_slot_ranges]
+        self.page_id_ranges = [tuple(r) for r in page_id_ranges]
+
+    @classmethod
+    def all(cls):
+        return cls(False)
+
+    @classmethod
+    def selected(cls, request_slot_ranges, page_id_ranges):
+        return cls(True, request_slot_ranges, page_id_ranges)
+
+    def _c(self):
+        slots, n_slots = _ranges(self.request_slot_ranges)
+        pages, n_pages = _ranges(self.page_id_ranges)
+        plan = _HibernationPlan(1 if self.is_selected else 0, slots, n_slots, pages, n_pages)
+        return plan, (slots, pages)  # the arrays must outlive the call
+
+
+# StateSnapshotFile
+SNAPSHOT_PAGE_ARENA, SNAPSHOT_MAIN_GQA_REQUEST_PAGE_TABLE, SNAPSHOT_MAIN_GDN_REQUEST_STATE_TABLE = 0, 1, 2
+SNAPSHOT_MAIN_GDN_RECURRENT_STATE, SNAPSHOT_MAIN_GDN_CONV_STATE = 3, 4
+SNAPSHOT_MTP_GQA_REQUEST_PAGE_TABLE, SNAPSHOT_DSPARK_GQA_REQUEST_PAGE_TABLE = 5, 6
+
+
+class StateSnapshotWriter:
+    """``StateSnapshotWriter``: files go into a temporary directory that ``commit`` publishes by rename."""
+
+    def __init__(self, destination, expected_files, plan: ExecutorHibernationPlan):
+        self._h = C.c_void_p()
+        files, n = _u32_array(list(expected_files))
+        c_plan, keep = plan._c()
+        _check(library().psi_snapshot_writer_create(str(destination).encode(), files, C.c_uint64(n), C.byref(c_plan),
+                                                    C.byref(self._h)))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            library().psi_snapshot_writer_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def write_pages(self, snapshot_file: int, pages):
+        _check(library().psi_snapshot_write_pages(self._h, C.c_uint32(snapshot_file), pages._h))
+
+    def write_table(self, snapshot_file: int, table):
+        _check(library().psi_snapshot_write_table(self._h, C.c_uint32(snapshot_file), table._h))
+
+    def write_full_buffer(self, snapshot_file: int, array):
+        _check(library().psi_snapshot_write_host_buffer(self._h, C.c_uint32(snapshot_file), C.c_void_p(array.ctypes.data),
+                                                        C.c_uint64(array.nbytes), None, C.c_uint64(0), C.c_uint64(0)))
+
+    def write_selected_buffer(self, snapshot_file: int, array, entry_ranges, entry_bytes: int):
+        ranges, n = _ranges(entry_ranges)
+        _check(library().psi_snapshot_write_host_buffer(self._h, C.c_uint32(snapshot_file), C.c_void_p(array.ctypes.data),
+                                                        C.c_uint64(array.nbytes), ranges, C.c_uint64(n),
+                                                        C.c_uint64(entry_bytes)))
+
+    def write_metadata(self, snapshot_file: int, payload: bytes):
+        _check(library().psi_snapshot_write_metadata(self._h, C.c_uint32(snapshot_file), payload, C.c_uint64(len(payload))))
+
+    def commit(self):
+        _check(library().psi_snapshot_writer_commit(self._h))
+
+
+class StateSnapshotReader:
+    """``StateSnapshotReader``: validates manifest, plan, file set and directory on open; ``finish`` checks that every
+    file was read."""
+
+    def __init__(self, path, expected_files, plan: ExecutorHibernationPlan):
+        self._h = C.c_void_p()
+        files, n = _u32_array(list(expected_files))
+        c_plan, keep = plan._c()
+        _check(library().psi_snapshot_reader_open(str(path).encode(), files, C.c_uint64(n), C.byref(c_plan),
+                                                  C.byref(self._h)))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            library().psi_snapshot_reader_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def read_pages(self, snapshot_file: int, pages):
+        _check(library().psi_snapshot_read_pages(self._h, C.c_uint32(snapshot_file), pages._h))
+
+    def read_table(self, snapshot_file: int, table):
+        _check(library().psi_snapshot_read_table(self._h, C.c_uint32(snapshot_file), table._h))
+
+    def read_full_buffer(self, snapshot_file: int, array):
+        _check(library().psi_snapshot_read_host_buffer(self._h, C.c_uint32(snapshot_file), C.c_void_p(array.ctypes.data),
+                                                       C.c_uint64(array.nbytes), None, C.c_uint64(0), C.c_uint64(0)))
+
+    def read_selected_buffer(self, snapshot_file: int, array, entry_ranges, entry_bytes: int):
+        ranges, n = _ranges(entry_ranges)
+        _check(library().psi_snapshot_read_host_buffer(self._h, C.c_uint32(snapshot_file), C.c_void_p(array.ctypes.data),
+                                                       C.c_uint64(array.nbytes), ranges, C.c_uint64(n),
+                                                       C.c_uint64(entry_bytes)))
+
+    def read_metadata(self, snapshot_file: int) -> bytes:
+        out = C.create_string_buffer(1 << 20)
+        n = C.c_uint64()
+        _check(library().psi_snapshot_read_metadata(self._h, C.c_uint32(snapshot_file), out, C.c_uint64(len(out)),
+                                                    C.byref(n)))
+        return out.raw[:n.value]
+
+    def finish(self):
+        _check(library().psi_snapshot_reader_finish(self._h))
+
+
 class U32IDAllocator:
     """Reference ``U32IDAllocator`` semantics: freed IDs first (oldest first), then fresh IDs."""
 
