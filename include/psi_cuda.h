@@ -389,6 +389,17 @@ PSI_API int32_t psi_gqa_attend_gated(psi_gqa* gqa, psi_pages* pages, psi_table* 
 PSI_API int32_t psi_gqa_attend_partial(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
                                        const void* q, float* o, float* m, float* l);
 
+/* Dense bidirectional attention of every query token against the tokens of its own block of block_size tokens
+ * (GQABlockSDPAKernel::invoke, crates/inference-backend-metal/src/components/gqa_block_attention.rs:129-271; shader
+ * metal/gqa_block_sdpa.metal:5-77), written in the same partial ABI as psi_gqa_attend_partial so that
+ * psi_gqa_combine merges it with the paged history of the same tokens (the DSpark composite).  q [T][Hq][D],
+ * local_k / local_v [T][Hkv][D]: device, component dtype, unpaged; num_tokens must be a whole number of blocks
+ * (block_size <= 256).  slot_indices: NULL (token t writes partial slot t) or device [T] slot numbers
+ * (block_sdpa_map_task_template_indices); o [slots][Hq][D], m and l [slots][Hq], device f32. */
+PSI_API int32_t psi_gqa_block_partial(psi_gqa* gqa, const void* q, const void* local_k, const void* local_v,
+                                      uint32_t num_tokens, uint32_t block_size, const uint32_t* slot_indices, float* o,
+                                      float* m, float* l);
+
 /* Merge n partials per (token, head) exactly like the reference reduce (gqa_split_kv_single_q_reduce.metal:27-48):
  * M = max m_i, w_i = exp(m_i - M) * l_i (0 when m_i is not finite), out = sum w_i o_i / sum w_i (0 when the sum is 0).
  * o/m/l are host arrays of n device pointers; out is device [num_tokens][Hq][D] in the component's dtype. */

@@ -1012,3 +1012,49 @@ PSI_ORACLE_API void psi_oracle_activation_gate(const void* attention_output, con
         store_elem(output, i, dtype, a * sig);
     }
 }
+
+/* Dense bidirectional attention of every query token against the tokens of its own block of `block_size` tokens
+ * (local, unpaged K/V), as a partial in the reduce's ABI: normalised output, natural-log max, exp-sum per
+ * (token, q head).  crates/inference-backend-metal/src/components/metal/gqa_block_sdpa.metal:5-77 and the reference
+ * computation of crates/inference-backend-metal/src/components/gqa_block_attention_test.rs:98-139.
+ * q [T][Hq][D], local_k / local_v [T][Hkv][D] in `dtype`; partial_output [T][Hq][D] f32 (unrounded), partial_max and
+ * partial_sum [T][Hq]. */
+PSI_ORACLE_API void psi_oracle_block_sdpa(const void* q, const void* local_k, const void* local_v, int dtype,
+                                          uint32_t num_tokens, uint32_t block_size, uint32_t num_q_heads,
+                                          uint32_t num_kv_heads, uint32_t head_dim, float scale, float* partial_output,
+                                          float* partial_max, float* partial_sum) {
+    uint32_t group = num_q_heads / num_kv_heads;
+    float* weights = (float*)malloc(sizeof(float) * block_size);
+    for (uint32_t t = 0; t < num_tokens; ++t) {
+        uint32_t begin = t / block_size * block_size;
+        for (uint32_t h = 0; h < num_q_heads; ++h) {
+            uint32_t kv_head = h / group;
+            size_t q_row = ((size_t)t * num_q_heads + h) * head_dim;
+            float max_logit = -INFINITY;
+            for (uint32_t j = 0; j < block_size; ++j) {
+                size_t k_row = ((size_t)(begin + j) * num_kv_heads + kv_head) * head_dim;
+                float score = 0.0f;
+                for (uint32_t d = 0; d < head_dim; ++d) score += load_elem(q, q_row + d, dtype) * load_elem(local_k, k_row + d, dtype);
+                weights[j] = score * scale;
+                if (weights[j] > max_logit) max_logit = weights[j];
+            }
+            float exp_sum = 0.0f;
+            for (uint32_t j = 0; j < block_size; ++j) {
+                weights[j] = expf(weights[j] - max_logit);
+                exp_sum += weights[j];
+            }
+            size_t out_row = (size_t)t * num_q_heads + h;
+            partial_max[out_row] = max_logit;
+            partial_sum[out_row] = exp_sum;
+            for (uint32_t d = 0; d < head_dim; ++d) {
+                float acc = 0.0f;
+                for (uint32_t j = 0; j < block_size; ++j) {
+                    size_t v_row = ((size_t)(begin + j) * num_kv_heads + kv_head) * head_dim;
+                    acc += weights[j] * load_elem(local_v, v_row + d, dtype);
+                }
+                partial_output[out_row * head_dim + d] = exp_sum > 0.0f ? acc / exp_sum : 0.0f;
+            }
+        }
+    }
+    free(weights);
+}

@@ -336,3 +336,17 @@ def activation_gate(attention_bits, gate_bits, dtype):
     out = np.zeros_like(a)
     lib().psi_oracle_activation_gate(_p(a), _p(g), C.c_int(dtype), C.c_size_t(a.size), _p(out))
     return out
+
+
+def block_sdpa(q_bits, k_bits, v_bits, dtype, num_tokens, block_size, num_q_heads, num_kv_heads, head_dim, scale):
+    """Dense bidirectional block attention partials: (output f32 [T][Hq][D], max [T][Hq], exp-sum [T][Hq])."""
+    q = np.ascontiguousarray(q_bits, dtype=np_dtype(dtype))
+    k = np.ascontiguousarray(k_bits, dtype=np_dtype(dtype))
+    v = np.ascontiguousarray(v_bits, dtype=np_dtype(dtype))
+    out = np.zeros((num_tokens, num_q_heads, head_dim), dtype=np.float32)
+    pm = np.zeros((num_tokens, num_q_heads), dtype=np.float32)
+    ps = np.zeros((num_tokens, num_q_heads), dtype=np.float32)
+    lib().psi_oracle_block_sdpa(_p(q), _p(k), _p(v), C.c_int(dtype), C.c_uint32(num_tokens), C.c_uint32(block_size),
+                                C.c_uint32(num_q_heads), C.c_uint32(num_kv_heads), C.c_uint32(head_dim),
+                                C.c_float(scale), _p(out), _p(pm), _p(ps))
+    return out, pm, ps

@@ -574,6 +574,12 @@ class GQA:
         _check(library().psi_gqa_attend_partial(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(q), _ptr(o),
                                                 _ptr(m), _ptr(l)), self.ctx._h)
 
+    def block_partial(self, q, local_k, local_v, num_tokens: int, block_size: int, o, m, l, slot_indices=None):
+        """Dense bidirectional block attention partials (``GQABlockSDPAKernel``) in the ``attend_partial`` ABI."""
+        _check(library().psi_gqa_block_partial(self._h, _ptr(q), _ptr(local_k), _ptr(local_v), C.c_uint32(num_tokens),
+                                               C.c_uint32(block_size), _ptr(slot_indices), _ptr(o), _ptr(m), _ptr(l)),
+               self.ctx._h)
+
     def combine(self, o_list, m_list, l_list, num_tokens, out):
         n = len(o_list)
         po = (C.c_void_p * n)(*[_ptr(x).value for x in o_list])

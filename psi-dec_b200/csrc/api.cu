@@ -1544,6 +1544,36 @@ static int32_t combine_impl(psi_gqa* g, const float* const* o, const float* cons
     });
 }
 
+int32_t psi_gqa_block_partial(psi_gqa* g, const void* q, const void* local_k, const void* local_v, uint32_t num_tokens,
+                              uint32_t block_size, const uint32_t* slot_indices, float* o, float* m, float* l) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(q != nullptr && local_k != nullptr && local_v != nullptr, "q, local_k and local_v must not be null");
+        require(o != nullptr && m != nullptr && l != nullptr, "partial outputs must not be null");
+        require(block_size > 0 && block_size <= 256, "GQA block SDPA block size must be in 1..=256");
+        require(num_tokens > 0, "GQA block SDPA requires tokens");
+        require(num_tokens % block_size == 0, "GQA block SDPA tokens must contain complete request blocks");
+        g->ctx->bind();
+        BlockPartialParams p{};
+        p.q = q;
+        p.local_k = local_k;
+        p.local_v = local_v;
+        p.slot_indices = slot_indices;
+        p.o = o;
+        p.m = m;
+        p.l = l;
+        p.num_tokens = num_tokens;
+        p.block_size = block_size;
+        p.num_q_heads = g->cfg.num_q_heads;
+        p.num_kv_heads = g->cfg.num_kv_heads;
+        p.head_dim = g->cfg.head_dim;
+        p.dtype = g->cfg.dtype;
+        p.scale = g->cfg.scale;
+        g->ctx->launches += 1;
+        cuda_check(launch_block_partial(p, g->ctx->stream), "block partial launch");
+    });
+}
+
 int32_t psi_gqa_combine(psi_gqa* g, const float* const* o, const float* const* m, const float* const* l, uint32_t n,
                         uint32_t num_tokens, void* out) {
     return combine_impl(g, o, m, l, n, num_tokens, out, nullptr, 0, 0);

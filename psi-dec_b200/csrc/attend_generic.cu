@@ -157,6 +157,59 @@ __global__ void __launch_bounds__(kReduceThreads) attend_reduce_kernel(AttendPar
     }
 }
 
+// Dense bidirectional attention of every query token against the tokens of its own block (local, unpaged K/V), written
+// as a partial in the reduce's ABI so that it can be merged with the paged history of the same tokens
+// (crates/inference-backend-metal/src/components/metal/gqa_block_sdpa.metal:5-77).  One warp per (token, q head): lanes
+// split head_dim for the dot products and for the output columns; the block's weights sit in shared memory.
+constexpr uint32_t kBlockPartialWarps = 4;
+constexpr uint32_t kBlockPartialMaxBlock = 256;
+
+__global__ void __launch_bounds__(kBlockPartialWarps * 32) block_partial_kernel(BlockPartialParams p) {
+    __shared__ float weights_s[kBlockPartialWarps][kBlockPartialMaxBlock];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint64_t pair = static_cast<uint64_t>(blockIdx.x) * kBlockPartialWarps + warp;
+    if (pair >= static_cast<uint64_t>(p.num_tokens) * p.num_q_heads) return;
+    const uint32_t token = static_cast<uint32_t>(pair / p.num_q_heads), head = static_cast<uint32_t>(pair % p.num_q_heads);
+    const uint32_t kv_head = head / (p.num_q_heads / p.num_kv_heads);
+    const uint32_t begin = token / p.block_size * p.block_size;
+    const uint64_t q_row = (static_cast<uint64_t>(token) * p.num_q_heads + head) * p.head_dim;
+    float* weights = weights_s[warp];
+
+    float block_max = -INFINITY;
+    for (uint32_t j = 0; j < p.block_size; ++j) {
+        const uint64_t k_row = (static_cast<uint64_t>(begin + j) * p.num_kv_heads + kv_head) * p.head_dim;
+        float score = 0.0f;
+        for (uint32_t d = lane; d < p.head_dim; d += 32)
+            score += load_as_float(p.q, q_row + d, p.dtype) * load_as_float(p.local_k, k_row + d, p.dtype);
+        score = warp_sum(score) * p.scale;
+        if (lane == 0) weights[j] = score;
+        block_max = fmaxf(block_max, score);
+    }
+    __syncwarp();
+    float exp_sum = 0.0f;
+    for (uint32_t j = 0; j < p.block_size; ++j) {
+        const float w = expf(weights[j] - block_max);
+        exp_sum += w;
+        __syncwarp();
+        if (lane == 0) weights[j] = w;
+    }
+    __syncwarp();
+    const uint64_t slot = p.slot_indices != nullptr ? p.slot_indices[token] : token;
+    const uint64_t out_row = slot * p.num_q_heads + head;
+    if (lane == 0) {
+        p.m[out_row] = block_max;
+        p.l[out_row] = exp_sum;
+    }
+    for (uint32_t d = lane; d < p.head_dim; d += 32) {
+        float acc = 0.0f;
+        for (uint32_t j = 0; j < p.block_size; ++j) {
+            const uint64_t v_row = (static_cast<uint64_t>(begin + j) * p.num_kv_heads + kv_head) * p.head_dim;
+            acc += weights[j] * load_as_float(p.local_v, v_row + d, p.dtype);
+        }
+        p.o[out_row * p.head_dim + d] = exp_sum > 0.0f ? acc / exp_sum : 0.0f;
+    }
+}
+
 // Cross-device merge of per-device partials in the natural-log domain (same algebra as above).
 __global__ void __launch_bounds__(kReduceThreads) combine_kernel(CombineParams p) {
     if (p.flags != nullptr) {
@@ -233,6 +286,15 @@ cudaError_t launch_attend_generic(const AttendParams& p, uint32_t num_ctas, cuda
 cudaError_t launch_attend_reduce(const AttendParams& p, uint32_t num_reduces, cudaStream_t stream) {
     if (num_reduces == 0) return cudaSuccess;
     attend_reduce_kernel<<<num_reduces, kReduceThreads, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_block_partial(const BlockPartialParams& p, cudaStream_t stream) {
+    const uint64_t pairs = static_cast<uint64_t>(p.num_tokens) * p.num_q_heads;
+    if (pairs == 0) return cudaSuccess;
+    if (p.block_size == 0 || p.block_size > kBlockPartialMaxBlock) return cudaErrorInvalidValue;
+    const uint64_t blocks = (pairs + kBlockPartialWarps - 1) / kBlockPartialWarps;
+    block_partial_kernel<<<static_cast<uint32_t>(blocks), kBlockPartialWarps * 32, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -112,6 +112,25 @@ struct CombineParams {
     void* out;
 };
 
+// Dense bidirectional block attention partials (one warp per (token, q head)).
+struct BlockPartialParams {
+    const void* q;                 // [T][Hq][D]
+    const void* local_k;           // [T][Hkv][D]
+    const void* local_v;           // [T][Hkv][D]
+    const uint32_t* slot_indices;  // nullptr (slot = token) or [T]: partial slot of each token
+    float* o;                      // [slots][Hq][D] normalised
+    float* m;                      // [slots][Hq] natural-log max
+    float* l;                      // [slots][Hq] exp-sum
+    uint32_t num_tokens;
+    uint32_t block_size;
+    uint32_t num_q_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;
+    uint32_t dtype;
+    float scale;
+};
+cudaError_t launch_block_partial(const BlockPartialParams& p, cudaStream_t stream);
+
 cudaError_t launch_kv_append(const AppendParams& p, cudaStream_t stream);
 cudaError_t launch_page_gather(const GatherParams& p, cudaStream_t stream);
 // One launch that copies three host-mapped (pinned) buffers into device memory; sizes are multiples of 16 bytes.

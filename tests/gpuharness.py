@@ -24,6 +24,15 @@ def to_device(values_f32, dtype, device="cuda:0"):
     return torch.from_numpy(bits.view(np.int16).copy()).to(device).view(torch_dtype(dtype))
 
 
+def bits_to_device(bits, dtype, device="cuda:0"):
+    """Storage bits (oracle encoding) -> device tensor of the storage dtype."""
+    import torch
+    bits = np.ascontiguousarray(bits)
+    if dtype == pkg.F32:
+        return torch.from_numpy(bits.view(np.float32).copy()).to(device)
+    return torch.from_numpy(bits.view(np.int16).copy()).to(device).view(torch_dtype(dtype))
+
+
 def bits_of(tensor):
     import torch
     t = tensor.detach().contiguous()

@@ -122,3 +122,89 @@ def test_gate_fused_into_the_attention_epilogue(index, scale_down, kernel_mode):
     exact = attn.astype(np.float64) / (1.0 + np.exp(-g64))
     assert np.abs(got[rows] - exact).max() <= 2e-2
     s.close()
+
+
+@pytest.mark.parametrize("dtype,tol", [(pkg.F32, 1e-5), (pkg.BF16, 1e-2)])
+def test_block_partial_matches_the_reference_vectors(dtype, tol):
+    # GQABlockSDPAKernel (crates/inference-backend-metal/src/components/gqa_block_attention_test.rs:23-139): block 3,
+    # 5 q heads over one KV head, head_dim 32, 6 tokens of ramp inputs; tolerances are the reference's
+    import torch
+    block, hq, hkv, d, t = 3, 5, 1, 32, 6
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(32.0)))
+    q = O.encode(np.arange(t * hq * d, dtype=np.float32) * np.float32(0.03125) - np.float32(0.4), dtype)
+    k = O.encode(np.arange(t * hkv * d, dtype=np.float32) * np.float32(-0.025) + np.float32(0.3), dtype)
+    v = O.encode(np.arange(t * hkv * d, dtype=np.float32) * np.float32(0.05) - np.float32(0.2), dtype)
+    want_o, want_m, want_l = O.block_sdpa(q, k, v, dtype, t, block, hq, hkv, d, scale)
+    rig = G.Rig(dtype, hq, hkv, d, 16, scale, (1, 1, 1, 1), 8, num_pages=1)
+    dq, dk, dv = (G.bits_to_device(x, dtype) for x in (q, k, v))
+    slots = torch.tensor([5, 4, 3, 2, 1, 0], dtype=torch.int32, device="cuda")   # partial slots in reverse order
+    o = torch.full((8, hq, d), 7.0, dtype=torch.float32, device="cuda")
+    m = torch.full((8, hq), 7.0, dtype=torch.float32, device="cuda")
+    l = torch.full((8, hq), 7.0, dtype=torch.float32, device="cuda")
+    rig.gqa.block_partial(dq, dk, dv, t, block, o, m, l, slot_indices=slots)
+    rig.ctx.sync()
+    got_o, got_m, got_l = (x.cpu().numpy() for x in (o, m, l))
+    for token in range(t):
+        assert np.abs(got_o[5 - token] - want_o[token]).max() < tol
+        assert np.abs(got_m[5 - token] - want_m[token]).max() < 1e-4
+        assert np.abs(got_l[5 - token] - want_l[token]).max() < 1e-4
+    assert np.all(got_o[6:] == 7.0) and np.all(got_m[6:] == 7.0)  # slots nobody was given stay untouched
+    with pytest.raises(pkg.PsiError, match="complete request blocks"):
+        rig.gqa.block_partial(dq, dk, dv, 5, block, o, m, l)
+    rig.close()
+
+
+def test_history_plus_block_composite():
+    # The DSpark composite: every draft token attends to the request's whole paged history (no causal cut inside the
+    # block) and, bidirectionally, to the tokens of its own draft block; history partial + block partial -> combine.
+    import torch
+    hq, hkv, d, p, block = 16, 2, 128, 16, 4
+    ctx = [300, 77]                                  # history tokens of two requests, one draft block each
+    scale = 1.0 / np.sqrt(d)
+    rig = G.Rig(pkg.BF16, hq, hkv, d, p, float(scale), (2, 1, 32, 1), 16, num_pages=64)
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    rig.arena.copy_((torch.randn(rig.arena.shape, device="cuda", generator=gen) * 0.5).to(torch.bfloat16))
+    rng = np.random.default_rng(3)
+    ids = rng.permutation(64).astype(np.uint32)
+    rig.set_pages(0, 0, ids[:32])
+    rig.set_pages(1, 0, ids[32:])
+    t = 2 * block
+    q = (torch.randn((t, hq, d), device="cuda", generator=gen)).to(torch.bfloat16)
+    lk = (torch.randn((t, hkv, d), device="cuda", generator=gen) * 0.5).to(torch.bfloat16)
+    lv = (torch.randn((t, hkv, d), device="cuda", generator=gen) * 0.5).to(torch.bfloat16)
+    # history partial: each draft token is a one-token "request" at the last history position, so it sees [0, ctx)
+    req_slots = [0] * block + [1] * block
+    positions = [ctx[0] - 1] * block + [ctx[1] - 1] * block
+    rig.gqa.prepare(req_slots, positions, list(range(t + 1)))
+    parts = []
+    for _ in range(2):
+        parts.append((torch.zeros((t, hq, d), dtype=torch.float32, device="cuda"),
+                      torch.zeros((t, hq), dtype=torch.float32, device="cuda"),
+                      torch.zeros((t, hq), dtype=torch.float32, device="cuda")))
+    rig.gqa.attend_partial(rig.pages, rig.table, 0, q, *parts[0])
+    rig.gqa.block_partial(q, lk, lv, t, block, *parts[1])
+    out = torch.zeros_like(q)
+    rig.gqa.combine([x[0] for x in parts], [x[1] for x in parts], [x[2] for x in parts], t, out)
+    rig.ctx.sync()
+    # expectation: one exact softmax over history keys followed by the block's keys, in float64
+    arena = O.decode(checks.to_numpy_bits(rig.arena), O.BF16).astype(np.float64).reshape(64, 2, hkv, p, d)
+    qf = O.decode(checks.to_numpy_bits(q), O.BF16).astype(np.float64)
+    kf = O.decode(checks.to_numpy_bits(lk), O.BF16).astype(np.float64)
+    vf = O.decode(checks.to_numpy_bits(lv), O.BF16).astype(np.float64)
+    got = O.decode(checks.to_numpy_bits(out), O.BF16)
+    worst = 0.0
+    for token in range(t):
+        r = token // block
+        pages = rig.table_host[r, 0].reshape(-1)
+        for head in range(hq):
+            kvh = head // (hq // hkv)
+            hist_k = np.concatenate([arena[pages[i], 0, kvh] for i in range(-(-ctx[r] // p))])[:ctx[r]]
+            hist_v = np.concatenate([arena[pages[i], 1, kvh] for i in range(-(-ctx[r] // p))])[:ctx[r]]
+            keys = np.concatenate([hist_k, kf[r * block:(r + 1) * block, kvh]])
+            values = np.concatenate([hist_v, vf[r * block:(r + 1) * block, kvh]])
+            scores = keys @ qf[token, head] * scale
+            w = np.exp(scores - scores.max())
+            want = w @ values / w.sum()
+            worst = max(worst, np.abs(got[token, head] - want).max())
+    assert worst <= 2e-2, worst
+    rig.close()

@@ -272,3 +272,25 @@ def test_activation_gate_sigmoid():
     assert np.max(np.abs(out - expected)) < 1e-6
     out16 = O.decode(O.activation_gate(O.encode(a, O.BF16), O.encode(g, O.BF16), O.BF16), O.BF16)
     assert np.max(np.abs(out16 - expected)) < 2e-2
+
+
+def test_block_sdpa_closed_form_vectors():
+    # crates/inference-backend-metal/src/components/gqa_block_attention_test.rs:33-139: block 3, 5 q heads over one
+    # KV head, head_dim 32, 6 tokens, ramp inputs; expectations recomputed in float64 from the same formulas
+    block, hq, hkv, d, t = 3, 5, 1, 32, 6
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(32.0)))
+    for dtype, tol in ((O.F32, 1e-5), (O.BF16, 1e-2)):
+        q = O.decode(O.encode(np.arange(t * hq * d, dtype=np.float32) * np.float32(0.03125) - np.float32(0.4), dtype), dtype)
+        k = O.decode(O.encode(np.arange(t * hkv * d, dtype=np.float32) * np.float32(-0.025) + np.float32(0.3), dtype), dtype)
+        v = O.decode(O.encode(np.arange(t * hkv * d, dtype=np.float32) * np.float32(0.05) - np.float32(0.2), dtype), dtype)
+        out, pm, ps = O.block_sdpa(O.encode(q, dtype), O.encode(k, dtype), O.encode(v, dtype), dtype, t, block, hq, hkv, d, scale)
+        q64, k64, v64 = q.astype(np.float64).reshape(t, hq, d), k.astype(np.float64).reshape(t, d), v.astype(np.float64).reshape(t, d)
+        for token in range(t):
+            begin = token // block * block
+            for head in range(hq):
+                scores = (k64[begin:begin + block] @ q64[token, head]) * scale
+                weights = np.exp(scores - scores.max())
+                assert abs(pm[token, head] - scores.max()) < 1e-4
+                assert abs(ps[token, head] - weights.sum()) < 1e-4
+                want = weights @ v64[begin:begin + block] / weights.sum()
+                assert np.abs(out[token, head] - want).max() < tol
