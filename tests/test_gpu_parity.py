@@ -497,6 +497,38 @@ def test_config3_full_size_sampled_parity_and_gather_round_trip():
     s.close()
 
 
+def test_config5_full_size_chunk_engines_agree_and_sample_matches_oracle():
+    # Configuration 5 at full size (256 sequences, 30 % with a 512-token query run, contexts up to 131,072): the
+    # tcgen05 chunk kernel against the CPU oracle on a sample of long-run sequences, and against the independent
+    # mma.sync chunk kernel on every output row (two engines, one plan, same pages after the step).
+    import torch
+    spec = W.config(5)
+    a = W.Session(spec)
+    stats = a.gqa.plan_stats()
+    assert stats["chunk_ctas"] >= 1
+    a.step()
+    a.ctx.sync()
+    assert a.gqa.device_status() == 0
+    assert a.gqa.plan_stats()["chunk_tcgen05_launches"] == 1
+    long_runs = np.flatnonzero(spec.q_len > 1)
+    by_cost = long_runs[np.argsort(spec.visible[long_runs])]
+    decode = np.flatnonzero(spec.q_len == 1)
+    sample = [int(by_cost[0]), int(by_cost[1]), int(by_cost[len(by_cost) // 3]), int(decode[0]), int(decode[-1])]
+    checks.assert_attention_close(a, sample)
+    out_tcgen05 = a.out.clone()
+    arena_after = a.arena.clone() if a.arena.numel() * 2 <= (8 << 30) else None
+    a.close()
+    b = W.Session(spec, kernel_mode=pkg.KERNEL_MMA_SYNC)
+    b.step()
+    b.ctx.sync()
+    assert b.gqa.plan_stats()["chunk_mma_sync_launches"] == 1
+    diff = (b.out.float() - out_tcgen05.float()).abs()
+    assert float(diff.max()) <= 2e-2 and float(diff.mean()) <= 2e-3, (float(diff.max()), float(diff.mean()))
+    if arena_after is not None:  # both steps appended the same rows to the same slots
+        assert torch.equal(arena_after.view(torch.int16), b.arena.view(torch.int16))
+    b.close()
+
+
 def test_partials_and_combine_match_full_attention():
     # KV-range split of configuration 4 (scaled): two local shards produce (o, m, l); combine equals the unsplit run.
     import torch
