@@ -458,6 +458,23 @@ def test_long_query_runs_through_the_chunk_kernel(heads, head_dim, page, max_cta
     s.close()
 
 
+@pytest.mark.parametrize("engine", ["tcgen05", "mma_sync"])
+def test_long_query_runs_in_f16(engine):
+    # the f16 instantiation of both chunk engines (the MMA instruction descriptor carries the element format)
+    spec = W.Spec("chunks-f16", pkg.F16, 16, 2, 128, 16, [900, 64, 2000], [128, 1, 70], seed=13)
+    s = W.Session(spec, kernel_mode=pkg.KERNEL_MMA if engine == "tcgen05" else pkg.KERNEL_MMA_SYNC)
+    assert s.gqa.plan_stats()["chunk_ctas"] >= 1
+    before = checks.to_numpy_bits(s.arena)
+    s.step()
+    s.ctx.sync()
+    assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), checks.expected_arena_after_append(s, before))
+    checks.assert_attention_close(s)
+    assert s.gqa.device_status() == 0
+    key = "chunk_tcgen05_launches" if engine == "tcgen05" else "chunk_mma_sync_launches"
+    assert s.gqa.plan_stats()[key] == 1
+    s.close()
+
+
 def test_config2_full_size_parity_and_idempotence():
     import torch
     s = W.Session(W.config(2))
