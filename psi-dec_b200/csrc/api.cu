@@ -1210,8 +1210,14 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
             const uint32_t min_tiles = g->kernel == PSI_KERNEL_MMA ? 16u : 4u;
             g->plan = build_balanced_plan(g->geo, req_slots, token_indices, cu_tokens, decode_reqs, g->grid_cap,
                                           min_tiles, g->item_start_cost);
+            // K/V the long runs touch: below a third of the L2 the order of the work cannot cost HBM traffic, and exactly
+            // equal shares beat stream order
+            uint64_t chunk_kv_bytes = 0;
+            for (uint32_t r : chunk_reqs)
+                chunk_kv_bytes += uint64_t(token_indices[r] + (cu_tokens[r + 1] - cu_tokens[r])) * (uint64_t(g->cfg.page_bytes) / g->tokens_per_page);
             g->chunk = build_chunk_plan(g->geo, req_slots, token_indices, cu_tokens, chunk_reqs, g->grid_cap,
-                                        g->plan.num_partial_slots, static_cast<uint32_t>(g->plan.reduces.size()));
+                                        g->plan.num_partial_slots, static_cast<uint32_t>(g->plan.reduces.size()),
+                                        chunk_kv_bytes <= (40ull << 20));
         }
         const WorkPlan& plan = g->plan;
         const ChunkPlan& chunk = g->chunk;

@@ -592,6 +592,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 if (tid < 8) {
                     const bool has_rows = tid * p.tokens_per_tile < v.num_tokens;
                     last_s[tid] = has_rows && atomicAdd(p.unit_counters + v.reduce_unit + tid, 1u) == v.unit_num_items - 1;
+                    __threadfence();  // the other pieces' partials are read (from L2) only after their arrivals were seen
                 }
                 row_threads_sync();
 #ifdef PSI_UMMA_TRACE
@@ -604,10 +605,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     trace_merges += 1;
                     trace_pieces += v.unit_num_items;
 #endif
-                    __threadfence();
-                    // 16 rows x D / 4 float4 outputs per tile, 8 per thread (row 2 j + tid / (D / 4) ... for D = 256);
-                    // the loads of one pass are independent of one another, so each pass costs one round trip per two
-                    // pieces rather than one per output
+                    // 16 rows x D / 4 float4 outputs per tile, 8 per thread (row 2 j + tid / (D / 4) ... for D = 256)
                     const uint32_t tile_tokens = min(p.tokens_per_tile, v.num_tokens - tile * p.tokens_per_tile);
                     const uint32_t tile_rows = tile_tokens * v.num_heads;
                     constexpr uint32_t kPerThread = kMaxRows * (D / 4) / kRowThreads;
@@ -619,44 +617,52 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     uint64_t row_off[kPerThread];
 #pragma unroll
                     for (uint32_t j = 0; j < kPerThread; ++j) row_off[j] = slot_rows + min(r0 + j * kRowStep, tile_rows - 1);
-                    float row_top[kPerThread];
-#pragma unroll
-                    for (uint32_t j = 0; j < kPerThread; ++j) row_top[j] = -INFINITY;
-#pragma unroll 4
-                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
-                        float pm[kPerThread];
-#pragma unroll
-                        for (uint32_t j = 0; j < kPerThread; ++j)
-                            pm[j] = __ldcg(p.partial_m + row_off[j] + static_cast<uint64_t>(s_i) * 8 * kMaxRows);
-#pragma unroll
-                        for (uint32_t j = 0; j < kPerThread; ++j) row_top[j] = fmaxf(row_top[j], pm[j]);
-                    }
-                    float sum[kPerThread];
+                    // one pass over the pieces with the running max of a row carried along (sums are rescaled when
+                    // a later piece raises it); the loads of piece s + 1 are in flight while piece s is folded in
+                    float row_top[kPerThread], sum[kPerThread];
                     float4 acc[kPerThread];
 #pragma unroll
                     for (uint32_t j = 0; j < kPerThread; ++j) {
+                        row_top[j] = -INFINITY;
                         sum[j] = 0.0f;
                         acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                     }
-#pragma unroll 2
-                    for (uint32_t s_i = 0; s_i < v.unit_num_items; ++s_i) {
-                        float pm[kPerThread], pl[kPerThread];
-                        float4 part[kPerThread];
+                    const float* stat_m = p.partial_m;
+                    const float* stat_l = p.partial_l;
+                    const float4* part_o = reinterpret_cast<const float4*>(p.partial_o) + c4;
+                    constexpr uint64_t kPieceRows = 8 * kMaxRows;  // rows between the same tile of consecutive pieces
+                    float pm[2][kPerThread], pl[2][kPerThread];
+                    float4 part[2][kPerThread];
+                    auto fetch = [&](uint32_t piece, float (&m_out)[kPerThread], float (&l_out)[kPerThread], float4 (&o_out)[kPerThread]) {
 #pragma unroll
                         for (uint32_t j = 0; j < kPerThread; ++j) {
-                            const uint64_t row = row_off[j] + static_cast<uint64_t>(s_i) * 8 * kMaxRows;
-                            pm[j] = __ldcg(p.partial_m + row);
-                            pl[j] = __ldcg(p.partial_l + row);
-                            part[j] = __ldcg(reinterpret_cast<const float4*>(p.partial_o + row * D + 4 * c4));
+                            const uint64_t row = row_off[j] + piece * kPieceRows;
+                            m_out[j] = __ldcg(stat_m + row);
+                            l_out[j] = __ldcg(stat_l + row);
+                            o_out[j] = __ldcg(part_o + row * (D / 4));
                         }
+                    };
+                    auto fold = [&](const float (&m_in)[kPerThread], const float (&l_in)[kPerThread], const float4 (&o_in)[kPerThread]) {
 #pragma unroll
                         for (uint32_t j = 0; j < kPerThread; ++j) {
-                            const float weight = pm[j] == -INFINITY ? 0.0f : exp2f(pm[j] - row_top[j]) * pl[j];
-                            sum[j] += weight;
-                            acc[j].x += weight * part[j].x;
-                            acc[j].y += weight * part[j].y;
-                            acc[j].z += weight * part[j].z;
-                            acc[j].w += weight * part[j].w;
+                            const float top = fmaxf(row_top[j], m_in[j]);
+                            const float carry = row_top[j] == -INFINITY ? 0.0f : fast_exp2(row_top[j] - top);
+                            const float w = m_in[j] == -INFINITY ? 0.0f : fast_exp2(m_in[j] - top) * l_in[j];
+                            sum[j] = sum[j] * carry + w;
+                            acc[j].x = acc[j].x * carry + w * o_in[j].x;
+                            acc[j].y = acc[j].y * carry + w * o_in[j].y;
+                            acc[j].z = acc[j].z * carry + w * o_in[j].z;
+                            acc[j].w = acc[j].w * carry + w * o_in[j].w;
+                            row_top[j] = top;
+                        }
+                    };
+                    fetch(0, pm[0], pl[0], part[0]);
+                    for (uint32_t s0 = 0; s0 < v.unit_num_items; s0 += 2) {
+                        if (s0 + 1 < v.unit_num_items) fetch(s0 + 1, pm[1], pl[1], part[1]);
+                        fold(pm[0], pl[0], part[0]);
+                        if (s0 + 1 < v.unit_num_items) {
+                            if (s0 + 2 < v.unit_num_items) fetch(s0 + 2, pm[0], pl[0], part[0]);
+                            fold(pm[1], pl[1], part[1]);
                         }
                     }
 #pragma unroll

@@ -393,7 +393,7 @@ WorkPlan build_reference_plan(const PlanGeometry& geo, const ReferenceMetadata& 
 
 ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
                            const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,
-                           uint32_t slot_base, uint32_t counter_base) {
+                           uint32_t slot_base, uint32_t counter_base, bool equal_shares) {
     ChunkPlan plan;
     // Units in stream order: all super-tiles of one (request, KV head) follow one another, so that CTAs working on
     // neighbouring units at the same time read the same K/V pages (once from HBM, then from L2).
@@ -422,6 +422,77 @@ ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, c
     plan.total_kv_tiles = total;
     if (total == 0) return plan;
     const uint64_t num_ctas = std::min<uint64_t>(std::max(1u, max_ctas), std::max<uint64_t>(1, total / 4));
+    auto make_item = [&](const Unit& u, uint64_t tile_begin, uint64_t tile_end) {
+        const uint32_t head_tile = u.head % geo.head_tiles;
+        DeviceItem d{};
+        d.kv_begin = static_cast<uint32_t>(tile_begin * kKvTile);
+        d.kv_end = static_cast<uint32_t>(std::min<uint64_t>(tile_end * kKvTile, u.ctx_end));
+        d.partial_slot = kU32Max;
+        d.flat_begin = u.flat_begin;
+        d.num_tokens = u.flat_end - u.flat_begin;
+        d.req_slot = req_slots[u.req];
+        d.kv_head = u.head / geo.head_tiles;
+        d.head0 = d.kv_head * geo.group + head_tile * geo.heads_per_tile;
+        d.num_heads = std::min(geo.heads_per_tile, geo.group - head_tile * geo.heads_per_tile);
+        d.first_pos = token_indices[u.req] + (u.flat_begin - cu_tokens[u.req]);
+        d.new_begin = token_indices[u.req];
+        d.flat_req_begin = cu_tokens[u.req];
+        d.writes_kv = head_tile == 0 ? 1u : 0u;
+        return d;
+    };
+    // `n` consecutive items starting at `first` are the pieces of one unit cut across CTAs: partial slots 8 apart,
+    // eight arrival counters
+    auto share_unit = [&](std::vector<DeviceItem*>& pieces) {
+        const uint32_t n = static_cast<uint32_t>(pieces.size());
+        if (n <= 1) return;
+        const uint32_t first_slot = slot_base + plan.num_partial_slots;
+        for (uint32_t k = 0; k < n; ++k) {
+            pieces[k]->partial_slot = first_slot + k * kChunkTilesPerItem;
+            pieces[k]->reduce_unit = counter_base + plan.num_counters;
+            pieces[k]->unit_first_slot = first_slot;
+            pieces[k]->unit_num_items = n;
+        }
+        plan.num_partial_slots += n * kChunkTilesPerItem;
+        plan.num_counters += kChunkTilesPerItem;
+    };
+    if (equal_shares) {
+        // A working set that stays in L2 whatever the order: contiguous shares of exactly equal size, units cut where a
+        // share ends (two or three pieces per cut unit instead of many), slivers below a quarter of the minimum piece
+        // folded into their neighbour.
+        const uint64_t sliver = kChunkMinPieceTiles / 4;
+        plan.items.reserve(units.size() + num_ctas);
+        std::vector<uint32_t> owner;  // CTA of every item, in item order
+        uint64_t cursor = 0;
+        uint32_t cta = 0;
+        auto share_end = [&](uint64_t c) { return total * (c + 1) / num_ctas; };
+        std::vector<std::pair<size_t, size_t>> unit_items;  // [first, last) item of every unit
+        for (const Unit& u : units) {
+            const uint64_t unit_tiles = div_ceil(u.ctx_end, kKvTile);
+            const size_t first = plan.items.size();
+            uint64_t done = 0;
+            while (done < unit_tiles) {
+                while (cta + 1 < num_ctas && cursor + done + (done == 0 ? sliver : 0) >= share_end(cta)) ++cta;
+                uint64_t take = std::min(unit_tiles - done, std::max<uint64_t>(share_end(cta) - (cursor + done), 1));
+                if (cta + 1 >= num_ctas || unit_tiles - done - take < sliver) take = unit_tiles - done;
+                plan.items.push_back(make_item(u, done, done + take));
+                owner.push_back(cta);
+                done += take;
+            }
+            cursor += unit_tiles;
+            unit_items.emplace_back(first, plan.items.size());
+        }
+        for (const auto& range : unit_items) {
+            std::vector<DeviceItem*> pieces;
+            for (size_t i = range.first; i < range.second; ++i) pieces.push_back(&plan.items[i]);
+            share_unit(pieces);
+        }
+        plan.cta_item_begin.assign(num_ctas + 1, static_cast<uint32_t>(plan.items.size()));
+        plan.cta_item_begin[0] = 0;
+        for (size_t i = plan.items.size(); i-- > 0;) plan.cta_item_begin[owner[i]] = static_cast<uint32_t>(i);
+        for (uint64_t c = num_ctas; c-- > 1;)  // CTAs without items start where the next one does
+            plan.cta_item_begin[c] = std::min(plan.cta_item_begin[c], plan.cta_item_begin[c + 1]);
+        return plan;
+    }
     // A unit longer than half a CTA's fair share is cut along its KV range into equal pieces (partial slots, merged
     // by the last arriver), which bounds how far the last CTA can trail the others; shorter units stay whole, since
     // every piece costs a partial write and a fence, and the merge reads all of them.

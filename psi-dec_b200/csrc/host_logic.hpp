@@ -174,9 +174,11 @@ constexpr uint32_t kChunkTilesPerItem = 8;  // one query tile per warp
 constexpr uint32_t kChunkMinPieceTiles = 64;   // a KV piece of a cut unit is at least this many 16-token tiles
 constexpr uint32_t kChunkStartCostTiles = 8;   // fixed cost of a work item (query load, epilogue) in KV tiles
 
+// `equal_shares`: contiguous shares of exactly equal size (for working sets that stay in L2 in any order); otherwise
+// units are dealt whole, in stream order, to the CTA that is free first, and only long units are cut.
 ChunkPlan build_chunk_plan(const PlanGeometry& geo, const uint32_t* req_slots, const uint32_t* token_indices,
                            const uint32_t* cu_tokens, const std::vector<uint32_t>& requests, uint32_t max_ctas,
-                           uint32_t slot_base, uint32_t counter_base);
+                           uint32_t slot_base, uint32_t counter_base, bool equal_shares = false);
 
 // Device form of a finished plan.
 std::vector<DeviceItem> flatten_plan(const WorkPlan& plan, const PlanGeometry& geo);
