@@ -483,6 +483,25 @@ typedef enum psi_kernel_class {
 PSI_API int32_t psi_ctx_enable_kernel_timing(psi_ctx* ctx, int32_t enable);
 PSI_API int32_t psi_ctx_kernel_timing(psi_ctx* ctx, uint32_t kernel_class, float* out_total_ms, uint64_t* out_launches);
 
+/* ---- replayed launch sequences (Stream::create_replay_program / submit_replay_with_arguments,
+ * crates/inference-backend-metal/src/metal/stream; ReplayU32::Parameter -> the device scalar block) ----------------
+ * The reference records a layer's kernels once per replay bucket into an indirect command buffer whose scalar
+ * arguments live in a parameter buffer rewritten per submission.  Here: psi_gqa_reserve_replay fixes, for the
+ * component's max_tokens, every array offset of the per-step device block, every scratch buffer and every launch
+ * grid (launches then always run append, map, chunk and reduce kernels at their capacity grids and take their active
+ * counts from the device block; a fused step becomes append + attend); psi_ctx_capture_begin / _end capture whatever the library launches
+ * on the context's stream in between (any number of layers; psi_gqa_prepare stays outside) into a CUDA graph;
+ * psi_graph_launch replays it after each step's psi_gqa_prepare.  One graph per (bucket capacity, buffer set), as
+ * the reference keeps one recorded program per bucket.  A step beyond the reserved capacity, or a buffer that would
+ * have to grow during capture, is refused with PSI_ERR_INVALID_ARGUMENT. */
+typedef struct psi_graph psi_graph;
+PSI_API int32_t psi_gqa_reserve_replay(psi_gqa* gqa);
+PSI_API int32_t psi_ctx_capture_begin(psi_ctx* ctx);
+PSI_API int32_t psi_ctx_capture_end(psi_ctx* ctx, psi_graph** out);
+PSI_API int32_t psi_graph_launch(psi_graph* graph);
+PSI_API int32_t psi_graph_kernel_count(psi_graph* graph, uint64_t* out);
+PSI_API int32_t psi_graph_destroy(psi_graph* graph);
+
 #ifdef __cplusplus
 }
 #endif

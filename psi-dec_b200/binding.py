@@ -116,6 +116,30 @@ def _check(status: int, ctx=None):
     raise PsiError(status, buf.value.decode("utf-8", "replace"))
 
 
+class Graph:
+    """A captured launch sequence (the reference's recorded replay program); ``launch`` replays it on the context's
+    stream after the step's ``GQA.prepare``."""
+
+    def __init__(self, ctx, handle):
+        self.ctx = ctx
+        self._h = handle
+
+    def launch(self):
+        _check(library().psi_graph_launch(self._h), self.ctx._h)
+
+    def kernel_count(self) -> int:
+        out = C.c_uint64()
+        _check(library().psi_graph_kernel_count(self._h, C.byref(out)), self.ctx._h)
+        return out.value
+
+    def close(self):
+        if getattr(self, "_h", None):
+            library().psi_graph_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+
 class Context:
     """One device + one stream (the reference's ``Device::system_default()`` + ``Stream``)."""
 
@@ -146,6 +170,15 @@ class Context:
         out = C.c_uint64()
         _check(library().psi_ctx_launch_count(self._h, C.byref(out)), self._h)
         return out.value
+
+    def capture_begin(self):
+        """Start capturing the library's launches on this context's stream (``Stream::create_replay_program``)."""
+        _check(library().psi_ctx_capture_begin(self._h), self._h)
+
+    def capture_end(self) -> "Graph":
+        handle = C.c_void_p()
+        _check(library().psi_ctx_capture_end(self._h, C.byref(handle)), self._h)
+        return Graph(self, handle)
 
     def enable_kernel_timing(self, enable: bool = True):
         _check(library().psi_ctx_enable_kernel_timing(self._h, C.c_int32(1 if enable else 0)), self._h)
@@ -573,6 +606,10 @@ class GQA:
     def attend_partial(self, pages, table, layer, q, o, m, l):
         _check(library().psi_gqa_attend_partial(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(q), _ptr(o),
                                                 _ptr(m), _ptr(l)), self.ctx._h)
+
+    def reserve_replay(self):
+        """Fix every offset, scratch size and launch grid for ``max_tokens`` so that captured graphs stay valid."""
+        _check(library().psi_gqa_reserve_replay(self._h), self.ctx._h)
 
     def block_partial(self, q, local_k, local_v, num_tokens: int, block_size: int, o, m, l, slot_indices=None):
         """Dense bidirectional block attention partials (``GQABlockSDPAKernel``) in the ``attend_partial`` ABI."""

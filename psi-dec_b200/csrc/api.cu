@@ -46,6 +46,7 @@ struct psi_ctx {
     uint64_t launches = 0;
     std::string last_error;
     bool timing = false;
+    bool capturing = false;  // between psi_ctx_capture_begin and psi_ctx_capture_end
     // (begin, end) event pairs per kernel class, recorded while timing is on
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed[kKernelClasses];
     void bind() const { cuda_check(cudaSetDevice(device), "cudaSetDevice"); }
@@ -68,7 +69,7 @@ struct LaunchScope {
     cudaEvent_t end = nullptr;
     LaunchScope(psi_ctx* c, uint32_t kernel_class) : ctx(c) {
         ctx->launches += 1;
-        if (!ctx->timing) return;
+        if (!ctx->timing || ctx->capturing) return;
         cudaEvent_t begin = nullptr;
         cuda_check(cudaEventCreate(&begin), "cudaEventCreate");
         cuda_check(cudaEventCreate(&end), "cudaEventCreate");
@@ -90,6 +91,7 @@ struct DeviceBuffer {
     uint64_t bytes = 0;
     void ensure(psi_ctx* ctx, uint64_t wanted, bool zero) {
         if (wanted <= bytes) return;
+        require(!ctx->capturing, "a device buffer would have to grow during stream capture: reserve replay capacity first");
         if (ptr != nullptr) {
             cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
             cuda_check(cudaFree(ptr), "cudaFree");
@@ -134,6 +136,13 @@ struct psi_table {
     }
 };
 
+struct psi_graph {
+    psi_ctx* ctx = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernel_nodes = 0;
+};
+
 struct psi_snapshot_writer {
     SnapshotWriter impl;
     psi_snapshot_writer(const std::string& d, const std::vector<uint32_t>& f, const SnapshotPlan& p) : impl(d, f, p) {}
@@ -175,6 +184,10 @@ struct psi_gqa {
     uint64_t off_req_slots = 0, off_token_indices = 0, off_cta = 0, off_reduces = 0, off_items = 0;
     uint64_t off_chunk_cta = 0, off_chunk_items = 0;
     uint64_t off_first_items = 0;  // copies of every CTA's first item (mma kernel)
+    // Replay reservation: every array of the device block at a fixed offset sized for max_tokens, every scratch buffer
+    // at its largest, every launch at its capacity grid, so that a captured graph stays valid from step to step.
+    bool replay_reserved = false;
+    uint64_t cap_items = 0, cap_chunk_items = 0, cap_reduces = 0;
 
     DeviceBuffer partial_o, partial_ml;  // [slots][16][D] and [2][slots][16]
     DeviceBuffer unit_counters;          // [slots] u32, zero between launches
@@ -296,7 +309,11 @@ AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* 
 void run_attend(psi_gqa* g, const AttendParams& params) {
     psi_ctx* ctx = g->ctx;
     AttendParams p = params;
-    if (p.new_k != nullptr && g->chunk.num_ctas() > 0) {
+    // Under a replay reservation a captured launch sequence has to be right for every later plan: always the same
+    // launches (append, map, chunk, reduce where the kernel needs one), each at its capacity grid, each reading its
+    // active counts from the device block.
+    const bool fixed = g->replay_reserved;
+    if (p.new_k != nullptr && (fixed || g->chunk.num_ctas() > 0)) {
         // A fused step that carries long query runs: their K/V tiles are fetched page-wise by TMA, so the step's rows
         // go to their pages first (one more launch, against milliseconds of attention) and both kernels read pages only.
         AppendParams a{};
@@ -314,7 +331,7 @@ void run_attend(psi_gqa* g, const AttendParams& params) {
         p.new_k = nullptr;
         p.new_v = nullptr;
     }
-    const uint32_t num_ctas = g->plan.num_ctas();
+    const uint32_t num_ctas = fixed ? g->grid_cap : g->plan.num_ctas();
     if (num_ctas > 0) {
         LaunchScope scope(ctx, PSI_KERNEL_CLASS_ATTEND_MAP);
         if (g->kernel == PSI_KERNEL_MMA) {
@@ -323,7 +340,8 @@ void run_attend(psi_gqa* g, const AttendParams& params) {
             cuda_check(launch_attend_generic(p, num_ctas, ctx->stream), "attend (generic) launch");
         }
     }
-    if (g->chunk.num_ctas() > 0) {
+    const uint32_t chunk_ctas = fixed ? (g->chunk_supported ? g->grid_cap : 0u) : g->chunk.num_ctas();
+    if (chunk_ctas > 0) {
         AttendParams c = p;
         c.items = reinterpret_cast<const DeviceItem*>(block_words(g, g->off_chunk_items));
         c.cta_item_begin = block_words(g, g->off_chunk_cta);
@@ -331,11 +349,11 @@ void run_attend(psi_gqa* g, const AttendParams& params) {
         cudaError_t launched = cudaErrorNotSupported;
         if (g->chunk_umma) {
             c.status = static_cast<uint32_t*>(g->status_word.ptr);
-            launched = launch_attend_chunk_umma(c, g->chunk.num_ctas(), ctx->stream);
+            launched = launch_attend_chunk_umma(c, chunk_ctas, ctx->stream);
         }
         // an arena the TMA unit cannot address (alignment, size) keeps the mma.sync kernel
         if (launched == cudaErrorNotSupported) {
-            launched = launch_attend_chunk(c, g->chunk.num_ctas(), ctx->stream);
+            launched = launch_attend_chunk(c, chunk_ctas, ctx->stream);
             g->chunk_launches[1] += 1;
         } else {
             g->chunk_launches[0] += 1;
@@ -344,7 +362,9 @@ void run_attend(psi_gqa* g, const AttendParams& params) {
     }
     // The mma kernel merges a unit's partials in the CTA that delivers the last one; the generic kernel needs the
     // separate reduce pass.
-    const uint32_t num_reduces = g->kernel == PSI_KERNEL_MMA ? 0u : static_cast<uint32_t>(g->plan.reduces.size());
+    const uint32_t num_reduces = g->kernel == PSI_KERNEL_MMA
+                                     ? 0u
+                                     : static_cast<uint32_t>(fixed ? g->cap_reduces : g->plan.reduces.size());
     if (num_reduces > 0) {
         LaunchScope scope(ctx, PSI_KERNEL_CLASS_ATTEND_REDUCE);
         cuda_check(launch_attend_reduce(p, num_reduces, ctx->stream), "attend reduce launch");
@@ -469,6 +489,72 @@ int32_t psi_ctx_kernel_timing(psi_ctx* ctx, uint32_t kernel_class, float* out_to
         }
         *out_total_ms = total;
         *out_launches = ctx->timed[kernel_class].size();
+    });
+}
+
+int32_t psi_ctx_capture_begin(psi_ctx* ctx) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        require(!ctx->capturing, "a stream capture is already open on this context");
+        require(!ctx->timing, "switch kernel timing off before capturing");
+        ctx->bind();
+        cuda_check(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+        ctx->capturing = true;
+    });
+}
+
+int32_t psi_ctx_capture_end(psi_ctx* ctx, psi_graph** out) {
+    if (ctx == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        require(out != nullptr, "out must not be null");
+        *out = nullptr;
+        require(ctx->capturing, "no stream capture is open on this context");
+        ctx->capturing = false;
+        cudaGraph_t graph = nullptr;
+        cuda_check(cudaStreamEndCapture(ctx->stream, &graph), "cudaStreamEndCapture");
+        auto holder = std::make_unique<psi_graph>();
+        holder->ctx = ctx;
+        holder->graph = graph;
+        size_t nodes = 0;
+        cuda_check(cudaGraphGetNodes(graph, nullptr, &nodes), "cudaGraphGetNodes");
+        std::vector<cudaGraphNode_t> list(nodes);
+        if (nodes > 0) cuda_check(cudaGraphGetNodes(graph, list.data(), &nodes), "cudaGraphGetNodes");
+        for (cudaGraphNode_t node : list) {
+            cudaGraphNodeType type;
+            cuda_check(cudaGraphNodeGetType(node, &type), "cudaGraphNodeGetType");
+            if (type == cudaGraphNodeTypeKernel) holder->kernel_nodes += 1;
+        }
+        cudaError_t err = cudaGraphInstantiate(&holder->exec, graph, 0);
+        if (err != cudaSuccess) {
+            (void)cudaGraphDestroy(graph);
+            cuda_check(err, "cudaGraphInstantiate");
+        }
+        *out = holder.release();
+    });
+}
+
+int32_t psi_graph_launch(psi_graph* graph) {
+    if (graph == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(graph->ctx, [&] {
+        require(!graph->ctx->capturing, "a graph cannot be launched into an open capture of its own context");
+        graph->ctx->bind();
+        cuda_check(cudaGraphLaunch(graph->exec, graph->ctx->stream), "cudaGraphLaunch");
+        graph->ctx->launches += graph->kernel_nodes;
+    });
+}
+
+int32_t psi_graph_kernel_count(psi_graph* graph, uint64_t* out) {
+    if (graph == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    *out = graph->kernel_nodes;
+    return PSI_OK;
+}
+
+int32_t psi_graph_destroy(psi_graph* graph) {
+    return guarded(nullptr, [&] {
+        if (graph == nullptr) return;
+        if (graph->exec != nullptr) (void)cudaGraphExecDestroy(graph->exec);
+        if (graph->graph != nullptr) (void)cudaGraphDestroy(graph->graph);
+        delete graph;
     });
 }
 
@@ -1151,6 +1237,73 @@ int32_t psi_gqa_set_token_topology_boundaries(psi_gqa* g, const uint32_t* bounda
     });
 }
 
+// Offsets (in words) of the device block's arrays under a replay reservation: everything sized for max_tokens, the
+// arrays whose used length varies most placed last, so that an upload still moves only a prefix.
+static void reserved_layout(psi_gqa* g) {
+    constexpr uint64_t kItemWords = sizeof(DeviceItem) / sizeof(uint32_t);
+    const uint64_t t = g->cfg.max_tokens;
+    uint64_t cursor = pad_words(kScalarCount);
+    g->off_req_slots = cursor;
+    cursor += pad_words(t);
+    g->off_token_indices = cursor;
+    cursor += pad_words(t);
+    g->off_cta = cursor;
+    cursor += pad_words(g->grid_cap + 2);
+    g->off_first_items = cursor;
+    cursor += pad_words(uint64_t(g->grid_cap) * kItemWords);
+    g->off_chunk_cta = cursor;
+    cursor += pad_words(g->grid_cap + 2);
+    g->off_items = cursor;
+    cursor += pad_words(g->cap_items * kItemWords);
+    g->off_chunk_items = cursor;
+    cursor += pad_words(g->cap_chunk_items * kItemWords);
+    g->off_reduces = cursor;
+    cursor += pad_words(g->cap_reduces * 2);
+    g->staging_words = cursor;
+}
+
+int32_t psi_gqa_reserve_replay(psi_gqa* g) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        if (g->replay_reserved) return;
+        psi_ctx* ctx = g->ctx;
+        require(!ctx->capturing, "replay capacity cannot be reserved during stream capture");
+        ctx->bind();
+        // worst cases for max_tokens: every token a query tile of its own, every unit cut at every CTA boundary
+        const uint64_t heads = uint64_t(g->geo.num_kv_heads) * g->geo.head_tiles;
+        const uint64_t units = uint64_t(g->cfg.max_tokens) * heads;
+        const uint64_t cap_items = units + g->grid_cap;
+        const uint64_t chunk_units = g->chunk_supported ? units / 3 + heads : 0;
+        const uint64_t cap_chunk_items = g->chunk_supported ? chunk_units + 2ull * g->grid_cap + 8 : 0;
+        const uint64_t slots = cap_items + cap_chunk_items * kChunkTilesPerItem;
+        const uint64_t partial_bytes = slots * kMaxRows * g->cfg.head_dim * sizeof(float);
+        require(partial_bytes <= (2ull << 30),
+                "replay reservation needs more than 2 GiB of partial-output scratch for this max_tokens: create the "
+                "component with the largest batch the replayed steps carry");
+        cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+        g->cap_items = cap_items;
+        g->cap_chunk_items = cap_chunk_items;
+        g->cap_reduces = units;
+        if (g->staging != nullptr) {
+            cuda_check(cudaFreeHost(g->staging), "cudaFreeHost");
+            g->staging = nullptr;
+        }
+        reserved_layout(g);
+        cuda_check(cudaMallocHost(reinterpret_cast<void**>(&g->staging), g->staging_words * sizeof(uint32_t)), "cudaMallocHost");
+        std::memset(g->staging, 0, g->staging_words * sizeof(uint32_t));
+        g->block.ensure(ctx, g->staging_words * sizeof(uint32_t), true);
+        g->partial_o.ensure(ctx, partial_bytes, false);
+        g->partial_ml.ensure(ctx, 2 * slots * kMaxRows * sizeof(float), false);
+        g->unit_counters.release();  // counters restart from zero at their new size
+        g->unit_counters.ensure(ctx, slots * sizeof(uint32_t), true);
+        g->partial_slots_cap = slots;
+        g->status_word.ensure(ctx, sizeof(uint32_t), true);
+        cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+        g->prepared = false;  // the block moved: the next step prepares again
+        g->replay_reserved = true;
+    });
+}
+
 int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
                         uint32_t num_reqs, uint32_t capacity_mode, uint32_t caller_num_total_tokens,
                         psi_replay_shape* out_shape) {
@@ -1225,37 +1378,52 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         const uint32_t total_slots = plan.num_partial_slots + chunk.num_partial_slots;
         const uint32_t total_counters = static_cast<uint32_t>(plan.reduces.size()) + chunk.num_counters;
 
+        require(!ctx->capturing, "psi_gqa_prepare uploads the step's plan and stays outside captured graphs");
         // Pack the device block: scalars | req_slots | flat_token_indices | cta ranges | reduces | items.
-        uint64_t cursor = pad_words(kScalarCount);
-        g->off_req_slots = cursor;
-        cursor += pad_words(num_tokens);
-        g->off_token_indices = cursor;
-        cursor += pad_words(num_tokens);
-        g->off_cta = cursor;
-        cursor += pad_words(plan.cta_item_begin.size());
-        g->off_reduces = cursor;
-        cursor += pad_words(plan.reduces.size() * 2);
-        g->off_items = cursor;
-        cursor += pad_words(device_items.size() * (sizeof(DeviceItem) / sizeof(uint32_t)));
-        g->off_first_items = cursor;
-        cursor += pad_words(static_cast<uint64_t>(plan.num_ctas()) * (sizeof(DeviceItem) / sizeof(uint32_t)));
-        g->off_chunk_cta = cursor;
-        cursor += pad_words(chunk.cta_item_begin.size());
-        g->off_chunk_items = cursor;
-        cursor += pad_words(chunk.items.size() * (sizeof(DeviceItem) / sizeof(uint32_t)));
-        const uint64_t words = cursor;
-
-        if (g->staging_words < words) {
-            if (g->staging != nullptr) {
-                cuda_check(cudaEventSynchronize(g->upload_done), "cudaEventSynchronize");
-                cuda_check(cudaFreeHost(g->staging), "cudaFreeHost");
-                g->staging = nullptr;
-            }
-            const uint64_t grown = std::max<uint64_t>(words * 2, 4096);
-            cuda_check(cudaMallocHost(reinterpret_cast<void**>(&g->staging), grown * sizeof(uint32_t)), "cudaMallocHost");
-            g->staging_words = grown;
-        } else {
+        uint64_t words = 0;
+        if (g->replay_reserved) {
+            // fixed offsets (reserved_layout); only the used prefix is uploaded
+            constexpr uint64_t kItemWords = sizeof(DeviceItem) / sizeof(uint32_t);
+            require(device_items.size() <= g->cap_items && chunk.items.size() <= g->cap_chunk_items &&
+                        plan.reduces.size() <= g->cap_reduces && total_slots <= g->partial_slots_cap &&
+                        plan.num_ctas() <= g->grid_cap && chunk.num_ctas() <= g->grid_cap,
+                    "the step exceeds the reserved replay capacity");
+            words = g->off_items + device_items.size() * kItemWords;
+            if (!chunk.items.empty()) words = g->off_chunk_items + chunk.items.size() * kItemWords;
+            if (!plan.reduces.empty()) words = g->off_reduces + plan.reduces.size() * 2;
             cuda_check(cudaEventSynchronize(g->upload_done), "cudaEventSynchronize");  // previous upload left staging
+        } else {
+            uint64_t cursor = pad_words(kScalarCount);
+            g->off_req_slots = cursor;
+            cursor += pad_words(num_tokens);
+            g->off_token_indices = cursor;
+            cursor += pad_words(num_tokens);
+            g->off_cta = cursor;
+            cursor += pad_words(plan.cta_item_begin.size());
+            g->off_reduces = cursor;
+            cursor += pad_words(plan.reduces.size() * 2);
+            g->off_items = cursor;
+            cursor += pad_words(device_items.size() * (sizeof(DeviceItem) / sizeof(uint32_t)));
+            g->off_first_items = cursor;
+            cursor += pad_words(static_cast<uint64_t>(plan.num_ctas()) * (sizeof(DeviceItem) / sizeof(uint32_t)));
+            g->off_chunk_cta = cursor;
+            cursor += pad_words(chunk.cta_item_begin.size());
+            g->off_chunk_items = cursor;
+            cursor += pad_words(chunk.items.size() * (sizeof(DeviceItem) / sizeof(uint32_t)));
+            words = cursor;
+
+            if (g->staging_words < words) {
+                if (g->staging != nullptr) {
+                    cuda_check(cudaEventSynchronize(g->upload_done), "cudaEventSynchronize");
+                    cuda_check(cudaFreeHost(g->staging), "cudaFreeHost");
+                    g->staging = nullptr;
+                }
+                const uint64_t grown = std::max<uint64_t>(words * 2, 4096);
+                cuda_check(cudaMallocHost(reinterpret_cast<void**>(&g->staging), grown * sizeof(uint32_t)), "cudaMallocHost");
+                g->staging_words = grown;
+            } else {
+                cuda_check(cudaEventSynchronize(g->upload_done), "cudaEventSynchronize");  // previous upload left staging
+            }
         }
         g->block.ensure(ctx, g->staging_words * sizeof(uint32_t), false);
         if (total_slots > g->partial_slots_cap) {
@@ -1278,6 +1446,17 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         std::copy(g->md->flat_token_indices.begin(), g->md->flat_token_indices.begin() + num_tokens,
                   s + g->off_token_indices);
         std::copy(plan.cta_item_begin.begin(), plan.cta_item_begin.end(), s + g->off_cta);
+        if (g->replay_reserved) {
+            // launches run at the capacity grid: CTAs beyond the plan's find an empty range and a zero first item
+            constexpr uint64_t kItemWords = sizeof(DeviceItem) / sizeof(uint32_t);
+            const uint32_t items_end = static_cast<uint32_t>(device_items.size());
+            for (uint64_t c = plan.cta_item_begin.size(); c < g->grid_cap + 2ull; ++c) s[g->off_cta + c] = items_end;
+            if (plan.cta_item_begin.empty()) s[g->off_cta] = 0;
+            std::fill(s + g->off_first_items, s + g->off_first_items + uint64_t(g->grid_cap) * kItemWords, 0u);
+            const uint32_t chunk_end = static_cast<uint32_t>(chunk.items.size());
+            for (uint64_t c = chunk.cta_item_begin.size(); c < g->grid_cap + 2ull; ++c) s[g->off_chunk_cta + c] = chunk_end;
+            if (chunk.cta_item_begin.empty()) s[g->off_chunk_cta] = 0;
+        }
         if (!plan.reduces.empty())
             std::memcpy(s + g->off_reduces, plan.reduces.data(), plan.reduces.size() * sizeof(ReduceUnit));
         if (!device_items.empty())
