@@ -290,6 +290,17 @@ PSI_API int32_t psi_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, co
                                  uint64_t items_cap,
                                  uint32_t* out_cta_item_begin, uint64_t cta_cap, uint32_t* out_counts);
 
+/* The work plan of the long-query (chunk) kernels for a batch in which EVERY request carries a long run, computed on
+ * the host.  equal_shares selects the plan for working sets that stay in L2 (contiguous shares of equal size) instead
+ * of stream order.  out_items receives 10 u32 per item {request, kv head, flat token begin, tokens, kv_begin, kv_end,
+ * partial slot or 0xFFFFFFFF, pieces of its unit, first slot of the unit, first arrival counter of the unit};
+ * out_cta_item_begin num_ctas+1 entries; out_counts {items, ctas, partial slots, arrival counters, total 16-token KV
+ * tiles (saturated)}.  No reference counterpart. */
+PSI_API int32_t psi_chunk_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint32_t* token_indices,
+                                       const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
+                                       uint32_t equal_shares, uint32_t* out_items, uint64_t items_cap,
+                                       uint32_t* out_cta_item_begin, uint64_t cta_cap, uint32_t* out_counts);
+
 /* U32IDAllocator (crates/inference-runtime-core/src/memory/u32_id_allocator.rs:69-172): freed IDs first, in the order
  * they were freed, then fresh IDs from a counter.  Runtime core keeps its own allocator; this one drives synthetic
  * admit/finish traces with the same observable behaviour. */

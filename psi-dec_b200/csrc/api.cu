@@ -1111,6 +1111,52 @@ int32_t psi_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint
     });
 }
 
+int32_t psi_chunk_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint32_t* token_indices,
+                               const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas, uint32_t equal_shares,
+                               uint32_t* out_items, uint64_t items_cap, uint32_t* out_cta_item_begin, uint64_t cta_cap,
+                               uint32_t* out_counts) {
+    return guarded(nullptr, [&] {
+        require(token_indices && cu_tokens && out_counts, "plan inputs must not be null");
+        require(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
+                "GQA q heads must be a positive multiple of kv heads");
+        require(num_reqs > 0 && cu_tokens[0] == 0, "GQA batch cu_tokens must start at zero");
+        std::vector<uint32_t> slots(num_reqs), requests(num_reqs);
+        for (uint32_t r = 0; r < num_reqs; ++r) {
+            require(cu_tokens[r] < cu_tokens[r + 1], "every request of a long-run plan needs query tokens");
+            slots[r] = r;
+            requests[r] = r;
+        }
+        const ChunkPlan plan = build_chunk_plan(plan_geometry(num_q_heads, num_kv_heads), slots.data(), token_indices,
+                                                cu_tokens, requests, max_ctas, 0, 0, equal_shares != 0);
+        out_counts[0] = static_cast<uint32_t>(plan.items.size());
+        out_counts[1] = plan.num_ctas();
+        out_counts[2] = plan.num_partial_slots;
+        out_counts[3] = plan.num_counters;
+        out_counts[4] = static_cast<uint32_t>(std::min<uint64_t>(plan.total_kv_tiles, kU32Max));
+        if (out_items != nullptr) {
+            require(items_cap >= plan.items.size(), "item output capacity too small");
+            for (size_t i = 0; i < plan.items.size(); ++i) {
+                const DeviceItem& d = plan.items[i];
+                uint32_t* o = out_items + i * 10;
+                o[0] = d.req_slot;
+                o[1] = d.kv_head;
+                o[2] = d.flat_begin;
+                o[3] = d.num_tokens;
+                o[4] = d.kv_begin;
+                o[5] = d.kv_end;
+                o[6] = d.partial_slot;
+                o[7] = d.partial_slot == kU32Max ? 1u : d.unit_num_items;
+                o[8] = d.partial_slot == kU32Max ? kU32Max : d.unit_first_slot;
+                o[9] = d.partial_slot == kU32Max ? kU32Max : d.reduce_unit;
+            }
+        }
+        if (out_cta_item_begin != nullptr) {
+            require(cta_cap >= plan.cta_item_begin.size(), "cta output capacity too small");
+            std::copy(plan.cta_item_begin.begin(), plan.cta_item_begin.end(), out_cta_item_begin);
+        }
+    });
+}
+
 int32_t psi_id_allocator_create(uint64_t capacity, psi_id_allocator** out) {
     return guarded(nullptr, [&] {
         require(out != nullptr, "out must not be null");

@@ -562,8 +562,17 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 if (row_valid) {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) o[e] *= inv;
-                    if (is_partial || p.ext_o != nullptr) {
-                        float* dst = is_partial ? p.partial_o + prow * D + c : p.ext_o + out_row * D + c;
+                    if (is_partial) {
+                        // a partial slot of this kernel is stored column-major in float4 units, [D / 4][16 rows]: the
+                        // 16 rows of a tile are 16 consecutive lanes here, so every store instruction writes whole
+                        // 256-byte runs (the merge below reads them the same way)
+                        float4* dst = reinterpret_cast<float4*>(p.partial_o + static_cast<uint64_t>(v.partial_slot + w) * kMaxRows * D) +
+                                      static_cast<uint64_t>(c / 4) * kMaxRows + rr;
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4)
+                            dst[static_cast<uint64_t>(e / 4) * kMaxRows] = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+                    } else if (p.ext_o != nullptr) {
+                        float* dst = p.ext_o + out_row * D + c;
 #pragma unroll
                         for (int e = 0; e < 32; e += 4)
                             *reinterpret_cast<float4*>(dst + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
@@ -605,56 +614,49 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     trace_merges += 1;
                     trace_pieces += v.unit_num_items;
 #endif
-                    // 16 rows x D / 4 float4 outputs per tile, 8 per thread (row 2 j + tid / (D / 4) ... for D = 256)
+                    // 16 rows x D / 4 float4 outputs per tile: a thread takes row tid % 16 and the float4 columns
+                    // tid / 16 + 8 j (16 consecutive lanes read 256 consecutive bytes of the column-major slots)
                     const uint32_t tile_tokens = min(p.tokens_per_tile, v.num_tokens - tile * p.tokens_per_tile);
                     const uint32_t tile_rows = tile_tokens * v.num_heads;
                     constexpr uint32_t kPerThread = kMaxRows * (D / 4) / kRowThreads;
-                    constexpr uint32_t kRowStep = kRowThreads / (D / 4);  // rows between a thread's consecutive outputs
-                    const uint32_t c4 = tid % (D / 4), r0 = tid / (D / 4);
-                    const uint64_t slot_rows = static_cast<uint64_t>(v.unit_first_slot + tile) * kMaxRows;
-                    // rows beyond the tile's last one are computed on the last row and dropped at the end: the loops
+                    constexpr uint32_t kColumnStep = kRowThreads / kMaxRows;  // float4 columns between a thread's outputs
+                    // a row beyond the tile's last one is computed on the last row and dropped at the end: the loops
                     // below are then straight-line code whose loads all go out before the first one is used
-                    uint64_t row_off[kPerThread];
-#pragma unroll
-                    for (uint32_t j = 0; j < kPerThread; ++j) row_off[j] = slot_rows + min(r0 + j * kRowStep, tile_rows - 1);
+                    const uint32_t r = min(tid % kMaxRows, tile_rows - 1), c4_0 = tid / kMaxRows;
+                    const bool row_present = tid % kMaxRows < tile_rows;
+                    const uint64_t slot_rows = static_cast<uint64_t>(v.unit_first_slot + tile) * kMaxRows;
                     // one pass over the pieces with the running max of a row carried along (sums are rescaled when
                     // a later piece raises it); the loads of piece s + 1 are in flight while piece s is folded in
-                    float row_top[kPerThread], sum[kPerThread];
                     float4 acc[kPerThread];
 #pragma unroll
-                    for (uint32_t j = 0; j < kPerThread; ++j) {
-                        row_top[j] = -INFINITY;
-                        sum[j] = 0.0f;
-                        acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                    const float* stat_m = p.partial_m;
-                    const float* stat_l = p.partial_l;
-                    const float4* part_o = reinterpret_cast<const float4*>(p.partial_o) + c4;
+                    for (uint32_t j = 0; j < kPerThread; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                     constexpr uint64_t kPieceRows = 8 * kMaxRows;  // rows between the same tile of consecutive pieces
-                    float pm[2][kPerThread], pl[2][kPerThread];
+                    float pm[2], pl[2];
                     float4 part[2][kPerThread];
-                    auto fetch = [&](uint32_t piece, float (&m_out)[kPerThread], float (&l_out)[kPerThread], float4 (&o_out)[kPerThread]) {
+                    auto fetch = [&](uint32_t piece, float& m_out, float& l_out, float4 (&o_out)[kPerThread]) {
+                        const uint64_t rows = slot_rows + piece * kPieceRows;
+                        m_out = __ldcg(p.partial_m + rows + r);
+                        l_out = __ldcg(p.partial_l + rows + r);
+                        const float4* slot = reinterpret_cast<const float4*>(p.partial_o + rows * D) + r;
 #pragma unroll
-                        for (uint32_t j = 0; j < kPerThread; ++j) {
-                            const uint64_t row = row_off[j] + piece * kPieceRows;
-                            m_out[j] = __ldcg(stat_m + row);
-                            l_out[j] = __ldcg(stat_l + row);
-                            o_out[j] = __ldcg(part_o + row * (D / 4));
-                        }
+                        for (uint32_t j = 0; j < kPerThread; ++j)
+                            o_out[j] = __ldcg(slot + static_cast<uint64_t>(c4_0 + j * kColumnStep) * kMaxRows);
                     };
-                    auto fold = [&](const float (&m_in)[kPerThread], const float (&l_in)[kPerThread], const float4 (&o_in)[kPerThread]) {
+                    // one row per thread: a single running max, sum and carry for all of its columns
+                    float top_all = -INFINITY, sum_all = 0.0f;
+                    auto fold = [&](float m_in, float l_in, const float4 (&o_in)[kPerThread]) {
+                        const float top = fmaxf(top_all, m_in);
+                        const float carry = top_all == -INFINITY ? 0.0f : fast_exp2(top_all - top);
+                        const float w = m_in == -INFINITY ? 0.0f : fast_exp2(m_in - top) * l_in;
+                        sum_all = sum_all * carry + w;
 #pragma unroll
                         for (uint32_t j = 0; j < kPerThread; ++j) {
-                            const float top = fmaxf(row_top[j], m_in[j]);
-                            const float carry = row_top[j] == -INFINITY ? 0.0f : fast_exp2(row_top[j] - top);
-                            const float w = m_in[j] == -INFINITY ? 0.0f : fast_exp2(m_in[j] - top) * l_in[j];
-                            sum[j] = sum[j] * carry + w;
                             acc[j].x = acc[j].x * carry + w * o_in[j].x;
                             acc[j].y = acc[j].y * carry + w * o_in[j].y;
                             acc[j].z = acc[j].z * carry + w * o_in[j].z;
                             acc[j].w = acc[j].w * carry + w * o_in[j].w;
-                            row_top[j] = top;
                         }
+                        top_all = top;
                     };
                     fetch(0, pm[0], pl[0], part[0]);
                     for (uint32_t s0 = 0; s0 < v.unit_num_items; s0 += 2) {
@@ -665,23 +667,24 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                             fold(pm[1], pl[1], part[1]);
                         }
                     }
-#pragma unroll
-                    for (uint32_t j = 0; j < kPerThread; ++j) {
-                        const uint32_t r = r0 + j * kRowStep;
-                        if (r >= tile_rows) continue;
-                        const float scale = sum[j] > 0.0f ? 1.0f / sum[j] : 0.0f;
-                        const float4 value = make_float4(acc[j].x * scale, acc[j].y * scale, acc[j].z * scale, acc[j].w * scale);
+                    if (row_present) {
+                        const float scale = sum_all > 0.0f ? 1.0f / sum_all : 0.0f;
                         const uint64_t row =
                             static_cast<uint64_t>(v.flat_begin + tile * p.tokens_per_tile + r / v.num_heads) * p.num_q_heads +
                             v.head0 + r % v.num_heads;
-                        if (p.ext_o != nullptr) {
-                            *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = value;
-                            if (c4 == 0) {
-                                p.ext_m[row] = row_top[j] * kLn2;
-                                p.ext_l[row] = sum[j];
+#pragma unroll
+                        for (uint32_t j = 0; j < kPerThread; ++j) {
+                            const uint32_t c4 = c4_0 + j * kColumnStep;
+                            const float4 value = make_float4(acc[j].x * scale, acc[j].y * scale, acc[j].z * scale, acc[j].w * scale);
+                            if (p.ext_o != nullptr) {
+                                *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = value;
+                            } else {
+                                store_out4<T>(p, row * D + 4 * c4, value);
                             }
-                        } else {
-                            store_out4<T>(p, row * D + 4 * c4, value);
+                        }
+                        if (p.ext_o != nullptr && c4_0 == 0) {
+                            p.ext_m[row] = top_all * kLn2;
+                            p.ext_l[row] = sum_all;
                         }
                     }
                     if (tid == 0) p.unit_counters[v.reduce_unit + tile] = 0;  // ready for the next launch

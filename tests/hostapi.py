@@ -65,3 +65,18 @@ def plan_preview(num_q_heads, num_kv_heads, token_indices, cu_tokens, max_ctas, 
                                     p(ctas), C.c_uint64(len(ctas)), p(counts))
     assert status == 0
     return items, ctas, counts
+
+
+def chunk_plan_preview(num_q_heads, num_kv_heads, token_indices, cu_tokens, max_ctas, equal_shares):
+    p = lambda a: a.ctypes.data_as(C.POINTER(C.c_uint32))
+    ti = np.ascontiguousarray(token_indices, dtype=np.uint32)
+    cu = np.ascontiguousarray(cu_tokens, dtype=np.uint32)
+    counts = np.zeros(5, dtype=np.uint32)
+    args = (C.c_uint32(num_q_heads), C.c_uint32(num_kv_heads), p(ti), p(cu), C.c_uint32(len(ti)), C.c_uint32(max_ctas),
+            C.c_uint32(1 if equal_shares else 0))
+    assert lib().psi_chunk_plan_preview(*args, None, C.c_uint64(0), None, C.c_uint64(0), p(counts)) == 0
+    items = np.zeros((int(counts[0]), 10), dtype=np.uint32)
+    ctas = np.zeros(int(counts[1]) + 1, dtype=np.uint32)
+    assert lib().psi_chunk_plan_preview(*args, p(items), C.c_uint64(len(items)), p(ctas), C.c_uint64(len(ctas)),
+                                        p(counts)) == 0
+    return items, ctas, counts

@@ -296,3 +296,57 @@ def test_rope_parameters_yarn_golden_and_oracle():
     assert np.allclose(inv, O.rope_parameters(64, 1_000_000.0)[0], rtol=1e-6)
     with pytest.raises(pkg.PsiError, match="Yarn rope_theta must be greater than 1"):
         pkg.rope_parameters(pkg.NormRopeConfig(64, 1e-6, 1.0, 1, 2.0, 1.0, 2.0, 1.0, 4096, 0))
+
+
+@pytest.mark.parametrize("equal_shares", [False, True])
+@pytest.mark.parametrize("max_ctas", [1, 7, 148])
+def test_chunk_plan_covers_every_unit_once_and_keeps_its_books(equal_shares, max_ctas):
+    # long query runs: units = (request, KV head, super-tile of 8 query tiles = 16 tokens at group 8); every unit's KV
+    # range [0, context + tokens so far) must be covered exactly once by its pieces, pieces of a cut unit own disjoint
+    # partial-slot groups and one group of eight arrival counters, every item belongs to exactly one CTA
+    rng = np.random.default_rng(11)
+    for trial in range(6):
+        n = int(rng.integers(1, 9))
+        ctx = rng.integers(0, 20000, size=n)
+        runs = rng.integers(10, 700, size=n)
+        cu = np.concatenate([[0], np.cumsum(runs)])
+        items, ctas, counts = H.chunk_plan_preview(16, 2, ctx, cu, max_ctas, equal_shares)
+        assert counts[0] == len(items) and ctas[0] == 0 and ctas[-1] == len(items) and np.all(np.diff(ctas.astype(np.int64)) >= 0)
+        assert len(ctas) - 1 <= max_ctas
+        units = {}
+        for req, head, flat, tokens, kb, ke, slot, pieces, first_slot, counter in items.tolist():
+            assert kb < ke and kb % 16 == 0 and 1 <= tokens <= 16
+            units.setdefault((req, head, flat), []).append((kb, ke, slot, pieces, first_slot, counter, tokens))
+        expected_units = sum(-(-int(r) // 16) for r in runs) * 2
+        assert len(units) == expected_units
+        slot_groups, counter_groups = set(), set()
+        total_tiles = 0
+        for (req, head, flat), pieces in units.items():
+            pieces.sort()
+            done = flat - int(cu[req])                      # tokens of the request before this super-tile
+            tokens = pieces[0][6]
+            end = int(ctx[req]) + done + tokens             # keys the super-tile's last token sees
+            assert pieces[0][0] == 0 and pieces[-1][1] == end
+            assert all(a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
+            assert all(a[1] % 16 == 0 for a in pieces[:-1])
+            total_tiles += -(-end // 16)
+            if len(pieces) == 1:
+                assert pieces[0][2] == 0xFFFFFFFF
+            else:
+                firsts = {x[4] for x in pieces}
+                assert len(firsts) == 1 and {x[3] for x in pieces} == {len(pieces)} and len({x[5] for x in pieces}) == 1
+                first = firsts.pop()
+                assert sorted(x[2] for x in pieces) == [first + 8 * k for k in range(len(pieces))]
+                group = set(range(first, first + 8 * len(pieces)))
+                assert not (group & slot_groups)
+                slot_groups |= group
+                counters = set(range(pieces[0][5], pieces[0][5] + 8))
+                assert not (counters & counter_groups)
+                counter_groups |= counters
+        assert counts[4] == total_tiles
+        assert counts[2] == len(slot_groups) and counts[3] == len(counter_groups)
+        if equal_shares and len(ctas) - 1 > 1:
+            loads = [sum(-(-(int(items[i, 5]) - int(items[i, 4])) // 16) for i in range(ctas[c], ctas[c + 1]))
+                     for c in range(len(ctas) - 1)]
+            share = total_tiles / (len(ctas) - 1)
+            assert max(loads) <= share + 2 * 16 + 8 and min(loads) >= share - 2 * 16 - 8, (min(loads), share, max(loads))
