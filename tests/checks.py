@@ -129,3 +129,15 @@ def time_oracle_sample(session, seconds_target=15.0, max_seqs=None):
     kv_bytes = int(spec.visible[chosen].sum()) * 2 * spec.num_kv_heads * spec.head_dim * spec.elem_bytes
     desc = f"{len(chosen)} shortest of {spec.num_seqs} sequences ({int(spec.visible[chosen].sum())} visible tokens)"
     return tokens / elapsed, kv_bytes / elapsed, desc, O.num_threads()
+
+
+_GOLDEN = None
+
+
+def golden(name):
+    """A stored expectation from tests/golden/attention_vectors.npz (see tests/golden/make_fixtures.py)."""
+    global _GOLDEN
+    if _GOLDEN is None:
+        from pathlib import Path
+        _GOLDEN = np.load(Path(__file__).resolve().parent / "golden" / "attention_vectors.npz")
+    return _GOLDEN[name]

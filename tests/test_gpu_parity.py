@@ -212,6 +212,7 @@ def test_single_q_fixed_and_random(plan_mode, _name, case):
     actual = _run_single_q(rig, q, [0], [0], [0, 2])
     expected = O.projected_gqa_reference(4, 2, 2, 0.5, [0, 2], [0], q, [k], [v])
     assert np.max(np.abs(actual - expected)) <= 2e-5
+    assert np.max(np.abs(actual - checks.golden("single_q_" + case))) <= 2e-5   # the stored vectors
     rig.close()
 
 
@@ -229,6 +230,7 @@ def test_single_q_ragged_random(plan_mode, _name):
     actual = _run_single_q(rig, q, [0, 1], [1, 0], [0, 1, 3])
     expected = O.projected_gqa_reference(4, 2, 2, 0.5, [0, 1, 3], [1, 0], q, [r0k, r1k], [r0v, r1v])
     assert np.max(np.abs(actual - expected)) <= 2e-5
+    assert np.max(np.abs(actual - checks.golden("single_q_ragged"))) <= 2e-5
     rig.close()
 
 
@@ -278,7 +280,8 @@ def test_single_q_bucketed_replay_preserves_output_tail(plan_mode, _name):
 KERNELS = [(pkg.KERNEL_MMA, "mma"), (pkg.KERNEL_GENERIC, "generic")]
 
 
-def _run_tiled_case(num_tokens_per_req, num_q_heads, head_dim, tokens_per_page, start, plan_mode, kernel_mode):
+def _run_tiled_case(num_tokens_per_req, num_q_heads, head_dim, tokens_per_page, start, plan_mode, kernel_mode,
+                    golden_name=None):
     # run_case(): crates/inference-executor-metal/tests/gqa_split_kv_tiled_q.rs:247-462
     import torch
     reqs = len(num_tokens_per_req)
@@ -319,20 +322,22 @@ def _run_tiled_case(num_tokens_per_req, num_q_heads, head_dim, tokens_per_page, 
     assert stats["kernel"] == kernel_mode
     assert np.max(np.abs(actual - expected)) <= 0.02, np.max(np.abs(actual - expected))
     assert np.mean(np.abs(actual - expected)) <= 2e-3
+    if golden_name is not None:  # the stored vectors keep every 7th element
+        assert np.max(np.abs(actual[::7] - checks.golden(golden_name))) <= 0.02
 
 
 @pytest.mark.parametrize("kernel_mode,_kname", KERNELS)
 @pytest.mark.parametrize("plan_mode,_name", MODES)
-@pytest.mark.parametrize("case", [
-    ([16], 8, 256, 16, 17),                          # test_fixed
-    ([16], 6, 256, 8, 9),                            # test_qwen38_27b_profile
-    ([1, 2, 4, 6, 8, 11, 16, 16], 6, 256, 16, 17),   # test_ragged
-    ([32, 8], 8, 256, 16, 17),                       # test_multiple_tiles
-    ([1, 4, 8, 13], 5, 128, 8, 9),                   # test_qwen3_profile
+@pytest.mark.parametrize("case,golden_name", [
+    (([16], 8, 256, 16, 17), "tiled_fixed"),                                 # test_fixed
+    (([16], 6, 256, 8, 9), "tiled_qwen38_27b"),                              # test_qwen38_27b_profile
+    (([1, 2, 4, 6, 8, 11, 16, 16], 6, 256, 16, 17), "tiled_ragged"),         # test_ragged
+    (([32, 8], 8, 256, 16, 17), "tiled_multiple_tiles"),                     # test_multiple_tiles
+    (([1, 4, 8, 13], 5, 128, 8, 9), "tiled_qwen3"),                          # test_qwen3_profile
 ])
-def test_tiled_q_integration_cases(case, plan_mode, _name, kernel_mode, _kname):
+def test_tiled_q_integration_cases(case, golden_name, plan_mode, _name, kernel_mode, _kname):
     # crates/inference-executor-metal/tests/gqa_split_kv_tiled_q.rs:27-50
-    _run_tiled_case(*case, plan_mode, kernel_mode)
+    _run_tiled_case(*case, plan_mode, kernel_mode, golden_name)
 
 
 @pytest.mark.parametrize("kernel_mode,_kname", KERNELS)

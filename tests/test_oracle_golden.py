@@ -294,3 +294,20 @@ def test_block_sdpa_closed_form_vectors():
                 assert abs(ps[token, head] - weights.sum()) < 1e-4
                 want = weights @ v64[begin:begin + block] / weights.sum()
                 assert np.abs(out[token, head] - want).max() < tol
+
+
+def test_oracle_reproduces_the_committed_fixtures():
+    # tests/golden/attention_vectors.npz (written by tests/golden/make_fixtures.py from the reference tests' own
+    # deterministic inputs): the oracle must keep producing them
+    import importlib.util
+    from pathlib import Path
+    golden_dir = Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_fixtures", golden_dir / "make_fixtures.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    stored = np.load(golden_dir / "attention_vectors.npz")
+    fresh = module.vectors()
+    assert sorted(stored.files) == sorted(fresh)
+    for name in stored.files:
+        assert stored[name].shape == fresh[name].shape, name
+        assert np.abs(stored[name] - fresh[name]).max() <= 1e-6, name
