@@ -497,6 +497,8 @@ int32_t psi_ctx_capture_begin(psi_ctx* ctx) {
     return guarded(ctx, [&] {
         require(!ctx->capturing, "a stream capture is already open on this context");
         require(!ctx->timing, "switch kernel timing off before capturing");
+        require(ctx->stream != nullptr && ctx->stream != cudaStreamLegacy,
+                "the legacy default stream cannot be captured: create the context on a stream of its own");
         ctx->bind();
         cuda_check(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
         ctx->capturing = true;
@@ -1359,6 +1361,7 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         require(capacity_mode <= PSI_CAPACITY_CALLER_TOKENS, "unknown capacity mode");
         require(num_reqs > 0, "GQA batch metadata requires tokens");
         psi_ctx* ctx = g->ctx;
+        require(!ctx->capturing, "psi_gqa_prepare uploads the step's plan and stays outside captured graphs");
         ctx->bind();
         g->prepared = false;
 
@@ -1424,7 +1427,6 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         const uint32_t total_slots = plan.num_partial_slots + chunk.num_partial_slots;
         const uint32_t total_counters = static_cast<uint32_t>(plan.reduces.size()) + chunk.num_counters;
 
-        require(!ctx->capturing, "psi_gqa_prepare uploads the step's plan and stays outside captured graphs");
         // Pack the device block: scalars | req_slots | flat_token_indices | cta ranges | reduces | items.
         uint64_t words = 0;
         if (g->replay_reserved) {

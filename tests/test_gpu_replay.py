@@ -23,8 +23,26 @@ BATCHES = [
 ]
 
 
+@pytest.fixture
+def side_stream():
+    """The legacy default stream cannot be captured: the rig (which adopts torch's current stream) and the torch
+    work around it run on a stream of their own."""
+    import torch
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        yield stream
+    torch.cuda.synchronize()
+
+
+def test_the_default_stream_is_refused():
+    rig = G.Rig(pkg.BF16, 8, 2, 128, 16, 0.1, (2, 1, 8, 1), 16, num_pages=16)
+    with pytest.raises(pkg.PsiError, match="legacy default stream"):
+        rig.ctx.capture_begin()
+    rig.close()
+
+
 @pytest.mark.parametrize("kernel_mode", [pkg.KERNEL_MMA, pkg.KERNEL_GENERIC])
-def test_one_captured_graph_serves_changing_batches(kernel_mode):
+def test_one_captured_graph_serves_changing_batches(kernel_mode, side_stream):
     import torch
     hq, hkv, d, p = 16, 2, 128, 16
     scale = 1.0 / np.sqrt(d)
@@ -87,7 +105,7 @@ def test_one_captured_graph_serves_changing_batches(kernel_mode):
     rig.close()
 
 
-def test_capture_refuses_buffers_that_would_grow():
+def test_capture_refuses_buffers_that_would_grow(side_stream):
     import torch
     rig = G.Rig(pkg.BF16, 8, 2, 128, 16, 0.1, (2, 1, 8, 1), 16, num_pages=16)
     for slot in range(2):
