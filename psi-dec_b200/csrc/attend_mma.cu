@@ -141,8 +141,10 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                     cp_async_16(dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4), src, 16u);
                 }
             } else {
+                // The item's last tile (ragged end, or this step's own tokens) is rare: a rolled loop keeps its code to
+                // a few instruction-cache lines, which are fetched in mid-stream behind the K/V traffic of all SMs.
                 const unsigned char* fresh = static_cast<const unsigned char*>((h & 1) ? p.new_v : p.new_k);
-#pragma unroll
+#pragma unroll 1
                 for (uint32_t it = 0; it < kTile / kRowsPerCopy; ++it) {
                     const uint32_t row0 = it * kRowsPerCopy;
                     const uint32_t token = token0 + row0 + copy_row;
