@@ -273,6 +273,9 @@ def bench_ours(args):
                     "h2d_bytes_per_step": int(job_h2d), "d2h_bytes_per_step": int(job_d2h)},
             "gpu_launches": int(launches),
             "clocks": clocks,
+            # rank 0's per-step distribution (the headline ms_per_step is the mean of the slowest rank)
+            "ms_per_step_rank0": {"median": round(statistics.median(step_ms), 5), "min": round(min(step_ms), 5),
+                                  "max": round(max(step_ms), 5)},
         }
         if chunk_n and chunk_ms > map_ms:
             # long query runs dominate the step: the chunk kernel is a contraction, bounded by the tensor pipe
@@ -291,6 +294,11 @@ def bench_ours(args):
         per_byte = NCU_DRAM_BYTES_PER_ALGORITHMIC_BYTE.get(base.name)
         if per_byte and stats["kernel"] == 2 and line["roofline"]["bound"] == "hbm":
             line["roofline"]["traffic"] = int(per_byte * alg["total"])
+        if world == 1 and line["roofline"]["bound"] == "hbm" and not args.no_read_probe:
+            # the ceiling of a kernel that only reads HBM (4 GiB through 16-byte loads), beside the copy figure in `peak`
+            probe = session.ctx.read_bandwidth(4 << 30, 5)
+            line["roofline"]["read_only_probe_gbs"] = round(probe, 1)
+            line["roofline"]["frac_of_read_only_probe"] = round(achieved / probe, 4) if probe > 0 else None
         if world == 1 and not args.no_cpu_baseline:
             import checks
             tok_s, bytes_s, desc, threads = checks.time_oracle_sample(session, seconds_target=12.0)
@@ -386,6 +394,7 @@ def main():
     parser.add_argument("--scale-down", type=int, default=1,
                         help="divide batch and context sizes (small cases for profiler captures; not a bench value)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-read-probe", action="store_true", help="skip the read-only HBM bandwidth probe")
     parser.add_argument("--kernel", choices=["auto", "mma", "generic", "mma_sync"], default="auto",
                         help="attention kernel: tensor-core kernels (default where supported), the CUDA-core kernel, or "
                              "mma_sync = tensor-core kernels with long query runs kept off the tcgen05 kernel")

@@ -157,6 +157,11 @@ PSI_API int32_t psi_ctx_last_error(psi_ctx* ctx, char* buf, size_t n);
 /* Last error of the calling thread for calls that have no context yet (creation failures). */
 PSI_API int32_t psi_last_error(char* buf, size_t n);
 
+/* Measurement aid with no counterpart in the reference: streams `bytes` (>= 16, rounded down to 16) of a scratch
+ * buffer through read-only 16-byte loads `iterations` times after one warm-up pass and returns the best pass in GB/s:
+ * the ceiling of a kernel that only reads HBM, to stand beside the read+write copy bandwidth. */
+PSI_API int32_t psi_ctx_read_bandwidth(psi_ctx* ctx, uint64_t bytes, uint32_t iterations, double* out_gbs);
+
 /* ---- page arena (crates/inference-executor-metal/src/model/page_arena.rs:6-46) ------------------------------------ */
 
 /* PageArena::new: num_pages x page_bytes of device memory, zero-filled. */

@@ -159,6 +159,12 @@ class Context:
     def sync(self):
         _check(library().psi_ctx_sync(self._h), self._h)
 
+    def read_bandwidth(self, num_bytes: int, iterations: int = 5) -> float:
+        """GB/s of a kernel that only reads ``num_bytes`` of HBM with 16-byte loads (best of ``iterations`` passes)."""
+        out = C.c_double()
+        _check(library().psi_ctx_read_bandwidth(self._h, C.c_uint64(num_bytes), C.c_uint32(iterations), C.byref(out)), self._h)
+        return float(out.value)
+
     @property
     def sm_count(self) -> int:
         out = C.c_int32()

@@ -447,6 +447,46 @@ int32_t psi_ctx_sync(psi_ctx* ctx) {
     });
 }
 
+int32_t psi_ctx_read_bandwidth(psi_ctx* ctx, uint64_t bytes, uint32_t iterations, double* out_gbs) {
+    if (ctx == nullptr || out_gbs == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        require(bytes >= 16 && iterations > 0, "the probe needs at least 16 bytes and one iteration");
+        require(!ctx->capturing, "the bandwidth probe synchronises and stays outside captured graphs");
+        ctx->bind();
+        bytes &= ~uint64_t(15);
+        DeviceBuffer scratch, sink;
+        struct Release {
+            DeviceBuffer& a;
+            DeviceBuffer& b;
+            ~Release() {
+                a.release();
+                b.release();
+            }
+        } release{scratch, sink};
+        scratch.ensure(ctx, bytes, true);
+        sink.ensure(ctx, sizeof(uint32_t), true);
+        cudaEvent_t begin = nullptr, end = nullptr;
+        cuda_check(cudaEventCreate(&begin), "cudaEventCreate");
+        cuda_check(cudaEventCreate(&end), "cudaEventCreate");
+        const uint32_t num_ctas = static_cast<uint32_t>(ctx->sm_count) * 8;
+        float best_ms = 0.0f;
+        cudaError_t err = cudaSuccess;
+        for (uint32_t it = 0; it <= iterations && err == cudaSuccess; ++it) {  // pass 0 warms up
+            err = cudaEventRecord(begin, ctx->stream);
+            if (err == cudaSuccess) err = launch_read_stream(scratch.ptr, bytes, static_cast<uint32_t*>(sink.ptr), num_ctas, ctx->stream);
+            if (err == cudaSuccess) err = cudaEventRecord(end, ctx->stream);
+            if (err == cudaSuccess) err = cudaEventSynchronize(end);
+            float ms = 0.0f;
+            if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, begin, end);
+            if (err == cudaSuccess && it > 0 && (best_ms == 0.0f || ms < best_ms)) best_ms = ms;
+        }
+        (void)cudaEventDestroy(begin);
+        (void)cudaEventDestroy(end);
+        cuda_check(err, "read bandwidth probe");
+        *out_gbs = best_ms > 0.0f ? static_cast<double>(bytes) / (static_cast<double>(best_ms) * 1e6) : 0.0;
+    });
+}
+
 int32_t psi_ctx_stream(psi_ctx* ctx, void** out) {
     if (ctx == nullptr || out == nullptr) return PSI_ERR_INVALID_ARGUMENT;
     *out = ctx->stream;

@@ -148,6 +148,9 @@ cudaError_t launch_attend_mma(const AttendParams& p, uint32_t num_ctas, cudaStre
 bool attend_chunk_supported(uint32_t dtype, uint32_t head_dim, uint32_t tokens_per_page);
 cudaError_t launch_attend_chunk(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
 // The same work items on the tcgen05 tensor cores (accumulators in TMEM); same profiles as launch_attend_chunk.
+// Streams `bytes` of device memory through 16-byte read-only loads (bandwidth probe; writes nothing but one sink word).
+cudaError_t launch_read_stream(const void* src, uint64_t bytes, uint32_t* sink, uint32_t num_ctas, cudaStream_t stream);
+
 cudaError_t launch_attend_chunk_umma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
 cudaError_t launch_attend_reduce(const AttendParams& p, uint32_t num_reduces, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);

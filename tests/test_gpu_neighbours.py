@@ -208,3 +208,13 @@ def test_history_plus_block_composite():
             worst = max(worst, np.abs(got[token, head] - want).max())
     assert worst <= 2e-2, worst
     rig.close()
+
+
+def test_read_bandwidth_probe_reports_a_plausible_figure():
+    """The read-only probe streams a buffer larger than L2 and reports HBM-scale bandwidth; bad sizes are refused."""
+    ctx = pkg.Context(0)
+    gbs = ctx.read_bandwidth(1 << 30, 3)
+    assert 1000.0 < gbs < 12000.0, gbs
+    with pytest.raises(pkg.PsiError):
+        ctx.read_bandwidth(8, 1)
+    ctx.close()
