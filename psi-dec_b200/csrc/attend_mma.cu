@@ -52,7 +52,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     using L = SmemLayout<D, NSLOT>;
     constexpr uint32_t kChunks = D / 8;                      // 16-byte chunks per row
     constexpr uint32_t kRowsPerCopy = 32 / (kChunks < 32 ? kChunks : 32);
-    constexpr int kKSteps = D / 16;
 
     const uint32_t cta = blockIdx.x;
 #ifdef PSI_MMA_TRACE
@@ -274,12 +273,16 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             merge_l[warp][quad_row + 8] = st.l1;
         }
         {
-            float* mine = merge_o + warp * kTile * L::kMergeStride;
+            // Rows 8..15 are padding when the item carries at most eight query rows (decode rows of a GQA group of
+            // eight): the merge below never reads them, so they are not written.
+            float* mine = merge_o + warp * kTile * L::kMergeStride + 2 * quad_col;
 #pragma unroll
-            for (int j = 0; j < D / 8; ++j) {
-                const uint32_t col = 8 * j + 2 * quad_col;
-                *reinterpret_cast<float2*>(mine + quad_row * L::kMergeStride + col) = make_float2(st.o[j][0], st.o[j][1]);
-                *reinterpret_cast<float2*>(mine + (quad_row + 8) * L::kMergeStride + col) = make_float2(st.o[j][2], st.o[j][3]);
+            for (int j = 0; j < D / 8; ++j)
+                *reinterpret_cast<float2*>(mine + quad_row * L::kMergeStride + 8 * j) = make_float2(st.o[j][0], st.o[j][1]);
+            if (v.rows > 8) {
+#pragma unroll
+                for (int j = 0; j < D / 8; ++j)
+                    *reinterpret_cast<float2*>(mine + (quad_row + 8) * L::kMergeStride + 8 * j) = make_float2(st.o[j][2], st.o[j][3]);
             }
         }
         __syncthreads();
