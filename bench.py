@@ -124,7 +124,7 @@ def bench_ours(args):
     # sequences, sequence-sharded, no collective in the step (weak scaling).  Configurations 3 and 5 shard their fixed
     # batch by sequence, configuration 4 splits every sequence's KV range across the ranks and exchanges partials
     # (strong scaling).
-    base = W.config(args.config, scale_down=args.scale_down)
+    base = workload(W, args)
     exchange = None
     scaling, parallelism = "weak", f"sequence-sharded x{world}"
     if world == 1:
@@ -325,7 +325,7 @@ def bench_reference(args):
     from oracle import psi_oracle as O
     from psi_dec_b200 import workloads as W
 
-    base = W.config(args.config, scale_down=args.scale_down)
+    base = workload(W, args)
     order = np.argsort(base.visible, kind="stable")
     budget = 400_000 * max(1, O.num_threads()) // 8  # visible tokens per step: a step of roughly a second
     chosen, total = [], 0
@@ -384,6 +384,18 @@ def bench_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def workload(W, args):
+    """The benchmark configuration, or the custom decode batch --shape describes."""
+    if args.shape is None:
+        return W.config(args.config, scale_down=args.scale_down)
+    if args.gpus != 1:
+        raise SystemExit("--shape runs on one GPU")
+    values = [int(x) for x in args.shape.split(",")]
+    if len(values) not in (7, 8):
+        raise SystemExit("--shape wants HQ,HKV,D,PAGE,BATCH,CTX_LO,CTX_HI[,Q_LEN]")
+    return W.custom(*values)
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -393,6 +405,8 @@ def main():
     parser.add_argument("--config", type=int, default=2, help="benchmark configuration (2 = the headline)")
     parser.add_argument("--scale-down", type=int, default=1,
                         help="divide batch and context sizes (small cases for profiler captures; not a bench value)")
+    parser.add_argument("--shape", default=None, metavar="HQ,HKV,D,PAGE,BATCH,CTX_LO,CTX_HI[,Q_LEN]",
+                        help="one GPU only: a decode batch of another model profile instead of --config")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-read-probe", action="store_true", help="skip the read-only HBM bandwidth probe")
     parser.add_argument("--kernel", choices=["auto", "mma", "generic", "mma_sync"], default="auto",

@@ -175,6 +175,15 @@ def config(index: int, scale_down: int = 1, seed: int | None = None) -> Spec:
     raise ValueError(f"unknown configuration {index}")
 
 
+def custom(num_q_heads: int, num_kv_heads: int, head_dim: int, tokens_per_page: int, batch: int, ctx_lo: int,
+           ctx_hi: int, q_len: int = 1, seed: int = 11) -> Spec:
+    """A decode batch of another model profile: contexts uniform in [ctx_lo, ctx_hi], ``q_len`` tokens per sequence."""
+    rng = np.random.default_rng(seed)
+    ctx = rng.integers(ctx_lo, ctx_hi + 1, size=batch)
+    name = f"custom-hq{num_q_heads}-hkv{num_kv_heads}-d{head_dim}-p{tokens_per_page}-b{batch}-ctx{ctx_lo}-{ctx_hi}-q{q_len}"
+    return Spec(name, B.BF16, num_q_heads, num_kv_heads, head_dim, tokens_per_page, ctx, q_len, seed)
+
+
 class Session:
     """One workload resident on one GPU: arena (random K/V everywhere), block tables, GQA component, q/k/v/out."""
 
