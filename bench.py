@@ -163,6 +163,10 @@ def bench_ours(args):
         With an exchange in the step every rank enters each step together (barrier), as a serving loop would."""
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        # A few sweeps ahead of the first window keep the GPU busy while the host enqueues it: without them the first
+        # window also measures how long the host takes to submit the step after the preceding synchronize.
+        for _ in range(4):
+            flush.sum()
         for i in range(steps):
             flush.sum()
             if exchange:
