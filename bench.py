@@ -204,8 +204,8 @@ def bench_ours(args):
     batch = spec.batch()
 
     def e2e_step():
-        session.gqa.prepare(*batch)
         if exchange:
+            session.gqa.prepare(*batch)
             session.q.copy_(qh, non_blocking=True)
             if spec.do_append:
                 session.k.copy_(kh, non_blocking=True)
@@ -215,7 +215,7 @@ def bench_ours(args):
                 oh.copy_(session.out, non_blocking=True)
             session.stream.synchronize()
         else:
-            session.gqa.decode_step_host(session.pages, session.table, spec.layer, kh, vh, qh, oh)
+            session.gqa.step_host(session.pages, session.table, spec.layer, *batch, kh, vh, qh, oh)
 
     for _ in range(3):
         e2e_step()

@@ -14,7 +14,7 @@
  *     PSI_ERR_INVALID_ARGUMENT, with the message available from psi_ctx_last_error / psi_last_error.
  *   - a psi_ctx is bound to one device and one stream and is used from one host thread at a time (the reference
  *     executor is one thread with one in-flight submission per stream).  Calls enqueue work on the context's stream
- *     and return; only psi_ctx_sync, the *_read / *_export functions and psi_gqa_decode_step_host block.
+ *     and return; only psi_ctx_sync, the *_read / *_export functions, psi_gqa_decode_step_host and psi_gqa_step_host block.
  *   - device data layouts are the reference's, row-major, innermost last:
  *       q, out        dtype [T][Hq][D]
  *       k, v (append) dtype [T][Hkv][D]
@@ -443,6 +443,16 @@ PSI_API int32_t psi_gqa_device_status(psi_gqa* gqa, int32_t* out);
  * buffers the inputs are staged through device copies first. */
 PSI_API int32_t psi_gqa_decode_step_host(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
                                          const void* k_host, const void* v_host, const void* q_host, void* out_host);
+
+/* psi_gqa_prepare (exact capacity) and psi_gqa_decode_step_host in one call, for a host loop that hands over a step's
+ * metadata and buffers together (the executor's update-then-submit pair of
+ * crates/inference-executor-metal/src/attn/gqa/batch_metadata.rs:128-317 and backend.rs:493-612): with pinned buffers
+ * the q/k/v transfer is under way while the step is planned, and the plan reaches the device without a copy-engine
+ * transfer.  Same result as the two calls. */
+PSI_API int32_t psi_gqa_step_host(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
+                                  const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
+                                  uint32_t num_reqs, const void* k_host, const void* v_host, const void* q_host,
+                                  void* out_host);
 
 /* Page gather: tokens [tok_begin, tok_end) of one request slot and layer into contiguous device K and V
  * [n][Hkv][D].  The reference fuses this address walk into its map kernels

@@ -650,6 +650,14 @@ class GQA:
         _check(library().psi_gqa_device_status(self._h, C.byref(out)), self.ctx._h)
         return out.value
 
+    def step_host(self, pages, table, layer, req_slots, token_indices, cu_tokens, k_host, v_host, q_host, out_host):
+        """``prepare`` + ``decode_step_host`` in one call: q/k/v travel while the step is planned."""
+        rs, n = _u32_array(req_slots)
+        ti, _ = _u32_array(token_indices)
+        cu, _ = _u32_array(cu_tokens)
+        _check(library().psi_gqa_step_host(self._h, pages._h, table._h, C.c_uint32(layer), rs, ti, cu, C.c_uint32(n),
+                                           _ptr(k_host), _ptr(v_host), _ptr(q_host), _ptr(out_host)), self.ctx._h)
+
     def decode_step_host(self, pages, table, layer, k_host, v_host, q_host, out_host):
         _check(library().psi_gqa_decode_step_host(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(k_host),
                                                   _ptr(v_host), _ptr(q_host), _ptr(out_host)), self.ctx._h)

@@ -1392,11 +1392,16 @@ int32_t psi_gqa_reserve_replay(psi_gqa* g) {
     });
 }
 
-int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
-                        uint32_t num_reqs, uint32_t capacity_mode, uint32_t caller_num_total_tokens,
-                        psi_replay_shape* out_shape) {
-    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
-    return guarded(g->ctx, [&] {
+}  // extern "C"
+
+namespace {
+
+// GQAMetadataBuffers::update plus this library's plan.  With `defer_upload` the packed block stays in the pinned
+// staging buffer and its size comes back in *deferred_words: the caller brings it to the device itself.
+void prepare_impl(psi_gqa* g, const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
+                  uint32_t num_reqs, uint32_t capacity_mode, uint32_t caller_num_total_tokens,
+                  psi_replay_shape* out_shape, bool defer_upload, uint64_t* deferred_words) {
+    {
         require(req_slots != nullptr && token_indices != nullptr && cu_tokens != nullptr, "metadata inputs must not be null");
         require(capacity_mode <= PSI_CAPACITY_CALLER_TOKENS, "unknown capacity mode");
         require(num_reqs > 0, "GQA batch metadata requires tokens");
@@ -1560,14 +1565,32 @@ int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* t
         std::copy(chunk.cta_item_begin.begin(), chunk.cta_item_begin.end(), s + g->off_chunk_cta);
         if (!chunk.items.empty())
             std::memcpy(s + g->off_chunk_items, chunk.items.data(), chunk.items.size() * sizeof(DeviceItem));
-        cuda_check(cudaMemcpyAsync(g->block.ptr, s, words * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream),
-                   "cudaMemcpyAsync");
-        cuda_check(cudaEventRecord(g->upload_done, ctx->stream), "cudaEventRecord");
+        if (defer_upload) {
+            *deferred_words = words;
+        } else {
+            cuda_check(cudaMemcpyAsync(g->block.ptr, s, words * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream),
+                       "cudaMemcpyAsync");
+            cuda_check(cudaEventRecord(g->upload_done, ctx->stream), "cudaEventRecord");
+        }
 
         g->shape = shape;
         g->variant = variant;
         g->prepared = true;
         if (out_shape != nullptr) *out_shape = shape;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t psi_gqa_prepare(psi_gqa* g, const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
+                        uint32_t num_reqs, uint32_t capacity_mode, uint32_t caller_num_total_tokens,
+                        psi_replay_shape* out_shape) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        prepare_impl(g, req_slots, token_indices, cu_tokens, num_reqs, capacity_mode, caller_num_total_tokens, out_shape,
+                     false, nullptr);
     });
 }
 
@@ -1946,6 +1969,103 @@ int32_t psi_gqa_decode_step_host(psi_gqa* g, psi_pages* pages, psi_table* table,
         }
         run_attend(g, p);
         cuda_check(cudaMemcpyAsync(out_host, g->step_out.ptr, q_bytes, cudaMemcpyDeviceToHost, ctx->stream), "D2H out");
+        cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    });
+}
+
+int32_t psi_gqa_step_host(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const uint32_t* req_slots,
+                          const uint32_t* token_indices, const uint32_t* cu_tokens, uint32_t num_reqs, const void* k_host,
+                          const void* v_host, const void* q_host, void* out_host) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(k_host != nullptr && v_host != nullptr && q_host != nullptr && out_host != nullptr,
+                "host buffers must not be null");
+        require(req_slots != nullptr && token_indices != nullptr && cu_tokens != nullptr, "metadata inputs must not be null");
+        require(num_reqs > 0, "GQA batch metadata requires tokens");
+        psi_ctx* ctx = g->ctx;
+        require(!ctx->capturing, "psi_gqa_step_host waits for its result and stays outside captured graphs");
+        ctx->bind();
+        const uint32_t num_tokens = cu_tokens[num_reqs];
+        require(num_tokens > 0, "GQA batch metadata requires tokens");
+        require(num_tokens <= g->cfg.max_tokens, "GQA batch exceeds the metadata token capacity");
+        const uint64_t esz = dtype_bytes(g->cfg.dtype);
+        const uint64_t kv_cap = uint64_t(g->cfg.max_tokens) * g->cfg.num_kv_heads * g->cfg.head_dim * esz;
+        const uint64_t q_cap = uint64_t(g->cfg.max_tokens) * g->cfg.num_q_heads * g->cfg.head_dim * esz;
+        const uint64_t kv_bytes = uint64_t(num_tokens) * g->cfg.num_kv_heads * g->cfg.head_dim * esz;
+        const uint64_t q_bytes = uint64_t(num_tokens) * g->cfg.num_q_heads * g->cfg.head_dim * esz;
+        g->step_k.ensure(ctx, kv_cap, false);
+        g->step_v.ensure(ctx, kv_cap, false);
+        g->step_q.ensure(ctx, q_cap, false);
+        auto mapped = [](const void* host) -> void* {
+            cudaPointerAttributes attr{};
+            if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+                attr.devicePointer != nullptr && (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15u) == 0) {
+                return attr.devicePointer;
+            }
+            (void)cudaGetLastError();
+            return nullptr;
+        };
+        void *dk = nullptr, *dv = nullptr, *dq = nullptr, *dout = nullptr;
+        bool in_place = g->kernel == PSI_KERNEL_MMA && kv_bytes % 16 == 0 && q_bytes % 16 == 0;
+        if (in_place) {
+            dk = mapped(k_host);
+            dv = mapped(v_host);
+            dq = mapped(q_host);
+            dout = mapped(out_host);
+            in_place = dk != nullptr && dv != nullptr && dq != nullptr && dout != nullptr;
+        }
+        if (!in_place) {  // pageable buffers or the generic kernel: the two calls this one stands for
+            prepare_impl(g, req_slots, token_indices, cu_tokens, num_reqs, PSI_CAPACITY_EXACT, 0, nullptr, false, nullptr);
+            g->step_out.ensure(ctx, q_cap, false);
+            cuda_check(cudaMemcpyAsync(g->step_k.ptr, k_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D k");
+            cuda_check(cudaMemcpyAsync(g->step_v.ptr, v_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D v");
+            cuda_check(cudaMemcpyAsync(g->step_q.ptr, q_host, q_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D q");
+            AttendParams p = attend_params(g, pages, table, layer, g->step_q.ptr);
+            p.out = g->step_out.ptr;
+            if (g->kernel == PSI_KERNEL_MMA) {
+                p.new_k = g->step_k.ptr;
+                p.new_v = g->step_v.ptr;
+            } else {
+                run_append(g, pages, table, layer, g->step_k.ptr, g->step_v.ptr);
+            }
+            run_attend(g, p);
+            cuda_check(cudaMemcpyAsync(out_host, g->step_out.ptr, q_bytes, cudaMemcpyDeviceToHost, ctx->stream), "D2H out");
+            cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+            return;
+        }
+        // q/k/v start their way over the host link before the step is planned: the pull runs while the host builds
+        // the plan.  The packed plan then follows through a second small pull from its pinned staging buffer instead
+        // of a copy-engine transfer, and the attention launch stores `out` straight into the host buffer.
+        {
+            const void* const src[3] = {dq, dk, dv};
+            void* const dst[3] = {g->step_q.ptr, g->step_k.ptr, g->step_v.ptr};
+            const uint64_t bytes[3] = {q_bytes, kv_bytes, kv_bytes};
+            ctx->launches += 1;
+            cuda_check(launch_host_pull(src, dst, bytes, ctx->stream), "host pull launch");
+        }
+        uint64_t words = 0;
+        prepare_impl(g, req_slots, token_indices, cu_tokens, num_reqs, PSI_CAPACITY_EXACT, 0, nullptr, true, &words);
+        const uint64_t padded_words = (words + 3) / 4 * 4;
+        void* staging_dev = nullptr;
+        if (padded_words <= g->staging_words &&
+            cudaHostGetDevicePointer(&staging_dev, g->staging, 0) == cudaSuccess && staging_dev != nullptr &&
+            (reinterpret_cast<uintptr_t>(staging_dev) & 15u) == 0) {
+            const void* const src[3] = {staging_dev, nullptr, nullptr};
+            void* const dst[3] = {g->block.ptr, nullptr, nullptr};
+            const uint64_t bytes[3] = {padded_words * sizeof(uint32_t), 0, 0};
+            ctx->launches += 1;
+            cuda_check(launch_host_pull(src, dst, bytes, ctx->stream), "plan pull launch");
+        } else {
+            (void)cudaGetLastError();
+            cuda_check(cudaMemcpyAsync(g->block.ptr, g->staging, words * sizeof(uint32_t), cudaMemcpyHostToDevice,
+                                       ctx->stream), "cudaMemcpyAsync");
+        }
+        cuda_check(cudaEventRecord(g->upload_done, ctx->stream), "cudaEventRecord");
+        AttendParams p = attend_params(g, pages, table, layer, g->step_q.ptr);
+        p.out = dout;
+        p.new_k = g->step_k.ptr;
+        p.new_v = g->step_v.ptr;
+        run_attend(g, p);
         cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
     });
 }

@@ -618,6 +618,38 @@ def test_decode_step_through_host_buffers(pinned):
     s.close()
 
 
+@pytest.mark.parametrize("pinned", [True, False])
+def test_one_call_host_step_equals_prepare_plus_host_step(pinned):
+    # psi_gqa_step_host plans the step while q/k/v travel; same arena and same output bits as the two separate calls,
+    # also on the second call of the same component (the plan's staging buffer is reused)
+    import torch
+    spec = W.config(2, scale_down=8)
+    a, b = W.Session(spec), W.Session(spec)
+    pin = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
+    kh, vh, qh = pin(a.k.cpu()), pin(a.v.cpu()), pin(a.q.cpu())
+    two, one = pin(torch.zeros_like(qh)), pin(torch.zeros_like(qh))
+    batch = spec.batch()
+    for repeat in range(2):
+        slots, starts, cu = batch
+        qh.mul_(-0.5)   # another query each time: the outputs differ between the repeats
+        before = checks.to_numpy_bits(a.arena) if repeat == 0 else None
+        a.gqa.prepare(slots, starts, cu)
+        a.gqa.decode_step_host(a.pages, a.table, 0, kh, vh, qh, two)
+        b.gqa.step_host(b.pages, b.table, 0, slots, starts, cu, kh, vh, qh, one)
+        assert torch.equal(one.view(torch.int16), two.view(torch.int16))
+        assert torch.equal(a.arena.view(torch.int16), b.arena.view(torch.int16))
+        if before is not None:
+            assert not np.array_equal(checks.to_numpy_bits(a.arena), before)   # the step did append
+    a.close()
+    b.close()
+    with pytest.raises(pkg.PsiError):
+        c = W.Session(spec)
+        try:
+            c.gqa.step_host(c.pages, c.table, 0, batch[0], batch[1], batch[2], None, vh, qh, one)
+        finally:
+            c.close()
+
+
 def test_layer_index_selects_the_table_row():
     # two layers share one arena; each layer's rows map the same logical pages to different physical pages
     import torch
