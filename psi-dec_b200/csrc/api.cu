@@ -386,6 +386,39 @@ void run_append(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, 
     cuda_check(launch_kv_append(p, g->ctx->stream), "kv append launch");
 }
 
+// Device-side address of a pinned, device-mapped host buffer (16-byte aligned), or nullptr for any other memory.
+void* mapped_device_pointer(const void* host) {
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+        attr.devicePointer != nullptr && (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15u) == 0) {
+        return attr.devicePointer;
+    }
+    (void)cudaGetLastError();
+    return nullptr;
+}
+
+// A prepared step through pageable host buffers: inputs staged by copy-engine transfers, output copied back, waited for.
+void run_staged_host_step(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* k_host,
+                          const void* v_host, const void* q_host, void* out_host, uint64_t kv_bytes, uint64_t q_bytes,
+                          uint64_t q_cap) {
+    psi_ctx* ctx = g->ctx;
+    g->step_out.ensure(ctx, q_cap, false);
+    cuda_check(cudaMemcpyAsync(g->step_k.ptr, k_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D k");
+    cuda_check(cudaMemcpyAsync(g->step_v.ptr, v_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D v");
+    cuda_check(cudaMemcpyAsync(g->step_q.ptr, q_host, q_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D q");
+    AttendParams p = attend_params(g, pages, table, layer, g->step_q.ptr);
+    p.out = g->step_out.ptr;
+    if (g->kernel == PSI_KERNEL_MMA) {
+        p.new_k = g->step_k.ptr;
+        p.new_v = g->step_v.ptr;
+    } else {
+        run_append(g, pages, table, layer, g->step_k.ptr, g->step_v.ptr);
+    }
+    run_attend(g, p);
+    cuda_check(cudaMemcpyAsync(out_host, g->step_out.ptr, q_bytes, cudaMemcpyDeviceToHost, ctx->stream), "D2H out");
+    cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -1926,20 +1959,11 @@ int32_t psi_gqa_decode_step_host(psi_gqa* g, psi_pages* pages, psi_table* table,
         // Pinned, device-mapped host buffers: one launch pulls q/k/v over the host link into device staging (every
         // work item re-reads its query rows, so they should be read from HBM, not from the host), and the attention
         // launch stores `out` straight into the host buffer.  Two launches and one wait, no copy engine round trips.
-        auto mapped = [](const void* host) -> void* {
-            cudaPointerAttributes attr{};
-            if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
-                attr.devicePointer != nullptr && (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15u) == 0) {
-                return attr.devicePointer;
-            }
-            (void)cudaGetLastError();
-            return nullptr;
-        };
         if (g->kernel == PSI_KERNEL_MMA && kv_bytes % 16 == 0 && q_bytes % 16 == 0) {
-            void* dk = mapped(k_host);
-            void* dv = mapped(v_host);
-            void* dq = mapped(q_host);
-            void* dout = mapped(out_host);
+            void* dk = mapped_device_pointer(k_host);
+            void* dv = mapped_device_pointer(v_host);
+            void* dq = mapped_device_pointer(q_host);
+            void* dout = mapped_device_pointer(out_host);
             if (dk != nullptr && dv != nullptr && dq != nullptr && dout != nullptr) {
                 const void* const src[3] = {dq, dk, dv};
                 void* const dst[3] = {g->step_q.ptr, g->step_k.ptr, g->step_v.ptr};
@@ -1955,21 +1979,7 @@ int32_t psi_gqa_decode_step_host(psi_gqa* g, psi_pages* pages, psi_table* table,
                 return;
             }
         }
-        g->step_out.ensure(ctx, q_cap, false);
-        cuda_check(cudaMemcpyAsync(g->step_k.ptr, k_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D k");
-        cuda_check(cudaMemcpyAsync(g->step_v.ptr, v_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D v");
-        cuda_check(cudaMemcpyAsync(g->step_q.ptr, q_host, q_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D q");
-        AttendParams p = attend_params(g, pages, table, layer, g->step_q.ptr);
-        p.out = g->step_out.ptr;
-        if (g->kernel == PSI_KERNEL_MMA) {
-            p.new_k = g->step_k.ptr;
-            p.new_v = g->step_v.ptr;
-        } else {
-            run_append(g, pages, table, layer, g->step_k.ptr, g->step_v.ptr);
-        }
-        run_attend(g, p);
-        cuda_check(cudaMemcpyAsync(out_host, g->step_out.ptr, q_bytes, cudaMemcpyDeviceToHost, ctx->stream), "D2H out");
-        cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+        run_staged_host_step(g, pages, table, layer, k_host, v_host, q_host, out_host, kv_bytes, q_bytes, q_cap);
     });
 }
 
@@ -1996,41 +2006,18 @@ int32_t psi_gqa_step_host(psi_gqa* g, psi_pages* pages, psi_table* table, uint32
         g->step_k.ensure(ctx, kv_cap, false);
         g->step_v.ensure(ctx, kv_cap, false);
         g->step_q.ensure(ctx, q_cap, false);
-        auto mapped = [](const void* host) -> void* {
-            cudaPointerAttributes attr{};
-            if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
-                attr.devicePointer != nullptr && (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15u) == 0) {
-                return attr.devicePointer;
-            }
-            (void)cudaGetLastError();
-            return nullptr;
-        };
         void *dk = nullptr, *dv = nullptr, *dq = nullptr, *dout = nullptr;
         bool in_place = g->kernel == PSI_KERNEL_MMA && kv_bytes % 16 == 0 && q_bytes % 16 == 0;
         if (in_place) {
-            dk = mapped(k_host);
-            dv = mapped(v_host);
-            dq = mapped(q_host);
-            dout = mapped(out_host);
+            dk = mapped_device_pointer(k_host);
+            dv = mapped_device_pointer(v_host);
+            dq = mapped_device_pointer(q_host);
+            dout = mapped_device_pointer(out_host);
             in_place = dk != nullptr && dv != nullptr && dq != nullptr && dout != nullptr;
         }
         if (!in_place) {  // pageable buffers or the generic kernel: the two calls this one stands for
             prepare_impl(g, req_slots, token_indices, cu_tokens, num_reqs, PSI_CAPACITY_EXACT, 0, nullptr, false, nullptr);
-            g->step_out.ensure(ctx, q_cap, false);
-            cuda_check(cudaMemcpyAsync(g->step_k.ptr, k_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D k");
-            cuda_check(cudaMemcpyAsync(g->step_v.ptr, v_host, kv_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D v");
-            cuda_check(cudaMemcpyAsync(g->step_q.ptr, q_host, q_bytes, cudaMemcpyHostToDevice, ctx->stream), "H2D q");
-            AttendParams p = attend_params(g, pages, table, layer, g->step_q.ptr);
-            p.out = g->step_out.ptr;
-            if (g->kernel == PSI_KERNEL_MMA) {
-                p.new_k = g->step_k.ptr;
-                p.new_v = g->step_v.ptr;
-            } else {
-                run_append(g, pages, table, layer, g->step_k.ptr, g->step_v.ptr);
-            }
-            run_attend(g, p);
-            cuda_check(cudaMemcpyAsync(out_host, g->step_out.ptr, q_bytes, cudaMemcpyDeviceToHost, ctx->stream), "D2H out");
-            cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+            run_staged_host_step(g, pages, table, layer, k_host, v_host, q_host, out_host, kv_bytes, q_bytes, q_cap);
             return;
         }
         // q/k/v start their way over the host link before the step is planned: the pull runs while the host builds
