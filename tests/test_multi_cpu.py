@@ -23,6 +23,24 @@ def test_sequence_sharding_partitions_the_batch():
         assert max(loads) <= 1.15 * (sum(loads) / world)
 
 
+def test_custom_decode_batch_and_its_bench_argument():
+    # bench.py --shape HQ,HKV,D,PAGE,BATCH,CTX_LO,CTX_HI[,Q_LEN] builds a seeded decode batch of another model profile
+    import argparse
+    import bench
+    spec = W.custom(32, 8, 128, 8, 12, 100, 900, 2)
+    assert (spec.num_q_heads, spec.num_kv_heads, spec.head_dim, spec.tokens_per_page, spec.num_seqs) == (32, 8, 128, 8, 12)
+    assert spec.context_lens.min() >= 100 and spec.context_lens.max() <= 900 and np.all(spec.q_len == 2)
+    assert np.array_equal(spec.context_lens, W.custom(32, 8, 128, 8, 12, 100, 900, 2).context_lens)   # seeded
+    assert len(spec.block_tables) == 12 and all(len(t) == -(-(c + 2) // 8) for t, c in zip(spec.block_tables, spec.context_lens))
+    args = argparse.Namespace(shape="32,8,128,8,12,100,900,2", gpus=1, config=2, scale_down=1)
+    assert bench.workload(W, args).name == spec.name
+    assert bench.workload(W, argparse.Namespace(shape=None, gpus=1, config=2, scale_down=1)).name == W.config(2).name
+    with pytest.raises(SystemExit):
+        bench.workload(W, argparse.Namespace(shape="1,2,3", gpus=1, config=2, scale_down=1))
+    with pytest.raises(SystemExit):
+        bench.workload(W, argparse.Namespace(shape="32,8,128,8,12,100,900", gpus=2, config=2, scale_down=1))
+
+
 def test_kv_range_sharding_covers_each_context_once():
     whole = W.config(4, scale_down=16)
     for world in (2, 4, 8):
