@@ -393,6 +393,17 @@ PSI_API int32_t psi_gqa_set_norm_rope(psi_gqa* gqa, const psi_norm_rope_config* 
  * are copied into theirs.  q_in/q_out [T][Hq][D], k_in/v_in [T][Hkv][D], device, positions = the prepared batch. */
 PSI_API int32_t psi_gqa_norm_rope_append(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
                                          const void* q_in, const void* k_in, const void* v_in, void* q_out);
+/* psi_gqa_norm_rope_append reading q, k and v (and the gates) where the fused projection left them, which also
+ * removes the de-interleave stage GQA::record puts in front of them (backend.rs:449-464; GQAQGKVSplitKernel,
+ * crates/inference-backend-metal/src/components/gqa_qgkv_split.rs:152-200 with metal/gqa_qgkv_split.metal:14-42, and
+ * the ungated GQAQKVSplitKernel of ungated_backend.rs:218-227, gqa_qkv_split.rs with metal/gqa_qkv_split.metal:13-36).  projection: device
+ * [T][width] in the I/O dtype; gated = 1: width = 2*Hq*D + 2*Hkv*D, per token Hq pairs (q[D] | gate[D]), then Hkv k
+ * rows, then Hkv v rows; gated = 0: width = Hq*D + 2*Hkv*D, q rows, k rows, v rows.  q_out [T][Hq][D] receives the
+ * normalised, rotated queries; gates_out [T][Hq][D] (gated only, else may be NULL) a bit copy of the gate rows, ready
+ * for psi_gqa_attend_gated.  T * width beyond the u32 range is refused with the reference's message. */
+PSI_API int32_t psi_gqa_projection_norm_rope_append(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
+                                                    const void* projection, uint32_t gated, void* q_out,
+                                                    void* gates_out);
 /* psi_gqa_attend with the stage the reference records after it fused into the epilogue: out = attention *
  * sigmoid(gates) (backend.rs:613-624, metal/gqa_activation_gate.metal).  gates: device [T][Hq][D] in the I/O dtype. */
 PSI_API int32_t psi_gqa_attend_gated(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer, const void* q,

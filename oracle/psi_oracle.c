@@ -992,6 +992,42 @@ PSI_ORACLE_API void psi_oracle_rms_norm_rope(const void* input, int dtype, const
     }
 }
 
+/* De-interleave of the fused projection output, one element at a time as the shaders do.  gated != 0:
+ * per token Hq pairs (q[D] | g[D]), then Hkv k rows, then Hkv v rows
+ * (crates/inference-backend-metal/src/components/metal/gqa_qgkv_split.metal:14-42); gated == 0: q rows, k rows, v rows
+ * and no g (metal/gqa_qkv_split.metal:13-36).  Elements are moved as bits (elem_bytes = 2 or 4). */
+PSI_ORACLE_API void psi_oracle_projection_split(const void* projection, uint32_t elem_bytes, uint32_t gated,
+                                                uint32_t num_tokens, uint32_t num_q_heads, uint32_t num_kv_heads,
+                                                uint32_t head_dim, void* q, void* g, void* k, void* v) {
+    const size_t q_slots = (size_t)num_q_heads * head_dim, kv_slots = (size_t)num_kv_heads * head_dim;
+    const size_t token_width = (gated ? 2 : 1) * q_slots + 2 * kv_slots;
+    const unsigned char* src = (const unsigned char*)projection;
+    for (size_t gid = 0; gid < (size_t)num_tokens * token_width; ++gid) {
+        const size_t token = gid / token_width;
+        size_t slot = gid - token * token_width;
+        unsigned char* dst;
+        size_t index;
+        if (gated && slot < 2 * q_slots) {
+            const size_t pair = slot / (2 * (size_t)head_dim), in_pair = slot - pair * 2 * head_dim;
+            index = (token * num_q_heads + pair) * head_dim + in_pair % head_dim;
+            dst = (unsigned char*)(in_pair < head_dim ? q : g);
+        } else if (!gated && slot < q_slots) {
+            index = token * q_slots + slot;
+            dst = (unsigned char*)q;
+        } else {
+            slot -= (gated ? 2 : 1) * q_slots;
+            if (slot < kv_slots) {
+                index = token * kv_slots + slot;
+                dst = (unsigned char*)k;
+            } else {
+                index = token * kv_slots + (slot - kv_slots);
+                dst = (unsigned char*)v;
+            }
+        }
+        memcpy(dst + index * elem_bytes, src + gid * elem_bytes, elem_bytes);
+    }
+}
+
 /* out = attention_output * sigmoid(gate) with the shader's per-dtype arithmetic: f32 throughout, or every step
  * rounded to bf16.  crates/inference-backend-metal/src/components/metal/gqa_activation_gate.metal:5-39 */
 PSI_ORACLE_API void psi_oracle_activation_gate(const void* attention_output, const void* gates, int dtype, size_t n,

@@ -330,6 +330,19 @@ def rms_norm_rope(values_bits, dtype, norm_weight_bf16, positions, num_heads, he
     return out
 
 
+def projection_split(projection_bits, dtype, gated, num_tokens, num_q_heads, num_kv_heads, head_dim):
+    """De-interleave a fused projection output [T][width] into (q, g, k, v); g is None for the ungated layout."""
+    x = np.ascontiguousarray(projection_bits, dtype=np_dtype(dtype)).reshape(-1)
+    q = np.zeros((num_tokens, num_q_heads, head_dim), dtype=x.dtype)
+    g = np.zeros_like(q)
+    k = np.zeros((num_tokens, num_kv_heads, head_dim), dtype=x.dtype)
+    v = np.zeros_like(k)
+    lib().psi_oracle_projection_split(_p(x), C.c_uint32(x.dtype.itemsize), C.c_uint32(1 if gated else 0),
+                                      C.c_uint32(num_tokens), C.c_uint32(num_q_heads), C.c_uint32(num_kv_heads),
+                                      C.c_uint32(head_dim), _p(q), _p(g), _p(k), _p(v))
+    return q, (g if gated else None), k, v
+
+
 def activation_gate(attention_bits, gate_bits, dtype):
     a = np.ascontiguousarray(attention_bits, dtype=np_dtype(dtype))
     g = np.ascontiguousarray(gate_bits, dtype=np_dtype(dtype))

@@ -604,6 +604,13 @@ class GQA:
         _check(library().psi_gqa_norm_rope_append(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(q_in),
                                                   _ptr(k_in), _ptr(v_in), _ptr(q_out)), self.ctx._h)
 
+    def projection_norm_rope_append(self, pages, table, layer, projection, gated, q_out, gates_out=None):
+        """``norm_rope_append`` reading q, k, v (and the gates) in place from the fused projection output ``[T][width]``
+        (GQAQGKVSplitKernel / GQAQKVSplitKernel layouts); ``gates_out`` receives the gate rows when ``gated``."""
+        _check(library().psi_gqa_projection_norm_rope_append(
+            self._h, pages._h, table._h, C.c_uint32(layer), _ptr(projection), C.c_uint32(1 if gated else 0),
+            _ptr(q_out), _ptr(gates_out)), self.ctx._h)
+
     def attend_gated(self, pages, table, layer, q, gates, out):
         """Attention with ``out = attention * sigmoid(gates)`` fused into the epilogue."""
         _check(library().psi_gqa_attend_gated(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(q), _ptr(gates),

@@ -1767,6 +1767,31 @@ int32_t psi_gqa_set_norm_rope(psi_gqa* g, const psi_norm_rope_config* config, co
     });
 }
 
+namespace {
+
+// Fills everything of the front-stage launch that does not depend on where q, k, v and the gates come from.
+PrepParams norm_rope_params(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer) {
+    PrepParams p{};
+    p.geo = page_geometry(g, pages, table, layer);
+    const uint64_t weight_bytes = (uint64_t(g->cfg.head_dim) * 2 + 15) / 16 * 16;
+    const auto* base = static_cast<const unsigned char*>(g->norm_rope.ptr);
+    p.q_weight = base;
+    p.k_weight = base + weight_bytes;
+    p.inverse_frequencies = reinterpret_cast<const float*>(base + 2 * weight_bytes);
+    p.attention_factor = g->norm_rope_attention_factor;
+    p.eps = g->norm_rope_cfg.eps;
+    p.rope_dim = g->norm_rope_cfg.rope_dim;
+    p.num_q_heads = g->cfg.num_q_heads;
+    p.dtype = g->cfg.dtype;
+    p.req_slots = block_words(g, g->off_req_slots);
+    p.flat_token_indices = block_words(g, g->off_token_indices);
+    p.scalars = block_words(g, 0);
+    p.num_total_tokens = g->shape.num_total_tokens;
+    return p;
+}
+
+}  // namespace
+
 int32_t psi_gqa_norm_rope_append(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* q_in,
                                  const void* k_in, const void* v_in, void* q_out) {
     if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
@@ -1775,28 +1800,52 @@ int32_t psi_gqa_norm_rope_append(psi_gqa* g, psi_pages* pages, psi_table* table,
         require(g->has_norm_rope, "psi_gqa_set_norm_rope must be called before psi_gqa_norm_rope_append");
         require(q_in != nullptr && k_in != nullptr && v_in != nullptr && q_out != nullptr, "buffers must not be null");
         g->ctx->bind();
-        PrepParams p{};
-        p.geo = page_geometry(g, pages, table, layer);
+        PrepParams p = norm_rope_params(g, pages, table, layer);
         p.q_in = q_in;
         p.k_in = k_in;
         p.v_in = v_in;
         p.q_out = q_out;
-        const uint64_t weight_bytes = (uint64_t(g->cfg.head_dim) * 2 + 15) / 16 * 16;
-        const auto* base = static_cast<const unsigned char*>(g->norm_rope.ptr);
-        p.q_weight = base;
-        p.k_weight = base + weight_bytes;
-        p.inverse_frequencies = reinterpret_cast<const float*>(base + 2 * weight_bytes);
-        p.attention_factor = g->norm_rope_attention_factor;
-        p.eps = g->norm_rope_cfg.eps;
-        p.rope_dim = g->norm_rope_cfg.rope_dim;
-        p.num_q_heads = g->cfg.num_q_heads;
-        p.dtype = g->cfg.dtype;
-        p.req_slots = block_words(g, g->off_req_slots);
-        p.flat_token_indices = block_words(g, g->off_token_indices);
-        p.scalars = block_words(g, 0);
-        p.num_total_tokens = g->shape.num_total_tokens;
+        p.q_head_stride = g->cfg.head_dim;
+        p.q_token_stride = uint64_t(g->cfg.num_q_heads) * g->cfg.head_dim;
+        p.kv_token_stride = uint64_t(g->cfg.num_kv_heads) * g->cfg.head_dim;
         LaunchScope scope(g->ctx, PSI_KERNEL_CLASS_NORM_ROPE_APPEND);
         cuda_check(launch_norm_rope_append(p, g->ctx->stream), "norm/rope/append launch");
+    });
+}
+
+int32_t psi_gqa_projection_norm_rope_append(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer,
+                                            const void* projection, uint32_t gated, void* q_out, void* gates_out) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(g->prepared, "GQA batch metadata must be updated before recording");
+        require(g->has_norm_rope, "psi_gqa_set_norm_rope must be called before psi_gqa_projection_norm_rope_append");
+        require(projection != nullptr && q_out != nullptr, "buffers must not be null");
+        require(gated <= 1, "gated must be 0 or 1");
+        require(gated == 0 || gates_out != nullptr, "a gated projection needs gates_out");
+        const uint64_t d = g->cfg.head_dim, hq = g->cfg.num_q_heads, hkv = g->cfg.num_kv_heads;
+        const uint64_t q_width = (gated ? 2 : 1) * hq * d, width = q_width + 2 * hkv * d;
+        // the reference's split shaders index one projection element per thread with a u32
+        // (crates/inference-backend-metal/src/components/gqa_qgkv_split.rs:121-125, gqa_qkv_split.rs)
+        require(uint64_t(g->shape.num_total_tokens) * width <= 0xFFFFFFFFull,
+                gated ? "GQA projection elements exceeds the shader u32 count domain"
+                      : "ungated GQA projection elements exceeds the shader u32 count domain");
+        g->ctx->bind();
+        PrepParams p = norm_rope_params(g, pages, table, layer);
+        const uint64_t esz = dtype_bytes(g->cfg.dtype);
+        const auto* base = static_cast<const unsigned char*>(projection);
+        p.q_in = base;
+        p.q_head_stride = gated ? 2 * d : d;
+        p.q_token_stride = width;
+        p.kv_token_stride = width;
+        p.k_in = base + q_width * esz;
+        p.v_in = base + (q_width + hkv * d) * esz;
+        p.q_out = q_out;
+        if (gated) {
+            p.g_in = base + d * esz;  // head h of a token: q at h * 2D, its gate at h * 2D + D
+            p.g_out = gates_out;
+        }
+        LaunchScope scope(g->ctx, PSI_KERNEL_CLASS_NORM_ROPE_APPEND);
+        cuda_check(launch_norm_rope_append(p, g->ctx->stream), "projection split/norm/rope/append launch");
     });
 }
 

@@ -60,6 +60,14 @@ struct PrepParams {
     const uint32_t* flat_token_indices;
     const uint32_t* scalars;
     uint32_t num_total_tokens;
+    // Source strides in elements: row (token, head) of q starts at token * q_token_stride + head * q_head_stride, of
+    // k / v at token * kv_token_stride + head * head_dim.  Contiguous [T][H][D] inputs and the rows of a fused
+    // projection output [T][q|g pairs, k heads, v heads] are both described this way.
+    uint64_t q_token_stride;
+    uint64_t q_head_stride;
+    uint64_t kv_token_stride;
+    const void* g_in;             // gate rows, strided like q_in; nullptr without gates
+    void* g_out;                  // [T][Hq][D] contiguous copy of the gate rows
 };
 
 struct GatherParams {

@@ -5,6 +5,11 @@
 // kv_page_write), shader crates/inference-backend-metal/src/components/metal/rms_norm_rope.metal:7-82 and
 // metal/gqa_kv_page_write.metal:20-52.  One warp per (token, head) row; the rounding order of the shader is kept:
 // T(weight) * T(x * inv_rms) in the storage dtype T, rotation in f32, one final rounding to T.
+//
+// The inputs are addressed through strides, so the same launch also stands for the stage before those three: the
+// de-interleave of the fused projection output (metal/gqa_qgkv_split.metal:14-42 with gates,
+// metal/gqa_qkv_split.metal:13-36 without).  Its q, g, k and v rows are read where the projection left them; only the
+// gate rows, which the attention epilogue wants contiguous, are copied out.
 #include "device_common.cuh"
 
 namespace psi {
@@ -20,14 +25,33 @@ __device__ __forceinline__ float round_to(float v) {
 
 constexpr int kPrepWarps = 8;
 
+// Bit copy of one element (V rows and gate rows pass through unchanged, NaN payloads included).
+__device__ __forceinline__ void copy_element(void* dst, uint64_t dst_index, const void* src, uint64_t src_index,
+                                             uint32_t dtype) {
+    if (dtype == PSI_DTYPE_F32) {
+        static_cast<uint32_t*>(dst)[dst_index] = static_cast<const uint32_t*>(src)[src_index];
+    } else {
+        static_cast<uint16_t*>(dst)[dst_index] = static_cast<const uint16_t*>(src)[src_index];
+    }
+}
+
 template <uint32_t DTYPE>
 __global__ void __launch_bounds__(kPrepWarps * 32) norm_rope_append_kernel(PrepParams p) {
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t num_active = min(p.scalars[kScalarNumActiveTokens], p.num_total_tokens);
     const uint32_t hq = p.num_q_heads, hkv = p.geo.num_kv_heads, D = p.geo.head_dim;
     const uint64_t q_rows = static_cast<uint64_t>(num_active) * hq, kv_rows = static_cast<uint64_t>(num_active) * hkv;
+    const uint64_t g_rows = p.g_in != nullptr ? q_rows : 0;
     const uint64_t row = static_cast<uint64_t>(blockIdx.x) * kPrepWarps + (threadIdx.x >> 5);
-    if (row >= q_rows + 2 * kv_rows) return;
+    if (row >= q_rows + 2 * kv_rows + g_rows) return;
+
+    if (row >= q_rows + 2 * kv_rows) {
+        // gate row: a bit copy out of the projection into the contiguous [T][Hq][D] the attention epilogue reads
+        const uint64_t local = row - q_rows - 2 * kv_rows;
+        const uint64_t src_base = (local / hq) * p.q_token_stride + (local % hq) * p.q_head_stride;
+        for (uint32_t d = lane; d < D; d += 32) copy_element(p.g_out, local * D + d, p.g_in, src_base + d, DTYPE);
+        return;
+    }
 
     // which tensor, which (token, head)
     const bool is_q = row < q_rows, is_v = row >= q_rows + kv_rows;
@@ -35,11 +59,12 @@ __global__ void __launch_bounds__(kPrepWarps * 32) norm_rope_append_kernel(PrepP
     const uint32_t heads = is_q ? hq : hkv;
     const uint32_t token = static_cast<uint32_t>(local / heads), head = static_cast<uint32_t>(local % heads);
     const void* src = is_q ? p.q_in : (is_v ? p.v_in : p.k_in);
-    const uint64_t src_base = local * D;
+    const uint64_t src_base = is_q ? token * p.q_token_stride + head * p.q_head_stride
+                                   : token * p.kv_token_stride + static_cast<uint64_t>(head) * D;
 
     // destination: q_out row, or the row's place in its page
     void* dst = p.q_out;
-    uint64_t dst_base = src_base;
+    uint64_t dst_base = local * D;
     if (!is_q) {
         const uint32_t pos = p.flat_token_indices[token];
         const uint32_t page_index = pos / p.geo.tokens_per_page;
@@ -49,7 +74,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) norm_rope_append_kernel(PrepP
         dst_base = kv_row_offset(p.geo, page_id, head, pos % p.geo.tokens_per_page) + (is_v ? v_region_offset(p.geo) : 0);
     }
     if (is_v) {
-        for (uint32_t d = lane; d < D; d += 32) store_from_float(dst, dst_base + d, DTYPE, load_as_float(src, src_base + d, DTYPE));
+        for (uint32_t d = lane; d < D; d += 32) copy_element(dst, dst_base + d, src, src_base + d, DTYPE);
         return;
     }
 
@@ -84,7 +109,8 @@ __global__ void __launch_bounds__(kPrepWarps * 32) norm_rope_append_kernel(PrepP
 }  // namespace
 
 cudaError_t launch_norm_rope_append(const PrepParams& p, cudaStream_t stream) {
-    const uint64_t rows = static_cast<uint64_t>(p.num_total_tokens) * (p.num_q_heads + 2ull * p.geo.num_kv_heads);
+    const uint64_t rows = static_cast<uint64_t>(p.num_total_tokens) *
+                          ((p.g_in != nullptr ? 2ull : 1ull) * p.num_q_heads + 2ull * p.geo.num_kv_heads);
     if (rows == 0) return cudaSuccess;
     const unsigned blocks = static_cast<unsigned>((rows + kPrepWarps - 1) / kPrepWarps);
     switch (p.dtype) {

@@ -100,6 +100,67 @@ def test_fused_norm_rope_append_then_attention_matches_the_staged_oracle(dtype, 
     s.close()
 
 
+@pytest.mark.parametrize("dtype,head_dim,gated", [(pkg.BF16, 256, True), (pkg.BF16, 128, False), (pkg.F16, 128, True),
+                                                  (pkg.F32, 64, True)])
+def test_projection_layout_front_stage_equals_split_then_norm_rope_append(dtype, head_dim, gated):
+    # The de-interleave of the fused projection (GQAQGKVSplitKernel / GQAQKVSplitKernel) folded into the front-stage
+    # launch: reading q, k, v in place from [T][width] must give exactly what the split followed by
+    # psi_gqa_norm_rope_append gives - same kernel arithmetic, only the source addresses differ - and the gate rows
+    # must come out as a bit copy.  The split itself is the oracle's, pinned to the reference's vector.
+    import torch
+    rng = np.random.default_rng(head_dim + int(gated))
+    spec = W.Spec("projection", dtype, 8, 2, head_dim, 16, [300, 41, 0, 1000], [3, 1, 20, 2], seed=23)
+    a, b = W.Session(spec), W.Session(spec)
+    wq = O.encode(1.0 + 0.1 * rng.standard_normal(head_dim).astype(np.float32), O.BF16)
+    wk = O.encode(1.0 + 0.1 * rng.standard_normal(head_dim).astype(np.float32), O.BF16)
+    cfg = pkg.NormRopeConfig(64 if head_dim > 64 else 32, 1e-6, 1_000_000.0, 0, 1, 1, 1, 1, 1, 0)
+    t, hq, hkv = spec.num_tokens, spec.num_q_heads, spec.num_kv_heads
+    width = (2 if gated else 1) * hq * head_dim + 2 * hkv * head_dim
+    projection = torch.randn((t, width), device=a.device).to(a.tdtype)
+    q_bits, g_bits, k_bits, v_bits = O.projection_split(checks.to_numpy_bits(projection), dtype, gated, t, hq, hkv,
+                                                        head_dim)
+    as_device = lambda bits, like: torch.from_numpy(bits.view(np.int16) if dtype != pkg.F32 else bits).to(a.device) \
+        .view(like.dtype).reshape(like.shape)
+    # staged: split on the host, then the contiguous front stage
+    a.gqa.set_norm_rope(cfg, wq.tolist(), wk.tolist())
+    q_a = torch.zeros_like(a.q)
+    a.gqa.norm_rope_append(a.pages, a.table, 0, as_device(q_bits, a.q), as_device(k_bits, a.k), as_device(v_bits, a.v),
+                           q_a)
+    a.ctx.sync()
+    # fused: the projection as it is
+    b.gqa.set_norm_rope(cfg, wq.tolist(), wk.tolist())
+    q_b = torch.zeros_like(b.q)
+    gates = torch.full_like(b.q, 7.0) if gated else None
+    b.gqa.projection_norm_rope_append(b.pages, b.table, 0, projection, gated, q_b, gates)
+    b.ctx.sync()
+    assert np.array_equal(checks.to_numpy_bits(q_a), checks.to_numpy_bits(q_b))
+    assert np.array_equal(checks.to_numpy_bits(a.arena), checks.to_numpy_bits(b.arena))
+    if gated:
+        assert np.array_equal(checks.to_numpy_bits(gates).reshape(-1), g_bits.reshape(-1))
+    # the V rows are in their pages bit for bit: gather the appended positions of the longest request
+    seq = int(np.argmax(spec.context_lens))
+    cu = np.concatenate([[0], np.cumsum(spec.q_len)])
+    lo, n = int(spec.context_lens[seq]), int(spec.q_len[seq])
+    kout = torch.zeros((n, hkv, head_dim), dtype=b.tdtype, device=b.device)
+    vout = torch.zeros_like(kout)
+    b.gqa.page_gather(b.pages, b.table, seq, 0, lo, lo + n, kout, vout)
+    b.ctx.sync()
+    assert np.array_equal(checks.to_numpy_bits(vout), v_bits[cu[seq]:cu[seq] + n])
+    # and the attention over those pages with those queries against the oracle
+    b.q.copy_(q_b)
+    b.attend()
+    b.ctx.sync()
+    checks.assert_attention_close(b)
+    if not gated:   # a gated profile without gates_out is refused before any launch
+        b.close()
+        a.close()
+        return
+    with pytest.raises(pkg.PsiError, match="needs gates_out"):
+        b.gqa.projection_norm_rope_append(b.pages, b.table, 0, projection, True, q_b, None)
+    a.close()
+    b.close()
+
+
 @pytest.mark.parametrize("index,scale_down,kernel_mode", [(2, 8, pkg.KERNEL_AUTO), (5, 64, pkg.KERNEL_AUTO),
                                                           (3, 16, pkg.KERNEL_GENERIC)])
 def test_gate_fused_into_the_attention_epilogue(index, scale_down, kernel_mode):

@@ -519,6 +519,34 @@ def test_config3_full_size_sampled_parity_and_gather_round_trip():
     s.close()
 
 
+def test_config4_full_size_sampled_parity_and_idempotence():
+    # Configuration 4 at full size: four sequences of 262,144 context tokens behind randomly permuted block tables
+    # (16,385 table entries each after the append).  One sequence against the CPU oracle, the appended position read
+    # back bit for bit, and a second pass over the same slots leaving pages and outputs unchanged.
+    import torch
+    spec = W.config(4)
+    s = W.Session(spec)
+    assert s.gqa.plan_stats()["kernel"] == pkg.KERNEL_MMA
+    s.step()
+    s.ctx.sync()
+    checks.assert_attention_close(s, [spec.num_seqs - 1])
+    first = s.out.clone()
+    for seq in range(spec.num_seqs):
+        lo = int(spec.context_lens[seq])
+        kout = torch.zeros((1, spec.num_kv_heads, spec.head_dim), dtype=s.tdtype, device=s.device)
+        vout = torch.zeros_like(kout)
+        s.gqa.page_gather(s.pages, s.table, seq, 0, lo, lo + 1, kout, vout)
+        s.ctx.sync()
+        assert torch.equal(kout.view(torch.int16), s.k[seq:seq + 1].view(torch.int16))
+        assert torch.equal(vout.view(torch.int16), s.v[seq:seq + 1].view(torch.int16))
+    arena = s.arena.clone()
+    s.step()
+    s.ctx.sync()
+    assert torch.equal(arena.view(torch.int16), s.arena.view(torch.int16))
+    assert torch.equal(first.view(torch.int16), s.out.view(torch.int16))
+    s.close()
+
+
 def test_config5_full_size_chunk_engines_agree_and_sample_matches_oracle():
     # Configuration 5 at full size (256 sequences, 30 % with a 512-token query run, contexts up to 131,072): the
     # tcgen05 chunk kernel against the CPU oracle on a sample of long-run sequences, and against the independent

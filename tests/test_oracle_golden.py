@@ -311,3 +311,22 @@ def test_oracle_reproduces_the_committed_fixtures():
     for name in stored.files:
         assert stored[name].shape == fresh[name].shape, name
         assert np.abs(stored[name] - fresh[name]).max() <= 1e-6, name
+
+
+def test_projection_split_vectors():
+    # GQAQKVSplitKernel test_fixed (crates/inference-backend-metal/src/components/gqa_qkv_split.rs:212-242):
+    # 2 q heads, 1 KV head, head_dim 2, two tokens of 0..15
+    x = np.arange(16, dtype=np.float32)
+    q, g, k, v = O.projection_split(x, O.F32, False, 2, 2, 1, 2)
+    assert g is None
+    assert q.reshape(-1).tolist() == [0.0, 1.0, 2.0, 3.0, 8.0, 9.0, 10.0, 11.0]
+    assert k.reshape(-1).tolist() == [4.0, 5.0, 12.0, 13.0]
+    assert v.reshape(-1).tolist() == [6.0, 7.0, 14.0, 15.0]
+    # the gated layout (metal/gqa_qgkv_split.metal:14-42): per head a (q | gate) pair, then k, then v; the same
+    # profile widens a token to 2*2*2 + 2*2 = 12 elements
+    x = np.arange(24, dtype=np.uint16)
+    q, g, k, v = O.projection_split(x, O.BF16, True, 2, 2, 1, 2)
+    assert q.reshape(-1).tolist() == [0, 1, 4, 5, 12, 13, 16, 17]
+    assert g.reshape(-1).tolist() == [2, 3, 6, 7, 14, 15, 18, 19]
+    assert k.reshape(-1).tolist() == [8, 9, 20, 21]
+    assert v.reshape(-1).tolist() == [10, 11, 22, 23]
