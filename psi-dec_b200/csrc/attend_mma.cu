@@ -36,10 +36,12 @@ struct SmemLayout {
 };
 
 #ifdef PSI_MMA_TRACE
-// Build-time tracing (-DPSI_MMA_TRACE): per CTA the global-timer stamps (ns) of kernel entry, first K/V tile landed,
-// end of the last tile loop and exit, how many units it merged, and the prologue's stages (metadata read, page ids
-// read, first copies issued, query rows staged); read back with psi_debug_mma_cta.
+// Build-time tracing (-DPSI_MMA_TRACE): per work slot the global-timer stamps (ns) of kernel entry, first K/V tile
+// landed, end of the last tile loop and exit, how many units it merged, the prologue's stages (metadata read, page ids
+// read, first copies issued) and the SM that ran it; read back with psi_debug_mma_cta.  psi_debug_mma_set_rotation
+// shifts the work slots over the CTAs, which separates what follows the slot from what follows the SM.
 __device__ unsigned long long g_mma_cta[148 * 10];
+__device__ unsigned g_mma_rotation;  // work slot of a CTA = (blockIdx.x + rotation) % gridDim.x
 __device__ __forceinline__ unsigned long long trace_now() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -53,11 +55,13 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     constexpr uint32_t kChunks = D / 8;                      // 16-byte chunks per row
     constexpr uint32_t kRowsPerCopy = 32 / (kChunks < 32 ? kChunks : 32);
 
-    const uint32_t cta = blockIdx.x;
 #ifdef PSI_MMA_TRACE
+    const uint32_t cta = (blockIdx.x + g_mma_rotation) % gridDim.x;
     const unsigned long long trace_t0 = trace_now();
     unsigned long long trace_first = 0, trace_loop_end = 0, trace_merged = 0, trace_items = 0;
     unsigned long long trace_meta = 0, trace_ids = 0, trace_issued = 0, trace_staged = 0;
+#else
+    const uint32_t cta = blockIdx.x;
 #endif
     // One round trip for everything the first tile copies depend on: the CTA count, this CTA's item range and a copy
     // of its first item all go out before the first of them is needed.
@@ -416,7 +420,10 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         g_mma_cta[cta * 10 + 6] = trace_meta;
         g_mma_cta[cta * 10 + 7] = trace_ids;
         g_mma_cta[cta * 10 + 8] = trace_issued;
-        g_mma_cta[cta * 10 + 9] = trace_staged;
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_mma_cta[cta * 10 + 9] = smid;
+        (void)trace_staged;
     }
 #endif
 }
@@ -471,6 +478,9 @@ uint32_t attend_mma_ctas_per_sm(uint32_t /*head_dim*/) { return 1; }
 extern "C" __attribute__((visibility("default"))) int psi_debug_mma_cta(unsigned long long* out) {
     if (cudaDeviceSynchronize() != cudaSuccess) return 1;
     return cudaMemcpyFromSymbol(out, g_mma_cta, sizeof(g_mma_cta)) == cudaSuccess ? 0 : 1;
+}
+extern "C" __attribute__((visibility("default"))) int psi_debug_mma_set_rotation(unsigned rotation) {
+    return cudaMemcpyToSymbol(g_mma_rotation, &rotation, sizeof(rotation)) == cudaSuccess ? 0 : 1;
 }
 #endif
 
