@@ -459,7 +459,9 @@ PSI_API int32_t psi_gqa_decode_step_host(psi_gqa* gqa, psi_pages* pages, psi_tab
  * metadata and buffers together (the executor's update-then-submit pair of
  * crates/inference-executor-metal/src/attn/gqa/batch_metadata.rs:128-317 and backend.rs:493-612): with pinned buffers
  * the q/k/v transfer is under way while the step is planned, and the plan reaches the device without a copy-engine
- * transfer.  Same result as the two calls. */
+ * transfer; from 1 MiB of q + k + v on (and no long query runs in the step) the attention launch reads the pinned
+ * buffers in place, so that the transfer runs under the K/V stream instead of in front of it.  Same result as the two
+ * calls. */
 PSI_API int32_t psi_gqa_step_host(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
                                   const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
                                   uint32_t num_reqs, const void* k_host, const void* v_host, const void* q_host,

@@ -646,12 +646,15 @@ def test_decode_step_through_host_buffers(pinned):
     s.close()
 
 
+@pytest.mark.parametrize("index,scale_down", [(2, 8), (3, 2)])
 @pytest.mark.parametrize("pinned", [True, False])
-def test_one_call_host_step_equals_prepare_plus_host_step(pinned):
+def test_one_call_host_step_equals_prepare_plus_host_step(pinned, index, scale_down):
     # psi_gqa_step_host plans the step while q/k/v travel; same arena and same output bits as the two separate calls,
-    # also on the second call of the same component (the plan's staging buffer is reused)
+    # also on the second call of the same component (the plan's staging buffer is reused).  The second workload
+    # (128 verify tokens, 2 MiB of q/k/v) is past the size from which pinned buffers are read in place by the
+    # attention launch instead of being pulled into device staging first.
     import torch
-    spec = W.config(2, scale_down=8)
+    spec = W.config(index, scale_down=scale_down)
     a, b = W.Session(spec), W.Session(spec)
     pin = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
     kh, vh, qh = pin(a.k.cpu()), pin(a.v.cpu()), pin(a.q.cpu())
