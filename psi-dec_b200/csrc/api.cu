@@ -2009,24 +2009,30 @@ int32_t psi_gqa_decode_step_host(psi_gqa* g, psi_pages* pages, psi_table* table,
         g->step_k.ensure(ctx, kv_cap, false);
         g->step_v.ensure(ctx, kv_cap, false);
         g->step_q.ensure(ctx, q_cap, false);
-        // Pinned, device-mapped host buffers: one launch pulls q/k/v over the host link into device staging (every
-        // work item re-reads its query rows, so they should be read from HBM, not from the host), and the attention
-        // launch stores `out` straight into the host buffer.  Two launches and one wait, no copy engine round trips.
+        // Pinned, device-mapped host buffers: one launch pulls q/k/v over the host link into device staging (small
+        // steps: every work item waits for its query rows, which come sooner from HBM than from the host), and the
+        // attention launch stores `out` straight into the host buffer.  Two launches and one wait, no copy engine
+        // round trips.
         if (g->kernel == PSI_KERNEL_MMA && kv_bytes % 16 == 0 && q_bytes % 16 == 0) {
             void* dk = mapped_device_pointer(k_host);
             void* dv = mapped_device_pointer(v_host);
             void* dq = mapped_device_pointer(q_host);
             void* dout = mapped_device_pointer(out_host);
             if (dk != nullptr && dv != nullptr && dq != nullptr && dout != nullptr) {
-                const void* const src[3] = {dq, dk, dv};
-                void* const dst[3] = {g->step_q.ptr, g->step_k.ptr, g->step_v.ptr};
-                const uint64_t bytes[3] = {q_bytes, kv_bytes, kv_bytes};
-                ctx->launches += 1;
-                cuda_check(launch_host_pull(src, dst, bytes, ctx->stream), "host pull launch");
-                AttendParams p = attend_params(g, pages, table, layer, g->step_q.ptr);
+                // the size rule of psi_gqa_step_host: large steps without long query runs are read in place
+                const bool direct = q_bytes + 2 * kv_bytes >= kDirectHostBytes && !g->replay_reserved &&
+                                    g->chunk.num_ctas() == 0;
+                if (!direct) {
+                    const void* const src[3] = {dq, dk, dv};
+                    void* const dst[3] = {g->step_q.ptr, g->step_k.ptr, g->step_v.ptr};
+                    const uint64_t bytes[3] = {q_bytes, kv_bytes, kv_bytes};
+                    ctx->launches += 1;
+                    cuda_check(launch_host_pull(src, dst, bytes, ctx->stream), "host pull launch");
+                }
+                AttendParams p = attend_params(g, pages, table, layer, direct ? dq : g->step_q.ptr);
                 p.out = dout;
-                p.new_k = g->step_k.ptr;
-                p.new_v = g->step_v.ptr;
+                p.new_k = direct ? dk : g->step_k.ptr;
+                p.new_v = direct ? dv : g->step_v.ptr;
                 run_attend(g, p);
                 cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
                 return;

@@ -655,7 +655,7 @@ def test_one_call_host_step_equals_prepare_plus_host_step(pinned, index, scale_d
     # attention launch instead of being pulled into device staging first.
     import torch
     spec = W.config(index, scale_down=scale_down)
-    a, b = W.Session(spec), W.Session(spec)
+    a, b, c = W.Session(spec), W.Session(spec), W.Session(spec)
     pin = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
     kh, vh, qh = pin(a.k.cpu()), pin(a.v.cpu()), pin(a.q.cpu())
     two, one = pin(torch.zeros_like(qh)), pin(torch.zeros_like(qh))
@@ -669,10 +669,17 @@ def test_one_call_host_step_equals_prepare_plus_host_step(pinned, index, scale_d
         b.gqa.step_host(b.pages, b.table, 0, slots, starts, cu, kh, vh, qh, one)
         assert torch.equal(one.view(torch.int16), two.view(torch.int16))
         assert torch.equal(a.arena.view(torch.int16), b.arena.view(torch.int16))
+        # the device-resident fused step on the same inputs: the same launch, whichever memory q/k/v are read from
+        c.q.copy_(qh)
+        c.step()
+        c.ctx.sync()
+        assert torch.equal(c.out.cpu().view(torch.int16), one.view(torch.int16))
+        assert torch.equal(c.arena.view(torch.int16), b.arena.view(torch.int16))
         if before is not None:
             assert not np.array_equal(checks.to_numpy_bits(a.arena), before)   # the step did append
     a.close()
     b.close()
+    c.close()
     with pytest.raises(pkg.PsiError):
         c = W.Session(spec)
         try:
