@@ -98,6 +98,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     const uint64_t v_region_bytes = v_region_offset(p.geo) * 2;
 
     const FragmentLanes frag(lane, L::kRowBytes);
+    const uint64_t stream_policy = l2_evict_first_policy();  // full K/V tiles are read once per launch
 
     // copy lane roles: this lane moves chunk copy_chunk of rows copy_row, copy_row + kRowsPerCopy, ...
     const uint32_t copy_row = lane / kChunks, copy_chunk = lane % kChunks;
@@ -141,7 +142,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                 for (uint32_t it = 0; it < kTile / kRowsPerCopy; ++it) {
                     const uint32_t row0 = it * kRowsPerCopy;  // this lane's row is row0 + copy_row
                     const unsigned char* src = row0 < 8 ? src_lo + row0 * L::kRowBytes : src_hi + (row0 - 8) * L::kRowBytes;
-                    cp_async_16(dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4), src, 16u);
+                    cp_async_16_hinted(dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4), src, 16u, stream_policy);
                 }
             } else {
                 // The item's last tile (ragged end, or this step's own tokens) is rare: a rolled loop keeps its code to

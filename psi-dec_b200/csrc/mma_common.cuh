@@ -69,6 +69,21 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint3
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 
+// An L2 policy for data that is read once: its lines are the first to be evicted, so that a K/V stream several times
+// the size of the L2 does not push out what the launch reads again (plan, page table rows, partial outputs).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+    return policy;
+}
+
+// cp_async_16 under an L2 cache policy.
+__device__ __forceinline__ void cp_async_16_hinted(uint32_t dst, const void* src, uint32_t src_bytes, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(dst), "l"(src),
+                 "r"(src_bytes), "l"(policy)
+                 : "memory");
+}
+
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 
 template <int N>
