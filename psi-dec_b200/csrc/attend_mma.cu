@@ -349,24 +349,29 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                 trace_merged += 1;
 #endif
                 __threadfence();
-                // Every thread merges its own outputs (row r, four columns) from all pieces: the pieces' statistics of
-                // row r and their O values go out together, four pieces at a time, so a unit of up to four pieces costs
-                // one round trip.
+                // Every thread merges its own outputs (row r, four columns in each half of the row) from all pieces:
+                // the pieces' statistics of row r and their O values go out together, four pieces at a time, so a
+                // unit of up to four pieces and eight rows costs every thread one round trip.  The two column groups
+                // are half a row apart, which keeps each store instruction of a warp contiguous (the output may be a
+                // buffer in host memory, where partly written lines cross the host link one by one).
                 const uint32_t n = v.unit_num_items, rows = v.rows;
-                for (uint32_t i = tid; i < rows * (D / 4); i += kThreads) {
-                    const uint32_t r = i / (D / 4), c4 = i % (D / 4);
+                constexpr uint32_t kHalf = D / 8;  // float4 columns per half row
+                for (uint32_t i = tid; i < rows * kHalf; i += kThreads) {
+                    const uint32_t r = i / kHalf, c4 = i % kHalf;
                     const uint64_t prow0 = static_cast<uint64_t>(v.unit_first_slot) * kMaxRows + r;
                     float run_max = -INFINITY, sum = 0.0f;
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
                     for (uint32_t s0 = 0; s0 < n; s0 += 4) {
                         float pm[4], pl[4];
-                        float4 part[4];
+                        float4 part0[4], part1[4];
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k) {
                             const uint64_t prow = prow0 + static_cast<uint64_t>(min(s0 + k, n - 1)) * kMaxRows;
                             pm[k] = __ldcg(p.partial_m + prow);
                             pl[k] = __ldcg(p.partial_l + prow);
-                            part[k] = __ldcg(reinterpret_cast<const float4*>(p.partial_o + prow * D + 4 * c4));
+                            const float4* src = reinterpret_cast<const float4*>(p.partial_o + prow * D) + c4;
+                            part0[k] = __ldcg(src);
+                            part1[k] = __ldcg(src + kHalf);
                         }
                         float group_max = run_max;
 #pragma unroll
@@ -374,36 +379,50 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                             if (s0 + k < n) group_max = fmaxf(group_max, pm[k]);
                         const float carry = run_max == -INFINITY ? 0.0f : exp2f(run_max - group_max);
                         sum *= carry;
-                        acc.x *= carry;
-                        acc.y *= carry;
-                        acc.z *= carry;
-                        acc.w *= carry;
+                        acc0.x *= carry;
+                        acc0.y *= carry;
+                        acc0.z *= carry;
+                        acc0.w *= carry;
+                        acc1.x *= carry;
+                        acc1.y *= carry;
+                        acc1.z *= carry;
+                        acc1.w *= carry;
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k) {
                             const float weight =
                                 (s0 + k < n && pm[k] != -INFINITY) ? exp2f(pm[k] - group_max) * pl[k] : 0.0f;
                             sum += weight;
-                            acc.x += weight * part[k].x;
-                            acc.y += weight * part[k].y;
-                            acc.z += weight * part[k].z;
-                            acc.w += weight * part[k].w;
+                            acc0.x += weight * part0[k].x;
+                            acc0.y += weight * part0[k].y;
+                            acc0.z += weight * part0[k].z;
+                            acc0.w += weight * part0[k].w;
+                            acc1.x += weight * part1[k].x;
+                            acc1.y += weight * part1[k].y;
+                            acc1.z += weight * part1[k].z;
+                            acc1.w += weight * part1[k].w;
                         }
                         run_max = group_max;
                     }
                     const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-                    acc.x *= inv;
-                    acc.y *= inv;
-                    acc.z *= inv;
-                    acc.w *= inv;
+                    acc0.x *= inv;
+                    acc0.y *= inv;
+                    acc0.z *= inv;
+                    acc0.w *= inv;
+                    acc1.x *= inv;
+                    acc1.y *= inv;
+                    acc1.z *= inv;
+                    acc1.w *= inv;
                     const uint64_t row = item_row_index(p, v, r);
                     if (p.ext_o != nullptr) {
-                        *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc;
+                        *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc0;
+                        *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * (c4 + kHalf)) = acc1;
                         if (c4 == 0) {
                             p.ext_m[row] = run_max * kLn2;
                             p.ext_l[row] = sum;
                         }
                     } else {
-                        store_out4<T>(p, row * D + 4 * c4, acc);
+                        store_out4<T>(p, row * D + 4 * c4, acc0);
+                        store_out4<T>(p, row * D + 4 * (c4 + kHalf), acc1);
                     }
                 }
                 if (tid == 0) p.unit_counters[v.reduce_unit] = 0;  // ready for the next launch
