@@ -403,7 +403,7 @@ def workload(W, args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--config", type=int, default=2, help="benchmark configuration (2 = the headline)")
