@@ -432,6 +432,30 @@ def test_fused_step_equals_append_then_attend(index, scale_down):
     b.close()
 
 
+@pytest.mark.parametrize("kernel_mode,_kname", KERNELS)
+@pytest.mark.parametrize("page,head_dim", [(16, 256), (8, 128), (32, 64)])
+def test_page_and_tile_boundaries(page, head_dim, kernel_mode, _kname):
+    # Contexts that end just before, on and just after a page and a 16-token tile boundary, from an empty cache up,
+    # with query runs of one to three tokens (a verify run that starts on the last slot of a page appends into two
+    # pages): pages bit-exact after the step, attention within tolerance, fused step against the two-stage order.
+    contexts = [0, 1, 7, 8, 9, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257]
+    runs = [1 + (i % 3) for i in range(len(contexts))]
+    spec = W.Spec("boundaries", pkg.BF16, 8, 2, head_dim, page, contexts, runs, seed=29)
+    s, t = W.Session(spec, kernel_mode=kernel_mode), W.Session(spec, kernel_mode=kernel_mode)
+    before = checks.to_numpy_bits(s.arena)
+    s.step()
+    t.step_unfused()
+    s.ctx.sync()
+    t.ctx.sync()
+    expected = checks.expected_arena_after_append(s, before)
+    assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), expected)
+    assert np.array_equal(checks.to_numpy_bits(t.arena).reshape(-1), expected)
+    checks.assert_attention_close(s)
+    checks.assert_attention_close(t)
+    s.close()
+    t.close()
+
+
 @pytest.mark.parametrize("engine", ["tcgen05", "mma_sync"])
 @pytest.mark.parametrize("max_ctas", [1, 5, 148])
 @pytest.mark.parametrize("heads,head_dim,page", [((16, 2), 256, 16), ((24, 4), 128, 8), ((8, 8), 128, 32)])
