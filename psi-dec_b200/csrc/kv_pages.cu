@@ -70,11 +70,18 @@ struct PullParams {
 };
 
 __global__ void host_pull_kernel(PullParams p) {
+    // A thread's loads from the three buffers go out together: a load over the host link takes a microsecond or two,
+    // and one buffer after the other would put three of those round trips in a row.
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-    for (int b = 0; b < 3; ++b) {
-        for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.chunks[b]; i += stride) {
-            p.dst[b][i] = p.src[b][i];
-        }
+    const uint64_t most = max(p.chunks[0], max(p.chunks[1], p.chunks[2]));
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < most; i += stride) {
+        uint4 value[3];
+#pragma unroll
+        for (int b = 0; b < 3; ++b)
+            if (i < p.chunks[b]) value[b] = p.src[b][i];
+#pragma unroll
+        for (int b = 0; b < 3; ++b)
+            if (i < p.chunks[b]) p.dst[b][i] = value[b];
     }
 }
 
