@@ -458,8 +458,8 @@ PSI_API int32_t psi_gqa_decode_step_host(psi_gqa* gqa, psi_pages* pages, psi_tab
 /* psi_gqa_prepare (exact capacity) and psi_gqa_decode_step_host in one call, for a host loop that hands over a step's
  * metadata and buffers together (the executor's update-then-submit pair of
  * crates/inference-executor-metal/src/attn/gqa/batch_metadata.rs:128-317 and backend.rs:493-612): with pinned buffers
- * the q/k/v transfer is under way while the step is planned, and the plan reaches the device without a copy-engine
- * transfer; from 1 MiB of q + k + v on (and no long query runs in the step) the attention launch reads the pinned
+ * one launch pulls the packed plan and q/k/v over the host link (no copy-engine transfer) and the attention launch
+ * stores out straight into the host buffer; from 1 MiB of q + k + v on (and no long query runs in the step) the attention launch reads the pinned
  * buffers in place, so that the transfer runs under the K/V stream instead of in front of it.  Same result as the two
  * calls. */
 PSI_API int32_t psi_gqa_step_host(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,

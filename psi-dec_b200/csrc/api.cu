@@ -2023,9 +2023,9 @@ int32_t psi_gqa_decode_step_host(psi_gqa* g, psi_pages* pages, psi_table* table,
                 const bool direct = q_bytes + 2 * kv_bytes >= kDirectHostBytes && !g->replay_reserved &&
                                     g->chunk.num_ctas() == 0;
                 if (!direct) {
-                    const void* const src[3] = {dq, dk, dv};
-                    void* const dst[3] = {g->step_q.ptr, g->step_k.ptr, g->step_v.ptr};
-                    const uint64_t bytes[3] = {q_bytes, kv_bytes, kv_bytes};
+                    const void* const src[kPullBuffers] = {dq, dk, dv, nullptr};
+                    void* const dst[kPullBuffers] = {g->step_q.ptr, g->step_k.ptr, g->step_v.ptr, nullptr};
+                    const uint64_t bytes[kPullBuffers] = {q_bytes, kv_bytes, kv_bytes, 0};
                     ctx->launches += 1;
                     cuda_check(launch_host_pull(src, dst, bytes, ctx->stream), "host pull launch");
                 }
@@ -2079,10 +2079,7 @@ int32_t psi_gqa_step_host(psi_gqa* g, psi_pages* pages, psi_table* table, uint32
             run_staged_host_step(g, pages, table, layer, k_host, v_host, q_host, out_host, kv_bytes, q_bytes, q_cap);
             return;
         }
-        // q/k/v start their way over the host link before the step is planned: the pull runs while the host builds
-        // the plan.  The packed plan then follows through a second small pull from its pinned staging buffer instead
-        // of a copy-engine transfer, and the attention launch stores `out` straight into the host buffer.
-        // Small steps pull q/k/v into device staging with one launch that runs while the host plans.  From
+        // Small steps pull q/k/v into device staging.  From
         // kDirectHostBytes on, that pull would sit in front of the attention for longer than the attention loses by
         // fetching each item's query rows and the step's K/V rows over the host link itself, so the launch reads the
         // host buffers in place and the transfer hides under the K/V stream (256 verify tokens of 24/4 heads, 5.2 MB:
@@ -2095,29 +2092,29 @@ int32_t psi_gqa_step_host(psi_gqa* g, psi_pages* pages, psi_table* table, uint32
                 if (tiles >= kChunkMinTiles) direct = false;
             }
         }
-        if (!direct) {
-            const void* const src[3] = {dq, dk, dv};
-            void* const dst[3] = {g->step_q.ptr, g->step_k.ptr, g->step_v.ptr};
-            const uint64_t bytes[3] = {q_bytes, kv_bytes, kv_bytes};
-            ctx->launches += 1;
-            cuda_check(launch_host_pull(src, dst, bytes, ctx->stream), "host pull launch");
-        }
+        // The step is planned first; then ONE launch pulls the packed plan from its pinned staging buffer together with
+        // q/k/v (or the plan alone when q/k/v are read in place), and the attention launch stores `out` straight into
+        // the host buffer.
         uint64_t words = 0;
         prepare_impl(g, req_slots, token_indices, cu_tokens, num_reqs, PSI_CAPACITY_EXACT, 0, nullptr, true, &words);
         const uint64_t padded_words = (words + 3) / 4 * 4;
         void* staging_dev = nullptr;
-        if (padded_words <= g->staging_words &&
-            cudaHostGetDevicePointer(&staging_dev, g->staging, 0) == cudaSuccess && staging_dev != nullptr &&
-            (reinterpret_cast<uintptr_t>(staging_dev) & 15u) == 0) {
-            const void* const src[3] = {staging_dev, nullptr, nullptr};
-            void* const dst[3] = {g->block.ptr, nullptr, nullptr};
-            const uint64_t bytes[3] = {padded_words * sizeof(uint32_t), 0, 0};
-            ctx->launches += 1;
-            cuda_check(launch_host_pull(src, dst, bytes, ctx->stream), "plan pull launch");
-        } else {
+        const bool plan_mapped = padded_words <= g->staging_words &&
+                                 cudaHostGetDevicePointer(&staging_dev, g->staging, 0) == cudaSuccess &&
+                                 staging_dev != nullptr && (reinterpret_cast<uintptr_t>(staging_dev) & 15u) == 0;
+        if (!plan_mapped) {
             (void)cudaGetLastError();
             cuda_check(cudaMemcpyAsync(g->block.ptr, g->staging, words * sizeof(uint32_t), cudaMemcpyHostToDevice,
                                        ctx->stream), "cudaMemcpyAsync");
+        }
+        if (plan_mapped || !direct) {
+            const void* const src[kPullBuffers] = {direct ? nullptr : dq, direct ? nullptr : dk, direct ? nullptr : dv,
+                                                   plan_mapped ? staging_dev : nullptr};
+            void* const dst[kPullBuffers] = {g->step_q.ptr, g->step_k.ptr, g->step_v.ptr, g->block.ptr};
+            const uint64_t bytes[kPullBuffers] = {direct ? 0 : q_bytes, direct ? 0 : kv_bytes, direct ? 0 : kv_bytes,
+                                                  plan_mapped ? padded_words * sizeof(uint32_t) : 0};
+            ctx->launches += 1;
+            cuda_check(launch_host_pull(src, dst, bytes, ctx->stream), "host pull launch");
         }
         cuda_check(cudaEventRecord(g->upload_done, ctx->stream), "cudaEventRecord");
         AttendParams p = attend_params(g, pages, table, layer, direct ? dq : g->step_q.ptr);

@@ -142,7 +142,9 @@ cudaError_t launch_block_partial(const BlockPartialParams& p, cudaStream_t strea
 cudaError_t launch_kv_append(const AppendParams& p, cudaStream_t stream);
 cudaError_t launch_page_gather(const GatherParams& p, cudaStream_t stream);
 // One launch that copies three host-mapped (pinned) buffers into device memory; sizes are multiples of 16 bytes.
-cudaError_t launch_host_pull(const void* const src[3], void* const dst[3], const uint64_t bytes[3], cudaStream_t stream);
+constexpr int kPullBuffers = 4;
+cudaError_t launch_host_pull(const void* const src[kPullBuffers], void* const dst[kPullBuffers],
+                             const uint64_t bytes[kPullBuffers], cudaStream_t stream);
 cudaError_t launch_norm_rope_append(const PrepParams& p, cudaStream_t stream);
 
 // Map kernels.  `num_ctas` CTAs walk cta_item_begin.  The generic kernel takes any profile with head_dim <= 256; the

@@ -62,25 +62,27 @@ __global__ void page_gather_kernel(GatherParams p, uint32_t units_per_row) {
         pages[(src_elem + v_region_offset(p.geo)) * scale / sizeof(Unit) + unit];
 }
 
-// Pulls up to three host-mapped buffers into device memory in one launch (16-byte chunks, grid-stride).
+// Pulls up to four host-mapped buffers into device memory in one launch (16-byte chunks, grid-stride).
 struct PullParams {
-    const uint4* src[3];
-    uint4* dst[3];
-    uint64_t chunks[3];
+    const uint4* src[kPullBuffers];
+    uint4* dst[kPullBuffers];
+    uint64_t chunks[kPullBuffers];
 };
 
 __global__ void host_pull_kernel(PullParams p) {
-    // A thread's loads from the three buffers go out together: a load over the host link takes a microsecond or two,
-    // and one buffer after the other would put three of those round trips in a row.
+    // A thread's loads from all buffers go out together: a load over the host link takes a microsecond or two, and
+    // one buffer after the other would put those round trips in a row.
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-    const uint64_t most = max(p.chunks[0], max(p.chunks[1], p.chunks[2]));
-    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < most; i += stride) {
-        uint4 value[3];
+    uint64_t most = 0;
 #pragma unroll
-        for (int b = 0; b < 3; ++b)
+    for (int b = 0; b < kPullBuffers; ++b) most = max(most, p.chunks[b]);
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < most; i += stride) {
+        uint4 value[kPullBuffers];
+#pragma unroll
+        for (int b = 0; b < kPullBuffers; ++b)
             if (i < p.chunks[b]) value[b] = p.src[b][i];
 #pragma unroll
-        for (int b = 0; b < 3; ++b)
+        for (int b = 0; b < kPullBuffers; ++b)
             if (i < p.chunks[b]) p.dst[b][i] = value[b];
     }
 }
@@ -125,11 +127,11 @@ cudaError_t launch_page_gather(const GatherParams& p, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-cudaError_t launch_host_pull(const void* const src[3], void* const dst[3], const uint64_t bytes[3],
-                             cudaStream_t stream) {
+cudaError_t launch_host_pull(const void* const src[kPullBuffers], void* const dst[kPullBuffers],
+                             const uint64_t bytes[kPullBuffers], cudaStream_t stream) {
     PullParams p{};
     uint64_t total = 0;
-    for (int b = 0; b < 3; ++b) {
+    for (int b = 0; b < kPullBuffers; ++b) {
         p.src[b] = static_cast<const uint4*>(src[b]);
         p.dst[b] = static_cast<uint4*>(dst[b]);
         p.chunks[b] = bytes[b] / 16;
