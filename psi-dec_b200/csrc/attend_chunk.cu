@@ -12,6 +12,7 @@
 // This is the arithmetic of crates/inference-backend-metal/src/components/metal/gqa_split_kv_tiled_q.metal:49-319
 // (Q tokens x Q-head tile per threadblock, K/V tiles staged in threadgroup memory, in-kernel causal mask) with the
 // reduce of :324-378 folded in.
+#include "launch_util.hpp"
 #include "mma_common.cuh"
 
 namespace psi {
@@ -292,15 +293,9 @@ cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t st
     constexpr int NSTAGE = chunk_stages<D>();
     using L = ChunkSmem<D, NSTAGE>;
     auto kernel = attend_chunk_kernel<T, D, NSTAGE>;
-    static int configured_device = -1;
-    int device = 0;
-    cudaError_t err = cudaGetDevice(&device);
+    static std::atomic<uint64_t> configured{0};  // per instantiation, one bit per device
+    cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), static_cast<int>(L::kTotal), configured);
     if (err != cudaSuccess) return err;
-    if (configured_device != device) {
-        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kTotal));
-        if (err != cudaSuccess) return err;
-        configured_device = device;
-    }
     kernel<<<num_ctas, kThreads, L::kTotal, stream>>>(p);
     return cudaGetLastError();
 }

@@ -25,6 +25,7 @@
 #include <mutex>
 #include <type_traits>
 
+#include "launch_util.hpp"
 #include "mma_common.cuh"
 
 namespace psi {
@@ -763,15 +764,9 @@ cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t st
     CUtensorMap map;
     if (!make_kv_map(p, box_rows, &map)) return cudaErrorNotSupported;
     auto kernel = attend_chunk_umma_kernel<T, D>;
-    static int configured_device = -1;
-    int device = 0;
-    cudaError_t err = cudaGetDevice(&device);
+    static std::atomic<uint64_t> configured{0};  // per instantiation, one bit per device
+    cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), static_cast<int>(kSmem), configured);
     if (err != cudaSuccess) return err;
-    if (configured_device != device) {
-        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
-        if (err != cudaSuccess) return err;
-        configured_device = device;
-    }
     kernel<<<num_ctas, kUmmaThreads, kSmem, stream>>>(p, map, box_rows);
     return cudaGetLastError();
 }

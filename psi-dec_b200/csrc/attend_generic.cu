@@ -9,6 +9,7 @@
 #include <cmath>
 
 #include "device_common.cuh"
+#include "exchange.cuh"
 
 namespace psi {
 
@@ -212,30 +213,20 @@ __global__ void __launch_bounds__(kBlockPartialWarps * 32) block_partial_kernel(
 
 // Cross-device merge of per-device partials in the natural-log domain (same algebra as above).
 __global__ void __launch_bounds__(kReduceThreads) combine_kernel(CombineParams p) {
+    bool ready = true;
     if (p.flags != nullptr) {
-        // Partials arrive from other devices: wait, with a bound, until every producer has published this step.
-        __shared__ uint32_t ready_s;
-        if (threadIdx.x == 0) {
-            uint32_t ready = 1;
-            for (uint32_t i = 0; i < p.n && ready; ++i) {
-                uint32_t polls = 0, seen = 0;
-                for (;;) {
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.flags + i) : "memory");
-                    if (static_cast<int32_t>(seen - p.flag_value) >= 0) break;
-                    if (++polls >= p.max_polls) {
-                        ready = 0;
-                        break;
-                    }
-                    __nanosleep(100);
-                }
-            }
-            if (!ready) atomicExch(p.status, static_cast<uint32_t>(PSI_ERR_TIMEOUT));
-            ready_s = ready;
+        // Partials arrive from other devices: wait, with a bound, until every producer has published this step.  The
+        // launch reaches one verdict (settle_verdict), so `out` is written completely or not at all.
+        __shared__ uint32_t verdict_s;
+        if (threadIdx.x < 32) {
+            const uint32_t verdict = settle_verdict(p.sync_words + kSyncVerdict, p.flags, p.n, p.flag_value, p.max_polls);
+            if (threadIdx.x == 0) verdict_s = verdict;
         }
         __syncthreads();
-        if (!ready_s) return;
+        ready = verdict_s == kVerdictReady;
+        if (!ready && threadIdx.x == 0) atomicExch(p.status, static_cast<uint32_t>(PSI_ERR_TIMEOUT));
     }
-    const uint64_t total = static_cast<uint64_t>(p.num_rows) * p.head_dim;
+    const uint64_t total = ready ? static_cast<uint64_t>(p.num_rows) * p.head_dim : 0;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kReduceThreads + threadIdx.x; i < total;
          i += static_cast<uint64_t>(gridDim.x) * kReduceThreads) {
         const uint64_t row = i / p.head_dim;
@@ -249,6 +240,17 @@ __global__ void __launch_bounds__(kReduceThreads) combine_kernel(CombineParams p
             acc += w * __ldcg(p.o[s] + i);
         }
         store_from_float(p.out, i, p.dtype, sum > 0.0f ? acc / sum : 0.0f);
+    }
+    if (p.flags != nullptr) {
+        // the CTA that leaves last clears the verdict for the next launch
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(p.sync_words + kSyncMergeArrivals, 1u) + 1 == gridDim.x) {
+                p.sync_words[kSyncMergeArrivals] = 0;
+                p.sync_words[kSyncVerdict] = 0;
+            }
+        }
     }
 }
 

@@ -17,6 +17,8 @@
 // The arithmetic this replaces: crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_map.metal
 // (decode rows) and metal/gqa_split_kv_tiled_q.metal:161-319 (several query tokens of one request with the in-kernel
 // causal limit).
+#include "exchange.cuh"
+#include "launch_util.hpp"
 #include "mma_common.cuh"
 
 namespace psi {
@@ -49,7 +51,9 @@ __device__ __forceinline__ unsigned long long trace_now() {
 }
 #endif
 
-template <typename T, int D, int NSLOT>
+// kExchange: the launch is one rank's part of a KV-range exchange (exchange.cuh); the outputs go to the rank's slot of
+// the owner's receive area (ext_*), and the launch ends with the flag publication and, on the owner, the merge.
+template <typename T, int D, int NSLOT, bool kExchange>
 __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p) {
     using L = SmemLayout<D, NSLOT>;
     constexpr uint32_t kChunks = D / 8;                      // 16-byte chunks per row
@@ -79,8 +83,12 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     __shared__ float merge_m[kWarps][kTile];
     __shared__ float merge_l[kWarps][kTile];
     __shared__ uint32_t arrival_s;
+    __shared__ uint32_t slot_free_s;  // exchange launches: this CTA may store into the rank's slot
 
     const uint32_t tid = threadIdx.x;
+    // The consumed word lives on the owner: its value is requested now and looked at before the first store.
+    uint32_t consumed_early = 0;
+    if (kExchange && tid == 0 && p.xchg.step >= 3) consumed_early = ld_relaxed_sys(p.xchg.consumed);
     const uint32_t warp = tid >> 5;
     const uint32_t lane = tid & 31;
     const uint32_t quad_row = lane >> 2;  // accumulator rows quad_row and quad_row + 8
@@ -266,6 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
 #endif
         // ---- merge the warps' partial results --------------------------------------------------------------------------
         cp_async_wait<0>();
+        if (kExchange && index == item_begin && tid == 0) slot_free_s = slot_is_free(p.xchg, consumed_early) ? 1u : 0u;
         __syncthreads();  // every warp is done with its ring: the merge buffer may overwrite it
         st.l0 += __shfl_xor_sync(0xFFFFFFFFu, st.l0, 1);
         st.l0 += __shfl_xor_sync(0xFFFFFFFFu, st.l0, 2);
@@ -326,7 +335,9 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                 }
             } else {
                 const uint64_t row = item_row_index(p, v, r);
-                if (p.ext_o != nullptr) {
+                if (kExchange && !slot_free_s) {
+                    // the slot still holds a step the owner has not merged: nothing is stored, the flag stays back
+                } else if (p.ext_o != nullptr) {
                     *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc;
                     if (c4 == 0) {
                         p.ext_m[row] = row_max * kLn2;
@@ -413,7 +424,9 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                     acc1.z *= inv;
                     acc1.w *= inv;
                     const uint64_t row = item_row_index(p, v, r);
-                    if (p.ext_o != nullptr) {
+                    if (kExchange && !slot_free_s) {
+                        // as above: no store into a slot that is not free
+                    } else if (p.ext_o != nullptr) {
                         *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * c4) = acc0;
                         *reinterpret_cast<float4*>(p.ext_o + row * D + 4 * (c4 + kHalf)) = acc1;
                         if (c4 == 0) {
@@ -428,6 +441,10 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                 if (tid == 0) p.unit_counters[v.reduce_unit] = 0;  // ready for the next launch
             }
         }
+    }
+    if (kExchange) {
+        exchange_publish(p.xchg, p.status, num_ctas, item_begin < item_end && slot_free_s == 0);
+        if (p.xchg.recv != nullptr) exchange_merge<kThreads>(p.xchg, p.status, p.out, p.dtype, D, cta, num_ctas);
     }
 #ifdef PSI_MMA_TRACE
     if (tid == 0 && cta < 148) {
@@ -453,32 +470,24 @@ constexpr int stages_for() {
     return D == 256 ? 3 : (D == 128 ? 6 : 8);  // ring slots (one K or V tile each) per warp
 }
 
-template <typename T, int D>
+template <typename T, int D, bool kExchange>
 cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     constexpr int NSLOT = stages_for<D>();
     using L = SmemLayout<D, NSLOT>;
-    auto kernel = attend_mma_kernel<T, D, NSLOT>;
-    static bool configured = false;  // per instantiation; the attribute is per device, set again on every device below
-    static int configured_device = -1;
-    int device = 0;
-    cudaError_t err = cudaGetDevice(&device);
+    auto kernel = attend_mma_kernel<T, D, NSLOT, kExchange>;
+    static std::atomic<uint64_t> configured{0};  // per instantiation, one bit per device
+    cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), static_cast<int>(L::kTotal), configured);
     if (err != cudaSuccess) return err;
-    if (!configured || configured_device != device) {
-        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kTotal));
-        if (err != cudaSuccess) return err;
-        configured = true;
-        configured_device = device;
-    }
     kernel<<<num_ctas, kThreads, L::kTotal, stream>>>(p);
     return cudaGetLastError();
 }
 
-template <typename T>
+template <typename T, bool kExchange>
 cudaError_t launch_for_dim(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     switch (p.geo.head_dim) {
-        case 64: return launch_one<T, 64>(p, num_ctas, stream);
-        case 128: return launch_one<T, 128>(p, num_ctas, stream);
-        case 256: return launch_one<T, 256>(p, num_ctas, stream);
+        case 64: return launch_one<T, 64, kExchange>(p, num_ctas, stream);
+        case 128: return launch_one<T, 128, kExchange>(p, num_ctas, stream);
+        case 256: return launch_one<T, 256, kExchange>(p, num_ctas, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -510,8 +519,13 @@ cudaError_t launch_attend_mma(const AttendParams& p, uint32_t num_ctas, cudaStre
         (p.out != nullptr && (reinterpret_cast<uintptr_t>(p.out) & 7u) != 0)) {
         return cudaErrorMisalignedAddress;
     }
-    return p.dtype == PSI_DTYPE_BF16 ? launch_for_dim<__nv_bfloat16>(p, num_ctas, stream)
-                                     : launch_for_dim<__half>(p, num_ctas, stream);
+    if (p.xchg.flag != nullptr) {
+        if (p.ext_o == nullptr || p.xchg.sync_words == nullptr || p.xchg.consumed == nullptr) return cudaErrorInvalidValue;
+        return p.dtype == PSI_DTYPE_BF16 ? launch_for_dim<__nv_bfloat16, true>(p, num_ctas, stream)
+                                         : launch_for_dim<__half, true>(p, num_ctas, stream);
+    }
+    return p.dtype == PSI_DTYPE_BF16 ? launch_for_dim<__nv_bfloat16, false>(p, num_ctas, stream)
+                                     : launch_for_dim<__half, false>(p, num_ctas, stream);
 }
 
 }  // namespace psi

@@ -79,6 +79,26 @@ struct GatherParams {
     void* v_out;
 };
 
+// KV-range exchange fused into the map launch: every rank of a group holds one slice of each sequence's KV range and
+// writes its partial (o, m, l) into its slot of the owner's receive area (peer-mapped memory, plain stores).  The CTA
+// that finishes a rank's launch last publishes the rank's arrival flag; on the owner the CTAs then wait, with a bound,
+// for every rank's flag and merge the partials into `out`.  `flag == nullptr` means the launch has no exchange.
+struct ExchangeParams {
+    uint32_t* flag;               // this rank's arrival flag, in the owner's memory as mapped on this device
+    const uint32_t* consumed;     // the owner's "last merged step" word, as mapped on this device
+    uint32_t* sync_words;         // this device, zero between launches: [0] launch arrivals, [1] merge arrivals, [2] verdict
+    const float* recv;            // owner only: this step's receive area in local memory, `world` slots of `slot_stride`
+    const uint32_t* flags;        // owner only: the `world` arrival flags, local memory
+    uint32_t* consumed_local;     // owner only: the consumed word, local memory
+    uint64_t slot_stride;         // floats from one rank's slot to the next; a slot is o [rows][D] | m [rows] | l [rows]
+    uint32_t world;
+    uint32_t step;                // 1, 2, 3, ...: flag value of this step; slot parity = step & 1
+    uint32_t max_polls;           // bound of every wait (about 100 ns per poll)
+    uint32_t num_rows;            // query tokens * q heads
+};
+
+enum SyncWord : uint32_t { kSyncLaunchArrivals = 0, kSyncMergeArrivals = 1, kSyncVerdict = 2, kSyncWordCount = 4 };
+
 struct AttendParams {
     PageGeometry geo;
     const void* q;
@@ -103,6 +123,7 @@ struct AttendParams {
     uint32_t dtype;
     float scale_log2;             // scale * log2(e)
     uint32_t* status;             // nullptr, or the word a bounded device-side wait writes PSI_ERR_TIMEOUT to
+    ExchangeParams xchg;          // KV-range exchange in the same launch (mma kernel); xchg.flag == nullptr: none
 };
 
 struct CombineParams {
@@ -113,6 +134,7 @@ struct CombineParams {
     uint32_t flag_value;
     uint32_t max_polls;           // bound of the wait; on expiry *status = PSI_ERR_TIMEOUT and nothing is written
     uint32_t* status;
+    uint32_t* sync_words;         // with flags: this device's sync words (zero between launches), see SyncWord
     uint32_t n;
     uint32_t num_rows;            // num_tokens * Hq
     uint32_t head_dim;
@@ -164,6 +186,12 @@ cudaError_t launch_read_stream(const void* src, uint64_t bytes, uint32_t* sink, 
 cudaError_t launch_attend_chunk_umma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
 cudaError_t launch_attend_reduce(const AttendParams& p, uint32_t num_reduces, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
+// KV-range exchange without the fused attention launch: push a finished local partial into the rank's slot and publish
+// the flag; on the owner, wait for every rank and merge (at most `max_ctas` CTAs, one row each at a time).
+cudaError_t launch_exchange_push(const ExchangeParams& x, const float* local, float* slot, uint64_t floats,
+                                 uint32_t* status, cudaStream_t stream);
+cudaError_t launch_exchange_merge(const ExchangeParams& x, void* out, uint32_t dtype, uint32_t head_dim, uint32_t* status,
+                                  uint32_t max_ctas, cudaStream_t stream);
 // Release-stores `value` to *flag (local or peer memory) once all earlier work of the stream is visible system-wide.
 cudaError_t launch_signal(uint32_t* flag, uint32_t value, cudaStream_t stream);
 
