@@ -446,6 +446,42 @@ PSI_API int32_t psi_gqa_signal(psi_gqa* gqa, uint32_t* flag, uint32_t value);
 PSI_API int32_t psi_gqa_combine_wait(psi_gqa* gqa, const float* const* o, const float* const* m, const float* const* l,
                                      uint32_t n, uint32_t num_tokens, void* out, const uint32_t* flags,
                                      uint32_t flag_value, uint32_t max_polls);
+
+/* The same exchange as ONE launch per rank.  A group of `world` devices each holds one page-aligned slice of every
+ * sequence's KV range; the owner holds a receive area (memory every rank can store to: peer-mapped or symmetric
+ * memory) of 2 x world slots, one pair per rank, each slot `slot_floats` f32 laid out as o [T][Hq][D] | m [T][Hq] |
+ * l [T][Hq], followed wherever the caller likes by `world` u32 arrival flags and one u32 "consumed" word, all zero
+ * before the first step.  Every rank calls psi_gqa_attend_exchange once per step with the same `step` = 1, 2, 3, ...:
+ *   - the attention launch writes the rank's partial straight into slot [step & 1][rank] (plain peer stores; no bulk
+ *     or tensor copies touch peer memory), and the CTA that finishes the launch last release-stores `step` into
+ *     flags[rank];
+ *   - on the owner the same launch then waits, with a bound, until every flag has reached `step` and merges the
+ *     partials into `out` with the reference's reduce algebra (gqa_split_kv_single_q_reduce.metal:27-48), after which
+ *     it release-stores `step` into the consumed word;
+ *   - slots alternate with the step's parity and a rank stores step s only once the consumed word has reached
+ *     s - 2 (bounded wait), so ranks may run ahead of the owner without overwriting a partial it has not merged.
+ * Every wait gives up after max_polls polls of about 100 ns (0 = default, a fraction of a second): the launch then
+ * writes no output at all (one verdict per launch), records PSI_ERR_TIMEOUT for psi_gqa_device_status, and the context
+ * stays usable.  `k`/`v` (nullable, both or neither) are this step's K/V rows for the rank that holds the end of the
+ * range; they are appended by the same launch.  `out` is needed on the owner only.  Profiles without the tensor-core
+ * decode kernel (f32, odd page sizes) and steps with long query runs run the same protocol as three launches
+ * (attention into local scratch, push + flag, wait + merge).  On the owner, all of the launch's CTAs must be able to
+ * be resident together (they are: the launch never has more CTAs than the device has SMs), because the merging CTAs
+ * wait for the launch's own flag.  No reference counterpart: the reference splits a KV range only within one device
+ * (docs/executor_gqa.md:104-109,556-587). */
+typedef struct psi_kv_exchange {
+    uint32_t rank;
+    uint32_t world;        /* 1..64 */
+    uint32_t owner;        /* rank whose memory holds slots, flags and consumed, and which produces `out` */
+    uint32_t step;         /* >= 1, the same on every rank, +1 per call */
+    float* slots;          /* the owner's receive area as addressed from THIS device: f32 [2][world][slot_floats] */
+    uint64_t slot_floats;  /* >= T * Hq * (D + 2), a multiple of 4 */
+    uint32_t* flags;       /* u32 [world] in the owner's memory, as addressed from this device */
+    uint32_t* consumed;    /* u32 [1] in the owner's memory, as addressed from this device */
+    uint32_t max_polls;    /* 0 = default */
+} psi_kv_exchange;
+PSI_API int32_t psi_gqa_attend_exchange(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer, const void* k,
+                                        const void* v, const void* q, const psi_kv_exchange* exchange, void* out);
 PSI_API int32_t psi_gqa_device_status(psi_gqa* gqa, int32_t* out);
 
 /* One whole decode step through host memory: k, v [T][Hkv][D] and q [T][Hq][D] come from host buffers, out [T][Hq][D]
@@ -490,7 +526,9 @@ PSI_API int32_t psi_page_gather(psi_gqa* gqa, psi_pages* pages, psi_table* table
  * by psi_gqa_attend) and PSI_STATIC_MAX_ITEMS work items - roughly (query tiles x KV heads) + PSI_STATIC_MAX_CTAS; a
  * step beyond them returns PSI_ERR_INVALID_ARGUMENT with the reason in `error` and enqueues nothing.
  * The first call on a device resolves the scratch address (cudaGetSymbolAddress); make that call outside any stream
- * capture.  All calls on a device share the one scratch, which keeps the previous call's contents: each call
+ * capture.  Every call uploads its plan from host memory that is gone when the call returns, so a call on a stream
+ * that is being captured is refused (PSI_ERR_INVALID_ARGUMENT, nothing enqueued).  The caller's current device is
+ * the same after the call as before it.  All calls on a device share the one scratch, which keeps the previous call's contents: each call
  * rewrites its plan and clears the arrival counters itself, and two calls whose work overlaps on the GPU (different
  * streams, or different host threads) race on it - serialise them on one stream.  `error` (may be NULL) receives a
  * NUL-terminated message on failure. */

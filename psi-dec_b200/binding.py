@@ -67,6 +67,13 @@ def rope_parameters(config: "NormRopeConfig"):
     return list(inv[: config.rope_dim // 2]), factor.value, low.value, high.value
 
 
+class KvExchange(C.Structure):
+    """``psi_kv_exchange``: one rank's view of a KV-range exchange group (addresses as seen from this rank's device)."""
+    _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("owner", C.c_uint32), ("step", C.c_uint32),
+                ("slots", C.c_void_p), ("slot_floats", C.c_uint64), ("flags", C.c_void_p), ("consumed", C.c_void_p),
+                ("max_polls", C.c_uint32)]
+
+
 class GQAConfig(C.Structure):
     _fields_ = [("num_q_heads", C.c_uint32), ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32),
                 ("scale", C.c_float), ("page_bytes", C.c_uint32), ("dtype", C.c_uint32),
@@ -650,6 +657,12 @@ class GQA:
         pl = (C.c_void_p * n)(*[_ptr(x).value for x in l_list])
         _check(library().psi_gqa_combine_wait(self._h, po, pm, pl, C.c_uint32(n), C.c_uint32(num_tokens), _ptr(out),
                                               _ptr(flags), C.c_uint32(flag_value), C.c_uint32(max_polls)), self.ctx._h)
+
+    def attend_exchange(self, pages, table, layer, q, exchange: "KvExchange", out=None, k=None, v=None):
+        """One rank's step of a KV-range exchange as one launch (``psi_gqa_attend_exchange``): the partial goes into
+        the rank's slot on the owner, the flag is published, and on the owner the merged output lands in ``out``."""
+        _check(library().psi_gqa_attend_exchange(self._h, pages._h, table._h, C.c_uint32(layer), _ptr(k), _ptr(v),
+                                                 _ptr(q), C.byref(exchange), _ptr(out)), self.ctx._h)
 
     def device_status(self) -> int:
         """Waits for the stream; returns 0, or the status a bounded device-side wait recorded (4 = timeout)."""

@@ -58,6 +58,8 @@ static int32_t combine_impl(psi_gqa* g, const float* const* o, const float* cons
             p.flag_value = flag_value;
             p.max_polls = max_polls == 0 ? 2000000u : max_polls;  // ~100 ns per poll: a fraction of a second by default
             p.status = static_cast<uint32_t*>(g->status_word.ptr);
+            g->sync_words.ensure(ctx, kSyncWordCount * sizeof(uint32_t), true);
+            p.sync_words = static_cast<uint32_t*>(g->sync_words.ptr);
         }
         LaunchScope scope(ctx, PSI_KERNEL_CLASS_COMBINE);
         cuda_check(launch_combine(p, ctx->stream), "combine launch");
@@ -113,6 +115,84 @@ int32_t psi_gqa_signal(psi_gqa* g, uint32_t* flag, uint32_t value) {
         g->ctx->bind();
         g->ctx->launches += 1;
         cuda_check(launch_signal(flag, value, g->ctx->stream), "signal launch");
+    });
+}
+
+int32_t psi_gqa_attend_exchange(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* k,
+                                const void* v, const void* q, const psi_kv_exchange* exchange, void* out) {
+    if (g == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(g->ctx, [&] {
+        require(exchange != nullptr, "exchange must not be null");
+        const psi_kv_exchange& e = *exchange;
+        require(e.world >= 1 && e.world <= 64 && e.rank < e.world && e.owner < e.world,
+                "exchange rank, owner and world are out of range");
+        require(e.step >= 1, "exchange steps count from 1");
+        require(e.slots != nullptr && e.flags != nullptr && e.consumed != nullptr, "exchange buffers must not be null");
+        require((k == nullptr) == (v == nullptr), "k and v come together or not at all");
+        const bool is_owner = e.rank == e.owner;
+        require(!is_owner || out != nullptr, "the owner of the exchange needs an output buffer");
+        psi_ctx* ctx = g->ctx;
+        require(!ctx->capturing, "the exchange carries a step counter and stays outside captured graphs");
+        ctx->bind();
+        AttendParams p = attend_params(g, pages, table, layer, q);
+        const uint64_t rows = uint64_t(g->shape.num_tokens) * g->cfg.num_q_heads;
+        const uint64_t floats = rows * (uint64_t(g->cfg.head_dim) + 2);
+        require(e.slot_floats >= floats && e.slot_floats % 4 == 0,
+                "exchange slot_floats must hold T * Hq * (D + 2) floats and be a multiple of 4");
+        require((reinterpret_cast<uintptr_t>(e.slots) & 15u) == 0, "exchange slots must be 16-byte aligned");
+        g->status_word.ensure(ctx, sizeof(uint32_t), true);
+        g->sync_words.ensure(ctx, kSyncWordCount * sizeof(uint32_t), true);
+
+        float* parity_base = e.slots + uint64_t(e.step & 1u) * e.world * e.slot_floats;
+        float* slot = parity_base + uint64_t(e.rank) * e.slot_floats;
+        ExchangeParams x{};
+        x.flag = e.flags + e.rank;
+        x.consumed = e.consumed;
+        x.sync_words = static_cast<uint32_t*>(g->sync_words.ptr);
+        x.recv = is_owner ? parity_base : nullptr;
+        x.flags = is_owner ? e.flags : nullptr;
+        x.consumed_local = is_owner ? e.consumed : nullptr;
+        x.slot_stride = e.slot_floats;
+        x.world = e.world;
+        x.step = e.step;
+        x.max_polls = e.max_polls == 0 ? 2000000u : e.max_polls;
+        x.num_rows = static_cast<uint32_t>(rows);
+        p.status = static_cast<uint32_t*>(g->status_word.ptr);
+
+        const bool fused = g->kernel == PSI_KERNEL_MMA && g->chunk.num_ctas() == 0 && !g->replay_reserved;
+        if (fused) {
+            if (k != nullptr) {
+                require((reinterpret_cast<uintptr_t>(k) & 15u) == 0 && (reinterpret_cast<uintptr_t>(v) & 15u) == 0,
+                        "k and v must be 16-byte aligned");
+                p.new_k = k;
+                p.new_v = v;
+            }
+            p.ext_o = slot;
+            p.ext_m = slot + rows * g->cfg.head_dim;
+            p.ext_l = p.ext_m + rows;
+            p.out = out;
+            p.xchg = x;
+            run_attend(g, p);
+            return;
+        }
+        // Three launches: the ordinary attention into local scratch, the push with the flag, the owner's wait and merge.
+        if (k != nullptr) run_append(g, pages, table, layer, k, v);
+        g->xchg_local.ensure(ctx, e.slot_floats * sizeof(float), false);
+        float* local = static_cast<float*>(g->xchg_local.ptr);
+        p.ext_o = local;
+        p.ext_m = local + rows * g->cfg.head_dim;
+        p.ext_l = p.ext_m + rows;
+        run_attend(g, p);
+        {
+            LaunchScope scope(ctx, PSI_KERNEL_CLASS_COMBINE);
+            cuda_check(launch_exchange_push(x, local, slot, (floats + 3) / 4 * 4, p.status, ctx->stream), "exchange push launch");
+        }
+        if (is_owner) {
+            LaunchScope scope(ctx, PSI_KERNEL_CLASS_COMBINE);
+            cuda_check(launch_exchange_merge(x, out, g->cfg.dtype, g->cfg.head_dim, p.status,
+                                             static_cast<uint32_t>(ctx->sm_count), ctx->stream),
+                       "exchange merge launch");
+        }
     });
 }
 

@@ -68,6 +68,8 @@ int32_t psi_gqa_destroy(psi_gqa* g) {
         g->step_out.release();
         g->combine_ptrs.release();
         g->status_word.release();
+        g->sync_words.release();
+        g->xchg_local.release();
         g->norm_rope.release();
         if (g->staging != nullptr) (void)cudaFreeHost(g->staging);
         if (g->upload_done != nullptr) (void)cudaEventDestroy(g->upload_done);

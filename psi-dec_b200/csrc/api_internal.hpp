@@ -193,6 +193,8 @@ struct psi_gqa {
     psi::DeviceBuffer step_k, step_v, step_q, step_out;  // psi_gqa_decode_step_host staging
     psi::DeviceBuffer combine_ptrs;
     psi::DeviceBuffer status_word;  // u32 written by bounded device-side waits
+    psi::DeviceBuffer sync_words;   // SyncWord counters of launches that wait or exchange; zero between launches
+    psi::DeviceBuffer xchg_local;   // KV-range exchange without the fused launch: this rank's partial before the push
     bool chunk_umma = false;   // long query runs on the tcgen05 kernel (else the mma.sync chunk kernel)
     uint32_t chunk_launches[2] = {0, 0};  // tcgen05, mma.sync
     psi::DeviceBuffer norm_rope;    // q weight bf16[D] | k weight bf16[D] | inverse frequencies f32[rope_dim/2]

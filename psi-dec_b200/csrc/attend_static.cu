@@ -72,6 +72,23 @@ int32_t fail(int32_t status, const std::string& message, char* error, size_t err
     return status;
 }
 
+// Makes `device` current for the call and puts the caller's device back on every way out.
+struct DeviceGuard {
+    int previous = -1;
+    bool switched = false;
+    cudaError_t enter(int device) {
+        cudaError_t err = cudaGetDevice(&previous);
+        if (err != cudaSuccess) return err;
+        if (previous == device) return cudaSuccess;
+        err = cudaSetDevice(device);
+        switched = err == cudaSuccess;
+        return err;
+    }
+    ~DeviceGuard() {
+        if (switched) (void)cudaSetDevice(previous);
+    }
+};
+
 }  // namespace
 
 extern "C" int32_t psi_gqa_attend_static(int32_t device, void* cuda_stream, const psi_gqa_config* config,
@@ -89,6 +106,7 @@ extern "C" int32_t psi_gqa_attend_static(int32_t device, void* cuda_stream, cons
         require(c.head_dim > 0 && c.head_dim <= kStaticMaxHeadDim,
                 "head_dim exceeds the static scratch (PSI_STATIC_MAX_HEAD_DIM)");
         require(c.dtype <= PSI_DTYPE_F16 && c.scale > 0.0f && std::isfinite(c.scale), "unsupported dtype or scale");
+        require(c.kernel_mode <= PSI_KERNEL_MMA_SYNC, "unknown kernel mode");
         const uint64_t per_token = uint64_t(c.num_kv_heads) * c.head_dim * 2u * dtype_bytes(c.dtype);
         require(c.page_bytes > 0 && c.page_bytes % per_token == 0,
                 "GQA page_bytes must be divisible by the K/V bytes per token");
@@ -105,7 +123,20 @@ extern "C" int32_t psi_gqa_attend_static(int32_t device, void* cuda_stream, cons
         }
         require(cu_tokens[num_reqs] > 0, "GQA batch metadata requires tokens");
 
-        if (cudaSetDevice(device) != cudaSuccess) return fail(PSI_ERR_CUDA, "cudaSetDevice failed", error, error_len);
+        DeviceGuard guard;
+        if (guard.enter(device) != cudaSuccess) return fail(PSI_ERR_CUDA, "cudaSetDevice failed", error, error_len);
+        cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+        // The plan is uploaded from a buffer that lives only for this call, so the call cannot be part of a captured
+        // graph: a replay would read freed host memory.
+        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(PSI_ERR_CUDA, "cudaStreamIsCapturing failed", error, error_len);
+        }
+        if (capture != cudaStreamCaptureStatusNone) {
+            return fail(PSI_ERR_INVALID_ARGUMENT, "psi_gqa_attend_static cannot be recorded into a stream capture", error,
+                        error_len);
+        }
         unsigned char* scratch = nullptr;
         cudaError_t err = scratch_address(device, &scratch);
         if (err != cudaSuccess) {
@@ -115,15 +146,16 @@ extern "C" int32_t psi_gqa_attend_static(int32_t device, void* cuda_stream, cons
         err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
         if (err != cudaSuccess) return fail(PSI_ERR_CUDA, cudaGetErrorString(err), error, error_len);
 
-        // Plan on the host exactly as psi_gqa_prepare does in PSI_PLAN_BALANCED, with the CTA count capped by the scratch.
+        // Plan on the host as psi_gqa_prepare does in PSI_PLAN_BALANCED (same kernel choice, same balance costs), with
+        // the CTA count capped by the scratch.  Long query runs stay on this kernel: the chunk kernels are not used.
         const PlanGeometry geo = plan_geometry(c.num_q_heads, c.num_kv_heads);
         const bool mma = c.kernel_mode != PSI_KERNEL_GENERIC && attend_mma_supported(c.dtype, c.head_dim, tokens_per_page);
-        require(mma || c.kernel_mode != PSI_KERNEL_MMA, "the mma kernel does not support this profile");
+        require(mma || c.kernel_mode < PSI_KERNEL_MMA, "the mma kernel does not support this profile");
         const uint32_t per_sm = mma ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm();
         uint32_t max_ctas = std::min<uint32_t>(kStaticMaxCtas, static_cast<uint32_t>(sm_count) * per_sm);
         if (c.max_ctas > 0) max_ctas = std::min(max_ctas, c.max_ctas);
         const WorkPlan plan = build_balanced_plan(geo, req_slots, token_indices, cu_tokens, num_reqs, max_ctas,
-                                                  mma ? 16u : 4u);
+                                                  mma ? 16u : 4u, mma ? 32u : 0u);
         if (plan.items.size() > kStaticMaxItems) {
             return fail(PSI_ERR_INVALID_ARGUMENT,
                         "the step needs " + std::to_string(plan.items.size()) + " work items; the static scratch holds " +
@@ -146,7 +178,6 @@ extern "C" int32_t psi_gqa_attend_static(int32_t device, void* cuda_stream, cons
         const std::vector<DeviceItem> items = flatten_plan(plan, geo);
         if (!items.empty()) std::memcpy(block.data() + kOffItems, items.data(), items.size() * sizeof(DeviceItem));
 
-        cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
         const uint64_t used = kOffItems + items.size() * sizeof(DeviceItem);
         // Pageable source: the runtime stages the bytes before the call returns.  Everything below is stream-ordered
         // after it, and overwrites what the previous call left in the scratch.
@@ -179,6 +210,7 @@ extern "C" int32_t psi_gqa_attend_static(int32_t device, void* cuda_stream, cons
         p.unit_counters = reinterpret_cast<uint32_t*>(scratch + kOffCounters);
         p.scalars = reinterpret_cast<const uint32_t*>(scratch + kOffScalars);
         p.num_q_heads = c.num_q_heads;
+        p.tokens_per_tile = geo.tokens_per_tile;
         p.dtype = c.dtype;
         p.scale_log2 = c.scale * 1.4426950408889634f;
         if (mma) {

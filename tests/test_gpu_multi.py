@@ -25,9 +25,9 @@ def _run(args, world=2, port=29541):
 
 
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["nccl", "p2p"])
+@pytest.mark.parametrize("mode", ["nccl", "p2p", "p2p3"])
 def test_kv_range_split_partials_cross_devices_and_merge(mode):
-    _run(["kv_range", mode], port=29541 if mode == "nccl" else 29542)
+    _run(["kv_range", mode], port={"nccl": 29541, "p2p": 29542, "p2p3": 29544}[mode])
 
 
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
