@@ -50,7 +50,9 @@ typedef enum psi_status {
     PSI_ERR_RESOURCE_EXHAUSTED = 2, /* "not enough ID", out of device memory */
     PSI_ERR_INTERNAL = 3,
     PSI_ERR_TIMEOUT = 4, /* a bounded device-side wait gave up */
-    PSI_ERR_CUDA = 5     /* a CUDA runtime call failed; the message holds the CUDA error string */
+    PSI_ERR_CUDA = 5,    /* a CUDA runtime call failed; the message holds the CUDA error string */
+    PSI_ERR_PAGE_ID = 6  /* a kernel met a page ID or table index out of bounds: that access was skipped (reads go to
+                            page 0 instead), the launch's results are not valid; from psi_gqa_device_status */
 } psi_status;
 
 /* Storage dtype of q/k/v/out and of the page arena.  F32 and BF16 are the reference's dtypes
@@ -240,6 +242,13 @@ PSI_API int32_t psi_table_destroy(psi_table* table);
 /* write_page_ids: n must equal num_page_ids_per_block. */
 PSI_API int32_t psi_table_write(psi_table* table, uint32_t req_slot, uint32_t layer, uint32_t block,
                                 const uint32_t* page_ids, uint32_t n);
+/* Declares the number of pages of the arena this table indexes (0 = no bound, the initial state).  From then on
+ * psi_table_write, psi_table_write_row and psi_snapshot_read_table refuse page IDs at or beyond it with the message of
+ * the reference's check at the point where IDs enter the table (crates/inference-executor-metal/src/state/gqa.rs:97-102),
+ * before anything reaches the device.  Independently of this, every kernel compares the IDs it reads with the page
+ * count of the psi_pages it was given (PSI_ERR_PAGE_ID through psi_gqa_device_status). */
+PSI_API int32_t psi_table_set_page_bound(psi_table* table, uint64_t num_cache_pages);
+
 /* Qwen3xGQAState::write_page_ids (crates/inference-executor-metal/src/model/qwen/v3_x/state/gqa.rs:88-106): one block
  * of every layer, n == num_gqa_layers * num_page_ids_per_block, every id < num_cache_pages. */
 PSI_API int32_t psi_table_write_all_layers(psi_table* table, uint32_t req_slot, uint32_t block,

@@ -274,6 +274,10 @@ class GQARequestPageTable:
         _check(library().psi_table_write_all_layers(self._h, C.c_uint32(req_slot), C.c_uint32(block_index), arr,
                                                     C.c_uint32(n), C.c_uint64(num_cache_pages)), self.ctx._h)
 
+    def set_page_bound(self, num_cache_pages: int):
+        """Declare the arena's page count: later writes and snapshot loads refuse page IDs at or beyond it."""
+        _check(library().psi_table_set_page_bound(self._h, C.c_uint64(num_cache_pages)), self.ctx._h)
+
     def write_row(self, req_slot, layer_index, page_ids):
         """Bulk load of the leading entries of one (slot, layer) row; ``page_ids`` may be a numpy u32 array."""
         if hasattr(page_ids, "ctypes"):

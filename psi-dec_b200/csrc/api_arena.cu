@@ -176,10 +176,25 @@ int32_t psi_table_write(psi_table* table, uint32_t req_slot, uint32_t layer, uin
         table_check(table, req_slot, layer, block);
         require(n == table->layout.num_page_ids_per_block,
                 "GQA page-id count must match one request/GQA-layer/block entry");
+        table->check_ids(page_ids, n);
         table->ctx->bind();
         const uint64_t start = table->start_index(req_slot, layer, block);
         std::copy(page_ids, page_ids + n, table->host.begin() + start);
         table_upload(table, start, n);
+    });
+}
+
+int32_t psi_table_set_page_bound(psi_table* table, uint64_t num_cache_pages) {
+    if (table == nullptr) return PSI_ERR_INVALID_ARGUMENT;
+    return guarded(table->ctx, [&] {
+        require(num_cache_pages <= (uint64_t(1) << 32), "GQA page IDs are u32");
+        // IDs stored before the bound was declared are held to it as well (zero rows are page 0, always inside)
+        if (num_cache_pages != 0) {
+            for (uint32_t id : table->host) {
+                require(id < num_cache_pages, "the page table already holds a page ID outside the declared bound");
+            }
+        }
+        table->page_bound = num_cache_pages;
     });
 }
 
@@ -211,6 +226,7 @@ int32_t psi_table_write_row(psi_table* table, uint32_t req_slot, uint32_t layer,
         require(ids != nullptr, "ids must not be null");
         table_check(table, req_slot, layer, 0);
         require(n <= table->row_words(), "page-id count exceeds one request/GQA-layer row");
+        table->check_ids(ids, n);
         table->ctx->bind();
         const uint64_t start = table->start_index(req_slot, layer, 0);
         std::copy(ids, ids + n, table->host.begin() + start);

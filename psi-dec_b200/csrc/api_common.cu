@@ -46,6 +46,7 @@ PageGeometry page_geometry(const psi_gqa* g, const psi_pages* pages, const psi_t
     geo.tokens_per_page = g->tokens_per_page;
     geo.num_kv_heads = g->cfg.num_kv_heads;
     geo.head_dim = g->cfg.head_dim;
+    geo.fault = static_cast<uint32_t*>(g->status_word.ptr);
     return geo;
 }
 

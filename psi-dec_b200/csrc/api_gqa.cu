@@ -42,7 +42,7 @@ int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out
         g->chunk_supported = g->kernel == PSI_KERNEL_MMA && c.plan_mode == PSI_PLAN_BALANCED &&
                              attend_chunk_supported(c.dtype, c.head_dim, g->tokens_per_page);
         g->chunk_umma = g->chunk_supported && c.kernel_mode != PSI_KERNEL_MMA_SYNC;
-        if (g->chunk_umma) g->status_word.ensure(ctx, sizeof(uint32_t), true);
+        g->status_word.ensure(ctx, sizeof(uint32_t), true);  // bounded waits and bounds checks report here
         if (c.dtype != PSI_DTYPE_F16) {
             g->selector = std::make_unique<SplitKvSelector>(c.dtype, c.page_bytes, c.num_q_heads, c.num_kv_heads,
                                                             c.head_dim, false);

@@ -127,6 +127,13 @@ struct psi_table {
     psi_page_table_layout layout{};
     uint32_t* dev = nullptr;
     std::vector<uint32_t> host;
+    uint64_t page_bound = 0;  // 0: none declared; else every stored page ID must be below it
+    void check_ids(const uint32_t* ids, uint64_t n) const {
+        if (page_bound == 0) return;
+        for (uint64_t i = 0; i < n; ++i) {
+            psi::require(ids[i] < page_bound, "runtime supplied a GQA page ID outside the cache-page buffer");
+        }
+    }
     uint64_t row_words() const { return uint64_t(layout.num_blocks) * layout.num_page_ids_per_block; }
     uint64_t start_index(uint32_t slot, uint32_t layer, uint32_t block) const {
         return ((uint64_t(slot) * layout.num_gqa_layers + layer) * layout.num_blocks + block) *

@@ -137,12 +137,26 @@ int32_t psi_snapshot_read_table(psi_snapshot_reader* reader, uint32_t file, psi_
         const SnapshotBuffer buffer{table->host.data(), table->host.size() * sizeof(uint32_t), false};
         const uint64_t slot_bytes = table_slot_bytes(table);
         std::vector<U32Range> slots;
-        if (reader->impl.plan().selected) {
-            slots = reader->impl.plan().request_slot_ranges;
-            reader->impl.read_selected_buffer(file, buffer, slots, slot_bytes);
-        } else {
-            slots.emplace_back(0u, table->layout.num_req_slots);
-            reader->impl.read_full_buffer(file, buffer);
+        // With a bound declared the mirror is kept aside: a snapshot taken against a larger arena must not bring IDs
+        // beyond the bound, and a refused load leaves mirror and device table as they were.
+        std::vector<uint32_t> before;
+        if (table->page_bound != 0) before = table->host;
+        try {
+            if (reader->impl.plan().selected) {
+                slots = reader->impl.plan().request_slot_ranges;
+                reader->impl.read_selected_buffer(file, buffer, slots, slot_bytes);
+            } else {
+                slots.emplace_back(0u, table->layout.num_req_slots);
+                reader->impl.read_full_buffer(file, buffer);
+            }
+            for (const auto& range : slots) {
+                const uint64_t words = slot_bytes / sizeof(uint32_t);
+                table->check_ids(table->host.data() + uint64_t(range.first) * words,
+                                 uint64_t(range.second - range.first) * words);
+            }
+        } catch (...) {
+            if (table->page_bound != 0) table->host = before;
+            throw;
         }
         // the restored rows of the mirror go to the device table
         cuda_check(cudaStreamSynchronize(table->ctx->stream), "cudaStreamSynchronize");

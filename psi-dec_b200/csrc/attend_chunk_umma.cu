@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     const uint32_t end_page = min(last_page, (token0 + kUmmaN - 1) >> page_shift);
                     if (first_page < window_base || end_page >= window_base + 32) {
                         window_base = first_page;
-                        window_ids = first_page + lane <= last_page ? row_ids[first_page + lane] : 0u;
+                        window_ids = first_page + lane <= last_page ? page_id_or_zero(p.geo, row_ids, first_page + lane) : 0u;
                     }
                 }
                 {

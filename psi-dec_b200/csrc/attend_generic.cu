@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(kGenericThreads) attend_generic_kernel(AttendP
         const uint32_t* row_ids = table_row(p.geo, v.req_slot);
         const uint64_t v_off = v_region_offset(p.geo);
         for (uint32_t t = v.kv_begin; t < v.kv_end; ++t) {
-            const uint32_t page_id = row_ids[t / p.geo.tokens_per_page];
+            const uint32_t page_id = page_id_or_zero(p.geo, row_ids, t / p.geo.tokens_per_page);
             const uint64_t base = kv_row_offset(p.geo, page_id, v.kv_head, t % p.geo.tokens_per_page);
             float kreg[DPL], vreg[DPL];
 #pragma unroll

@@ -133,8 +133,8 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         // Page ids of the two 8-token halves of local tile i (equal when a page holds 16 tokens or more).
         auto lookup = [&](uint32_t i, uint32_t& id_lo, uint32_t& id_hi) {
             const uint32_t token = (first_tile + warp + i * kWarps) * kTile;
-            id_lo = token < paged_end ? row_ids[token >> page_shift] : 0u;
-            id_hi = token + 8 < paged_end ? row_ids[(token + 8) >> page_shift] : 0u;
+            id_lo = token < paged_end ? page_id_or_zero(p.geo, row_ids, token >> page_shift) : 0u;
+            id_hi = token + 8 < paged_end ? page_id_or_zero(p.geo, row_ids, (token + 8) >> page_shift) : 0u;
         };
         // Issues the copies of half-tile h (K of tile h/2 when h is even, else V) into ring slot `slot`.
         auto issue = [&](uint32_t h, uint32_t slot, uint32_t id_lo, uint32_t id_hi) {
@@ -218,12 +218,13 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             for (uint32_t i = tid; i < v.num_tokens * 2 * kChunks; i += kThreads) {
                 const uint32_t c = i % kChunks, which = (i / kChunks) & 1, j = i / (2 * kChunks);
                 const uint32_t pos = v.first_pos + j;
-                if (pos >= v.kv_begin && pos < v.kv_end) {
+                uint32_t write_id = 0;
+                if (pos >= v.kv_begin && pos < v.kv_end && checked_page_id(p.geo, row_ids, pos >> page_shift, write_id)) {
                     const unsigned char* fresh = static_cast<const unsigned char*>(which ? p.new_v : p.new_k);
                     const uint4 value = *reinterpret_cast<const uint4*>(
                         fresh + (static_cast<uint64_t>(v.flat_begin + j) * p.geo.num_kv_heads + v.kv_head) * L::kRowBytes + c * 16);
                     unsigned char* dst = const_cast<unsigned char*>(pages) +
-                                         static_cast<uint64_t>(row_ids[pos >> page_shift]) * page_bytes + head_bytes +
+                                         static_cast<uint64_t>(write_id) * page_bytes + head_bytes +
                                          (which ? v_region_bytes : 0) + (pos & page_mask) * L::kRowBytes + c * 16;
                     *reinterpret_cast<uint4*>(dst) = value;
                 }

@@ -29,6 +29,50 @@ __device__ __forceinline__ const uint32_t* table_row(const PageGeometry& g, uint
     return g.page_ids + (static_cast<uint64_t>(req_slot) * g.num_layers + g.layer) * g.pages_per_req;
 }
 
+// Bounds-checked page-table reads.  The reference checks page IDs where they enter the table
+// (crates/inference-executor-metal/src/state/gqa.rs:97-102) and table indices with debug assertions
+// (crates/inference-executor-metal/src/attn/gqa/request_page_table.rs:75,115); its shaders trust the table.  Here
+// every kernel compares the index with the row length and the ID with the arena's page count before forming an
+// address, and on a miss records PSI_ERR_PAGE_ID in the status word instead of touching memory outside the arena.
+// The checks cost a compare and a select per 16-token tile and are compiled in unless PSI_CUDA_CHECKED is defined 0.
+#ifndef PSI_CUDA_CHECKED
+#define PSI_CUDA_CHECKED 1
+#endif
+
+__device__ __forceinline__ void record_page_fault(const PageGeometry& g) {
+    if (g.fault != nullptr) *reinterpret_cast<volatile uint32_t*>(g.fault) = static_cast<uint32_t>(PSI_ERR_PAGE_ID);
+}
+
+// Page ID at `index` of a (slot, layer) table row; false (and id = 0) when the index or the ID is out of bounds: the
+// caller skips its write.
+__device__ __forceinline__ bool checked_page_id(const PageGeometry& g, const uint32_t* row_ids, uint32_t index,
+                                                uint32_t& id) {
+#if PSI_CUDA_CHECKED
+    id = 0;
+    if (index >= g.pages_per_req) {
+        record_page_fault(g);
+        return false;
+    }
+    const uint32_t raw = row_ids[index];
+    if (g.num_pages != 0 && raw >= g.num_pages) {
+        record_page_fault(g);
+        return false;
+    }
+    id = raw;
+    return true;
+#else
+    id = row_ids[index];
+    return true;
+#endif
+}
+
+// The same for reads: an out-of-bounds entry reads page 0 (valid memory) and the launch is flagged.
+__device__ __forceinline__ uint32_t page_id_or_zero(const PageGeometry& g, const uint32_t* row_ids, uint32_t index) {
+    uint32_t id;
+    (void)checked_page_id(g, row_ids, index, id);
+    return id;
+}
+
 // Element offset of K row (kv_head, token) inside the arena; V is `v_region` further.  Within one (slot, layer) row
 // the two-level (block, page_id_index) address of the reference collapses to token / tokens_per_page.
 __device__ __forceinline__ uint64_t kv_row_offset(const PageGeometry& g, uint32_t page_id, uint32_t kv_head,

@@ -30,6 +30,7 @@ struct PageGeometry {
     uint32_t num_kv_heads;
     uint32_t head_dim;
     uint32_t elem_bytes;
+    uint32_t* fault;              // nullptr, or the status word a failed bounds check writes PSI_ERR_PAGE_ID to
 };
 
 struct AppendParams {

@@ -26,8 +26,8 @@ __global__ void kv_append_kernel(AppendParams p, uint32_t units_per_row) {
 
     const uint32_t token = p.flat_token_indices[write];
     const uint32_t page_index = token / p.geo.tokens_per_page;
-    if (page_index >= p.geo.pages_per_req) return;  // outside the table row: the host rejects this before launch
-    const uint32_t page_id = table_row(p.geo, p.req_slots[write])[page_index];
+    uint32_t page_id;
+    if (!checked_page_id(p.geo, table_row(p.geo, p.req_slots[write]), page_index, page_id)) return;  // write skipped
     const uint64_t dst_elem = kv_row_offset(p.geo, page_id, head, token % p.geo.tokens_per_page);
     const uint64_t src_elem = (static_cast<uint64_t>(write) * p.geo.num_kv_heads + head) * p.geo.head_dim;
     const uint64_t scale = p.geo.elem_bytes;  // element offsets -> byte offsets -> Unit offsets
@@ -51,8 +51,8 @@ __global__ void page_gather_kernel(GatherParams p, uint32_t units_per_row) {
     const uint32_t local = static_cast<uint32_t>(row / p.geo.num_kv_heads);
     const uint32_t token = p.tok_begin + local;
     const uint32_t page_index = token / p.geo.tokens_per_page;
-    if (page_index >= p.geo.pages_per_req) return;
-    const uint32_t page_id = table_row(p.geo, p.req_slot)[page_index];
+    uint32_t page_id;
+    if (!checked_page_id(p.geo, table_row(p.geo, p.req_slot), page_index, page_id)) return;  // row left untouched
     const uint64_t src_elem = kv_row_offset(p.geo, page_id, head, token % p.geo.tokens_per_page);
     const uint64_t dst_elem = (static_cast<uint64_t>(local) * p.geo.num_kv_heads + head) * p.geo.head_dim;
     const uint64_t scale = p.geo.elem_bytes;

@@ -68,8 +68,8 @@ __global__ void __launch_bounds__(kPrepWarps * 32) norm_rope_append_kernel(PrepP
     if (!is_q) {
         const uint32_t pos = p.flat_token_indices[token];
         const uint32_t page_index = pos / p.geo.tokens_per_page;
-        if (page_index >= p.geo.pages_per_req) return;  // the host rejects this before launch
-        const uint32_t page_id = table_row(p.geo, p.req_slots[token])[page_index];
+        uint32_t page_id;
+        if (!checked_page_id(p.geo, table_row(p.geo, p.req_slots[token]), page_index, page_id)) return;  // write skipped
         dst = const_cast<void*>(p.geo.pages);
         dst_base = kv_row_offset(p.geo, page_id, head, pos % p.geo.tokens_per_page) + (is_v ? v_region_offset(p.geo) : 0);
     }
