@@ -259,3 +259,218 @@ class Session:
         self.table.close()
         self.pages.close()
         self.ctx.close()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Continuous-batching churn (the fifth benchmark configuration)
+# ---------------------------------------------------------------------------------------------------------------------
+def _zipf_contexts(rng, n: int, lo: int, hi: int, s: float = 1.1) -> np.ndarray:
+    """Inverse-CDF samples of a Zipf(s) law over the integers [lo, hi]."""
+    support = np.arange(lo, hi + 1, dtype=np.float64)
+    weights = support ** -s
+    cdf = np.cumsum(weights) / weights.sum()
+    return lo + np.searchsorted(cdf, rng.random(n))
+
+
+class ChurnTrace:
+    """A seeded admit / finish / append trace over a fixed set of request slots, host only.
+
+    Per step: ``chunk_fraction`` of the live sequences append a ``chunk``-token block (causal within the block plus
+    the paged history), the others one decode token; then ``finish_fraction`` of the sequences finish and new ones
+    (context drawn from Zipf(1.1) over [lo, hi]) move into the slots they leave.  Slot ``s`` belongs to rank
+    ``s % world`` for good (its pages live in that rank's arena).  The one freedom a sticky assignment leaves is which
+    freed slot a newly admitted sequence takes: the most expensive newcomer goes to the freed slot of the rank that
+    carries the least work, under the same cost model as ``Spec.shard``.
+    """
+
+    def __init__(self, slots: int = 256, steps: int = 50, seed: int = 5, world: int = 1, chunk: int = 512,
+                 lo: int = 128, hi: int = 131072, chunk_fraction: float = 0.3, finish_fraction: float = 0.1,
+                 num_q_heads: int = 16, num_kv_heads: int = 2, head_dim: int = 256, elem_bytes: int = 2):
+        rng = np.random.default_rng(seed)
+        self.slots, self.steps, self.seed, self.world, self.chunk = slots, steps, seed, world, chunk
+        self.num_q_heads, self.num_kv_heads, self.head_dim, self.elem_bytes = num_q_heads, num_kv_heads, head_dim, elem_bytes
+        self.context = np.zeros((steps, slots), dtype=np.int64)   # tokens cached before the step's append
+        self.q_len = np.zeros((steps, slots), dtype=np.int64)
+        self.finished = []                                        # per step: slots that finish after it
+        self.admitted = []                                        # per step: {slot: context of the newcomer}
+        ctx = _zipf_contexts(rng, slots, lo, hi)
+        n_finish = max(1, int(round(finish_fraction * slots))) if finish_fraction > 0 else 0
+        for t in range(steps):
+            # the chunked sequences are drawn rank by rank, so every rank carries its share of them
+            q = np.ones(slots, dtype=np.int64)
+            for r in range(world):
+                own = np.arange(r, slots, world)
+                q[rng.choice(own, size=int(round(chunk_fraction * len(own))), replace=False)] = chunk
+            self.context[t], self.q_len[t] = ctx, q
+            ctx = ctx + q
+            leaving = np.sort(rng.choice(slots, size=n_finish, replace=False)) if n_finish else np.zeros(0, dtype=np.int64)
+            newcomers = np.sort(_zipf_contexts(rng, len(leaving), lo, hi))[::-1]
+            loads = np.zeros(world)
+            staying = np.ones(slots, dtype=bool)
+            staying[leaving] = False
+            cost = self._cost(ctx, np.full(slots, 1 + (chunk - 1) * chunk_fraction))
+            for r in range(world):
+                loads[r] = cost[staying & (np.arange(slots) % world == r)].sum()
+            free = list(int(s) for s in leaving)
+            placed = {}
+            for c in newcomers:
+                slot = min(free, key=lambda s: (loads[s % world], s))
+                free.remove(slot)
+                placed[slot] = int(c)
+                loads[slot % world] += float(self._cost(np.array([c]), np.array([1 + (chunk - 1) * chunk_fraction]))[0])
+                ctx[slot] = c
+            self.finished.append([int(s) for s in leaving])
+            self.admitted.append(placed)
+
+    def _cost(self, context, q_len):
+        """Seconds a sequence costs per step: its K/V bytes at HBM speed plus, for a chunk, its flops at tensor speed."""
+        kv_bytes = (context + q_len) * (2 * self.num_kv_heads * self.head_dim * self.elem_bytes)
+        flops = 4.0 * self.head_dim * self.num_q_heads * (q_len * context + q_len * (q_len + 1) / 2) * (q_len > 1)
+        return kv_bytes / 6.5e12 + flops / 1.2e15
+
+    def rank_slots(self, rank: int) -> np.ndarray:
+        return np.arange(rank, self.slots, self.world)
+
+    def max_context(self) -> int:
+        return int((self.context + self.q_len).max())
+
+    def step_cost_share(self, t: int) -> float:
+        """Slowest rank's modelled step cost over the mean (1.0 = perfectly balanced)."""
+        cost = self._cost(self.context[t], self.q_len[t])
+        per_rank = np.array([cost[self.rank_slots(r)].sum() for r in range(self.world)])
+        return float(per_rank.max() / per_rank.mean())
+
+    def step_bytes_flops(self, t: int, slots: np.ndarray, chunk_tiles_min: int = 5, tokens_per_tile: int = 2):
+        """(decode-row algorithmic bytes, chunk-row flops, query tokens) of step ``t`` over ``slots``: decode rows are
+        the requests the decode kernel takes, chunk rows the long query runs the chunk kernel takes."""
+        ctx, q = self.context[t][slots], self.q_len[t][slots]
+        is_chunk = -(-q // tokens_per_tile) >= chunk_tiles_min
+        e = self.elem_bytes
+        row = 2 * self.num_kv_heads * self.head_dim * e
+        dec = ~is_chunk
+        decode_bytes = int(((ctx + q)[dec]).sum()) * row + int(q[dec].sum()) * (self.num_q_heads * self.head_dim * 2 * e + 2 * row)
+        keys = q * ctx + q * (q + 1) // 2
+        flops = int(4 * self.head_dim * self.num_q_heads * keys[is_chunk].sum())
+        return decode_bytes, flops, int(q.sum())
+
+
+class ChurnSession:
+    """One rank's share of a :class:`ChurnTrace` on one GPU, driven through the library's cache-ownership objects:
+    page IDs come from ``U32IDAllocator`` (freed IDs first), a finished slot's table rows are zeroed with
+    ``reset_req_slots``, its pages go back to the allocator and are handed out again without being cleared, and the
+    table is two-level (``ids_per_block`` page IDs per logical block, written block by block as the reference's
+    block-table deltas are)."""
+
+    def __init__(self, trace: ChurnTrace, rank: int = 0, device: int = 0, tokens_per_page: int = 16,
+                 ids_per_block: int = 128, kernel_mode: int = B.KERNEL_AUTO, dtype: int = B.BF16):
+        import torch
+        self.torch, self.trace, self.rank = torch, trace, rank
+        self.p, self.ipb = tokens_per_page, ids_per_block
+        self.mine = trace.rank_slots(rank)                      # global slot ids; local slot i = self.mine[i]
+        self.local_of = {int(s): i for i, s in enumerate(self.mine)}
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        self.stream = torch.cuda.current_stream(self.device)
+        self.ctx = B.Context(device, stream=self.stream.cuda_stream)
+        self.dtype = dtype
+        self.tdtype = {B.BF16: torch.bfloat16, B.F16: torch.float16}[dtype]
+        hq, hkv, d = trace.num_q_heads, trace.num_kv_heads, trace.head_dim
+        self.page_bytes = 2 * hkv * tokens_per_page * d * trace.elem_bytes
+        # the arena holds the largest number of pages this rank's slots ever own at once, plus one step of slack
+        pages_needed = -(-(trace.context + trace.q_len)[:, self.mine] // tokens_per_page)
+        self.num_pages = int(pages_needed.sum(axis=1).max()) + len(self.mine) * (-(-trace.chunk // tokens_per_page) + 1)
+        page_elems = self.page_bytes // trace.elem_bytes
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(trace.seed * 1000 + rank)
+        self.arena = torch.empty((self.num_pages, page_elems), dtype=self.tdtype, device=self.device)
+        step = max(1, (256 << 20) // (page_elems * 4))
+        for start in range(0, self.num_pages, step):
+            part = self.arena[start:start + step]
+            part.copy_(torch.randn(part.shape, generator=gen, device=self.device, dtype=torch.float32))
+        self.pages = B.PageArena(self.ctx, self.num_pages, self.page_bytes, device_ptr=self.arena)
+        blocks = -(-(-(-trace.max_context() // tokens_per_page)) // ids_per_block)
+        self.layout = B.GQAPageTableLayout(len(self.mine), 1, blocks, ids_per_block)
+        self.table = B.GQARequestPageTable(self.ctx, self.layout)
+        self.table.set_page_bound(self.num_pages)
+        self.allocator = B.U32IDAllocator(self.num_pages)
+        self.page_ids = [[] for _ in self.mine]                  # per local slot: physical pages in logical order
+        self.max_tokens = int(trace.q_len[:, self.mine].sum(axis=1).max())
+        cfg = B.GQAConfig(hq, hkv, d, 1.0 / math.sqrt(d), self.page_bytes, dtype, self.layout, self.max_tokens,
+                          B.PLAN_BALANCED, kernel_mode, 0)
+        self.gqa = B.GQA(self.ctx, cfg)
+        self.q = torch.randn((self.max_tokens, hq, d), generator=gen, device=self.device, dtype=torch.float32).to(self.tdtype)
+        self.k = torch.randn((self.max_tokens, hkv, d), generator=gen, device=self.device, dtype=torch.float32).to(self.tdtype)
+        self.v = torch.randn((self.max_tokens, hkv, d), generator=gen, device=self.device, dtype=torch.float32).to(self.tdtype)
+        self.out = torch.zeros_like(self.q)
+        self.reused_pages = 0
+        self._ever_freed = np.zeros(self.num_pages, dtype=bool)
+        for i in range(len(self.mine)):
+            self._grow(i, int(trace.context[0][self.mine[i]]))
+
+    def _grow(self, local: int, tokens: int):
+        """Pages for the first ``tokens`` tokens of local slot ``local``: new IDs from the allocator, and the logical
+        blocks they fall into written to the table."""
+        have = len(self.page_ids[local])
+        need = -(-tokens // self.p)
+        if need <= have:
+            return
+        fresh = self.allocator.alloc_many(need - have)
+        self.reused_pages += int(self._ever_freed[fresh].sum())
+        self.page_ids[local].extend(fresh)
+        ids = self.page_ids[local]
+        for block in range(have // self.ipb, -(-need // self.ipb)):
+            entry = ids[block * self.ipb:(block + 1) * self.ipb]
+            self.table.write_page_ids(local, 0, block, entry + [0] * (self.ipb - len(entry)))
+
+    def prepare_step(self, t: int):
+        """Host work in front of step ``t``: admissions of the previous step's leavers are already done; pages for this
+        step's appended tokens are allocated and the plan is uploaded.  Returns (table_seconds, prepare_seconds)."""
+        import time
+        tr = self.trace
+        t0 = time.perf_counter()
+        for i, s in enumerate(self.mine):
+            self._grow(i, int(tr.context[t][s] + tr.q_len[t][s]))
+        t1 = time.perf_counter()
+        q_len = tr.q_len[t][self.mine]
+        cu = np.concatenate([[0], np.cumsum(q_len)]).astype(np.uint32)
+        self.tokens = int(cu[-1])
+        self.batch = (np.arange(len(self.mine), dtype=np.uint32), tr.context[t][self.mine].astype(np.uint32), cu)
+        self.gqa.prepare(*self.batch)
+        return t1 - t0, time.perf_counter() - t1
+
+    def launch_step(self):
+        """The step on the device: this step's K/V rows into their pages and attention over everything visible."""
+        n = self.tokens
+        self.gqa.append_attend(self.pages, self.table, 0, self.k[:n], self.v[:n], self.q[:n], self.out[:n])
+
+    def finish_step(self, t: int):
+        """After step ``t``: the leavers' pages go back to the allocator, their table rows are zeroed, and the
+        newcomers' contexts get pages (possibly the very ones just freed, contents untouched)."""
+        tr = self.trace
+        leaving = [self.local_of[s] for s in tr.finished[t] if s in self.local_of]
+        for local in leaving:
+            ids = self.page_ids[local]
+            self.allocator.free_many(ids)
+            self._ever_freed[ids] = True
+            self.page_ids[local] = []
+        if leaving:
+            self.table.reset_req_slots(leaving)
+        for s, context in tr.admitted[t].items():
+            if s in self.local_of:
+                self._grow(self.local_of[s], context)
+
+    def sequence_view(self, t: int, local: int):
+        """What a checker needs for one sequence of step ``t`` (after ``launch_step``): its physical pages in logical
+        order, its context length, its query length and the flat row range of its tokens."""
+        q_len = self.trace.q_len[t][self.mine]
+        begin = int(q_len[:local].sum())
+        n = int(q_len[local])
+        return dict(pages=list(self.page_ids[local]), context=int(self.trace.context[t][self.mine[local]]), q_len=n,
+                    rows=(begin, begin + n))
+
+    def close(self):
+        self.ctx.sync()
+        self.gqa.close()
+        self.table.close()
+        self.pages.close()
+        self.ctx.close()

@@ -115,3 +115,30 @@ def test_allocator_driven_page_reuse_over_many_steps():
     assert reused > 50, "the trace must actually recycle page IDs"
     assert alloc.used() == sum(len(x) for x in pages)
     rig.close()
+
+
+def test_churn_session_trace_matches_the_oracle_and_reuses_pages():
+    # The benchmark's churn driver at a small scale: allocator-driven pages in a two-level table (8 page IDs per
+    # logical block), slot resets, page reuse without clearing; every step a sample of sequences against the oracle.
+    from psi_dec_b200 import workloads as PW
+    trace = PW.ChurnTrace(slots=20, steps=10, seed=17, world=1, hi=1500, chunk=48, num_q_heads=16, num_kv_heads=2,
+                          head_dim=128)
+    churn = PW.ChurnSession(trace, ids_per_block=8)
+    assert churn.layout.num_page_ids_per_block == 8
+    rng = np.random.default_rng(1)
+    for t in range(trace.steps):
+        churn.prepare_step(t)
+        churn.launch_step()
+        churn.ctx.sync()
+        assert churn.gqa.device_status() == 0
+        q_len = trace.q_len[t]
+        picks = set(rng.choice(trace.slots, size=3, replace=False).tolist())
+        picks.add(int(np.argmax(q_len)))                      # always one chunked sequence
+        picks.update(trace.finished[t - 1][:1] if t else [])  # and one that just moved into a reused slot
+        for local in sorted(picks):
+            max_abs, mean_abs = checks.churn_sequence_error(churn, t, local)
+            assert max_abs <= 2e-2 and mean_abs <= 2e-3, (t, local, max_abs, mean_abs)
+        churn.finish_step(t)
+    assert churn.reused_pages > 0
+    assert churn.allocator.used() == sum(len(ids) for ids in churn.page_ids)
+    churn.close()
