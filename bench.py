@@ -195,6 +195,11 @@ def workload(W, args, index=None):
     if args.gpus != 1:
         raise SystemExit("--shape runs on one GPU")
     values = [int(x) for x in args.shape.split(",")]
+    if getattr(args, "contexts", None) is not None:
+        if len(values) != 4:
+            raise SystemExit("with --contexts, --shape wants HQ,HKV,D,PAGE")
+        dtype = {"bf16": 1, "f16": 2, "f32": 0}[getattr(args, "dtype", "bf16")]
+        return W.explicit(*values, [int(x) for x in args.contexts.split(",")], dtype=dtype)
     if len(values) not in (7, 8):
         raise SystemExit("--shape wants HQ,HKV,D,PAGE,BATCH,CTX_LO,CTX_HI[,Q_LEN]")
     return W.custom(*values)
@@ -291,7 +296,7 @@ def measure_decode(job, pkg, W, index, main):
         record = {
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
-            "scaling": scaling, "vs_baseline": None, "dtype": "bf16" if spec.dtype == pkg.BF16 else "f16/f32",
+            "scaling": scaling, "vs_baseline": None, "dtype": {pkg.BF16: "bf16", pkg.F16: "f16", pkg.F32: "f32"}[spec.dtype],
             "data": "synthetic", "config": config_block(whole, parallelism),
             "tokens_per_s": round(job_tokens / (ms_per_step * 1e-3), 1),
             "kv_gbs": round(job_kv / (ms_per_step * 1e-3) / 1e9, 1),
@@ -676,6 +681,9 @@ def main():
                         help="divide batch and context sizes (small cases for profiler captures; not a bench value)")
     parser.add_argument("--shape", default=None, metavar="HQ,HKV,D,PAGE,BATCH,CTX_LO,CTX_HI[,Q_LEN]",
                         help="one GPU only: a decode batch of another model profile instead of --config")
+    parser.add_argument("--contexts", default=None, metavar="C1,C2,...",
+                        help="with --shape HQ,HKV,D,PAGE: one sequence per listed context length")
+    parser.add_argument("--dtype", choices=["bf16", "f16", "f32"], default="bf16", help="storage dtype of --contexts runs")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-read-probe", action="store_true", help="skip the read-only HBM bandwidth probe")
     parser.add_argument("--kernel", choices=["auto", "mma", "generic", "mma_sync"], default="auto",

@@ -51,8 +51,9 @@ typedef enum psi_status {
     PSI_ERR_INTERNAL = 3,
     PSI_ERR_TIMEOUT = 4, /* a bounded device-side wait gave up */
     PSI_ERR_CUDA = 5,    /* a CUDA runtime call failed; the message holds the CUDA error string */
-    PSI_ERR_PAGE_ID = 6  /* a kernel met a page ID or table index out of bounds: that access was skipped (reads go to
-                            page 0 instead), the launch's results are not valid; from psi_gqa_device_status */
+    PSI_ERR_PAGE_ID = 6  /* checked build of the library only (libpsi_cuda_checked.so): a kernel met a page ID or
+                            table index out of bounds; that access was skipped (reads go to page 0 instead) and the
+                            launch's results are not valid; from psi_gqa_device_status */
 } psi_status;
 
 /* Storage dtype of q/k/v/out and of the page arena.  F32 and BF16 are the reference's dtypes
@@ -245,8 +246,9 @@ PSI_API int32_t psi_table_write(psi_table* table, uint32_t req_slot, uint32_t la
 /* Declares the number of pages of the arena this table indexes (0 = no bound, the initial state).  From then on
  * psi_table_write, psi_table_write_row and psi_snapshot_read_table refuse page IDs at or beyond it with the message of
  * the reference's check at the point where IDs enter the table (crates/inference-executor-metal/src/state/gqa.rs:97-102),
- * before anything reaches the device.  Independently of this, every kernel compares the IDs it reads with the page
- * count of the psi_pages it was given (PSI_ERR_PAGE_ID through psi_gqa_device_status). */
+ * before anything reaches the device.  Independently of this, in the checked build of the library every kernel
+ * compares the IDs it reads with the page count of the psi_pages it was given (PSI_ERR_PAGE_ID through
+ * psi_gqa_device_status). */
 PSI_API int32_t psi_table_set_page_bound(psi_table* table, uint64_t num_cache_pages);
 
 /* Qwen3xGQAState::write_page_ids (crates/inference-executor-metal/src/model/qwen/v3_x/state/gqa.rs:88-106): one block
@@ -301,8 +303,8 @@ PSI_API int32_t psi_metadata_update_host(uint32_t max_tokens, const uint32_t* re
 PSI_API int32_t psi_plan_preview(uint32_t num_q_heads, uint32_t num_kv_heads, const uint32_t* token_indices,
                                  const uint32_t* cu_tokens, uint32_t num_reqs, uint32_t max_ctas,
                                  uint32_t min_kv_tiles_per_cta, uint32_t item_start_cost, uint32_t* out_items,
-                                 uint64_t items_cap,
-                                 uint32_t* out_cta_item_begin, uint64_t cta_cap, uint32_t* out_counts);
+                                 uint64_t items_cap, uint32_t* out_cta_item_begin, uint64_t cta_cap,
+                                 uint32_t* out_counts);
 
 /* The work plan of the long-query (chunk) kernels for a batch in which EVERY request carries a long run, computed on
  * the host.  equal_shares selects the plan for working sets that stay in L2 (contiguous shares of equal size) instead

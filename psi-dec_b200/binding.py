@@ -19,7 +19,18 @@ MD_REQ_SLOTS, MD_FLAT_TOKEN_INDICES, MD_Q_TOKEN_TILES, MD_KV_SPLITS, MD_CU_KV_SP
 
 _STATUS = {1: "invalid argument", 2: "resource exhausted", 3: "internal error", 4: "timeout", 5: "CUDA error"}
 
-_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libpsi_cuda.so"
+def _library_file() -> Path:
+    """``lib/libpsi_cuda.so``, or what the environment variable PSI_CUDA_LIBRARY names: ``checked`` for the
+    bounds-checked build ``lib/libpsi_cuda_checked.so``, or a path."""
+    import os
+    choice = os.environ.get("PSI_CUDA_LIBRARY", "")
+    lib_dir = Path(__file__).resolve().parent / "lib"
+    if choice == "checked":
+        return lib_dir / "libpsi_cuda_checked.so"
+    return Path(choice) if choice else lib_dir / "libpsi_cuda.so"
+
+
+_LIB_PATH = _library_file()
 _lib = None
 
 

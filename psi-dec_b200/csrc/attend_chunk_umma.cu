@@ -30,12 +30,6 @@
 
 namespace psi {
 
-#ifdef PSI_UMMA_TRACE
-// Build-time tracing (-DPSI_UMMA_TRACE): per CTA its cycles in the kernel, the 64-token tiles it processed and the
-// cycles its row threads spent waiting for S, at item ends, in merges of cut units (with their count and pieces) and
-// from an item's end to the start of its merge; read back with psi_debug_umma_cta.
-__device__ unsigned long long g_umma_cta[148 * 8];
-#endif
 
 namespace {
 
@@ -222,10 +216,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
     const uint32_t cta = blockIdx.x;
     if (cta >= p.scalars[kScalarNumChunkCtas]) return;
-#ifdef PSI_UMMA_TRACE
-    const long long trace_t0 = clock64();
-    long long trace_wait_s = 0, trace_item = 0, trace_merge = 0, trace_merges = 0, trace_pieces = 0, trace_partial = 0;
-#endif
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bars[kNumBarriers];
@@ -447,13 +437,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 const uint32_t tile = tile_base + i, buf = tile & 1;
                 const uint32_t token0 = (first_tile + i) * kUmmaN;
                 const uint32_t tmem_s = tmem + kColS + buf * kUmmaN + lane_base;
-#ifdef PSI_UMMA_TRACE
-                const long long trace_w0 = clock64();
-#endif
                 wait(kBarS + buf, tile >> 1);
-#ifdef PSI_UMMA_TRACE
-                trace_wait_s += clock64() - trace_w0;
-#endif
                 __syncwarp();  // the TMEM accesses below are warp-collective
                 tc_fence_after();
 
@@ -538,9 +522,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                 tc_fence_after();
             }
             tile_base += num_tiles;
-#ifdef PSI_UMMA_TRACE
-            const long long trace_e0 = clock64();
-#endif
             // The next item's query rows go to TMEM before this item's output is written: its first Q K^T products then
             // run under the epilogue (O is not touched before P of that item's first tile exists).
             if (index + 1 < item_end) load_q(view_item(p, index + 1));
@@ -605,16 +586,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     __threadfence();  // the other pieces' partials are read (from L2) only after their arrivals were seen
                 }
                 row_threads_sync();
-#ifdef PSI_UMMA_TRACE
-                const long long trace_m0 = clock64();
-                trace_partial += trace_m0 - trace_e0;
-#endif
                 for (uint32_t tile = 0; tile < 8; ++tile) {
                     if (!last_s[tile]) continue;
-#ifdef PSI_UMMA_TRACE
-                    trace_merges += 1;
-                    trace_pieces += v.unit_num_items;
-#endif
                     // 16 rows x D / 4 float4 outputs per tile: a thread takes row tid % 16 and the float4 columns
                     // tid / 16 + 8 j (16 consecutive lanes read 256 consecutive bytes of the column-major slots)
                     const uint32_t tile_tokens = min(p.tokens_per_tile, v.num_tokens - tile * p.tokens_per_tile);
@@ -691,28 +664,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
                     if (tid == 0) p.unit_counters[v.reduce_unit + tile] = 0;  // ready for the next launch
                 }
                 row_threads_sync();  // the flags are read before the next item overwrites them
-#ifdef PSI_UMMA_TRACE
-                trace_merge += clock64() - trace_m0;
-#endif
             }
-#ifdef PSI_UMMA_TRACE
-            trace_item += clock64() - trace_e0;
-#endif
         }
     }
 
-#ifdef PSI_UMMA_TRACE
-    if (tid == 0 && cta < 148) {
-        g_umma_cta[cta * 8] = clock64() - trace_t0;
-        g_umma_cta[cta * 8 + 1] = tile_base;
-        g_umma_cta[cta * 8 + 2] = trace_wait_s;
-        g_umma_cta[cta * 8 + 3] = trace_item;
-        g_umma_cta[cta * 8 + 4] = trace_merge;
-        g_umma_cta[cta * 8 + 5] = trace_merges;
-        g_umma_cta[cta * 8 + 6] = trace_pieces;
-        g_umma_cta[cta * 8 + 7] = trace_partial;
-    }
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {
@@ -784,12 +739,6 @@ cudaError_t launch_for_dim(const AttendParams& p, uint32_t num_ctas, cudaStream_
 
 // cudaErrorNotSupported: the arena cannot be described to the TMA unit (alignment, size); nothing was launched and
 // the caller takes launch_attend_chunk instead.
-#ifdef PSI_UMMA_TRACE
-extern "C" __attribute__((visibility("default"))) int psi_debug_umma_cta(unsigned long long* out) {
-    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
-    return cudaMemcpyFromSymbol(out, g_umma_cta, sizeof(g_umma_cta)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 cudaError_t launch_attend_chunk_umma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     if (num_ctas == 0) return cudaSuccess;

@@ -37,19 +37,6 @@ struct SmemLayout {
     static constexpr uint32_t kTotal = kRingOffset + (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes);
 };
 
-#ifdef PSI_MMA_TRACE
-// Build-time tracing (-DPSI_MMA_TRACE): per work slot the global-timer stamps (ns) of kernel entry, first K/V tile
-// landed, end of the last tile loop and exit, how many units it merged, the prologue's stages (metadata read, page ids
-// read, first copies issued) and the SM that ran it; read back with psi_debug_mma_cta.  psi_debug_mma_set_rotation
-// shifts the work slots over the CTAs, which separates what follows the slot from what follows the SM.
-__device__ unsigned long long g_mma_cta[148 * 10];
-__device__ unsigned g_mma_rotation;  // work slot of a CTA = (blockIdx.x + rotation) % gridDim.x
-__device__ __forceinline__ unsigned long long trace_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#endif
 
 // kExchange: the launch is one rank's part of a KV-range exchange (exchange.cuh); the outputs go to the rank's slot of
 // the owner's receive area (ext_*), and the launch ends with the flag publication and, on the owner, the merge.
@@ -59,14 +46,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     constexpr uint32_t kChunks = D / 8;                      // 16-byte chunks per row
     constexpr uint32_t kRowsPerCopy = 32 / (kChunks < 32 ? kChunks : 32);
 
-#ifdef PSI_MMA_TRACE
-    const uint32_t cta = (blockIdx.x + g_mma_rotation) % gridDim.x;
-    const unsigned long long trace_t0 = trace_now();
-    unsigned long long trace_first = 0, trace_loop_end = 0, trace_merged = 0, trace_items = 0;
-    unsigned long long trace_meta = 0, trace_ids = 0, trace_issued = 0, trace_staged = 0;
-#else
     const uint32_t cta = blockIdx.x;
-#endif
     // One round trip for everything the first tile copies depend on: the CTA count, this CTA's item range and a copy
     // of its first item all go out before the first of them is needed.
     const uint32_t num_ctas = p.scalars[kScalarNumCtas];
@@ -74,9 +54,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     const bool have_first = p.cta_first_items != nullptr;
     const ItemView first_item = view_item(have_first ? p.cta_first_items + cta : p.items);
     if (cta >= num_ctas) return;
-#ifdef PSI_MMA_TRACE
-    trace_meta = trace_now();
-#endif
 
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint32_t limit_s[kTile];
@@ -114,6 +91,8 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     const uint32_t copy_x = copy_chunk ^ copy_row;                  // copy_row < 8: XOR-able with the row step below
 
     const bool fused = p.new_k != nullptr;
+    const PageBounds bounds(p.geo);
+    uint32_t bad_page = 0;  // set when a table index or page ID was out of bounds (that read went to page 0 instead)
     for (uint32_t index = item_begin; index < item_end; ++index) {
         const ItemView v = (have_first && index == item_begin) ? first_item : view_item(p, index);
         __syncthreads();  // the previous item's merge is done with the ring, with q and with limit_s
@@ -127,18 +106,19 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         const uint32_t item_tiles = end_tile - first_tile;
         const uint32_t my_tiles = item_tiles > warp ? (item_tiles - warp + kWarps - 1) / kWarps : 0;
         const uint32_t my_halves = 2 * my_tiles;  // K tile, V tile, K tile, ...
+        auto tile_of = [&](uint32_t j) { return first_tile + warp + j * kWarps; };
         const uint32_t* row_ids = table_row(p.geo, v.req_slot);
         const uint64_t head_bytes = static_cast<uint64_t>(v.kv_head) * p.geo.tokens_per_page * L::kRowBytes;
 
         // Page ids of the two 8-token halves of local tile i (equal when a page holds 16 tokens or more).
         auto lookup = [&](uint32_t i, uint32_t& id_lo, uint32_t& id_hi) {
-            const uint32_t token = (first_tile + warp + i * kWarps) * kTile;
-            id_lo = token < paged_end ? page_id_or_zero(p.geo, row_ids, token >> page_shift) : 0u;
-            id_hi = token + 8 < paged_end ? page_id_or_zero(p.geo, row_ids, (token + 8) >> page_shift) : 0u;
+            const uint32_t token = tile_of(i) * kTile;
+            id_lo = token < paged_end ? bounds.read(row_ids, token >> page_shift, bad_page) : 0u;
+            id_hi = token + 8 < paged_end ? bounds.read(row_ids, (token + 8) >> page_shift, bad_page) : 0u;
         };
         // Issues the copies of half-tile h (K of tile h/2 when h is even, else V) into ring slot `slot`.
         auto issue = [&](uint32_t h, uint32_t slot, uint32_t id_lo, uint32_t id_hi) {
-            const uint32_t token0 = (first_tile + warp + (h >> 1) * kWarps) * kTile;
+            const uint32_t token0 = tile_of(h >> 1) * kTile;
             const uint32_t dst0 = ring_base + slot * L::kTileBytes + copy_row * L::kRowBytes;
             const uint64_t region = head_bytes + ((h & 1) ? v_region_bytes : 0) + copy_src;
             const unsigned char* src_lo =
@@ -192,9 +172,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         uint32_t cur_lo = 0, cur_hi = 0, next_lo = 0, next_hi = 0;
         if (my_tiles > 0) lookup(0, cur_lo, cur_hi);
         if (my_tiles > 1) lookup(1, next_lo, next_hi);
-#ifdef PSI_MMA_TRACE
-        if (trace_ids == 0) trace_ids = (cur_lo == 0xFFFFFFFFu ? 1 : 0) + trace_now();
-#endif
 #pragma unroll
         for (uint32_t h = 0; h < NSLOT - 1; ++h) {
             if (h < my_halves) {
@@ -208,9 +185,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             cp_async_commit();
         }
 
-#ifdef PSI_MMA_TRACE
-        if (trace_issued == 0) trace_issued = trace_now();
-#endif
         // ---- with the first tiles in flight: the per-row causal limits, and in the fused step this item's share of the
         // step's K/V rows into their pages -------------------------------------------------------------------------------
         if (tid < kTile) limit_s[tid] = tid < v.rows ? item_row_limit(v, tid) : v.kv_end;
@@ -233,9 +207,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         cp_async_wait<NSLOT - 1>();  // the query rows (the oldest group) have landed; the K/V tiles stay in flight
         __syncthreads();
 
-#ifdef PSI_MMA_TRACE
-        if (trace_staged == 0) trace_staged = trace_now();
-#endif
         const uint32_t limit0 = limit_s[quad_row], limit1 = limit_s[quad_row + 8];
         uint32_t limit_min = v.kv_end;
         for (uint32_t r = 0; r < v.rows; ++r) limit_min = min(limit_min, limit_s[r]);
@@ -244,9 +215,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         for (uint32_t h = 0; h < my_halves; ++h) {
             cp_async_wait<NSLOT - 2>();
             __syncwarp();
-#ifdef PSI_MMA_TRACE
-            if (trace_first == 0) trace_first = trace_now();
-#endif
             const uint32_t ahead = h + NSLOT - 1;
             if (ahead < my_halves) {
                 issue(ahead, ahead % NSLOT, cur_lo, cur_hi);
@@ -260,7 +228,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
 
             const uint32_t slot_base = ring_base + (h % NSLOT) * L::kTileBytes;
             if ((h & 1) == 0) {
-                const uint32_t token0 = (first_tile + warp + (h >> 1) * kWarps) * kTile;
+                const uint32_t token0 = tile_of(h >> 1) * kTile;
                 const bool masked = token0 < v.kv_begin || token0 + kTile > limit_min;
                 TileMath<T, D>::scores(frag, q_base, slot_base, p.scale_log2, masked, token0, limit0, limit1,
                                        v.kv_begin, st, pa);
@@ -269,11 +237,8 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             }
         }
 
-#ifdef PSI_MMA_TRACE
-        trace_loop_end = trace_now();
-        trace_items += 1;
-#endif
         // ---- merge the warps' partial results --------------------------------------------------------------------------
+        const bool is_partial = v.partial_slot != kU32Max;
         cp_async_wait<0>();
         if (kExchange && index == item_begin && tid == 0) slot_free_s = slot_is_free(p.xchg, consumed_early) ? 1u : 0u;
         __syncthreads();  // every warp is done with its ring: the merge buffer may overwrite it
@@ -302,7 +267,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         }
         __syncthreads();
 
-        const bool is_partial = v.partial_slot != kU32Max;
         for (uint32_t i = tid; i < v.rows * (D / 4); i += kThreads) {
             const uint32_t r = i / (D / 4), c4 = i % (D / 4);
             float row_max = -INFINITY;
@@ -357,9 +321,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             if (tid == 0) arrival_s = atomicAdd(p.unit_counters + v.reduce_unit, 1u);
             __syncthreads();
             if (arrival_s == v.unit_num_items - 1) {
-#ifdef PSI_MMA_TRACE
-                trace_merged += 1;
-#endif
                 __threadfence();
                 // Every thread merges its own outputs (row r, four columns in each half of the row) from all pieces:
                 // the pieces' statistics of row r and their O values go out together, four pieces at a time, so a
@@ -443,27 +404,11 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             }
         }
     }
+    if (bad_page != 0) record_page_fault(p.geo);
     if (kExchange) {
         exchange_publish(p.xchg, p.status, num_ctas, item_begin < item_end && slot_free_s == 0);
         if (p.xchg.recv != nullptr) exchange_merge<kThreads>(p.xchg, p.status, p.out, p.dtype, D, cta, num_ctas);
     }
-#ifdef PSI_MMA_TRACE
-    if (tid == 0 && cta < 148) {
-        g_mma_cta[cta * 10] = trace_t0;
-        g_mma_cta[cta * 10 + 1] = trace_first;
-        g_mma_cta[cta * 10 + 2] = trace_loop_end;
-        g_mma_cta[cta * 10 + 3] = trace_now();
-        g_mma_cta[cta * 10 + 4] = trace_merged;
-        g_mma_cta[cta * 10 + 5] = trace_items;
-        g_mma_cta[cta * 10 + 6] = trace_meta;
-        g_mma_cta[cta * 10 + 7] = trace_ids;
-        g_mma_cta[cta * 10 + 8] = trace_issued;
-        unsigned smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        g_mma_cta[cta * 10 + 9] = smid;
-        (void)trace_staged;
-    }
-#endif
 }
 
 template <int D>
@@ -504,15 +449,6 @@ bool attend_mma_supported(uint32_t dtype, uint32_t head_dim, uint32_t tokens_per
 
 uint32_t attend_mma_ctas_per_sm(uint32_t /*head_dim*/) { return 1; }
 
-#ifdef PSI_MMA_TRACE
-extern "C" __attribute__((visibility("default"))) int psi_debug_mma_cta(unsigned long long* out) {
-    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
-    return cudaMemcpyFromSymbol(out, g_mma_cta, sizeof(g_mma_cta)) == cudaSuccess ? 0 : 1;
-}
-extern "C" __attribute__((visibility("default"))) int psi_debug_mma_set_rotation(unsigned rotation) {
-    return cudaMemcpyToSymbol(g_mma_rotation, &rotation, sizeof(rotation)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 cudaError_t launch_attend_mma(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     if (num_ctas == 0) return cudaSuccess;

@@ -184,6 +184,15 @@ def custom(num_q_heads: int, num_kv_heads: int, head_dim: int, tokens_per_page: 
     return Spec(name, B.BF16, num_q_heads, num_kv_heads, head_dim, tokens_per_page, ctx, q_len, seed)
 
 
+def explicit(num_q_heads: int, num_kv_heads: int, head_dim: int, tokens_per_page: int, contexts, q_len: int = 1,
+             seed: int = 11, dtype: int = B.BF16) -> Spec:
+    """A decode batch with the given context lengths, one sequence each (the reference's own bench fixtures are of
+    this kind: crates/inference-backend-metal/benches/gqa/split_kv.rs:19-54)."""
+    name = (f"explicit-hq{num_q_heads}-hkv{num_kv_heads}-d{head_dim}-p{tokens_per_page}-ctx"
+            + "+".join(str(int(c)) for c in contexts) + f"-q{q_len}")
+    return Spec(name, dtype, num_q_heads, num_kv_heads, head_dim, tokens_per_page, list(contexts), q_len, seed)
+
+
 class Session:
     """One workload resident on one GPU: arena (random K/V everywhere), block tables, GQA component, q/k/v/out."""
 

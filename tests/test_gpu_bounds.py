@@ -1,20 +1,23 @@
-"""Bounds checks on page IDs: on the host where IDs enter the table, and in every kernel before an address is formed.
+"""Bounds checks on page IDs: on the host where IDs enter the table (both builds of the library), and in every kernel
+before an address is formed (the checked build, libpsi_cuda_checked.so, driven by tests/checked_build_worker.py in a
+process of its own).
 
-The device cases declare an arena of 8 pages over a buffer that really holds 16 and put page ID 12 into the table: the
-access the check must skip would have stayed inside the buffer anyway, so no run of these tests can touch memory it
-does not own.  The reference checks IDs on the way into the table (crates/inference-executor-metal/src/state/gqa.rs:
-97-102) and table indices with debug assertions (crates/inference-executor-metal/src/attn/gqa/request_page_table.rs:
-75,115); its shaders trust the table.
+The reference checks IDs on the way into the table (crates/inference-executor-metal/src/state/gqa.rs:97-102) and table
+indices with debug assertions (crates/inference-executor-metal/src/attn/gqa/request_page_table.rs:75,115); its shaders
+trust the table, and so does the production build here.
 """
-import numpy as np
+import os
+import subprocess
+import sys
+from pathlib import Path
+
 import pytest
 
 import workloads as W
 
 pkg = W.pkg
 pytestmark = pytest.mark.gpu
-
-PSI_ERR_PAGE_ID = 6
+ROOT = Path(__file__).resolve().parent.parent
 
 
 class Small:
@@ -65,68 +68,11 @@ def test_table_refuses_page_ids_beyond_its_declared_bound():
     s.close()
 
 
-@pytest.mark.parametrize("dtype,kernel_mode", [(pkg.BF16, pkg.KERNEL_AUTO), (pkg.BF16, pkg.KERNEL_GENERIC),
-                                               (pkg.F32, pkg.KERNEL_AUTO)])
-def test_kernels_skip_an_out_of_range_page_id_and_report_it(dtype, kernel_mode):
-    import torch
-    s = Small(dtype=dtype, kernel_mode=kernel_mode)
-    s.table.write_row(0, 0, [3, 12, 1, 0])                  # logical page 1 -> physical 12, beyond the declared 8
-    before = s.buffer.clone()
-
-    # append of token 20 (logical page 1): the write is skipped, nothing in the buffer changes
-    s.gqa.prepare([0], [20], [0, 1])
-    s.gqa.kv_page_write(s.pages, s.table, 0, s.k, s.v)
-    assert s.gqa.device_status() == PSI_ERR_PAGE_ID
-    assert torch.equal(s.buffer.view(torch.uint8), before.view(torch.uint8))
-    assert s.gqa.device_status() == 0                       # cleared by the read
-
-    # attention over tokens 0..20 reads logical page 1: flagged (the read went to page 0 instead)
-    s.gqa.attend(s.pages, s.table, 0, s.q, s.out)
-    assert s.gqa.device_status() == PSI_ERR_PAGE_ID
-
-    # the fused step both reads and writes through the bad entry
-    s.gqa.append_attend(s.pages, s.table, 0, s.k, s.v, s.q, s.out)
-    assert s.gqa.device_status() == PSI_ERR_PAGE_ID
-    assert torch.equal(s.buffer.view(torch.uint8), before.view(torch.uint8))
-
-    # gather of tokens 16..24 leaves its outputs untouched
-    k_out = torch.full((8, s.hkv, s.d), 7.0, device="cuda:0", dtype=s.buffer.dtype)
-    v_out = torch.full_like(k_out, 7.0)
-    s.gqa.page_gather(s.pages, s.table, 0, 0, 16, 24, k_out, v_out)
-    assert s.gqa.device_status() == PSI_ERR_PAGE_ID
-    assert bool((k_out == 7.0).all()) and bool((v_out == 7.0).all())
-
-    # with the entry repaired the same calls run clean
-    s.table.write_row(0, 0, [3, 5, 1, 0])
-    s.gqa.append_attend(s.pages, s.table, 0, s.k, s.v, s.q, s.out)
-    assert s.gqa.device_status() == 0
-    assert not torch.equal(s.buffer.view(torch.uint8), before.view(torch.uint8))
-    s.close()
-
-
-def test_chunk_kernels_report_an_out_of_range_page_id():
-    # a long query run (96 tokens of one request = 12 query tiles of 8 tokens at G = 2) goes to the chunk kernels
-    import torch
-    for kernel_mode in (pkg.KERNEL_AUTO, pkg.KERNEL_MMA_SYNC):
-        s = Small(kernel_mode=kernel_mode, head_dim=128)
-        layout = pkg.GQAPageTableLayout(1, 1, 8, 1)
-        table = pkg.GQARequestPageTable(s.ctx, layout)
-        cfg = pkg.GQAConfig(s.hq, s.hkv, s.d, 0.1, s.page_bytes, pkg.BF16, layout, 96, pkg.PLAN_BALANCED, kernel_mode, 0)
-        gqa = pkg.GQA(s.ctx, cfg)
-        table.write_row(0, 0, [3, 12, 1, 0, 2, 4, 6, 7])    # 8 logical pages = 128 tokens; logical page 1 is bad
-        q = torch.randn((96, s.hq, s.d), device="cuda:0", dtype=torch.float32).to(torch.bfloat16)
-        out = torch.zeros_like(q)
-        gqa.prepare([0], [32], [0, 96])                     # 96 query tokens at positions 32..127
-        assert gqa.plan_stats()["chunk_ctas"] > 0
-        gqa.attend(s.pages, table, 0, q, out)
-        assert gqa.device_status() == PSI_ERR_PAGE_ID
-        table.write_row(0, 0, [3, 5, 1, 0, 2, 4, 6, 7])
-        gqa.attend(s.pages, table, 0, q, out)
-        assert gqa.device_status() == 0
-        s.ctx.sync()
-        gqa.close()
-        table.close()
-        s.close()
+def test_every_kernel_of_the_checked_build_skips_and_reports_an_out_of_range_page_id():
+    worker = ROOT / "tests" / "checked_build_worker.py"
+    done = subprocess.run([sys.executable, str(worker)], capture_output=True, text=True, timeout=900,
+                          env={**os.environ, "PSI_CUDA_LIBRARY": "checked"})
+    assert done.returncode == 0 and "checked build ok" in done.stdout, done.stdout[-3000:] + done.stderr[-3000:]
 
 
 def test_snapshot_load_refuses_ids_beyond_the_declared_bound(tmp_path):

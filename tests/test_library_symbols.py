@@ -20,6 +20,10 @@ def test_header_declares_and_library_exports_every_entry_point():
     assert len(names) >= 40
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
+    # the bounds-checked build is the same library with device-side checks compiled in: same exports
+    checked = C.CDLL(str(entry.load_package().library_path().with_name("libpsi_cuda_checked.so")))
+    missing = [n for n in names if not hasattr(checked, n)]
+    assert not missing, missing
 
 
 def test_no_cpu_fallback_without_a_device():

@@ -39,6 +39,10 @@ def test_custom_decode_batch_and_its_bench_argument():
         bench.workload(W, argparse.Namespace(shape="1,2,3", gpus=1, config=2, scale_down=1))
     with pytest.raises(SystemExit):
         bench.workload(W, argparse.Namespace(shape="32,8,128,8,12,100,900", gpus=2, config=2, scale_down=1))
+    # --shape HQ,HKV,D,PAGE --contexts C1,C2,...: one sequence per listed context (the reference's own bench fixtures)
+    ragged = bench.workload(W, argparse.Namespace(shape="32,8,128,16", contexts="128,128,4096", dtype="f32", gpus=1, config=2,
+                                                  scale_down=1))
+    assert ragged.context_lens.tolist() == [128, 128, 4096] and ragged.dtype == O.F32 and ragged.tokens_per_page == 16
 
 
 def test_kv_range_sharding_covers_each_context_once():
