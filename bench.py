@@ -61,11 +61,62 @@ def measured_tensor_peak():
     return FALLBACK_BF16_TFLOPS, "fallback"
 
 
+TRAFFIC_SUMMARY = ROOT / "profiles" / "attend_mma_dram_traffic.txt"
+KERNEL_SOURCES = ("attend_mma.cu", "mma_common.cuh", "device_common.cuh")
+
+
+def kernel_source_hash() -> str:
+    digest = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        digest.update((ROOT / "psi-dec_b200" / "csrc" / name).read_bytes())
+    return digest.hexdigest()
+
+
+def record_traffic(report: str, workload_name: str, command: str):
+    """Reads an ncu report of the decode kernel (here, no GPU needed) and writes the per-launch DRAM traffic beside the
+    profiler summaries, with the hash of the kernel sources it was taken with:
+
+        python bench.py --record-traffic gpurun_out/prof_attend_mma_cfg2.ncu-rep
+    """
+    import csv
+    raw = subprocess.run(["ncu", "-i", report, "--page", "raw", "--csv"], capture_output=True, text=True, check=True).stdout
+    rows = list(csv.reader(raw.splitlines()))
+    header, units = rows[0], rows[1]
+    col = {name: i for i, name in enumerate(header)}
+    scale = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    launches = []
+    for row in rows[2:]:
+        if "attend_mma_kernel" not in row[col["Kernel Name"]]:
+            continue
+        total = 0.0
+        for metric in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+            total += float(row[col[metric]]) * scale[units[col[metric]]]
+        launches.append(total)
+    if not launches:
+        raise SystemExit("the report holds no attend_mma_kernel launch")
+    import __graft_entry__ as entry
+    entry.load_package()
+    from psi_dec_b200 import workloads as W
+    spec = {c.name: c for c in (W.config(i) for i in (2, 3, 4))}[workload_name]
+    TRAFFIC_SUMMARY.write_text(
+        "# DRAM traffic of one attend_mma_kernel launch (ncu: dram__bytes_read.sum + dram__bytes_write.sum, mean of the\n"
+        "# captured launches); bench.py scales it by a run's algorithmic bytes for roofline.traffic and ignores it once\n"
+        "# the kernel sources named by the hash have changed.  Written by: python bench.py --record-traffic <report>\n"
+        f"workload: {workload_name}\n"
+        f"captured_launches: {len(launches)}\n"
+        f"dram_bytes_per_launch: {int(sum(launches) / len(launches))}\n"
+        f"algorithmic_bytes_per_launch: {spec.algorithmic_bytes()['total']}\n"
+        f"kernel_sources: {' '.join(KERNEL_SOURCES)}\n"
+        f"kernel_source_sha256: {kernel_source_hash()}\n"
+        f"capture_command: {command}\n")
+    print(TRAFFIC_SUMMARY.read_text())
+
+
 def recorded_traffic(workload_name: str, algorithmic_bytes: int):
     """DRAM bytes per launch of the decode kernel from the committed profiler summary of this workload, scaled by the
     launch's algorithmic bytes.  The summary names the kernel sources it was taken with (a hash); when they have
     changed since, the figure is stale and None is returned together with that fact."""
-    summary = ROOT / "profiles" / "attend_mma_dram_traffic.txt"
+    summary = TRAFFIC_SUMMARY
     if not summary.exists():
         return None, "no profiler summary"
     fields = {}
@@ -75,10 +126,7 @@ def recorded_traffic(workload_name: str, algorithmic_bytes: int):
             fields[key.strip()] = value.strip()
     if fields.get("workload") != workload_name:
         return None, "profiler summary covers another workload"
-    digest = hashlib.sha256()
-    for name in ("attend_mma.cu", "mma_common.cuh", "device_common.cuh"):
-        digest.update((ROOT / "psi-dec_b200" / "csrc" / name).read_bytes())
-    if fields.get("kernel_source_sha256") != digest.hexdigest():
+    if fields.get("kernel_source_sha256") != kernel_source_hash():
         return None, "profiler summary predates the current kernel source"
     per_byte = float(fields["dram_bytes_per_launch"]) / float(fields["algorithmic_bytes_per_launch"])
     return int(per_byte * algorithmic_bytes), "ncu dram__bytes_read.sum + dram__bytes_write.sum, scaled by algorithmic bytes"
@@ -692,7 +740,16 @@ def main():
     parser.add_argument("--exchange", choices=["p2p", "p2p3", "nccl"], default="p2p",
                         help="partial exchange of the KV-range-split configuration 4: one launch per rank (p2p), the "
                              "same data path as three launches (p2p3), or an NCCL all-gather")
+    parser.add_argument("--record-traffic", default=None, metavar="REPORT.ncu-rep",
+                        help="no run: read an ncu report of the decode kernel and write profiles/attend_mma_dram_traffic.txt")
+    parser.add_argument("--capture-command", default="ncu --set full --clock-control none -k regex:attend_mma -s 4 -c 2 -o "
+                        "gpurun_out/prof_attend_mma_cfg2 python bench.py --config 2 --steps 3 --warmup 3 --no-cpu-baseline "
+                        "--no-read-probe --no-splits", help="with --record-traffic: the command that made the report")
     args = parser.parse_args()
+    if args.record_traffic:
+        record_traffic(args.record_traffic, {2: "cfg2-a3b-layer-decode", 3: "cfg3-27b-mtp-verify", 4: "cfg4-long-context"}[args.config or 2],
+                       args.capture_command)
+        return
     if args.impl == "reference":
         bench_reference(args)
     else:

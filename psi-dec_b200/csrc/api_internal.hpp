@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <algorithm>
 #include <cmath>
@@ -65,21 +66,29 @@ struct psi_ctx {
 
 namespace psi {
 
-// Counts one launch and, while timing is on, brackets it with events on the context's stream.
+// Counts one launch, names it for a timeline profiler (an NVTX range per launch: a no-op costing a few nanoseconds
+// when no tool is attached), and, while timing is on, brackets it with events on the context's stream.
 struct LaunchScope {
     psi_ctx* ctx;
     cudaEvent_t end = nullptr;
     LaunchScope(psi_ctx* c, uint32_t kernel_class) : ctx(c) {
         ctx->launches += 1;
-        if (!ctx->timing || ctx->capturing) return;
-        cudaEvent_t begin = nullptr;
-        cuda_check(cudaEventCreate(&begin), "cudaEventCreate");
-        cuda_check(cudaEventCreate(&end), "cudaEventCreate");
-        ctx->timed[kernel_class].emplace_back(begin, end);
-        cuda_check(cudaEventRecord(begin, ctx->stream), "cudaEventRecord");
+        if (ctx->timing && !ctx->capturing) {
+            cudaEvent_t begin = nullptr;
+            cuda_check(cudaEventCreate(&begin), "cudaEventCreate");
+            cuda_check(cudaEventCreate(&end), "cudaEventCreate");
+            ctx->timed[kernel_class].emplace_back(begin, end);
+            cuda_check(cudaEventRecord(begin, ctx->stream), "cudaEventRecord");
+        }
+        // last, so that nothing that can throw stands between the push and the destructor's pop
+        static const char* const kNames[kKernelClasses] = {"psi kv_append",     "psi attend_map", "psi attend_reduce",
+                                                           "psi combine",       "psi page_gather", "psi attend_chunk",
+                                                           "psi norm_rope_append"};
+        nvtxRangePushA(kernel_class < kKernelClasses ? kNames[kernel_class] : "psi launch");
     }
     ~LaunchScope() {
         if (end != nullptr) (void)cudaEventRecord(end, ctx->stream);
+        nvtxRangePop();
     }
 };
 

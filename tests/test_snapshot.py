@@ -216,3 +216,21 @@ def test_writer_contracts(tmp_path):
     writer.close()
     with pytest.raises(pkg.PsiError, match="page ID ranges must be nonempty, sorted"):
         pkg.StateSnapshotWriter(tmp_path / "fourth", [PAGE_ARENA], Plan.selected([], [(3, 5), (5, 6)]))
+
+
+def test_manifest_bytes_match_the_committed_fixture(tmp_path):
+    # tests/golden/snapshot_manifest_selected.hex is the byte-for-byte manifest of a two-file Selected snapshot, one
+    # annotated field per line, kept so that a Rust-side test can decode it with the reference's own manifest type;
+    # here: the library still writes exactly those bytes, and they are what the independent restatement above gives.
+    import importlib.util
+    from pathlib import Path
+    golden = Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_manifest_fixture", golden / "make_manifest_fixture.py")
+    maker = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(maker)
+    raw = maker.write_snapshot(tmp_path / "snapshot")
+    stored = b"".join(bytes.fromhex(line.split("|")[0]) for line in
+                      (golden / "snapshot_manifest_selected.hex").read_text().splitlines() if not line.startswith("#"))
+    assert raw == stored
+    plan = Plan.selected(maker.REQUEST_SLOT_RANGES, maker.PAGE_ID_RANGES)
+    assert raw == manifest_bytes(plan, [(0, 0, 3 * 16), (2, 1, len(maker.METADATA))])
