@@ -316,12 +316,17 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
 
         // ---- the CTA that delivers a unit's last partial merges the unit -------------------------------------------------
         if (is_partial) {
-            __threadfence();  // this thread's partial stores are visible device-wide before the arrival is counted
+            // The barrier orders every thread's partial stores before thread 0's fence, and the fence (cumulative)
+            // makes them visible device-wide before the arrival is counted; the second fence orders the count before
+            // the reads of the other pieces' partials that follow the next barrier.
             __syncthreads();
-            if (tid == 0) arrival_s = atomicAdd(p.unit_counters + v.reduce_unit, 1u);
+            if (tid == 0) {
+                __threadfence();
+                arrival_s = atomicAdd(p.unit_counters + v.reduce_unit, 1u);
+                __threadfence();
+            }
             __syncthreads();
             if (arrival_s == v.unit_num_items - 1) {
-                __threadfence();
                 // Every thread merges its own outputs (row r, four columns in each half of the row) from all pieces:
                 // the pieces' statistics of row r and their O values go out together, four pieces at a time, so a
                 // unit of up to four pieces and eight rows costs every thread one round trip.  The two column groups

@@ -96,9 +96,11 @@ __device__ __forceinline__ uint32_t settle_verdict(uint32_t* word, const uint32_
 // the CTA that arrives last release-stores the step into the rank's flag.  `failed`: this CTA did not store (its wait
 // for the slot ran out), so the flag is held back and PSI_ERR_TIMEOUT recorded.
 __device__ __forceinline__ void exchange_publish(const ExchangeParams& x, uint32_t* status, uint32_t num_ctas, bool failed) {
-    __threadfence_system();  // this thread's stores into the slot are visible system-wide before the arrival counts
+    // The barrier orders every thread's stores into the slot before thread 0's system-wide fence (cumulative), which
+    // makes them visible to the owner before the arrival counts.
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         const uint32_t mine = failed ? (1u | kArrivalFailed) : 1u;
         const uint32_t total = atomicAdd(x.sync_words + kSyncLaunchArrivals, mine) + mine;
         if ((total & 0xFFFFu) == num_ctas) {
