@@ -449,9 +449,13 @@ PSI_API int32_t psi_gqa_combine(psi_gqa* gqa, const float* const* o, const float
  * to `flag` (in the owner's memory) once everything enqueued before it is visible system-wide.  The owner runs
  * psi_gqa_combine_wait: the merge of psi_gqa_combine, preceded by a BOUNDED wait until each of the n flags (device
  * array in the owner's own memory) has reached flag_value.  If a producer never publishes, the wait gives up after
- * max_polls polls (0 = default, roughly a fraction of a second), writes nothing to `out`, and records PSI_ERR_TIMEOUT,
- * which psi_gqa_device_status returns (and clears) after waiting for the stream; the context stays usable.  Flag values
- * should increase from step to step (a step counter), so flags never need resetting.  No reference counterpart: the
+ * max_polls polls (0 = default, roughly a fraction of a second), writes nothing to `out` (the launch reaches one
+ * verdict for all of its CTAs), and records PSI_ERR_TIMEOUT, which psi_gqa_device_status returns (and clears) after
+ * waiting for the stream; the context stays usable.  Flag values should increase from step to step (a step counter),
+ * so flags never need resetting.  This form has ONE receive buffer per producer and nothing in it holds a producer
+ * back: the caller must not let any producer start step s + 1 before the owner's psi_gqa_combine_wait of step s has
+ * finished (otherwise the merge can read a mix of two steps); psi_gqa_attend_exchange below carries that ordering in
+ * its own protocol and is the form to use.  No reference counterpart: the
  * reference has no multi-device path (crates/inference-runtime-core/src/network/mod.rs is empty). */
 PSI_API int32_t psi_gqa_signal(psi_gqa* gqa, uint32_t* flag, uint32_t value);
 PSI_API int32_t psi_gqa_combine_wait(psi_gqa* gqa, const float* const* o, const float* const* m, const float* const* l,

@@ -27,6 +27,7 @@
 
 #include "launch_util.hpp"
 #include "mma_common.cuh"
+#include "tma_common.cuh"
 
 namespace psi {
 
@@ -37,9 +38,6 @@ constexpr uint32_t kRowThreads = 128;   // warps 0-3: one accumulator row per th
 constexpr uint32_t kUmmaThreads = 224;  // + warp 4: MMA issue, warps 5 and 6: K and V tiles into the shared-memory ring
 constexpr uint32_t kUmmaM = 128;   // query rows per CTA = TMEM lanes
 constexpr uint32_t kUmmaN = 64;    // KV tokens per tile
-constexpr uint32_t kMaxPolls = 200000;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* ptr) { return static_cast<uint32_t>(__cvta_generic_to_shared(ptr)); }
 
 // Shared-memory matrix descriptor of a 128-byte-swizzled operand: start address, leading / stride byte offsets in
 // 16-byte units, descriptor version 1, layout type 2 (SWIZZLE_128B).
@@ -64,38 +62,8 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
         : "memory");
 }
 
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Bounded wait on one phase of an mbarrier; false when the bound ran out.
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-
-// Non-blocking test of one phase.
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kMaxPolls; ++i) {
-        if (mbar_try(bar, parity)) return true;
-    }
-    return false;
-}
 
 // 32 consecutive f32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
@@ -130,37 +98,8 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const float (&v)[32
 
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
-// Byte offset of the 16-byte chunk `chunk` (8 elements) of token row `row` in a K or V tile.  A tile is a stack of
-// [row / 8][element block of 64][row % 8][64 elements]: every (8 rows x 128 bytes) block is one swizzle atom (chunk
-// index XOR row % 8), the `blocks` atoms of an 8-row group follow one another, groups are blocks * 1024 bytes apart.
-__device__ __forceinline__ uint32_t operand_offset(uint32_t blocks, uint32_t row, uint32_t chunk) {
-    return ((row >> 3) * blocks + (chunk >> 3)) * 1024 + (row & 7) * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-}
 
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-// One TMA box of the page arena into shared memory; completion is counted in bytes on `bar`.  The arena is viewed as
-// [page][8-row group][element block][row in group][64 elements], a box takes whole groups of one page (all element
-// blocks), so the only coordinates that vary are the group and the page; the innermost one is always 0.
-// Executed by a whole converged warp; one elected lane issues the copy.
-__device__ __forceinline__ void tma_load_groups(uint32_t dst, const CUtensorMap* map, uint32_t bar, uint32_t group, uint32_t page) {
-    asm volatile(
-        "{\n\t.reg .pred e;\n\telect.sync _|e, 0xFFFFFFFF;\n\t"
-        "@e cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %4, %5}], [%2];\n\t}\n" ::"r"(dst),
-        "l"(map), "r"(bar), "r"(0u), "r"(group), "r"(page)
-        : "memory");
-}
 
 __device__ __forceinline__ void row_threads_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -673,43 +612,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
     }
-}
-
-// The page arena as a TMA tensor [page][8-row group][element block][row in group][64 elements]: a page holds
-// 2 * Hkv * tokens_per_page K and V rows of head_dim elements, a box is `box_rows / 8` consecutive groups with all their
-// element blocks, written with the 128-byte swizzle in exactly the order the MMA descriptors read a tile in.
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-    static EncodeTiled fn = [] {
-        void* entry = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) != cudaSuccess ||
-            result != cudaDriverEntryPointSuccess)
-            entry = nullptr;
-        return reinterpret_cast<EncodeTiled>(entry);
-    }();
-    return fn;
-}
-
-bool make_kv_map(const AttendParams& p, uint32_t box_rows, CUtensorMap* map) {
-    const EncodeTiled encode = encode_tiled();
-    if (encode == nullptr) return false;
-    const uint64_t page_bytes = p.geo.page_elems * 2;
-    const uint64_t row_bytes = p.geo.head_dim * 2ull;
-    const uint64_t rows_per_page = 2ull * p.geo.num_kv_heads * p.geo.tokens_per_page;
-    if (reinterpret_cast<uintptr_t>(p.geo.pages) % 16 != 0 || page_bytes % 16 != 0 || p.geo.num_pages == 0 ||
-        p.geo.num_pages > 0x7FFFFFFFull || rows_per_page * row_bytes > page_bytes || p.geo.tokens_per_page % 8 != 0)
-        return false;
-    const cuuint64_t dims[5] = {64, 8, p.geo.head_dim / 64, rows_per_page / 8, p.geo.num_pages};
-    const cuuint64_t strides[4] = {row_bytes, 128, 8 * row_bytes, page_bytes};
-    const cuuint32_t box[5] = {64, 8, p.geo.head_dim / 64, box_rows / 8, 1};
-    const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
-    const CUtensorMapDataType type = p.dtype == PSI_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    return encode(map, type, 5, const_cast<void*>(p.geo.pages), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <typename T, int D>

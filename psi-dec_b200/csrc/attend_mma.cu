@@ -17,9 +17,12 @@
 // The arithmetic this replaces: crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_map.metal
 // (decode rows) and metal/gqa_split_kv_tiled_q.metal:161-319 (several query tokens of one request with the in-kernel
 // causal limit).
+#include <cstdlib>
+
 #include "exchange.cuh"
 #include "launch_util.hpp"
 #include "mma_common.cuh"
+#include "tma_common.cuh"
 
 namespace psi {
 
@@ -40,9 +43,15 @@ struct SmemLayout {
 
 // kExchange: the launch is one rank's part of a KV-range exchange (exchange.cuh); the outputs go to the rank's slot of
 // the owner's receive area (ext_*), and the launch ends with the flag publication and, on the owner, the merge.
-template <typename T, int D, int NSLOT, bool kExchange>
-__global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p) {
+//
+// kTma: whole K/V tiles come from their pages as TMA boxes (cp.async.bulk.tensor, one instruction per 16-token tile
+// and warp, completion on one mbarrier per ring slot) instead of 16-byte cp.async copies; the tiles then lie in the
+// box layout of tma_common.cuh.  An item's ragged last tile and this step's own rows still come by cp.async.
+template <typename T, int D, int NSLOT, bool kExchange, bool kTma>
+__global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p, const __grid_constant__ CUtensorMap kv_map,
+                                                                uint32_t box_rows) {
     using L = SmemLayout<D, NSLOT>;
+    constexpr uint32_t kBlocks = D / 64;                     // 128-byte element blocks per row (TMA box layout)
     constexpr uint32_t kChunks = D / 8;                      // 16-byte chunks per row
     constexpr uint32_t kRowsPerCopy = 32 / (kChunks < 32 ? kChunks : 32);
 
@@ -61,6 +70,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     __shared__ float merge_l[kWarps][kTile];
     __shared__ uint32_t arrival_s;
     __shared__ uint32_t slot_free_s;  // exchange launches: this CTA may store into the rank's slot
+    __shared__ __align__(8) uint64_t ring_bar_s[kTma ? kWarps : 1][kTma ? NSLOT : 1];  // one mbarrier per ring slot
 
     const uint32_t tid = threadIdx.x;
     // The consumed word lives on the owner: its value is requested now and looked at before the first store.
@@ -82,7 +92,15 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     const uint64_t page_bytes = p.geo.page_elems * 2;
     const uint64_t v_region_bytes = v_region_offset(p.geo) * 2;
 
-    const FragmentLanes frag(lane, L::kRowBytes);
+    const FragmentLanes frag(lane, L::kRowBytes, kTma ? kBlocks * 1024u : 0u);
+    uint32_t tma_bits = 0;    // ring slots of this warp whose current fill is a TMA box (waited for on the slot's mbarrier)
+    uint32_t phase_bits = 0;  // parity of each slot's mbarrier phase that the next wait is for
+    bool ring_ok = true;      // false once a bounded mbarrier wait ran out: later waits are skipped
+    if (kTma) {
+        if (tid < kWarps * NSLOT) mbar_init(smem_u32(&ring_bar_s[tid / NSLOT][tid % NSLOT]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const uint32_t v_groups = p.geo.num_kv_heads * p.geo.tokens_per_page / 8;  // 8-row groups of a page's K region
     const uint64_t stream_policy = l2_evict_first_policy();  // full K/V tiles are read once per launch
 
     // copy lane roles: this lane moves chunk copy_chunk of rows copy_row, copy_row + kRowsPerCopy, ...
@@ -96,6 +114,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     for (uint32_t index = item_begin; index < item_end; ++index) {
         const ItemView v = (have_first && index == item_begin) ? first_item : view_item(p, index);
         __syncthreads();  // the previous item's merge is done with the ring, with q and with limit_s
+        if (kTma) fence_async_smem();  // ... before TMA boxes (another proxy) overwrite what the merge wrote there
 
         // Keys at or beyond `paged_end` are this step's own tokens: in the fused step they are read from new_k/new_v.
         const uint32_t paged_end = fused ? min(v.kv_end, v.new_begin) : v.kv_end;
@@ -109,6 +128,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         auto tile_of = [&](uint32_t j) { return first_tile + warp + j * kWarps; };
         const uint32_t* row_ids = table_row(p.geo, v.req_slot);
         const uint64_t head_bytes = static_cast<uint64_t>(v.kv_head) * p.geo.tokens_per_page * L::kRowBytes;
+        const uint32_t head_group = v.kv_head * p.geo.tokens_per_page / 8;
 
         // Page ids of the two 8-token halves of local tile i (equal when a page holds 16 tokens or more).
         auto lookup = [&](uint32_t i, uint32_t& id_lo, uint32_t& id_hi) {
@@ -125,7 +145,20 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                 pages + static_cast<uint64_t>(id_lo) * page_bytes + region + (token0 & page_mask) * L::kRowBytes;
             const unsigned char* src_hi =
                 pages + static_cast<uint64_t>(id_hi) * page_bytes + region + ((token0 + 8) & page_mask) * L::kRowBytes;
-            if (token0 + kTile <= paged_end) {
+            if (kTma && token0 + kTile <= paged_end) {
+                // one box of 16 rows, or two of 8 when a page holds 8 tokens; the elected lane issues
+                const uint32_t bar = smem_u32(&ring_bar_s[kTma ? warp : 0][kTma ? slot : 0]);
+                const uint32_t tile_base = ring_base + slot * L::kTileBytes;
+                const uint32_t group0 = ((h & 1) ? v_groups : 0u) + head_group;
+                if (lane == 0) mbar_expect_tx(bar, L::kTileBytes);
+                __syncwarp();
+                tma_load_groups_hinted(tile_base, &kv_map, bar, group0 + (token0 & page_mask) / 8, id_lo, stream_policy);
+                if (box_rows < kTile) {
+                    tma_load_groups_hinted(tile_base + kBlocks * 1024u, &kv_map, bar, group0 + ((token0 + 8) & page_mask) / 8,
+                                           id_hi, stream_policy);
+                }
+                tma_bits |= 1u << slot;
+            } else if (token0 + kTile <= paged_end) {
 #pragma unroll
                 for (uint32_t it = 0; it < kTile / kRowsPerCopy; ++it) {
                     const uint32_t row0 = it * kRowsPerCopy;  // this lane's row is row0 + copy_row
@@ -150,8 +183,11 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
                         src = fresh + (static_cast<uint64_t>(v.flat_req_begin + (token - v.new_begin)) * p.geo.num_kv_heads +
                                        v.kv_head) * L::kRowBytes + copy_chunk * 16;
                     }
-                    cp_async_16(dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4), src, bytes);
+                    const uint32_t dst = kTma ? ring_base + slot * L::kTileBytes + operand_offset(kBlocks, row0 + copy_row, copy_chunk)
+                                              : dst0 + row0 * L::kRowBytes + ((copy_x ^ (row0 & 7)) << 4);
+                    cp_async_16(dst, src, bytes);
                 }
+                tma_bits &= ~(1u << slot);
             }
         };
 
@@ -215,6 +251,18 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
         for (uint32_t h = 0; h < my_halves; ++h) {
             cp_async_wait<NSLOT - 2>();
             __syncwarp();
+            if (kTma) {
+                const uint32_t s = h % NSLOT;
+                if ((tma_bits >> s) & 1u) {
+                    const uint32_t bar = smem_u32(&ring_bar_s[kTma ? warp : 0][kTma ? s : 0]);
+                    const uint32_t parity = (phase_bits >> s) & 1u;
+                    if (ring_ok && !mbar_test(bar, parity) && !mbar_wait(bar, parity)) {
+                        ring_ok = false;  // the box never arrived: report it and stop waiting (the results are not valid)
+                        if (lane == 0 && p.status != nullptr) atomicExch(p.status, static_cast<uint32_t>(PSI_ERR_TIMEOUT));
+                    }
+                    phase_bits ^= 1u << s;
+                }
+            }
             const uint32_t ahead = h + NSLOT - 1;
             if (ahead < my_halves) {
                 issue(ahead, ahead % NSLOT, cur_lo, cur_hi);
@@ -230,10 +278,10 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
             if ((h & 1) == 0) {
                 const uint32_t token0 = tile_of(h >> 1) * kTile;
                 const bool masked = token0 < v.kv_begin || token0 + kTile > limit_min;
-                TileMath<T, D>::scores(frag, q_base, slot_base, p.scale_log2, masked, token0, limit0, limit1,
-                                       v.kv_begin, st, pa);
+                TileMath<T, D, kTma>::scores(frag, q_base, slot_base, p.scale_log2, masked, token0, limit0, limit1,
+                                             v.kv_begin, st, pa);
             } else {
-                TileMath<T, D>::values(frag, slot_base, pa, st);
+                TileMath<T, D, kTma>::values(frag, slot_base, pa, st);
             }
         }
 
@@ -416,29 +464,54 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p)
     }
 }
 
+// Temporary switch for the A/B measurement of the two feeds.
+bool attend_mma_tma_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("PSI_TUNE_TMA");
+        return e != nullptr && e[0] == '1';
+    }();
+    return on;
+}
+
 template <int D>
 constexpr int stages_for() {
     return D == 256 ? 3 : (D == 128 ? 6 : 8);  // ring slots (one K or V tile each) per warp
 }
 
-template <typename T, int D, bool kExchange>
-cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
+template <typename T, int D, bool kExchange, bool kTma>
+cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream, const CUtensorMap& map,
+                       uint32_t box_rows) {
     constexpr int NSLOT = stages_for<D>();
     using L = SmemLayout<D, NSLOT>;
-    auto kernel = attend_mma_kernel<T, D, NSLOT, kExchange>;
+    auto kernel = attend_mma_kernel<T, D, NSLOT, kExchange, kTma>;
     static std::atomic<uint64_t> configured{0};  // per instantiation, one bit per device
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), static_cast<int>(L::kTotal), configured);
     if (err != cudaSuccess) return err;
-    kernel<<<num_ctas, kThreads, L::kTotal, stream>>>(p);
+    kernel<<<num_ctas, kThreads, L::kTotal, stream>>>(p, map, box_rows);
     return cudaGetLastError();
 }
 
 template <typename T, bool kExchange>
 cudaError_t launch_for_dim(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
+    // TMA feed where the arena can be described to the TMA unit (it needs the arena's page count and alignment);
+    // otherwise, and for the exchange launches, the cp.async feed.
+    CUtensorMap map{};
+    const uint32_t box_rows = p.geo.tokens_per_page < static_cast<uint32_t>(kTile) ? p.geo.tokens_per_page : kTile;
+    const bool tma = !kExchange && attend_mma_tma_enabled() && make_kv_map(p, box_rows, &map);
+    if (tma) {
+        if constexpr (!kExchange) {
+            switch (p.geo.head_dim) {
+                case 64: return launch_one<T, 64, false, true>(p, num_ctas, stream, map, box_rows);
+                case 128: return launch_one<T, 128, false, true>(p, num_ctas, stream, map, box_rows);
+                case 256: return launch_one<T, 256, false, true>(p, num_ctas, stream, map, box_rows);
+                default: return cudaErrorInvalidValue;
+            }
+        }
+    }
     switch (p.geo.head_dim) {
-        case 64: return launch_one<T, 64, kExchange>(p, num_ctas, stream);
-        case 128: return launch_one<T, 128, kExchange>(p, num_ctas, stream);
-        case 256: return launch_one<T, 256, kExchange>(p, num_ctas, stream);
+        case 64: return launch_one<T, 64, kExchange, false>(p, num_ctas, stream, map, box_rows);
+        case 128: return launch_one<T, 128, kExchange, false>(p, num_ctas, stream, map, box_rows);
+        case 256: return launch_one<T, 256, kExchange, false>(p, num_ctas, stream, map, box_rows);
         default: return cudaErrorInvalidValue;
     }
 }

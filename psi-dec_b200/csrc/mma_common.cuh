@@ -143,14 +143,24 @@ struct FragmentLanes {
     uint32_t k_lane, k_x;   // B operand of Q K^T:               address = k_tile_base + k_lane + (k_x ^ 32*ks)
     uint32_t v_lane, v_x;   // B operand of P V (transposed):    address = v_tile_base + v_lane + (v_x ^ 32*j)
     uint32_t quad_row, quad_col;
-    __device__ __forceinline__ FragmentLanes(uint32_t lane, uint32_t row_bytes) {
+    // `atom_group_bytes` == 0: K and V tiles are rows of `row_bytes` with the chunk index XOR-ed over the whole row
+    // (what the cp.async copies write).  Otherwise they are in the layout a TMA box of the page arena lands in
+    // (operand_offset in tma_common.cuh): 8-row groups `atom_group_bytes` apart, each a run of 1 KiB swizzle atoms of
+    // 8 rows x 128 bytes; the k-step (or output-column) term then selects the atom as well as the chunk inside it.
+    // The query tile is always in the row layout.
+    __device__ __forceinline__ FragmentLanes(uint32_t lane, uint32_t row_bytes, uint32_t atom_group_bytes = 0) {
         const uint32_t mat = lane >> 3, mat_row = lane & 7;
         const uint32_t q_row = mat_row + 8 * (mat & 1), k_row = mat_row + 8 * (mat >> 1), v_row = mat_row + 8 * (mat & 1);
         q_lane = q_row * row_bytes;
         q_x = ((mat >> 1) ^ (q_row & 7)) << 4;
-        k_lane = k_row * row_bytes;
+        if (atom_group_bytes == 0) {
+            k_lane = k_row * row_bytes;
+            v_lane = v_row * row_bytes;
+        } else {
+            k_lane = (k_row >> 3) * atom_group_bytes + (k_row & 7) * 128;
+            v_lane = (v_row >> 3) * atom_group_bytes + (v_row & 7) * 128;
+        }
         k_x = ((mat & 1) ^ (k_row & 7)) << 4;
-        v_lane = v_row * row_bytes;
         v_x = ((mat >> 1) ^ (v_row & 7)) << 4;
         quad_row = lane >> 2;
         quad_col = lane & 3;
@@ -170,9 +180,15 @@ struct RowState {
     }
 };
 
-template <typename T, int D>
+// kAtom: the K/V tile is in the TMA box layout (see FragmentLanes); step s of a row then lives in atom s / 4 at
+// chunk pair s % 4.
+template <typename T, int D, bool kAtom = false>
 struct TileMath {
     static constexpr int kKSteps = D / 16;
+    __device__ __forceinline__ static constexpr uint32_t step_term(uint32_t x, int s) {
+        return kAtom ? static_cast<uint32_t>(s >> 2) * 1024u + (x ^ (32u * static_cast<uint32_t>(s & 3)))
+                     : (x ^ (32u * static_cast<uint32_t>(s)));
+    }
 
     // S = Q K^T for one 16-token K tile, visibility mask, online softmax update; leaves P (packed for the A operand
     // of P V) in `pa`.  Keys at or beyond a row's limit, or before `kv_begin`, do not count.
@@ -186,7 +202,7 @@ struct TileMath {
         for (int ks = 0; ks < kKSteps; ++ks) {
             uint32_t a[4], b[4];
             ldmatrix_x4(a, q_tile + f.q_lane + (f.q_x ^ (32u * ks)));
-            ldmatrix_x4(b, k_tile + f.k_lane + (f.k_x ^ (32u * ks)));
+            ldmatrix_x4(b, k_tile + f.k_lane + step_term(f.k_x, ks));
             if (ks & 1) {
                 Mma<T>::run(s_odd[0], a, b[0], b[1]);
                 Mma<T>::run(s_odd[1], a, b[2], b[3]);
@@ -251,7 +267,7 @@ struct TileMath {
 #pragma unroll
         for (int j = 0; j < D / 16; ++j) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, v_tile + f.v_lane + (f.v_x ^ (32u * j)));
+            ldmatrix_x4_trans(b, v_tile + f.v_lane + step_term(f.v_x, j));
             Mma<T>::run(st.o[2 * j], pa, b[0], b[1]);
             Mma<T>::run(st.o[2 * j + 1], pa, b[2], b[3]);
         }
