@@ -288,7 +288,7 @@ def measure_decode(job, pkg, W, index, main):
     base = workload(W, args, index)
     spec, scaling, parallelism, whole = spread(W, pkg, base, index, job, args)
     kernel_mode = {"auto": pkg.KERNEL_AUTO, "mma": pkg.KERNEL_MMA, "generic": pkg.KERNEL_GENERIC,
-                   "mma_sync": pkg.KERNEL_MMA_SYNC}[args.kernel]
+                   "mma_sync": pkg.KERNEL_MMA_SYNC, "mma_tma": pkg.KERNEL_MMA_TMA}[args.kernel]
     session = W.Session(spec, device=job.local_rank, kernel_mode=kernel_mode)
     exchange = KvRangeExchange(session, rank, world, mode=args.exchange) if (world > 1 and index == 4) else None
     step = exchange.step if exchange else session.step
@@ -479,7 +479,7 @@ def measure_churn(job, pkg, W, main):
     trace = W.ChurnTrace(slots=max(world, 256 // scale), steps=args.churn_steps, world=world, hi=max(256, 131072 // scale),
                          chunk=max(16, 512 // min(scale, 8)))
     kernel_mode = {"auto": pkg.KERNEL_AUTO, "mma": pkg.KERNEL_MMA, "generic": pkg.KERNEL_GENERIC,
-                   "mma_sync": pkg.KERNEL_MMA_SYNC}[args.kernel]
+                   "mma_sync": pkg.KERNEL_MMA_SYNC, "mma_tma": pkg.KERNEL_MMA_TMA}[args.kernel]
     churn = W.ChurnSession(trace, rank=rank, device=job.local_rank, kernel_mode=kernel_mode)
     ctx = churn.ctx
     mine = churn.mine
@@ -734,9 +734,10 @@ def main():
     parser.add_argument("--dtype", choices=["bf16", "f16", "f32"], default="bf16", help="storage dtype of --contexts runs")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-read-probe", action="store_true", help="skip the read-only HBM bandwidth probe")
-    parser.add_argument("--kernel", choices=["auto", "mma", "generic", "mma_sync"], default="auto",
+    parser.add_argument("--kernel", choices=["auto", "mma", "generic", "mma_sync", "mma_tma"], default="auto",
                         help="attention kernel: tensor-core kernels (default where supported), the CUDA-core kernel, or "
-                             "mma_sync = tensor-core kernels with long query runs kept off the tcgen05 kernel")
+                             "mma_sync = tensor-core kernels with long query runs kept off the tcgen05 kernel, mma_tma = decode kernel fed by "
+                             "TMA boxes instead of cp.async (both kept for A/B measurement)")
     parser.add_argument("--exchange", choices=["p2p", "p2p3", "nccl"], default="p2p",
                         help="partial exchange of the KV-range-split configuration 4: one launch per rank (p2p), the "
                              "same data path as three launches (p2p3), or an NCCL all-gather")

@@ -103,8 +103,12 @@ typedef enum psi_kernel_mode {
     PSI_KERNEL_AUTO = 0,    /* tensor-core kernel when the profile allows, else the generic kernel */
     PSI_KERNEL_GENERIC = 1, /* CUDA-core kernel: any dtype, head_dim <= 256, any tokens_per_page */
     PSI_KERNEL_MMA = 2,     /* bf16/f16 mma kernel: head_dim in {64,128,256}, tokens_per_page a power of two >= 8 */
-    PSI_KERNEL_MMA_SYNC = 3 /* as PSI_KERNEL_MMA, but long query runs stay on the mma.sync chunk kernel instead of
-                               the tcgen05 / TMEM kernel (kept for A/B measurement) */
+    PSI_KERNEL_MMA_SYNC = 3, /* as PSI_KERNEL_MMA, but long query runs stay on the mma.sync chunk kernel instead of
+                                the tcgen05 / TMEM kernel (kept for A/B measurement) */
+    PSI_KERNEL_MMA_TMA = 4   /* as PSI_KERNEL_MMA, but the decode kernel brings whole K/V tiles from their pages as
+                                TMA boxes (cp.async.bulk.tensor, one instruction per tile and warp) instead of 16-byte
+                                cp.async copies.  Kept for A/B measurement: it measured 1-5 % slower at head_dim 128
+                                and 256 and 22 % slower at head_dim 64, so it is not what PSI_KERNEL_AUTO picks. */
 } psi_kernel_mode;
 
 /* Replay capacity policy of psi_gqa_prepare (batch_metadata.rs:60-69, GQAReplayCapacity). */

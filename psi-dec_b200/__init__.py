@@ -4,7 +4,7 @@ The directory name carries a hyphen, so the package is loaded by path (``__graft
 registered as ``psi_dec_b200``.
 """
 from .binding import (  # noqa: F401
-    BF16, F16, F32, CAPACITY_BUCKETED, CAPACITY_CALLER_TOKENS, CAPACITY_EXACT, KERNEL_AUTO, KERNEL_GENERIC, KERNEL_MMA, KERNEL_MMA_SYNC,
+    BF16, F16, F32, CAPACITY_BUCKETED, CAPACITY_CALLER_TOKENS, CAPACITY_EXACT, KERNEL_AUTO, KERNEL_GENERIC, KERNEL_MMA, KERNEL_MMA_SYNC, KERNEL_MMA_TMA,
     PLAN_BALANCED, PLAN_REFERENCE, Context, GQA, GQAConfig, GQAPageTableLayout, KvExchange, GQAReplayShape, GQARequestPageTable,
     GQASplitKV, GQASplitKVVariant, NormRopeConfig, PageArena, PsiError, ReplayBucketPolicy, U32IDAllocator, ExecutorHibernationPlan, StateSnapshotReader, StateSnapshotWriter,
     SNAPSHOT_PAGE_ARENA, SNAPSHOT_MAIN_GQA_REQUEST_PAGE_TABLE, SNAPSHOT_MAIN_GDN_REQUEST_STATE_TABLE,

@@ -13,7 +13,7 @@ from pathlib import Path
 
 F32, BF16, F16 = 0, 1, 2
 PLAN_BALANCED, PLAN_REFERENCE = 0, 1
-KERNEL_AUTO, KERNEL_GENERIC, KERNEL_MMA, KERNEL_MMA_SYNC = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_MMA, KERNEL_MMA_SYNC, KERNEL_MMA_TMA = 0, 1, 2, 3, 4
 CAPACITY_EXACT, CAPACITY_BUCKETED, CAPACITY_CALLER_TOKENS = 0, 1, 2
 MD_REQ_SLOTS, MD_FLAT_TOKEN_INDICES, MD_Q_TOKEN_TILES, MD_KV_SPLITS, MD_CU_KV_SPLITS = range(5)
 

@@ -74,6 +74,8 @@ AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* 
     p.tokens_per_tile = g->geo.tokens_per_tile;
     p.dtype = g->cfg.dtype;
     p.scale_log2 = g->cfg.scale * 1.4426950408889634f;
+    p.tma_feed = g->cfg.kernel_mode == PSI_KERNEL_MMA_TMA ? 1u : 0u;
+    p.status = static_cast<uint32_t*>(g->status_word.ptr);
     return p;
 }
 

@@ -16,7 +16,7 @@ int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out
         require(c.scale > 0.0f && std::isfinite(c.scale), "GQA scale must be positive");
         require(c.dtype <= PSI_DTYPE_F16, "unsupported GQA dtype");
         require(c.max_tokens > 0, "GQA batch metadata requires tokens");
-        require(c.plan_mode <= PSI_PLAN_REFERENCE && c.kernel_mode <= PSI_KERNEL_MMA_SYNC, "unknown plan or kernel mode");
+        require(c.plan_mode <= PSI_PLAN_REFERENCE && c.kernel_mode <= PSI_KERNEL_MMA_TMA, "unknown plan or kernel mode");
         validate_layout(c.layout);
         const uint64_t per_token = uint64_t(c.num_kv_heads) * c.head_dim * 2u * dtype_bytes(c.dtype);
         require(per_token <= kU32Max, "GQA K/V bytes per token must fit u32");

@@ -17,8 +17,6 @@
 // The arithmetic this replaces: crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_map.metal
 // (decode rows) and metal/gqa_split_kv_tiled_q.metal:161-319 (several query tokens of one request with the in-kernel
 // causal limit).
-#include <cstdlib>
-
 #include "exchange.cuh"
 #include "launch_util.hpp"
 #include "mma_common.cuh"
@@ -464,15 +462,6 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p,
     }
 }
 
-// Temporary switch for the A/B measurement of the two feeds.
-bool attend_mma_tma_enabled() {
-    static const bool on = [] {
-        const char* e = std::getenv("PSI_TUNE_TMA");
-        return e != nullptr && e[0] == '1';
-    }();
-    return on;
-}
-
 template <int D>
 constexpr int stages_for() {
     return D == 256 ? 3 : (D == 128 ? 6 : 8);  // ring slots (one K or V tile each) per warp
@@ -493,11 +482,11 @@ cudaError_t launch_one(const AttendParams& p, uint32_t num_ctas, cudaStream_t st
 
 template <typename T, bool kExchange>
 cudaError_t launch_for_dim(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
-    // TMA feed where the arena can be described to the TMA unit (it needs the arena's page count and alignment);
-    // otherwise, and for the exchange launches, the cp.async feed.
+    // The TMA feed when the component asks for it and the arena can be described to the TMA unit (page count known,
+    // alignment); otherwise, and for the exchange launches, the cp.async feed.
     CUtensorMap map{};
     const uint32_t box_rows = p.geo.tokens_per_page < static_cast<uint32_t>(kTile) ? p.geo.tokens_per_page : kTile;
-    const bool tma = !kExchange && attend_mma_tma_enabled() && make_kv_map(p, box_rows, &map);
+    const bool tma = !kExchange && p.tma_feed != 0 && make_kv_map(p, box_rows, &map);
     if (tma) {
         if constexpr (!kExchange) {
             switch (p.geo.head_dim) {

@@ -106,7 +106,7 @@ extern "C" int32_t psi_gqa_attend_static(int32_t device, void* cuda_stream, cons
         require(c.head_dim > 0 && c.head_dim <= kStaticMaxHeadDim,
                 "head_dim exceeds the static scratch (PSI_STATIC_MAX_HEAD_DIM)");
         require(c.dtype <= PSI_DTYPE_F16 && c.scale > 0.0f && std::isfinite(c.scale), "unsupported dtype or scale");
-        require(c.kernel_mode <= PSI_KERNEL_MMA_SYNC, "unknown kernel mode");
+        require(c.kernel_mode <= PSI_KERNEL_MMA_SYNC, "unknown kernel mode (the TMA feed needs a psi_pages arena)");
         const uint64_t per_token = uint64_t(c.num_kv_heads) * c.head_dim * 2u * dtype_bytes(c.dtype);
         require(c.page_bytes > 0 && c.page_bytes % per_token == 0,
                 "GQA page_bytes must be divisible by the K/V bytes per token");

@@ -124,6 +124,7 @@ struct AttendParams {
     uint32_t dtype;
     float scale_log2;             // scale * log2(e)
     uint32_t* status;             // nullptr, or the word a bounded device-side wait writes PSI_ERR_TIMEOUT to
+    uint32_t tma_feed;            // decode kernel: whole K/V tiles by TMA boxes instead of cp.async (PSI_KERNEL_MMA_TMA)
     ExchangeParams xchg;          // KV-range exchange in the same launch (mma kernel); xchg.flag == nullptr: none
 };
 

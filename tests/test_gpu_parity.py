@@ -825,3 +825,37 @@ def test_flag_exchange_on_one_device_and_bounded_wait_timeout():
     assert torch.equal(canary.view(torch.int16), expect.view(torch.int16))
     for sh in shards:
         sh.close()
+
+
+@pytest.mark.parametrize("spec_args", [
+    dict(index=2, scale_down=1),                                  # configuration 2 at full size, fused append
+    dict(index=3, scale_down=8),                                  # two query tokens per sequence, 12 rows per item
+    dict(custom=(32, 8, 128, 16, 12, 300, 3000, 1)),              # head_dim 128
+    dict(custom=(16, 4, 64, 16, 9, 100, 2500, 1)),                # head_dim 64 (one swizzle atom per row group)
+    dict(custom=(16, 2, 256, 8, 7, 50, 1500, 2)),                 # 8-token pages: two boxes per tile
+    dict(custom=(16, 2, 256, 32, 5, 10, 900, 1)),                 # 32-token pages: a tile is half a page
+])
+def test_decode_kernel_with_the_tma_feed_matches_the_oracle_and_the_cp_async_feed(spec_args):
+    # PSI_KERNEL_MMA_TMA: the same decode kernel with whole K/V tiles brought from their pages as TMA boxes.  Same
+    # arithmetic in the same order on the same values, so the outputs equal the default kernel's bit for bit; the
+    # ragged last tile of every item and this step's own rows still travel by cp.async into the box layout.
+    import torch
+    spec = W.config(spec_args["index"], scale_down=spec_args["scale_down"]) if "index" in spec_args else W.W.custom(*spec_args["custom"])
+    a = W.Session(spec, kernel_mode=pkg.KERNEL_MMA_TMA)
+    before = checks.to_numpy_bits(a.arena)
+    a.step()
+    a.ctx.sync()
+    assert a.gqa.device_status() == 0
+    assert np.array_equal(checks.to_numpy_bits(a.arena).reshape(-1), checks.expected_arena_after_append(a, before))
+    checks.assert_attention_close(a)
+    b = W.Session(spec, kernel_mode=pkg.KERNEL_MMA)
+    b.step()
+    b.ctx.sync()
+    assert torch.equal(a.out.view(torch.int16), b.out.view(torch.int16))
+    # the two-stage order (append launch, then attention over pages only) through the TMA feed as well
+    a.out.zero_()
+    a.step_unfused()
+    a.ctx.sync()
+    assert torch.equal(a.out.view(torch.int16), b.out.view(torch.int16))
+    a.close()
+    b.close()
