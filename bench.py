@@ -76,7 +76,7 @@ def record_traffic(report: str, workload_name: str, command: str):
     """Reads an ncu report of the decode kernel (here, no GPU needed) and writes the per-launch DRAM traffic beside the
     profiler summaries, with the hash of the kernel sources it was taken with:
 
-        python bench.py --record-traffic gpurun_out/prof_attend_mma_cfg2.ncu-rep
+        python bench.py --record-traffic prof_attend_mma_cfg2.ncu-rep
     """
     import csv
     raw = subprocess.run(["ncu", "-i", report, "--page", "raw", "--csv"], capture_output=True, text=True, check=True).stdout
@@ -744,7 +744,7 @@ def main():
     parser.add_argument("--record-traffic", default=None, metavar="REPORT.ncu-rep",
                         help="no run: read an ncu report of the decode kernel and write profiles/attend_mma_dram_traffic.txt")
     parser.add_argument("--capture-command", default="ncu --set full --clock-control none -k regex:attend_mma -s 4 -c 2 -o "
-                        "gpurun_out/prof_attend_mma_cfg2 python bench.py --config 2 --steps 3 --warmup 3 --no-cpu-baseline "
+                        "prof_attend_mma_cfg2 python bench.py --config 2 --steps 3 --warmup 3 --no-cpu-baseline "
                         "--no-read-probe --no-splits", help="with --record-traffic: the command that made the report")
     args = parser.parse_args()
     if args.record_traffic:

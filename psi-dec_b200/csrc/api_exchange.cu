@@ -159,6 +159,9 @@ int32_t psi_gqa_attend_exchange(psi_gqa* g, psi_pages* pages, psi_table* table, 
         x.num_rows = static_cast<uint32_t>(rows);
         p.status = static_cast<uint32_t*>(g->status_word.ptr);
 
+        require(g->plan.num_ctas() + g->chunk.num_ctas() > 0,
+                "the rank's slice of the KV range is empty: a rank without keys has nothing to publish and must be left "
+                "out of the exchange group");
         const bool fused = g->kernel == PSI_KERNEL_MMA && g->chunk.num_ctas() == 0 && !g->replay_reserved;
         if (fused) {
             if (k != nullptr) {
