@@ -87,7 +87,7 @@ def _assert_close(group, out):
     assert diff.max() <= checks.MAX_ABS_16BIT and diff.mean() <= checks.MEAN_ABS_16BIT, (diff.max(), diff.mean())
 
 
-@pytest.mark.parametrize("world,kernel_mode", [(2, pkg.KERNEL_AUTO), (4, pkg.KERNEL_AUTO), (2, pkg.KERNEL_GENERIC)])
+@pytest.mark.parametrize("world,kernel_mode", [(2, pkg.KERNEL_AUTO), (4, pkg.KERNEL_AUTO), (8, pkg.KERNEL_AUTO), (2, pkg.KERNEL_GENERIC)])
 def test_exchange_merges_every_step_against_the_oracle(world, kernel_mode):
     # Queries change from step to step, so a merge that mixed two steps' partials would miss the oracle.
     import torch
