@@ -456,6 +456,67 @@ def test_page_and_tile_boundaries(page, head_dim, kernel_mode, _kname):
     t.close()
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_random_profiles_fused_step_against_the_oracle(seed):
+    # Seeded draws over the profile space the decode kernels accept: head counts and group sizes (including groups
+    # wider than one 16-row tile), head dims, page sizes, dtypes, ragged query runs, contexts from an empty cache up,
+    # CTA caps from one CTA to the whole GPU, both plan modes.  Pages bit-exact after the step, attention within
+    # tolerance, and the same step again leaves both unchanged.
+    import torch
+    rng = np.random.default_rng(1000 + seed)
+    hkv = int(rng.choice([1, 2, 4, 8]))
+    group = int(rng.choice([1, 2, 4, 6, 8, 16, 24]))
+    head_dim = int(rng.choice([64, 128, 256]))
+    page = int(rng.choice([8, 16, 32, 64]))
+    dtype = [pkg.BF16, pkg.F16][int(rng.integers(0, 2))]
+    batch = int(rng.integers(1, 24))
+    hi = int(rng.choice([40, 700, 5000]))
+    contexts = rng.integers(0, hi + 1, size=batch)
+    runs = rng.integers(1, 7, size=batch)
+    plan_mode = [pkg.PLAN_BALANCED, pkg.PLAN_REFERENCE][int(rng.integers(0, 2))]
+    max_ctas = int(rng.choice([0, 1, 3, 37, 148]))
+    spec = W.Spec(f"random-{seed}", dtype, hkv * group, hkv, head_dim, page, contexts, runs, seed=seed)
+    s = W.Session(spec, plan_mode=plan_mode, max_ctas=max_ctas)
+    before = checks.to_numpy_bits(s.arena)
+    s.step()
+    s.ctx.sync()
+    expected = checks.expected_arena_after_append(s, before)
+    assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), expected)
+    checks.assert_attention_close(s)
+    first = s.out.clone()
+    s.step()
+    s.ctx.sync()
+    assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), expected)
+    assert torch.equal(first.view(torch.int16), s.out.view(torch.int16))
+    assert s.gqa.device_status() == 0
+    s.close()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_profiles_on_the_correctness_path_against_the_oracle(seed):
+    # The same for what only the CUDA-core kernel takes: f32, head dims that are no multiple of 64, page sizes that
+    # are no power of two (f32 against the reference's own f32 tolerance).
+    rng = np.random.default_rng(2000 + seed)
+    hkv = int(rng.choice([1, 2, 3]))
+    group = int(rng.choice([1, 2, 5, 8]))
+    head_dim = int(rng.choice([8, 24, 96, 128, 256]))
+    page = int(rng.choice([3, 5, 8, 12, 16]))
+    dtype = [pkg.F32, pkg.BF16, pkg.F16][int(rng.integers(0, 3))]
+    batch = int(rng.integers(1, 12))
+    contexts = rng.integers(0, int(rng.choice([30, 400])) + 1, size=batch)
+    runs = rng.integers(1, 4, size=batch)
+    plan_mode = [pkg.PLAN_BALANCED, pkg.PLAN_REFERENCE][int(rng.integers(0, 2))]
+    spec = W.Spec(f"random-generic-{seed}", dtype, hkv * group, hkv, head_dim, page, contexts, runs, seed=seed)
+    s = W.Session(spec, plan_mode=plan_mode, kernel_mode=pkg.KERNEL_GENERIC, max_ctas=int(rng.choice([0, 2, 64])))
+    before = checks.to_numpy_bits(s.arena)
+    s.step()
+    s.ctx.sync()
+    assert np.array_equal(checks.to_numpy_bits(s.arena).reshape(-1), checks.expected_arena_after_append(s, before))
+    checks.assert_attention_close(s)
+    assert s.gqa.device_status() == 0
+    s.close()
+
+
 @pytest.mark.parametrize("engine", ["tcgen05", "mma_sync"])
 @pytest.mark.parametrize("max_ctas", [1, 5, 148])
 @pytest.mark.parametrize("heads,head_dim,page", [((16, 2), 256, 16), ((24, 4), 128, 8), ((8, 8), 128, 32)])
