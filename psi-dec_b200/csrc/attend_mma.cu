@@ -54,12 +54,16 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p,
     constexpr uint32_t kRowsPerCopy = 32 / (kChunks < 32 ? kChunks : 32);
 
     const uint32_t cta = blockIdx.x;
+    // The plan and the page table are read again by the next launch of the step (one launch per layer) while hundreds
+    // of megabytes of K/V pass through the L2 in between: their lines are loaded to be evicted last.
+    const uint64_t keep = l2_evict_last_policy();
     // One round trip for everything the first tile copies depend on: the CTA count, this CTA's item range and a copy
     // of its first item all go out before the first of them is needed.
-    const uint32_t num_ctas = p.scalars[kScalarNumCtas];
-    const uint32_t item_begin = p.cta_item_begin[cta], item_end = p.cta_item_begin[cta + 1];
+    const uint32_t num_ctas = ld_u32_hinted(p.scalars + kScalarNumCtas, keep);
+    const uint32_t item_begin = ld_u32_hinted(p.cta_item_begin + cta, keep);
+    const uint32_t item_end = ld_u32_hinted(p.cta_item_begin + cta + 1, keep);
     const bool have_first = p.cta_first_items != nullptr;
-    const ItemView first_item = view_item(have_first ? p.cta_first_items + cta : p.items);
+    const ItemView first_item = view_item_hinted(have_first ? p.cta_first_items + cta : p.items, keep);
     if (cta >= num_ctas) return;
 
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -110,7 +114,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p,
     const PageBounds bounds(p.geo);
     uint32_t bad_page = 0;  // set when a table index or page ID was out of bounds (that read went to page 0 instead)
     for (uint32_t index = item_begin; index < item_end; ++index) {
-        const ItemView v = (have_first && index == item_begin) ? first_item : view_item(p, index);
+        const ItemView v = (have_first && index == item_begin) ? first_item : view_item_hinted(p.items + index, keep);
         __syncthreads();  // the previous item's merge is done with the ring, with q and with limit_s
         if (kTma) fence_async_smem();  // ... before TMA boxes (another proxy) overwrite what the merge wrote there
 
@@ -131,8 +135,8 @@ __global__ void __launch_bounds__(kThreads, 1) attend_mma_kernel(AttendParams p,
         // Page ids of the two 8-token halves of local tile i (equal when a page holds 16 tokens or more).
         auto lookup = [&](uint32_t i, uint32_t& id_lo, uint32_t& id_hi) {
             const uint32_t token = tile_of(i) * kTile;
-            id_lo = token < paged_end ? bounds.read(row_ids, token >> page_shift, bad_page) : 0u;
-            id_hi = token + 8 < paged_end ? bounds.read(row_ids, (token + 8) >> page_shift, bad_page) : 0u;
+            id_lo = token < paged_end ? bounds.read_hinted(row_ids, token >> page_shift, bad_page, keep) : 0u;
+            id_hi = token + 8 < paged_end ? bounds.read_hinted(row_ids, (token + 8) >> page_shift, bad_page, keep) : 0u;
         };
         // Issues the copies of half-tile h (K of tile h/2 when h is even, else V) into ring slot `slot`.
         auto issue = [&](uint32_t h, uint32_t slot, uint32_t id_lo, uint32_t id_hi) {

@@ -24,6 +24,21 @@ __device__ __forceinline__ void store_from_float(void* base, uint64_t index, uin
     }
 }
 
+// Loads under an L2 cache policy (createpolicy).
+__device__ __forceinline__ uint32_t ld_u32_hinted(const uint32_t* src, uint64_t policy) {
+    uint32_t value;
+    asm volatile("ld.global.L2::cache_hint.u32 %0, [%1], %2;\n" : "=r"(value) : "l"(src), "l"(policy));
+    return value;
+}
+
+__device__ __forceinline__ uint4 ld_u128_hinted(const void* src, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(src), "l"(policy));
+    return v;
+}
+
 // First element of the (slot, layer) row of the page table.
 __device__ __forceinline__ const uint32_t* table_row(const PageGeometry& g, uint32_t req_slot) {
     return g.page_ids + (static_cast<uint64_t>(req_slot) * g.num_layers + g.layer) * g.pages_per_req;
@@ -94,6 +109,20 @@ struct PageBounds {
         return row_ids[index];
 #endif
     }
+    // The same read under an L2 cache policy.
+    __device__ __forceinline__ uint32_t read_hinted(const uint32_t* row_ids, uint32_t index, uint32_t& bad,
+                                                    uint64_t policy) const {
+#if PSI_CUDA_CHECKED
+        const bool index_ok = index < indices;
+        const uint32_t raw = ld_u32_hinted(row_ids + (index_ok ? index : 0u), policy);
+        const bool ok = index_ok && raw < ids;
+        bad |= ok ? 0u : 1u;
+        return ok ? raw : 0u;
+#else
+        (void)bad;
+        return ld_u32_hinted(row_ids + index, policy);
+#endif
+    }
 };
 
 // The same for reads: an out-of-bounds entry reads page 0 (valid memory) and the launch is flagged.
@@ -143,6 +172,15 @@ __device__ __forceinline__ ItemView view_item(const DeviceItem* item) {
     uint4* dst = reinterpret_cast<uint4*>(static_cast<DeviceItem*>(&v));
 #pragma unroll
     for (int i = 0; i < 4; ++i) dst[i] = src[i];
+    v.rows = v.num_tokens * v.num_heads;
+    return v;
+}
+
+__device__ __forceinline__ ItemView view_item_hinted(const DeviceItem* item, uint64_t policy) {
+    ItemView v;
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<DeviceItem*>(&v));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] = ld_u128_hinted(reinterpret_cast<const uint4*>(item) + i, policy);
     v.rows = v.num_tokens * v.num_heads;
     return v;
 }

@@ -77,6 +77,13 @@ __device__ __forceinline__ uint64_t l2_evict_first_policy() {
     return policy;
 }
 
+// Policy for what the next launch reads again (the step's plan, the page table): evicted last.
+__device__ __forceinline__ uint64_t l2_evict_last_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(policy));
+    return policy;
+}
+
 // cp_async_16 under an L2 cache policy.
 __device__ __forceinline__ void cp_async_16_hinted(uint32_t dst, const void* src, uint32_t src_bytes, uint64_t policy) {
     asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(dst), "l"(src),
