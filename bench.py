@@ -585,13 +585,61 @@ def measure_churn(job, pkg, W, main):
             record["roofline"] = dict(record["chunk_rows"], traffic=None)
     job.barrier()
     churn.close()
+    e2e = measure_churn_e2e(job, W, trace, kernel_mode, warm, min(trace.steps, 50 if main else 16))
+    if record is not None:
+        record["e2e"] = e2e
     return record
+
+
+def measure_churn_e2e(job, W, trace, kernel_mode, warm, steps):
+    """The first `steps` steps of the same trace again on a fresh session, every step through `psi_gqa_step_host` with
+    pinned host buffers: planning, q/k/v over the host link, append, attention and the output's way back inside the
+    timed region (CUDA events around the blocking call, and the host's clock)."""
+    torch = job.torch
+    churn = W.ChurnSession(trace, rank=job.rank, device=job.local_rank, kernel_mode=kernel_mode)
+    kh, vh, qh = churn.k.cpu().pin_memory(), churn.v.cpu().pin_memory(), churn.q.cpu().pin_memory()
+    oh = torch.empty_like(qh).pin_memory()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    wall, tokens, h2d, d2h = [], [], [], []
+    launches_before = churn.ctx.launch_count
+    job.barrier()
+    for t in range(steps):
+        churn.prepare_step(t, plan=False)
+        job.flush.sum()
+        torch.cuda.synchronize()
+        starts[t].record(churn.stream)
+        t0 = time.perf_counter()
+        churn.host_step(kh, vh, qh, oh)
+        wall.append(time.perf_counter() - t0)
+        ends[t].record(churn.stream)
+        n = churn.tokens
+        tokens.append(n)
+        h2d.append(n * (qh[0].numel() + 2 * kh[0].numel()) * qh.element_size())
+        d2h.append(n * oh[0].numel() * oh.element_size())
+        churn.finish_step(t)
+    torch.cuda.synchronize()
+    ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    launches = churn.ctx.launch_count - launches_before
+    status = churn.gqa.device_status()
+    churn.close()
+    warm = min(warm, steps - 1)
+    n_steps = steps - warm
+    job_tokens, job_h2d, job_d2h = job.reduce([sum(tokens[warm:]), sum(h2d[warm:]), sum(d2h[warm:])], "sum")
+    worst_ms, worst_wall, status_max = job.reduce([sum(ms[warm:]), sum(wall[warm:]) * 1e3, status], "max")
+    job.barrier()
+    return {"value": round(job_tokens / (worst_ms * 1e-3), 1), "unit": "tokens/s", "steps": n_steps,
+            "ms_per_step": round(worst_ms / n_steps, 4), "wall_ms_per_step": round(worst_wall / n_steps, 4),
+            "h2d_bytes_per_step": int(job_h2d / n_steps), "d2h_bytes_per_step": int(job_d2h / n_steps),
+            "launches_per_step_rank0": round(launches / steps, 1), "device_status": int(status_max),
+            "clock": "CUDA events around the blocking psi_gqa_step_host call (max over ranks of the sum); "
+                     "large steps run as groups of requests whose transfers and launches overlap"}
 
 
 SPLIT_KEYS = ("metric", "value", "unit", "scaling", "steps", "ms_per_step", "tokens_per_s", "kv_gbs",
               "frac_of_nominal_8tbs_per_gpu", "config", "roofline", "kernel_ms_per_step", "gpu_launches", "device_status",
               "decode_rows", "chunk_rows", "host_us_per_step", "slowest_rank_cost_share", "pages_reused", "parity",
-              "job_decode_gbs", "job_chunk_tflops", "wall_s_whole_trace")
+              "job_decode_gbs", "job_chunk_tflops", "wall_s_whole_trace", "e2e")
 
 
 def bench_ours(args):

@@ -516,7 +516,12 @@ PSI_API int32_t psi_gqa_decode_step_host(psi_gqa* gqa, psi_pages* pages, psi_tab
  * one launch pulls the packed plan and q/k/v over the host link (no copy-engine transfer) and the attention launch
  * stores out straight into the host buffer; from 1 MiB of q + k + v on (and no long query runs in the step) the attention launch reads the pinned
  * buffers in place, so that the transfer runs under the K/V stream instead of in front of it.  Same result as the two
- * calls. */
+ * calls.  A step with long query runs and 64 MiB or more of q + k + v in pinned buffers (balanced plan mode, no replay
+ * reservation) runs as up to eight groups of consecutive requests instead: group i's inputs travel on a copy stream
+ * while group i-1 is planned and launched and group i-2's output travels back on a second copy stream, so the step
+ * takes about as long as the slowest of transfer in, compute and transfer out rather than their sum.  Every group gets a
+ * plan of its own (its KV splits differ from the whole step's: results agree within the tolerance of any other split),
+ * and the component is left unprepared afterwards (its metadata would describe the last group only). */
 PSI_API int32_t psi_gqa_step_host(psi_gqa* gqa, psi_pages* pages, psi_table* table, uint32_t layer,
                                   const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
                                   uint32_t num_reqs, const void* k_host, const void* v_host, const void* q_host,

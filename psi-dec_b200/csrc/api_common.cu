@@ -197,8 +197,9 @@ void run_staged_host_step(psi_gqa* g, psi_pages* pages, psi_table* table, uint32
 // staging buffer and its size comes back in *deferred_words: the caller brings it to the device itself.
 void prepare_impl(psi_gqa* g, const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
                   uint32_t num_reqs, uint32_t capacity_mode, uint32_t caller_num_total_tokens,
-                  psi_replay_shape* out_shape, bool defer_upload, uint64_t* deferred_words) {
+                  psi_replay_shape* out_shape, bool defer_upload, uint64_t* deferred_words, bool plan_only) {
     {
+        require(!plan_only || g->cfg.plan_mode == PSI_PLAN_BALANCED, "a plan-only prepare needs the balanced plan mode");
         require(req_slots != nullptr && token_indices != nullptr && cu_tokens != nullptr, "metadata inputs must not be null");
         require(capacity_mode <= PSI_CAPACITY_CALLER_TOKENS, "unknown capacity mode");
         require(num_reqs > 0, "GQA batch metadata requires tokens");
@@ -226,8 +227,13 @@ void prepare_impl(psi_gqa* g, const uint32_t* req_slots, const uint32_t* token_i
             variant.num_threads_per_threadblock = 256;
             variant.q_head_tile_size = std::min(g->geo.group, 8u);
         }
-        const psi_replay_shape shape = g->md->update(req_slots, token_indices, cu_tokens, num_reqs, variant,
-                                                     capacity_mode, g->boundaries, caller_num_total_tokens);
+        psi_replay_shape shape{};
+        if (plan_only) {
+            shape.num_tokens = shape.num_total_tokens = g->md->expand_tokens(req_slots, token_indices, cu_tokens, num_reqs);
+        } else {
+            shape = g->md->update(req_slots, token_indices, cu_tokens, num_reqs, variant, capacity_mode, g->boundaries,
+                                  caller_num_total_tokens);
+        }
 
         const uint64_t table_tokens =
             uint64_t(g->cfg.layout.num_blocks) * g->cfg.layout.num_page_ids_per_block * g->tokens_per_page;

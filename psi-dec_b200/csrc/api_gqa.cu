@@ -71,6 +71,9 @@ int32_t psi_gqa_destroy(psi_gqa* g) {
         g->sync_words.release();
         g->xchg_local.release();
         g->norm_rope.release();
+        for (cudaEvent_t e : g->pipe_events) (void)cudaEventDestroy(e);
+        if (g->pipe_h2d != nullptr) (void)cudaStreamDestroy(g->pipe_h2d);
+        if (g->pipe_d2h != nullptr) (void)cudaStreamDestroy(g->pipe_d2h);
         if (g->staging != nullptr) (void)cudaFreeHost(g->staging);
         if (g->upload_done != nullptr) (void)cudaEventDestroy(g->upload_done);
     });

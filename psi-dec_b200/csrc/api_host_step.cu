@@ -3,6 +3,88 @@
 
 using namespace psi;
 
+namespace {
+
+// A large step with long query runs from pinned host buffers, cut into groups of consecutive requests.  Group i's
+// q/k/v travel on one copy stream while group i-1 is planned and launched on the context's stream and group i-2's
+// output travels back on a second copy stream, so the step takes about as long as the slowest of the three (on these
+// boxes the inbound transfer) instead of their sum.  Every group is a step of its own for the kernels: its own plan,
+// token offsets relative to its first token.
+void run_pipelined_host_step(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const uint32_t* req_slots,
+                             const uint32_t* token_indices, const uint32_t* cu_tokens, uint32_t num_reqs,
+                             const void* k_host, const void* v_host, const void* q_host, void* out_host) {
+    psi_ctx* ctx = g->ctx;
+    const uint64_t esz = dtype_bytes(g->cfg.dtype);
+    const uint64_t kv_row = uint64_t(g->cfg.num_kv_heads) * g->cfg.head_dim * esz;
+    const uint64_t q_row = uint64_t(g->cfg.num_q_heads) * g->cfg.head_dim * esz;
+    const uint32_t num_tokens = cu_tokens[num_reqs];
+    const uint64_t in_bytes = uint64_t(num_tokens) * (q_row + 2 * kv_row);
+    const uint32_t groups = static_cast<uint32_t>(
+        std::min<uint64_t>(std::min<uint64_t>(kPipelineMaxGroups, num_reqs), std::max<uint64_t>(2, in_bytes / kPipelineGroupBytes)));
+    // group boundaries (request indices): equal shares of the step's tokens, i.e. of its transfer bytes
+    std::vector<uint32_t> first_req(groups + 1, num_reqs);
+    first_req[0] = 0;
+    for (uint32_t i = 1, r = 0; i < groups; ++i) {
+        const uint64_t target = uint64_t(num_tokens) * i / groups;
+        while (r < num_reqs && cu_tokens[r] < target) ++r;
+        first_req[i] = std::max(r, first_req[i - 1]);
+    }
+
+    if (g->pipe_h2d == nullptr) cuda_check(cudaStreamCreateWithFlags(&g->pipe_h2d, cudaStreamNonBlocking), "cudaStreamCreate");
+    if (g->pipe_d2h == nullptr) cuda_check(cudaStreamCreateWithFlags(&g->pipe_d2h, cudaStreamNonBlocking), "cudaStreamCreate");
+    while (g->pipe_events.size() < 2 * kPipelineMaxGroups + 1) {
+        cudaEvent_t e = nullptr;
+        cuda_check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+        g->pipe_events.push_back(e);
+    }
+    g->step_out.ensure(ctx, uint64_t(g->cfg.max_tokens) * q_row, false);
+    // the copy streams start behind whatever the context's stream still holds (an earlier step that reads the staging)
+    cudaEvent_t entry = g->pipe_events[2 * kPipelineMaxGroups];
+    cuda_check(cudaEventRecord(entry, ctx->stream), "cudaEventRecord");
+    cuda_check(cudaStreamWaitEvent(g->pipe_h2d, entry, 0), "cudaStreamWaitEvent");
+    cuda_check(cudaStreamWaitEvent(g->pipe_d2h, entry, 0), "cudaStreamWaitEvent");
+
+    auto at = [](const void* base, uint64_t offset) { return static_cast<const unsigned char*>(base) + offset; };
+    auto at_mut = [](void* base, uint64_t offset) { return static_cast<unsigned char*>(base) + offset; };
+    for (uint32_t i = 0; i < groups; ++i) {  // all inbound copies are queued first: the copy engine never waits for the host
+        const uint32_t tok0 = cu_tokens[first_req[i]], ntok = cu_tokens[first_req[i + 1]] - tok0;
+        if (ntok == 0) continue;
+        cuda_check(cudaMemcpyAsync(at_mut(g->step_q.ptr, tok0 * q_row), at(q_host, tok0 * q_row), ntok * q_row,
+                                   cudaMemcpyHostToDevice, g->pipe_h2d), "H2D q");
+        cuda_check(cudaMemcpyAsync(at_mut(g->step_k.ptr, tok0 * kv_row), at(k_host, tok0 * kv_row), ntok * kv_row,
+                                   cudaMemcpyHostToDevice, g->pipe_h2d), "H2D k");
+        cuda_check(cudaMemcpyAsync(at_mut(g->step_v.ptr, tok0 * kv_row), at(v_host, tok0 * kv_row), ntok * kv_row,
+                                   cudaMemcpyHostToDevice, g->pipe_h2d), "H2D v");
+        cuda_check(cudaEventRecord(g->pipe_events[i], g->pipe_h2d), "cudaEventRecord");
+    }
+    std::vector<uint32_t> group_cu;
+    for (uint32_t i = 0; i < groups; ++i) {
+        const uint32_t r0 = first_req[i], r1 = first_req[i + 1];
+        const uint32_t tok0 = cu_tokens[r0], ntok = cu_tokens[r1] - tok0;
+        if (ntok == 0) continue;
+        group_cu.assign(r1 - r0 + 1, 0);
+        for (uint32_t r = r0; r <= r1; ++r) group_cu[r - r0] = cu_tokens[r] - tok0;
+        prepare_impl(g, req_slots + r0, token_indices + r0, group_cu.data(), r1 - r0, PSI_CAPACITY_EXACT, 0, nullptr,
+                     false, nullptr, /*plan_only=*/true);
+        cuda_check(cudaStreamWaitEvent(ctx->stream, g->pipe_events[i], 0), "cudaStreamWaitEvent");
+        AttendParams p = attend_params(g, pages, table, layer, at_mut(g->step_q.ptr, tok0 * q_row));
+        p.out = at_mut(g->step_out.ptr, tok0 * q_row);
+        p.new_k = at_mut(g->step_k.ptr, tok0 * kv_row);
+        p.new_v = at_mut(g->step_v.ptr, tok0 * kv_row);
+        run_attend(g, p);
+        cudaEvent_t done = g->pipe_events[kPipelineMaxGroups + i];
+        cuda_check(cudaEventRecord(done, ctx->stream), "cudaEventRecord");
+        cuda_check(cudaStreamWaitEvent(g->pipe_d2h, done, 0), "cudaStreamWaitEvent");
+        cuda_check(cudaMemcpyAsync(at_mut(out_host, tok0 * q_row), at(g->step_out.ptr, tok0 * q_row), ntok * q_row,
+                                   cudaMemcpyDeviceToHost, g->pipe_d2h), "D2H out");
+    }
+    cuda_check(cudaStreamSynchronize(g->pipe_d2h), "cudaStreamSynchronize");
+    cuda_check(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    g->prepared = false;  // the last plan covers the last group only
+}
+
+}  // namespace
+
 extern "C" {
 
 int32_t psi_gqa_decode_step_host(psi_gqa* g, psi_pages* pages, psi_table* table, uint32_t layer, const void* k_host,
@@ -104,6 +186,12 @@ int32_t psi_gqa_step_host(psi_gqa* g, psi_pages* pages, psi_table* table, uint32
                 const uint32_t tiles = (cu_tokens[r + 1] - cu_tokens[r] + g->geo.tokens_per_tile - 1) / g->geo.tokens_per_tile;
                 if (tiles >= kChunkMinTiles) direct = false;
             }
+        }
+        if (!direct && q_bytes + 2 * kv_bytes >= kPipelineHostBytes && num_reqs >= 2 && !g->replay_reserved &&
+            g->cfg.plan_mode == PSI_PLAN_BALANCED) {
+            run_pipelined_host_step(g, pages, table, layer, req_slots, token_indices, cu_tokens, num_reqs, k_host, v_host,
+                                    q_host, out_host);
+            return;
         }
         // The step is planned first; then ONE launch pulls the packed plan from its pinned staging buffer together with
         // q/k/v (or the plan alone when q/k/v are read in place), and the attention launch stores `out` straight into

@@ -211,6 +211,9 @@ struct psi_gqa {
     psi::DeviceBuffer status_word;  // u32 written by bounded device-side waits
     psi::DeviceBuffer sync_words;   // SyncWord counters of launches that wait or exchange; zero between launches
     psi::DeviceBuffer xchg_local;   // KV-range exchange without the fused launch: this rank's partial before the push
+    // psi_gqa_step_host on large pinned buffers: copy streams and per-group events of the pipelined step
+    cudaStream_t pipe_h2d = nullptr, pipe_d2h = nullptr;
+    std::vector<cudaEvent_t> pipe_events;
     bool chunk_umma = false;   // long query runs on the tcgen05 kernel (else the mma.sync chunk kernel)
     uint32_t chunk_launches[2] = {0, 0};  // tcgen05, mma.sync
     psi::DeviceBuffer norm_rope;    // q weight bf16[D] | k weight bf16[D] | inverse frequencies f32[rope_dim/2]
@@ -263,6 +266,11 @@ const uint32_t* block_words(const psi_gqa* g, uint64_t offset);
 constexpr uint32_t kChunkMinTiles = 5;
 // psi_gqa_step_host: from this many bytes of q + k + v the attention launch reads pinned host buffers in place.
 constexpr uint64_t kDirectHostBytes = 1ull << 20;
+// psi_gqa_step_host: from this many bytes of q + k + v in pinned buffers a step with long query runs is cut into groups
+// of requests whose transfers and launches overlap; a group carries about kPipelineGroupBytes of them.
+constexpr uint64_t kPipelineHostBytes = 64ull << 20;
+constexpr uint64_t kPipelineGroupBytes = 48ull << 20;
+constexpr uint32_t kPipelineMaxGroups = 8;
 
 AttendParams attend_params(psi_gqa* g, const psi_pages* pages, const psi_table* table, uint32_t layer, const void* q);
 void run_attend(psi_gqa* g, const AttendParams& params);
@@ -275,8 +283,10 @@ void run_staged_host_step(psi_gqa* g, psi_pages* pages, psi_table* table, uint32
                           uint64_t q_cap);
 // GQAMetadataBuffers::update plus this library's plan.  With `defer_upload` the packed block stays in the pinned
 // staging buffer and its size comes back in *deferred_words: the caller brings it to the device itself.
+// `plan_only` (balanced plan mode): the reference-format split plan is not computed, only the per-token arrays and this
+// library's plan; the replay shape then names the token count alone.
 void prepare_impl(psi_gqa* g, const uint32_t* req_slots, const uint32_t* token_indices, const uint32_t* cu_tokens,
                   uint32_t num_reqs, uint32_t capacity_mode, uint32_t caller_num_total_tokens,
-                  psi_replay_shape* out_shape, bool defer_upload, uint64_t* deferred_words);
+                  psi_replay_shape* out_shape, bool defer_upload, uint64_t* deferred_words, bool plan_only = false);
 
 }  // namespace psi

@@ -131,6 +131,27 @@ void refine_splits(std::vector<SplitCandidateTile>& tiles, uint64_t used, uint64
 
 }  // namespace
 
+uint32_t ReferenceMetadata::expand_tokens(const uint32_t* req_slots_by_req, const uint32_t* token_indices,
+                                          const uint32_t* cu_tokens, uint32_t num_reqs) {
+    require(num_reqs > 0, "GQA batch metadata requires tokens");
+    require(cu_tokens[0] == 0, "GQA batch cu_tokens must start at zero");
+    for (uint32_t r = 0; r < num_reqs; ++r) {
+        require(cu_tokens[r] <= cu_tokens[r + 1], "GQA batch cu_tokens must be nondecreasing");
+        require(uint64_t(token_indices[r]) + (cu_tokens[r + 1] - cu_tokens[r]) <= kU32Max,
+                "GQA request context length must fit u32");
+    }
+    const uint32_t num_tokens = cu_tokens[num_reqs];
+    require(num_tokens > 0, "GQA batch metadata requires tokens");
+    require(num_tokens <= max_tokens(), "GQA batch exceeds the metadata token capacity");
+    for (uint32_t r = 0, t = 0; r < num_reqs; ++r) {
+        for (uint32_t i = 0; i < cu_tokens[r + 1] - cu_tokens[r]; ++i, ++t) {
+            req_slots[t] = req_slots_by_req[r];
+            flat_token_indices[t] = token_indices[r] + i;
+        }
+    }
+    return num_tokens;
+}
+
 psi_replay_shape ReferenceMetadata::update(const uint32_t* req_slots_by_req, const uint32_t* token_indices,
                                            const uint32_t* cu_tokens, uint32_t num_reqs,
                                            const psi_split_kv_variant& variant, uint32_t capacity_mode,

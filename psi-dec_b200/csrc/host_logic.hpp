@@ -67,6 +67,10 @@ struct ReferenceMetadata {
     std::vector<uint32_t> req_slots, flat_token_indices, q_token_tiles, kv_splits, cu_kv_splits;
     explicit ReferenceMetadata(uint32_t max_tokens);
     uint32_t max_tokens() const { return static_cast<uint32_t>(req_slots.size()); }
+    // The per-token arrays alone (request slot and request-absolute position of every query token), with update()'s
+    // checks of the batch; returns the token count.  What a launch needs when no reference-format split plan is asked for.
+    uint32_t expand_tokens(const uint32_t* req_slots_by_req, const uint32_t* token_indices, const uint32_t* cu_tokens,
+                           uint32_t num_reqs);
     psi_replay_shape update(const uint32_t* req_slots_by_req, const uint32_t* token_indices, const uint32_t* cu_tokens,
                             uint32_t num_reqs, const psi_split_kv_variant& variant, uint32_t capacity_mode,
                             const std::vector<uint32_t>& token_topology_boundaries, uint32_t caller_num_total_tokens);

@@ -431,9 +431,10 @@ class ChurnSession:
             entry = ids[block * self.ipb:(block + 1) * self.ipb]
             self.table.write_page_ids(local, 0, block, entry + [0] * (self.ipb - len(entry)))
 
-    def prepare_step(self, t: int):
+    def prepare_step(self, t: int, plan: bool = True):
         """Host work in front of step ``t``: admissions of the previous step's leavers are already done; pages for this
-        step's appended tokens are allocated and the plan is uploaded.  Returns (table_seconds, prepare_seconds)."""
+        step's appended tokens are allocated and the plan is uploaded (``plan=False``: left to ``host_step``).
+        Returns (table_seconds, prepare_seconds)."""
         import time
         tr = self.trace
         t0 = time.perf_counter()
@@ -444,13 +445,21 @@ class ChurnSession:
         cu = np.concatenate([[0], np.cumsum(q_len)]).astype(np.uint32)
         self.tokens = int(cu[-1])
         self.batch = (np.arange(len(self.mine), dtype=np.uint32), tr.context[t][self.mine].astype(np.uint32), cu)
-        self.gqa.prepare(*self.batch)
+        if plan:
+            self.gqa.prepare(*self.batch)
         return t1 - t0, time.perf_counter() - t1
 
     def launch_step(self):
         """The step on the device: this step's K/V rows into their pages and attention over everything visible."""
         n = self.tokens
         self.gqa.append_attend(self.pages, self.table, 0, self.k[:n], self.v[:n], self.q[:n], self.out[:n])
+
+    def host_step(self, k_host, v_host, q_host, out_host):
+        """The same step from host buffers through ``psi_gqa_step_host``: plan, transfers in, append, attention and the
+        result's way back in one blocking call (large steps from pinned buffers are cut into groups of requests whose
+        transfers and launches overlap)."""
+        n = self.tokens
+        self.gqa.step_host(self.pages, self.table, 0, *self.batch, k_host[:n], v_host[:n], q_host[:n], out_host[:n])
 
     def finish_step(self, t: int):
         """After step ``t``: the leavers' pages go back to the allocator, their table rows are zeroed, and the

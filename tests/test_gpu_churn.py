@@ -142,3 +142,44 @@ def test_churn_session_trace_matches_the_oracle_and_reuses_pages():
     assert churn.reused_pages > 0
     assert churn.allocator.used() == sum(len(ids) for ids in churn.page_ids)
     churn.close()
+
+
+def test_churn_steps_from_pinned_host_buffers_run_as_overlapping_request_groups():
+    # Steps large enough for the grouped host step (more than 64 MB of q + k + v, long query runs present): the output
+    # that comes back in the host buffer against a twin session that runs the same trace from device memory (other
+    # plans, so other KV splits: tolerance), a sample of sequences against the oracle, and the two arenas bit for bit.
+    import torch
+    from psi_dec_b200 import workloads as PW
+    trace = PW.ChurnTrace(slots=64, steps=3, seed=23, world=1, hi=3000, chunk=512, chunk_fraction=0.4)
+    host, twin = PW.ChurnSession(trace), PW.ChurnSession(trace)
+    assert torch.equal(host.arena.view(torch.int16), twin.arena.view(torch.int16))
+    kh, vh, qh = host.k.cpu().pin_memory(), host.v.cpu().pin_memory(), host.q.cpu().pin_memory()
+    oh = torch.zeros_like(qh).pin_memory()
+    for t in range(trace.steps):
+        host.prepare_step(t, plan=False)
+        twin.prepare_step(t)
+        n = host.tokens
+        assert n * (qh[0].numel() + 2 * kh[0].numel()) * 2 >= 64 << 20
+        oh.fill_(float("nan"))
+        before = host.ctx.launch_count
+        host.host_step(kh, vh, qh, oh)
+        assert host.ctx.launch_count - before >= 4, "the step must have run as several groups"
+        twin.launch_step()
+        twin.ctx.sync()
+        assert host.gqa.device_status() == 0
+        got, want = oh[:n].float(), twin.out[:n].float().cpu()
+        assert torch.isfinite(got).all()
+        assert (got - want).abs().max().item() <= 2e-2
+        assert torch.equal(host.arena.view(torch.int16), twin.arena.view(torch.int16))
+        host.out[:n].copy_(oh[:n])   # the oracle helper reads the session's device output
+        q_len = trace.q_len[t]
+        for local in (0, int(np.argmax(q_len)), trace.slots - 1):
+            max_abs, mean_abs = checks.churn_sequence_error(host, t, local)
+            assert max_abs <= 2e-2 and mean_abs <= 2e-3, (t, local, max_abs, mean_abs)
+        # the component is left unprepared after a grouped step
+        with pytest.raises(pkg.PsiError, match="metadata must be updated"):
+            host.gqa.attend(host.pages, host.table, 0, host.q[:n], host.out[:n])
+        host.finish_step(t)
+        twin.finish_step(t)
+    host.close()
+    twin.close()
