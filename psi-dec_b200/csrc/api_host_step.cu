@@ -44,6 +44,15 @@ void run_pipelined_host_step(psi_gqa* g, psi_pages* pages, psi_table* table, uin
     cuda_check(cudaStreamWaitEvent(g->pipe_h2d, entry, 0), "cudaStreamWaitEvent");
     cuda_check(cudaStreamWaitEvent(g->pipe_d2h, entry, 0), "cudaStreamWaitEvent");
 
+    // Whatever happens below, no copy that names the caller's buffers is left in flight when the call returns.
+    struct Drain {
+        psi_gqa* g;
+        ~Drain() {
+            (void)cudaStreamSynchronize(g->pipe_h2d);
+            (void)cudaStreamSynchronize(g->ctx->stream);
+            (void)cudaStreamSynchronize(g->pipe_d2h);
+        }
+    } drain{g};
     auto at = [](const void* base, uint64_t offset) { return static_cast<const unsigned char*>(base) + offset; };
     auto at_mut = [](void* base, uint64_t offset) { return static_cast<unsigned char*>(base) + offset; };
     for (uint32_t i = 0; i < groups; ++i) {  // all inbound copies are queued first: the copy engine never waits for the host
