@@ -113,9 +113,14 @@ def test_c_program_runs_the_cpu_scale_configuration_end_to_end(abi_check, tmp_pa
     out_file = tmp_path / "step.bin"
     done = subprocess.run([str(abi_check), "step", str(out_file)], capture_output=True, text=True)
     assert done.returncode == 0 and "step ok" in done.stdout, done.stdout + done.stderr
+    check_cpu_scale_step(np.fromfile(out_file, dtype=np.uint16))
+
+
+def check_cpu_scale_step(raw):
+    """`raw` = q | k | v | arena after the step | out (f16 bits) of the CPU-scale configuration as the C and C++ callers
+    write it: the inputs are regenerated here, the arena and the output are held against the CPU oracle."""
     hq, hkv, d, p, pages, context = 4, 1, 128, 16, 64, 256
     page_elems = 2 * hkv * p * d
-    raw = np.fromfile(out_file, dtype=np.uint16)
     q, k, v, arena, out = np.split(raw, np.cumsum([hq * d, hkv * d, hkv * d, pages * page_elems]))
     # the program's inputs, regenerated: the same LCG, the same truncating float -> half conversion
     state = 0x4C8F17D2
