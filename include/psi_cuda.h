@@ -101,7 +101,8 @@ typedef enum psi_plan_mode {
 
 typedef enum psi_kernel_mode {
     PSI_KERNEL_AUTO = 0,    /* tensor-core kernel when the profile allows, else the generic kernel */
-    PSI_KERNEL_GENERIC = 1, /* CUDA-core kernel: any dtype, head_dim <= 256, any tokens_per_page */
+    PSI_KERNEL_GENERIC = 1, /* CUDA-core kernels: any dtype, head_dim <= 256, any tokens_per_page (staged in shared
+                               memory when head_dim is a multiple of four) */
     PSI_KERNEL_MMA = 2,     /* bf16/f16 mma kernel: head_dim in {64,128,256}, tokens_per_page a power of two >= 8 */
     PSI_KERNEL_MMA_SYNC = 3, /* as PSI_KERNEL_MMA, but long query runs stay on the mma.sync chunk kernel instead of
                                 the tcgen05 / TMEM kernel (kept for A/B measurement) */

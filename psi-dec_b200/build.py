@@ -18,7 +18,7 @@ ROOT = PKG.parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libpsi_cuda.so"
 LIB_CHECKED = PKG / "lib" / "libpsi_cuda_checked.so"
-SOURCES = ["api_common.cu", "api_context.cu", "api_arena.cu", "api_snapshot.cu", "api_policy.cu", "api_gqa.cu", "api_exchange.cu", "api_host_step.cu", "kv_pages.cu", "prep.cu", "attend_generic.cu", "attend_mma.cu", "attend_chunk.cu", "attend_chunk_umma.cu", "tma_map.cu", "attend_static.cu", "exchange.cu", "probe.cu", "host_logic.cpp", "snapshot.cpp"]
+SOURCES = ["api_common.cu", "api_context.cu", "api_arena.cu", "api_snapshot.cu", "api_policy.cu", "api_gqa.cu", "api_exchange.cu", "api_host_step.cu", "kv_pages.cu", "prep.cu", "attend_generic.cu", "attend_staged.cu", "attend_mma.cu", "attend_chunk.cu", "attend_chunk_umma.cu", "tma_map.cu", "attend_static.cu", "exchange.cu", "probe.cu", "host_logic.cpp", "snapshot.cpp"]
 
 
 def _nvcc() -> str:

@@ -1,6 +1,7 @@
 // Generic split-KV flash-decode map kernel on CUDA cores, the partial reduce and the cross-device combine.
 //
-// The generic map kernel takes every profile the reference's SingleQ kernel takes (f32 / bf16, any tokens_per_page,
+// launch_attend_generic hands a launch to the staged kernel of attend_staged.cu when it qualifies (head_dim a multiple
+// of four, aligned buffers); the one-warp kernel below takes the rest.  It takes every profile the reference's SingleQ kernel takes (f32 / bf16, any tokens_per_page,
 // head_dim up to 256) plus f16: one warp per CTA walks its work items; lanes split head_dim, every KV row is read
 // once per item and scored against all rows (tokens x group heads) of the item with f32 accumulation and an online
 // softmax in the log2 domain.  Semantics follow
@@ -266,10 +267,11 @@ cudaError_t launch_signal(uint32_t* flag, uint32_t value, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-uint32_t attend_generic_ctas_per_sm() { return 8; }
+uint32_t attend_generic_ctas_per_sm(uint32_t head_dim) { return head_dim % 4 == 0 ? 1u : 8u; }
 
 cudaError_t launch_attend_generic(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     if (num_ctas == 0) return cudaSuccess;
+    if (attend_staged_supported(p)) return launch_attend_staged(p, num_ctas, stream);
     const uint32_t dpl = (p.geo.head_dim + 31) / 32;
     if (dpl <= 1) {
         attend_generic_kernel<1><<<num_ctas, kGenericThreads, 0, stream>>>(p);
