@@ -36,7 +36,7 @@ int32_t psi_gqa_create(psi_ctx* ctx, const psi_gqa_config* config, psi_gqa** out
         if (c.kernel_mode >= PSI_KERNEL_MMA) require(mma_ok, "the mma kernel does not support this profile");
         g->kernel = (c.kernel_mode == PSI_KERNEL_GENERIC || !mma_ok) ? PSI_KERNEL_GENERIC : PSI_KERNEL_MMA;
         const uint32_t per_sm =
-            g->kernel == PSI_KERNEL_MMA ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm(c.head_dim);
+            g->kernel == PSI_KERNEL_MMA ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm(c.head_dim, c.dtype);
         g->grid_cap = c.max_ctas > 0 ? c.max_ctas : static_cast<uint32_t>(ctx->sm_count) * per_sm;
         g->item_start_cost = g->kernel == PSI_KERNEL_MMA ? 32u : 0u;
         g->chunk_supported = g->kernel == PSI_KERNEL_MMA && c.plan_mode == PSI_PLAN_BALANCED &&

@@ -267,7 +267,9 @@ cudaError_t launch_signal(uint32_t* flag, uint32_t value, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-uint32_t attend_generic_ctas_per_sm(uint32_t head_dim) { return head_dim % 4 == 0 ? 1u : 8u; }
+uint32_t attend_generic_ctas_per_sm(uint32_t head_dim, uint32_t dtype) {
+    return head_dim % 4 == 0 ? attend_staged_ctas_per_sm(dtype) : 8u;
+}
 
 cudaError_t launch_attend_generic(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     if (num_ctas == 0) return cudaSuccess;

@@ -64,8 +64,10 @@ __host__ __device__ constexpr uint32_t staged_smem_floats(uint32_t head_dim) {
            4 * kMaxRows + 4 * kStagedTile;
 }
 
+// Two CTAs per SM for the 16-bit types (one's loads under the other's arithmetic: 452 against 578 us on the layer-decode
+// batch); f32 holds twice the registers per piece and measured slower that way (spills), so it keeps one.
 template <typename T>
-__global__ void __launch_bounds__(kStagedThreads, 1) attend_staged_kernel(AttendParams p) {
+__global__ void __launch_bounds__(kStagedThreads, sizeof(T) == 4 ? 1 : 2) attend_staged_kernel(AttendParams p) {
     using Raw = typename Piece<T>::Raw;
     const uint32_t cta = blockIdx.x;
     if (cta >= p.scalars[kScalarNumCtas]) return;
@@ -291,6 +293,8 @@ cudaError_t launch_staged(const AttendParams& p, uint32_t num_ctas, cudaStream_t
 }
 
 }  // namespace
+
+uint32_t attend_staged_ctas_per_sm(uint32_t dtype) { return dtype == PSI_DTYPE_F32 ? 1u : 2u; }
 
 // head_dim a multiple of four up to 256, and arena, q and partial buffers on 16-byte boundaries.
 bool attend_staged_supported(const AttendParams& p) {

@@ -151,7 +151,7 @@ extern "C" int32_t psi_gqa_attend_static(int32_t device, void* cuda_stream, cons
         const PlanGeometry geo = plan_geometry(c.num_q_heads, c.num_kv_heads);
         const bool mma = c.kernel_mode != PSI_KERNEL_GENERIC && attend_mma_supported(c.dtype, c.head_dim, tokens_per_page);
         require(mma || c.kernel_mode < PSI_KERNEL_MMA, "the mma kernel does not support this profile");
-        const uint32_t per_sm = mma ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm(c.head_dim);
+        const uint32_t per_sm = mma ? attend_mma_ctas_per_sm(c.head_dim) : attend_generic_ctas_per_sm(c.head_dim, c.dtype);
         uint32_t max_ctas = std::min<uint32_t>(kStaticMaxCtas, static_cast<uint32_t>(sm_count) * per_sm);
         if (c.max_ctas > 0) max_ctas = std::min(max_ctas, c.max_ctas);
         const WorkPlan plan = build_balanced_plan(geo, req_slots, token_indices, cu_tokens, num_reqs, max_ctas,

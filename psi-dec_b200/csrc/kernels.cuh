@@ -175,9 +175,10 @@ cudaError_t launch_norm_rope_append(const PrepParams& p, cudaStream_t stream);
 // mma kernel needs bf16/f16, head_dim in {64,128,256} and tokens_per_page % 8 == 0.
 bool attend_mma_supported(uint32_t dtype, uint32_t head_dim, uint32_t tokens_per_page);
 uint32_t attend_mma_ctas_per_sm(uint32_t head_dim);
-// Resident CTAs per SM of the CUDA-core map kernel that a profile of this head_dim gets (the staged kernel when
-// head_dim is a multiple of four, else the one-warp kernel).
-uint32_t attend_generic_ctas_per_sm(uint32_t head_dim);
+// Resident CTAs per SM of the CUDA-core map kernel that a profile of this head_dim and dtype gets (the staged kernel
+// when head_dim is a multiple of four, else the one-warp kernel).
+uint32_t attend_generic_ctas_per_sm(uint32_t head_dim, uint32_t dtype);
+uint32_t attend_staged_ctas_per_sm(uint32_t dtype);
 // The staged CUDA-core map kernel (attend_staged.cu): taken by launch_attend_generic when the launch qualifies.
 bool attend_staged_supported(const AttendParams& p);
 cudaError_t launch_attend_staged(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream);
