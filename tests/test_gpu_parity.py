@@ -518,6 +518,33 @@ def test_random_profiles_on_the_correctness_path_against_the_oracle(seed):
     s.close()
 
 
+@pytest.mark.parametrize("index,scale_down,kernel_mode", [
+    (2, 1, pkg.KERNEL_AUTO), (3, 4, pkg.KERNEL_AUTO), (5, 8, pkg.KERNEL_AUTO), (5, 8, pkg.KERNEL_MMA_SYNC),
+    (3, 8, pkg.KERNEL_GENERIC), (2, 4, pkg.KERNEL_MMA_TMA)])
+def test_repeated_launches_are_bit_identical(index, scale_down, kernel_mode):
+    # A launch's result depends on nothing but its inputs: cut units are merged in slot order whoever arrives last,
+    # and no kernel reads shared or global memory that it has not written in the same launch.  Forty launches of the
+    # same step (an L2 sweep in between changes the timing of the loads), every output against the first, bit for bit.
+    import torch
+    s = W.Session(W.config(index, scale_down=scale_down), kernel_mode=kernel_mode)
+    sweep = torch.zeros(48 << 20, dtype=torch.float32, device=s.device)
+    s.step()
+    s.ctx.sync()
+    first = s.out.clone()
+    arena = s.arena.clone()
+    for launch in range(40):
+        if launch % 2:
+            sweep.sum()
+        s.out.fill_(float("nan"))
+        s.step()
+        s.ctx.sync()
+        assert torch.equal(first.view(torch.int16), s.out.view(torch.int16)), launch
+    assert torch.equal(arena.view(torch.int16), s.arena.view(torch.int16))
+    assert s.gqa.device_status() == 0
+    checks.assert_attention_close(s, seq_ids=list(range(min(4, s.spec.num_seqs))))
+    s.close()
+
+
 @pytest.mark.parametrize("engine", ["tcgen05", "mma_sync"])
 @pytest.mark.parametrize("max_ctas", [1, 5, 148])
 @pytest.mark.parametrize("heads,head_dim,page", [((16, 2), 256, 16), ((24, 4), 128, 8), ((8, 8), 128, 32)])
