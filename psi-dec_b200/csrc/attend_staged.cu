@@ -58,10 +58,19 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// Shared memory in floats: q [16][D] | K tile [32][D + 4] | V tile [32][D] | P [16][32] | per-row words.
-__host__ __device__ constexpr uint32_t staged_smem_floats(uint32_t head_dim) {
-    return kMaxRows * head_dim + kStagedTile * (head_dim + 4) + kStagedTile * head_dim + kMaxRows * kStagedTile +
-           4 * kMaxRows + 4 * kStagedTile;
+// Shared memory in floats: q [16][D] | `stages` x (K tile [32][D + 4] | V tile [32][D]) | P [16][32] | per-row words.
+__host__ __device__ constexpr uint32_t staged_tile_floats(uint32_t head_dim) {
+    return kStagedTile * (head_dim + 4) + kStagedTile * head_dim;
+}
+__host__ __device__ constexpr uint32_t staged_smem_floats(uint32_t head_dim, uint32_t stages) {
+    return kMaxRows * head_dim + stages * staged_tile_floats(head_dim) + kMaxRows * kStagedTile + 4 * kMaxRows +
+           4 * kStagedTile;
+}
+
+__device__ __forceinline__ void staged_cp_async_16(float* dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+                 "l"(src), "r"(src_bytes)
+                 : "memory");
 }
 
 // Two CTAs per SM for the 16-bit types (one's loads under the other's arithmetic: 452 against 578 us on the layer-decode
@@ -69,6 +78,11 @@ __host__ __device__ constexpr uint32_t staged_smem_floats(uint32_t head_dim) {
 template <typename T>
 __global__ void __launch_bounds__(kStagedThreads, sizeof(T) == 4 ? 1 : 2) attend_staged_kernel(AttendParams p) {
     using Raw = typename Piece<T>::Raw;
+    // f32 needs no conversion on the way in: its tiles go straight from the pages into one of two shared-memory
+    // stages by 16-byte cp.async (zero-filled beyond the item's range), the next tile's copies in flight under the
+    // current tile's arithmetic, and nothing is held in registers.
+    constexpr bool kAsync = sizeof(T) == 4;
+    constexpr uint32_t kStages = kAsync ? 2 : 1;
     const uint32_t cta = blockIdx.x;
     if (cta >= p.scalars[kScalarNumCtas]) return;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -76,9 +90,8 @@ __global__ void __launch_bounds__(kStagedThreads, sizeof(T) == 4 ? 1 : 2) attend
 
     extern __shared__ __align__(16) float staged_smem[];
     float* q_s = staged_smem;
-    float* k_s = q_s + kMaxRows * D;
-    float* v_s = k_s + kStagedTile * k_stride;
-    float* p_s = v_s + kStagedTile * D;
+    float* tiles_s = q_s + kMaxRows * D;  // stage s: K tile at s * staged_tile_floats(D), its V tile behind it
+    float* p_s = tiles_s + kStages * staged_tile_floats(D);
     float* corr_s = p_s + kMaxRows * kStagedTile;
     float* m_s = corr_s + kMaxRows;
     float* l_s = m_s + kMaxRows;
@@ -152,13 +165,41 @@ __global__ void __launch_bounds__(kStagedThreads, sizeof(T) == 4 ? 1 : 2) attend
                 row_s[(tile & 1u) * kStagedTile + tid] = kv_row_offset(p.geo, page_id, v.kv_head, at % p.geo.tokens_per_page);
             }
         };
+        // f32: the copies of tile `tile` into its stage (one commit group per tile and thread)
+        auto copy_async = [&](uint32_t tile) {
+            const unsigned long long* rows_of_tile = row_s + (tile & 1u) * kStagedTile;
+            const uint32_t in_range = v.kv_end - (v.kv_begin + tile * kStagedTile);
+            float* k_dst = tiles_s + (tile & 1u) * staged_tile_floats(D);
+            float* v_dst = k_dst + kStagedTile * k_stride;
+            uint32_t token = first_token, piece = first_piece;
+#pragma unroll
+            for (uint32_t j = 0; j < kStagedChunks; ++j) {
+                if (tid + kStagedThreads * j < tile_pieces) {
+                    const bool is_v = piece >= C4;
+                    const uint64_t elem = rows_of_tile[token] + (is_v ? v_off : 0) + 4 * (piece - (is_v ? C4 : 0));
+                    float* dst = is_v ? v_dst + token * D + 4 * (piece - C4) : k_dst + token * k_stride + 4 * piece;
+                    staged_cp_async_16(dst, arena + elem, token < in_range ? 16u : 0u);
+                }
+                token += step_token;
+                piece += step_piece;
+                if (piece >= pieces_per_token) {
+                    piece -= pieces_per_token;
+                    token += 1;
+                }
+            }
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+        };
         if (num_tiles > 0) row_offsets_of(0);
         __syncthreads();  // q_s, limit_s and the first tile's page ids are in place
-        if (num_tiles > 0) fetch(0);
+        if (num_tiles > 0) {
+            if constexpr (kAsync) copy_async(0); else fetch(0);
+        }
 
         for (uint32_t tile = 0; tile < num_tiles; ++tile) {
-            // ---- the held tile goes to shared memory as f32 -------------------------------------------------------------
-            {
+            float* k_s = tiles_s + (kAsync ? (tile & 1u) * staged_tile_floats(D) : 0u);
+            float* v_s = k_s + kStagedTile * k_stride;
+            // ---- 16-bit types: the held tile goes to shared memory as f32 -----------------------------------------------
+            if constexpr (!kAsync) {
                 const uint32_t in_range = v.kv_end - (v.kv_begin + tile * kStagedTile);  // tokens of this tile inside the item
                 uint32_t token = first_token, piece = first_piece;
 #pragma unroll
@@ -178,8 +219,11 @@ __global__ void __launch_bounds__(kStagedThreads, sizeof(T) == 4 ? 1 : 2) attend
                 }
             }
             if (tile + 1 < num_tiles) row_offsets_of(tile + 1);
+            if constexpr (kAsync) asm volatile("cp.async.wait_group 0;\n" ::: "memory");  // this thread's copies of the tile
             __syncthreads();
-            if (tile + 1 < num_tiles) fetch(tile + 1);  // in flight during the arithmetic below
+            if (tile + 1 < num_tiles) {  // in flight during the arithmetic below
+                if constexpr (kAsync) copy_async(tile + 1); else fetch(tile + 1);
+            }
 
             // ---- scores and online softmax: lane = token, this warp's rows ----------------------------------------------
             const uint32_t pos = v.kv_begin + tile * kStagedTile + lane;
@@ -282,11 +326,12 @@ __global__ void __launch_bounds__(kStagedThreads, sizeof(T) == 4 ? 1 : 2) attend
 template <typename T>
 cudaError_t launch_staged(const AttendParams& p, uint32_t num_ctas, cudaStream_t stream) {
     auto kernel = attend_staged_kernel<T>;
-    const int bytes = static_cast<int>(staged_smem_floats(p.geo.head_dim) * sizeof(float));
+    constexpr uint32_t stages = sizeof(T) == 4 ? 2 : 1;
+    const int bytes = static_cast<int>(staged_smem_floats(p.geo.head_dim, stages) * sizeof(float));
     static std::atomic<uint64_t> configured{0};
     // the largest head_dim sets the limit once; smaller ones fit under it
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel),
-                                          static_cast<int>(staged_smem_floats(256) * sizeof(float)), configured);
+                                          static_cast<int>(staged_smem_floats(256, stages) * sizeof(float)), configured);
     if (err != cudaSuccess) return err;
     kernel<<<num_ctas, kStagedThreads, bytes, stream>>>(p);
     return cudaGetLastError();
