@@ -4,8 +4,11 @@
         tests/multi_gpu_worker.py kv_range p2p
 
 Modes: ``kv_range p2p|p2p3|nccl`` (configuration 4 scaled down, KV range split across the ranks, partial exchange, merged
-output checked against the CPU oracle's merge of per-rank oracle partials) and ``sequence`` (configuration 3 scaled
-down, sequence-sharded, every rank checked against the oracle on its own shard).
+output checked against the CPU oracle's merge of per-rank oracle partials), ``kv_range_free_run`` (the one-launch
+exchange for a few hundred steps with no host synchronisation between them, so that ranks run ahead of one another
+and the protocol's own ordering - two slots by step parity, the consumed word - is what keeps steps apart; every
+step's output is checked afterwards) and ``sequence`` (configuration 3 scaled down, sequence-sharded, every rank
+checked against the oracle on its own shard).
 """
 import os
 import sys
@@ -39,6 +42,44 @@ def main():
         s.step()
         s.ctx.sync()
         checks.assert_attention_close(s)
+        s.close()
+    elif kind == "kv_range_free_run":
+        steps, distinct = 300, 6
+        spec = W.config(4, scale_down=32).kv_range_shard(rank, world)
+        s = W.Session(spec, device=local)
+        ex = KvRangeExchange(s, rank, world, mode="p2p")
+        prob = checks.host_problem(s)
+        queries = []
+        for i in range(distinct):      # the same queries on every rank
+            gen = torch.Generator(device=s.device)
+            gen.manual_seed(777 + i)
+            queries.append(torch.randn(s.q.shape, generator=gen, device=s.device, dtype=torch.float32).to(s.q.dtype))
+        outs = torch.zeros((steps,) + tuple(s.out.shape), dtype=s.out.dtype, device=s.device) if rank == ex.owner else None
+        dist.barrier()
+        for step in range(steps):
+            s.q.copy_(queries[step % distinct])   # stream-ordered in front of the launch
+            ex.step()
+            if rank == ex.owner:
+                outs[step].copy_(s.out)           # stream-ordered behind it
+        torch.cuda.synchronize()
+        assert s.gqa.device_status() == 0
+        dist.barrier()
+        expected = []
+        for i in range(distinct):
+            q = checks.to_numpy_bits(queries[i])[prob["tok_rows"]]
+            part = O.paged_attention(prob["arena"], spec.dtype, q, prob["req_slots"], prob["positions"], prob["table"], 0,
+                                     prob["layout"], spec.num_q_heads, spec.num_kv_heads, spec.head_dim,
+                                     spec.page_bytes, spec.scale, want_stats=True)
+            gathered = [None] * world
+            dist.all_gather_object(gathered, part)
+            if rank == ex.owner:
+                expected.append(checks.merged_oracle_partials(gathered, spec.num_tokens, spec.num_q_heads, spec.head_dim))
+        if rank == ex.owner:
+            got = O.decode(checks.to_numpy_bits(outs), spec.dtype)
+            for step in range(steps):
+                diff = np.abs(got[step] - expected[step % distinct])
+                assert diff.max() <= 2e-2 and diff.mean() <= 2e-3, (step, diff.max(), diff.mean())
+        dist.barrier()
         s.close()
     else:
         mode = sys.argv[2]

@@ -33,3 +33,8 @@ def test_kv_range_split_partials_cross_devices_and_merge(mode):
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_sequence_sharded_ranks_match_the_oracle():
     _run(["sequence"], port=29543)
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_kv_range_exchange_free_running_ranks_keep_their_steps_apart():
+    _run(["kv_range_free_run"], port=29545)
