@@ -120,33 +120,78 @@ __global__ void __launch_bounds__(kGenericThreads) attend_generic_kernel(AttendP
     }
 }
 
-// One CTA per (tile, head selection) unit that more than one item contributed to:
+// One CTA per (unit, query row) of every (tile, head selection) unit that more than one item contributed to:
 // M = max m_i, w_i = 2^(m_i - M) * l_i (0 when m_i is not finite), out = sum w_i o_i / sum w_i (0 when empty),
-// crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_reduce.metal:27-48.
+// crates/inference-backend-metal/src/components/metal/gqa_split_kv_single_q_reduce.metal:27-48.  The items' weights are
+// worked out once per CTA (a block-wide max and sum over the items' statistics, 128 items at a time) and kept in shared
+// memory; every thread then owns output columns and walks the items with independent, coalesced loads.
 constexpr int kReduceThreads = 128;
 
+__device__ __forceinline__ float reduce_warp_max(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, offset));
+    return v;
+}
+
 __global__ void __launch_bounds__(kReduceThreads) attend_reduce_kernel(AttendParams p) {
-    const uint32_t unit = blockIdx.x;
+    const uint32_t unit = blockIdx.x, r = blockIdx.y;
     if (unit >= p.scalars[kScalarNumReduces]) return;
     const ReduceUnit ru = p.reduces[unit];
     const ItemView v = view_item(p, ru.first_item);
-    const uint32_t D = p.geo.head_dim;
+    if (r >= v.rows) return;
+    const uint32_t D = p.geo.head_dim, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t first_slot = v.partial_slot;  // slots of one unit are consecutive
-    for (uint32_t i = threadIdx.x; i < v.rows * D; i += kReduceThreads) {
-        const uint32_t r = i / D, d = i % D;
-        float global_max = -INFINITY;
-        for (uint32_t s = 0; s < ru.num_items; ++s)
-            global_max = fmaxf(global_max, p.partial_m[static_cast<uint64_t>(first_slot + s) * kMaxRows + r]);
-        float sum = 0.0f, acc = 0.0f;
-        for (uint32_t s = 0; s < ru.num_items; ++s) {
-            const uint64_t prow = static_cast<uint64_t>(first_slot + s) * kMaxRows + r;
+    const uint32_t n = ru.num_items;
+    __shared__ float weight_s[kReduceThreads];
+    __shared__ float across_s[kReduceThreads / 32];
+
+    // the row's maximum over all items
+    float local_max = -INFINITY;
+    for (uint32_t s = tid; s < n; s += kReduceThreads)
+        local_max = fmaxf(local_max, p.partial_m[static_cast<uint64_t>(first_slot + s) * kMaxRows + r]);
+    local_max = reduce_warp_max(local_max);
+    if (lane == 0) across_s[warp] = local_max;
+    __syncthreads();
+    float global_max = across_s[0];
+#pragma unroll
+    for (int w = 1; w < kReduceThreads / 32; ++w) global_max = fmaxf(global_max, across_s[w]);
+    __syncthreads();
+
+    float acc[2] = {0.0f, 0.0f};  // columns tid and tid + 128 (head_dim <= 256)
+    float weight_sum = 0.0f;      // this thread's share of the weights; summed over the CTA at the end
+    for (uint32_t base = 0; base < n; base += kReduceThreads) {
+        const uint32_t count = min(n - base, static_cast<uint32_t>(kReduceThreads));
+        if (tid < count) {
+            const uint64_t prow = static_cast<uint64_t>(first_slot + base + tid) * kMaxRows + r;
             const float pm = p.partial_m[prow];
             const float w = isfinite(pm) ? exp2f(pm - global_max) * p.partial_l[prow] : 0.0f;
-            sum += w;
-            acc += w * p.partial_o[prow * D + d];
+            weight_s[tid] = w;
+            weight_sum += w;
         }
-        const float value = sum > 0.0f ? acc / sum : 0.0f;
-        const uint64_t row = item_row_index(p, v, r);
+        __syncthreads();
+        const float* o_row = p.partial_o + (static_cast<uint64_t>(first_slot + base) * kMaxRows + r) * D;
+#pragma unroll 4
+        for (uint32_t s = 0; s < count; ++s) {
+            const float w = weight_s[s];
+            const float* o = o_row + static_cast<uint64_t>(s) * kMaxRows * D;
+            if (tid < D) acc[0] += w * o[tid];
+            if (tid + kReduceThreads < D) acc[1] += w * o[tid + kReduceThreads];
+        }
+        __syncthreads();
+    }
+    weight_sum = warp_sum(weight_sum);
+    if (lane == 0) across_s[warp] = weight_sum;
+    __syncthreads();
+    float sum = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kReduceThreads / 32; ++w) sum += across_s[w];
+
+    const uint64_t row = item_row_index(p, v, r);
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j) {
+        const uint32_t d = tid + j * kReduceThreads;
+        if (d >= D) continue;
+        const float value = sum > 0.0f ? acc[j] / sum : 0.0f;
         if (p.ext_o != nullptr) {
             p.ext_o[row * D + d] = value;
             if (d == 0) {
@@ -291,7 +336,7 @@ cudaError_t launch_attend_generic(const AttendParams& p, uint32_t num_ctas, cuda
 
 cudaError_t launch_attend_reduce(const AttendParams& p, uint32_t num_reduces, cudaStream_t stream) {
     if (num_reduces == 0) return cudaSuccess;
-    attend_reduce_kernel<<<num_reduces, kReduceThreads, 0, stream>>>(p);
+    attend_reduce_kernel<<<dim3(num_reduces, kMaxRows), kReduceThreads, 0, stream>>>(p);
     return cudaGetLastError();
 }
 
