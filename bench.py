@@ -290,7 +290,9 @@ def measure_decode(job, pkg, W, index, main):
     kernel_mode = {"auto": pkg.KERNEL_AUTO, "mma": pkg.KERNEL_MMA, "generic": pkg.KERNEL_GENERIC,
                    "mma_sync": pkg.KERNEL_MMA_SYNC, "mma_tma": pkg.KERNEL_MMA_TMA}[args.kernel]
     session = W.Session(spec, device=job.local_rank, kernel_mode=kernel_mode)
-    exchange = KvRangeExchange(session, rank, world, mode=args.exchange) if (world > 1 and index == 4) else None
+    # wait bound of seconds (about 100 ns per poll): a rank whose host is held up for a moment is not a failed step
+    exchange = (KvRangeExchange(session, rank, world, mode=args.exchange, max_polls=20_000_000)
+                if (world > 1 and index == 4) else None)
     step = exchange.step if exchange else session.step
     ctx = session.ctx
     alg = spec.algorithmic_bytes()

@@ -192,7 +192,7 @@ def exchange_parity(rank, world, local_rank, mode="p2p", scale_down=32, steps=3)
     from psi_dec_b200.distributed import KvRangeExchange
     spec = W.config(4, scale_down=scale_down).kv_range_shard(rank, world)
     s = W.Session(spec, device=local_rank)
-    ex = KvRangeExchange(s, rank, world, mode=mode)
+    ex = KvRangeExchange(s, rank, world, mode=mode, max_polls=20_000_000)
     worst_max, worst_mean, ok = 0.0, 0.0, True
     for step in range(steps):
         gen = torch.Generator(device=s.device)
